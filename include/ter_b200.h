@@ -1,0 +1,167 @@
+/* ter_b200 — C ABI of the B200 (sm_100a) ternary matmul fabric and decode forward.
+ *
+ * The library keeps the conventions of the reference's K4 C interface
+ * (include/ter_k4/ter_k4.h:27-55, src/k4/ter_k4.cpp:14-75): an opaque handle,
+ * named slots in a fixed-size table with names of at most 31 characters
+ * (include/ter/kernels.hpp:21-38), integer return codes (0 ok, -1 null
+ * argument, -2 unknown name, -3 allocation failure, -4 more than 7 call
+ * arguments), void functions that ignore NULL, and no exception or exit()
+ * across the boundary.
+ *
+ * All `*_dev` pointers are CUDA device pointers on the handle's device;
+ * `stream` is a cudaStream_t passed as void* (NULL = the handle's own stream).
+ * A handle serves one GPU and is not thread-safe; use one handle per GPU/rank.
+ * There is no CPU fallback: every compute entry point runs CUDA kernels or
+ * returns an error code.
+ */
+#ifndef TER_B200_H
+#define TER_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct ter_b200_handle_t ter_b200_handle_t;
+
+/* ---- return codes (first four: src/k4/ter_k4.cpp:33,40,52-54) ---- */
+#define TER_B200_OK            0
+#define TER_B200_E_NULL       (-1)   /* null handle / name / pointer            */
+#define TER_B200_E_UNKNOWN    (-2)   /* no slot or operator of that name         */
+#define TER_B200_E_ALLOC      (-3)   /* host or device allocation failed         */
+#define TER_B200_E_NARGS      (-4)   /* ter_b200_call with more than 7 arguments */
+#define TER_B200_E_SHAPE      (-5)   /* unsupported K/N/M, misaligned pointer    */
+#define TER_B200_E_FULL       (-6)   /* every slot of the table is in use        */
+#define TER_B200_E_NAME       (-7)   /* name longer than 31 characters           */
+#define TER_B200_E_CUDA       (-8)   /* a CUDA runtime call failed               */
+#define TER_B200_E_NCCL       (-9)   /* an NCCL call failed                      */
+#define TER_B200_E_STATE      (-10)  /* call made in the wrong state             */
+#define TER_B200_E_TIMEOUT    (-11)  /* a bounded device-side wait ran out       */
+#define TER_B200_E_VALUE      (-12)  /* payload value outside {-1,0,+1}          */
+
+/* The reference's KernelTable has 32 slots of 32-character names
+ * (include/ter/kernels.hpp:21-38) because it holds five bytecode kernels.  Here a slot holds a
+ * weight tensor and one model has 7 per layer, so the fixed table is larger; the name limit and
+ * the behaviour on overflow (an error code, never an exception) are the reference's. */
+#define TER_B200_MAX_SLOTS     1024
+#define TER_B200_MAX_NAME      31
+
+const char* ter_b200_strerror(int code);
+
+/* ---- lifecycle: replaces ter_k4_create / ter_k4_destroy
+ *      (include/ter_k4/ter_k4.h:29-30).  `device` is the CUDA ordinal. */
+ter_b200_handle_t* ter_b200_create(int device);
+void               ter_b200_destroy(ter_b200_handle_t* h);
+
+/* ---- weight formats accepted at the boundary ------------------------------
+ * V11      bytes [N/4][K], byte (j/4)*K + k, column j in bits 2*(j%4)
+ *          (cuda/ter_cuda_forward_packed.cu:354-355,370-372;
+ *           tools/convert_llama_to_packed.py:128-140)
+ * ROWMAJOR bytes [K][N/4], byte k*(N/4) + j/4 (cuda/ter_cuda_packed.cu:32-34,47-53)
+ * I32      TritTensor payload, int32 [K][N] with values in {-1,0,+1}
+ *          (include/ter/numfmt.hpp:17-36; W[k*N+j] as mm_row reads it,
+ *           src/tx/forward.cpp:338)
+ * 2-bit code in both packed forms: 0 -> 0, 1 -> +1, 2 -> -1, 3 -> 0. */
+#define TER_B200_FMT_V11       0
+#define TER_B200_FMT_ROWMAJOR  1
+#define TER_B200_FMT_I32       2
+
+/* Blob header for ter_b200_install_kernel: the payload follows the header. */
+typedef struct {
+    uint32_t magic;      /* 'TB2W' = 0x54423257 */
+    uint32_t format;     /* TER_B200_FMT_* */
+    uint32_t K, N;
+    float    scale;      /* per-tensor weight scale */
+    uint32_t reserved[3];
+} ter_b200_blob_hdr_t;
+#define TER_B200_BLOB_MAGIC 0x54423257u
+
+/* Same verb and argument list as ter_k4_install_kernel
+ * (include/ter_k4/ter_k4.h:33-36): registers a weight tensor under `name`,
+ * copying (and re-packing) it to the device once.  blob_n_words counts 32-bit
+ * words including the header.  Re-installing an existing name replaces it. */
+int ter_b200_install_kernel(ter_b200_handle_t* h, const char* name,
+                            const void* blob_bytes, size_t blob_n_words);
+
+/* Typed form of the same operation.  `data` is a HOST pointer. */
+int ter_b200_install_weight(ter_b200_handle_t* h, const char* name, const void* data,
+                            int format, int K, int N, float scale);
+/* `data_dev` is a DEVICE pointer (the weights never visit the host). */
+int ter_b200_install_weight_dev(ter_b200_handle_t* h, const char* name, const void* data_dev,
+                                int format, int K, int N, float scale, void* stream);
+int ter_b200_remove_weight(ter_b200_handle_t* h, const char* name);
+int ter_b200_weight_info(const ter_b200_handle_t* h, const char* name, int* K, int* N, float* scale);
+
+/* ---- ter_k4_call (include/ter_k4/ter_k4.h:40-43): run a named operator with
+ * at most 7 int64 arguments.  Operator names are the reference's slot names
+ * (src/tx/forward.cpp:376-380):
+ *   "tk_matmul_b_9t"  args = { (int64)(const char*)weight_slot_name, x_dev, x_scale_dev,
+ *                              out_dev, M, stream }            M = 1 -> GEMV, M > 1 -> GEMM
+ *   "tk_rmsnorm"      args = { x_dev, gamma_dev, n, eps_bits, q_dev, scale_dev, stream }
+ *   "tk_silu"         args = { gate_dev, up_dev, n, q_dev, scale_dev, stream }
+ *   "tk_rope"         args = { v_dev, n_heads, head_dim, pos, neox, stream }   (table of the model)
+ *   "tk_softmax"      args = { q_dev, kcache_dev, vcache_dev, out_dev, seq_len, stream } (model dims)
+ */
+int ter_b200_call(ter_b200_handle_t* h, const char* name, const int64_t* args, size_t n_args);
+
+/* ---- op counters (include/ter_k4/ter_k4.h:46-55).  tvmac advances by
+ * ceil(K/27)*N per GEMV row, as mm_row accounts it (src/tx/forward.cpp:349-350). */
+typedef struct {
+    uint64_t total_ops;
+    uint64_t tvmac;
+    uint64_t tvadd;
+    uint64_t tvsub;
+    uint64_t tvmul;
+} ter_b200_op_counts_t;
+void ter_b200_op_counts(const ter_b200_handle_t* h, ter_b200_op_counts_t* out);
+void ter_b200_reset_counters(ter_b200_handle_t* h);
+
+/* ---- packed-trit GEMV, M = 1 ------------------------------------------------
+ * Replaces mm_packed_dispatch / mm_packed_v4 (cuda/ter_cuda_forward_packed.cu:346-397,
+ * 493-500) and mm_bitnet_addonly_dev (cuda/ter_cuda_forward_bitnet.cu:497-559), and
+ * computes what mm_row computes (src/tx/forward.cpp:299-352) for int8 X:
+ *   out[j] = (float)(sum_k x[k] * trit(k,j)) * (x_scale_dev[0] * w_scale),  exact int32 sum.
+ * x_dev: int8[K], 16-byte aligned.  out_dev: float[N]. */
+int ter_b200_gemv(ter_b200_handle_t* h, const char* slot, const int8_t* x_dev,
+                  const float* x_scale_dev, float* out_dev, void* stream);
+/* Raw int32 accumulators (no scale): the bit-exact check against mm_row. */
+int ter_b200_gemv_acc(ter_b200_handle_t* h, const char* slot, const int8_t* x_dev,
+                      int32_t* acc_dev, void* stream);
+/* Up to 4 weight slots with the same K sharing one activation vector in ONE launch
+ * (q/k/v: cuda/ter_cuda_forward_packed.cu:516-518; gate/up: :533-534). */
+int ter_b200_gemv_group(ter_b200_handle_t* h, const char* const* slots, int n_slots,
+                        const int8_t* x_dev, const float* x_scale_dev,
+                        float* const* outs_dev, void* stream);
+/* Host-buffer form: copies x (K bytes) and the scale in, the N floats out, on `stream`,
+ * asynchronously; ter_b200_sync() completes it.  Buffers must stay valid until then
+ * (pinned host memory makes the copies truly asynchronous). */
+int ter_b200_gemv_host(ter_b200_handle_t* h, const char* slot, const int8_t* x_host,
+                       float x_scale, float* out_host, void* stream);
+int ter_b200_sync(ter_b200_handle_t* h, void* stream);
+
+/* ---- batched ternary GEMM, M > 1 -------------------------------------------
+ * Replaces mm_bitnet_addonly_batched_k (cuda/ter_cuda_addonly_batched.cu:32-123) and
+ * mm_int4_tc* (cuda/ter_cuda_int4_tc.cu:36-82): X int8 [M][K] row-major, one scale per
+ * row, out float [M][N]; out[m][j] = (float)acc * (x_scales[m] * w_scale). */
+int ter_b200_gemm(ter_b200_handle_t* h, const char* slot, const int8_t* X_dev,
+                  const float* x_scales_dev, int M, float* out_dev, void* stream);
+int ter_b200_gemm_acc(ter_b200_handle_t* h, const char* slot, const int8_t* X_dev, int M,
+                      int32_t* acc_dev, void* stream);
+
+/* ---- device status ---------------------------------------------------------
+ * Kernels never spin without a bound; a wait that ran out records a code that this call
+ * returns (TER_B200_E_TIMEOUT) after synchronising the handle's streams. */
+int ter_b200_device_status(ter_b200_handle_t* h);
+/* Last CUDA error code seen by the handle (cudaError_t as int), 0 if none. */
+int ter_b200_last_cuda_error(const ter_b200_handle_t* h);
+/* Tuning knobs (integers): "gemv_ctas_per_sm", "gemv_stages", "pdl". Returns -2 if unknown. */
+int ter_b200_set_option(ter_b200_handle_t* h, const char* key, int value);
+/* Number of kernels this handle has launched since creation (or the last reset). */
+uint64_t ter_b200_launch_count(const ter_b200_handle_t* h);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TER_B200_H */

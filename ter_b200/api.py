@@ -1,0 +1,258 @@
+"""ctypes binding over ``libter_b200.so`` (the C ABI of ``include/ter_b200.h``).
+
+Host-side mirror of the reference's operator interface for the ternary matmul path:
+``TerB200.install`` / ``gemv`` / ``gemv_acc`` / ``gemm`` take the same arguments, in the same
+meaning, as ``mm_packed_dispatch(X, scale_x_dev, W{data, scale}, out, K, N, stream)``
+(cuda/ter_cuda_forward_packed.cu:493-500) and ``mm_row`` (src/tx/forward.cpp:299-303).
+Tensors are torch CUDA tensors used purely as device-memory holders; all arithmetic runs
+in the library's own kernels.  Missing library => RuntimeError (never a CPU fallback).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libter_b200.so")
+
+FMT_V11, FMT_ROWMAJOR, FMT_I32 = 0, 1, 2
+E_NULL, E_UNKNOWN, E_ALLOC, E_NARGS, E_SHAPE, E_FULL, E_NAME, E_CUDA, E_NCCL, E_STATE, E_TIMEOUT, E_VALUE = \
+    -1, -2, -3, -4, -5, -6, -7, -8, -9, -10, -11, -12
+
+
+class TerB200Error(RuntimeError):
+    def __init__(self, code: int, what: str = ""):
+        self.code = code
+        msg = lib().ter_b200_strerror(code).decode() if _lib is not None else str(code)
+        super().__init__(f"ter_b200 error {code} ({msg}) {what}".strip())
+
+
+class OpCounts(C.Structure):
+    _fields_ = [("total_ops", C.c_uint64), ("tvmac", C.c_uint64), ("tvadd", C.c_uint64),
+                ("tvsub", C.c_uint64), ("tvmul", C.c_uint64)]
+
+
+class BlobHdr(C.Structure):
+    _fields_ = [("magic", C.c_uint32), ("format", C.c_uint32), ("K", C.c_uint32), ("N", C.c_uint32),
+                ("scale", C.c_float), ("reserved", C.c_uint32 * 3)]
+
+
+BLOB_MAGIC = 0x54423257
+
+_lib = None
+
+# name -> (restype, argtypes); also the list the symbol-export test walks.
+_VP, _CP, _I, _F, _SZ, _U64 = C.c_void_p, C.c_char_p, C.c_int, C.c_float, C.c_size_t, C.c_uint64
+SIGNATURES = {
+    "ter_b200_strerror": (C.c_char_p, [_I]),
+    "ter_b200_create": (_VP, [_I]),
+    "ter_b200_destroy": (None, [_VP]),
+    "ter_b200_install_kernel": (_I, [_VP, _CP, _VP, _SZ]),
+    "ter_b200_install_weight": (_I, [_VP, _CP, _VP, _I, _I, _I, _F]),
+    "ter_b200_install_weight_dev": (_I, [_VP, _CP, _VP, _I, _I, _I, _F, _VP]),
+    "ter_b200_remove_weight": (_I, [_VP, _CP]),
+    "ter_b200_weight_info": (_I, [_VP, _CP, C.POINTER(_I), C.POINTER(_I), C.POINTER(_F)]),
+    "ter_b200_call": (_I, [_VP, _CP, C.POINTER(C.c_int64), _SZ]),
+    "ter_b200_op_counts": (None, [_VP, C.POINTER(OpCounts)]),
+    "ter_b200_reset_counters": (None, [_VP]),
+    "ter_b200_gemv": (_I, [_VP, _CP, _VP, _VP, _VP, _VP]),
+    "ter_b200_gemv_acc": (_I, [_VP, _CP, _VP, _VP, _VP]),
+    "ter_b200_gemv_group": (_I, [_VP, C.POINTER(_CP), _I, _VP, _VP, C.POINTER(_VP), _VP]),
+    "ter_b200_gemv_host": (_I, [_VP, _CP, _VP, _F, _VP, _VP]),
+    "ter_b200_sync": (_I, [_VP, _VP]),
+    "ter_b200_gemm": (_I, [_VP, _CP, _VP, _VP, _I, _VP, _VP]),
+    "ter_b200_gemm_acc": (_I, [_VP, _CP, _VP, _I, _VP, _VP]),
+    "ter_b200_device_status": (_I, [_VP]),
+    "ter_b200_last_cuda_error": (_I, [_VP]),
+    "ter_b200_set_option": (_I, [_VP, _CP, _I]),
+    "ter_b200_launch_count": (_U64, [_VP]),
+}
+
+
+def load(path: str = LIB_PATH):
+    """Load the shared library (building it in-tree first if it is absent and nvcc exists)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(path):
+        try:
+            from . import build as _b
+            _b.build()
+        except Exception as e:  # noqa: BLE001
+            raise RuntimeError(
+                f"ter_b200: CUDA library {path} is missing and could not be built ({e}); "
+                "there is no CPU fallback") from e
+    L = C.CDLL(path)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(L, name)   # AttributeError here = ABI drift; let it surface
+        fn.restype = res
+        fn.argtypes = args
+    _lib = L
+    return L
+
+
+def lib():
+    return load()
+
+
+def _check(rc: int, what: str = ""):
+    if rc != 0:
+        raise TerB200Error(rc, what)
+
+
+def _stream_ptr(stream=None):
+    import torch
+    if stream is None:
+        stream = torch.cuda.current_stream()
+    return C.c_void_p(stream.cuda_stream)
+
+
+class TerB200:
+    """One handle = one GPU.  Mirrors the ter_k4 lifecycle: create, install, call, counters, destroy."""
+
+    def __init__(self, device: int = 0):
+        import torch
+        if not torch.cuda.is_available():
+            raise RuntimeError("ter_b200 needs a CUDA device; there is no CPU fallback")
+        self.L = lib()
+        self.device = device
+        torch.cuda.set_device(device)
+        self.h = self.L.ter_b200_create(device)
+        if not self.h:
+            raise RuntimeError(f"ter_b200_create({device}) failed")
+        self._shapes = {}
+
+    # ---- lifecycle
+    def close(self):
+        if getattr(self, "h", None):
+            self.L.ter_b200_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:  # noqa: BLE001
+            pass
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.close()
+
+    # ---- weights
+    def install(self, name: str, data, fmt: int, K: int, N: int, scale: float):
+        """data: numpy array (host) or torch CUDA tensor (device) in a boundary format."""
+        import numpy as np
+        import torch
+        if isinstance(data, torch.Tensor) and data.is_cuda:
+            d = data.contiguous()
+            rc = self.L.ter_b200_install_weight_dev(self.h, name.encode(), C.c_void_p(d.data_ptr()), fmt, K, N,
+                                                    scale, _stream_ptr())
+        else:
+            a = np.ascontiguousarray(data)
+            rc = self.L.ter_b200_install_weight(self.h, name.encode(), C.c_void_p(a.ctypes.data), fmt, K, N, scale)
+        _check(rc, f"install {name}")
+        self._shapes[name] = (K, N)
+
+    def install_blob(self, name: str, data, fmt: int, K: int, N: int, scale: float):
+        """Same operation through the ter_k4-style blob verb."""
+        import numpy as np
+        a = np.ascontiguousarray(data)
+        hdr = BlobHdr(BLOB_MAGIC, fmt, K, N, scale)
+        blob = bytes(hdr) + a.tobytes()
+        blob += b"\0" * (-len(blob) % 4)
+        rc = self.L.ter_b200_install_kernel(self.h, name.encode(), blob, len(blob) // 4)
+        _check(rc, f"install_kernel {name}")
+        self._shapes[name] = (K, N)
+
+    def remove(self, name: str):
+        _check(self.L.ter_b200_remove_weight(self.h, name.encode()))
+        self._shapes.pop(name, None)
+
+    def weight_info(self, name: str):
+        K, N, s = C.c_int(), C.c_int(), C.c_float()
+        _check(self.L.ter_b200_weight_info(self.h, name.encode(), C.byref(K), C.byref(N), C.byref(s)))
+        return K.value, N.value, s.value
+
+    # ---- GEMV / GEMM
+    def gemv(self, name: str, x, x_scale, out=None, stream=None):
+        """x int8[K] cuda, x_scale float32[1] cuda -> float32[N]."""
+        import torch
+        K, N = self._shapes[name]
+        if out is None:
+            out = torch.empty(N, dtype=torch.float32, device=x.device)
+        _check(self.L.ter_b200_gemv(self.h, name.encode(), C.c_void_p(x.data_ptr()), C.c_void_p(x_scale.data_ptr()),
+                                    C.c_void_p(out.data_ptr()), _stream_ptr(stream)), f"gemv {name}")
+        return out
+
+    def gemv_acc(self, name: str, x, out=None, stream=None):
+        import torch
+        K, N = self._shapes[name]
+        if out is None:
+            out = torch.empty(N, dtype=torch.int32, device=x.device)
+        _check(self.L.ter_b200_gemv_acc(self.h, name.encode(), C.c_void_p(x.data_ptr()), C.c_void_p(out.data_ptr()),
+                                        _stream_ptr(stream)), f"gemv_acc {name}")
+        return out
+
+    def gemv_group(self, names, x, x_scale, outs=None, stream=None):
+        import torch
+        if outs is None:
+            outs = [torch.empty(self._shapes[n][1], dtype=torch.float32, device=x.device) for n in names]
+        arr_n = (C.c_char_p * len(names))(*[n.encode() for n in names])
+        arr_o = (C.c_void_p * len(names))(*[o.data_ptr() for o in outs])
+        _check(self.L.ter_b200_gemv_group(self.h, arr_n, len(names), C.c_void_p(x.data_ptr()),
+                                          C.c_void_p(x_scale.data_ptr()), arr_o, _stream_ptr(stream)), "gemv_group")
+        return outs
+
+    def gemv_host(self, name: str, x_host, x_scale: float, out_host, stream=None):
+        """x_host int8[K], out_host float32[N]: (pinned) host torch tensors or numpy arrays. Asynchronous."""
+        xp = x_host.data_ptr() if hasattr(x_host, "data_ptr") else x_host.ctypes.data
+        op = out_host.data_ptr() if hasattr(out_host, "data_ptr") else out_host.ctypes.data
+        _check(self.L.ter_b200_gemv_host(self.h, name.encode(), C.c_void_p(xp), float(x_scale), C.c_void_p(op),
+                                         _stream_ptr(stream)), f"gemv_host {name}")
+
+    def sync(self, stream=None):
+        _check(self.L.ter_b200_sync(self.h, _stream_ptr(stream)))
+
+    def gemm(self, name: str, X, x_scales, out=None, stream=None):
+        import torch
+        K, N = self._shapes[name]
+        M = X.shape[0]
+        if out is None:
+            out = torch.empty((M, N), dtype=torch.float32, device=X.device)
+        _check(self.L.ter_b200_gemm(self.h, name.encode(), C.c_void_p(X.data_ptr()), C.c_void_p(x_scales.data_ptr()),
+                                    M, C.c_void_p(out.data_ptr()), _stream_ptr(stream)), f"gemm {name}")
+        return out
+
+    def gemm_acc(self, name: str, X, out=None, stream=None):
+        import torch
+        K, N = self._shapes[name]
+        M = X.shape[0]
+        if out is None:
+            out = torch.empty((M, N), dtype=torch.int32, device=X.device)
+        _check(self.L.ter_b200_gemm_acc(self.h, name.encode(), C.c_void_p(X.data_ptr()), M,
+                                        C.c_void_p(out.data_ptr()), _stream_ptr(stream)), f"gemm_acc {name}")
+        return out
+
+    def call(self, op: str, args):
+        arr = (C.c_int64 * len(args))(*[int(a) for a in args])
+        return self.L.ter_b200_call(self.h, op.encode(), arr, len(args))
+
+    # ---- counters / status
+    def op_counts(self) -> dict:
+        c = OpCounts()
+        self.L.ter_b200_op_counts(self.h, C.byref(c))
+        return {k: getattr(c, k) for k, _ in OpCounts._fields_}
+
+    def reset_counters(self):
+        self.L.ter_b200_reset_counters(self.h)
+
+    def launch_count(self) -> int:
+        return int(self.L.ter_b200_launch_count(self.h))
+
+    def device_status(self) -> int:
+        return self.L.ter_b200_device_status(self.h)
+
+    def set_option(self, key: str, value: int):
+        _check(self.L.ter_b200_set_option(self.h, key.encode(), int(value)), f"set_option {key}")

@@ -1,0 +1,396 @@
+// extern "C" layer of include/ter_b200.h: handle lifecycle, the 32-slot weight table,
+// install / call / counters, and the GEMV entry points.  Mirrors the reference's
+// K4 wrapper (src/k4/ter_k4.cpp:14-75) in shape and error convention.
+#include <new>
+#include <stdio.h>
+#include <stdlib.h>
+
+#include "handle.h"
+
+using namespace terb;
+
+namespace terb {
+
+void free_weight(DevWeight* w) {
+    if (w->data) cudaFree(w->data);
+    *w = DevWeight();
+}
+
+int build_weight_from_dev(ter_b200_handle_t* h, const void* data_dev, int format, int K, int N, float scale,
+                          cudaStream_t st, DevWeight* out) {
+    if (K <= 0 || N <= 0 || K > kGemvMaxK) return TER_B200_E_SHAPE;
+    if (K % 16 != 0) return TER_B200_E_SHAPE;
+    if ((format == TER_B200_FMT_V11 || format == TER_B200_FMT_ROWMAJOR) && N % 4 != 0) return TER_B200_E_SHAPE;
+    DevWeight w;
+    w.K = K;
+    w.N = N;
+    w.Kpad = (K + 127) / 128 * 128;
+    w.Npad = (N + 15) / 16 * 16;
+    w.scale = scale;
+    TERB_CUDA(h, cudaMalloc((void**)&w.data, w.bytes()));
+    cudaError_t e = cudaSuccess;
+    int* bad_dev = nullptr;
+    switch (format) {
+        case TER_B200_FMT_V11:
+            e = launch_recode_v11((const uint8_t*)data_dev, w.data, K, N, w.Kpad, w.Npad, st);
+            break;
+        case TER_B200_FMT_ROWMAJOR:
+            e = launch_recode_rowmajor((const uint8_t*)data_dev, w.data, K, N, w.Kpad, w.Npad, st);
+            break;
+        case TER_B200_FMT_I32:
+            e = cudaMalloc((void**)&bad_dev, sizeof(int));
+            if (e == cudaSuccess) e = cudaMemsetAsync(bad_dev, 0, sizeof(int), st);
+            if (e == cudaSuccess)
+                e = launch_pack_i32((const int32_t*)data_dev, w.data, K, N, w.Kpad, w.Npad, bad_dev, st);
+            break;
+        default:
+            cudaFree(w.data);
+            return TER_B200_E_SHAPE;
+    }
+    h->launches += 1;
+    int bad = 0;
+    if (e == cudaSuccess && bad_dev) e = cudaMemcpyAsync(&bad, bad_dev, sizeof(int), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (bad_dev) cudaFree(bad_dev);
+    if (e != cudaSuccess) {
+        cudaFree(w.data);
+        return cuda_fail(h, e);
+    }
+    if (bad) {
+        cudaFree(w.data);
+        return TER_B200_E_VALUE;
+    }
+    *out = w;
+    return TER_B200_OK;
+}
+
+static size_t boundary_bytes(int format, int K, int N) {
+    if (format == TER_B200_FMT_I32) return (size_t)K * (size_t)N * 4u;
+    return (size_t)K * (size_t)(N / 4);
+}
+
+static int put_slot(ter_b200_handle_t* h, const char* name, const DevWeight& w) {
+    TerbSlot* s = find_slot(h, name);
+    if (s) {
+        free_weight(&s->w);
+        s->w = w;
+        return TER_B200_OK;
+    }
+    for (int i = 0; i < TER_B200_MAX_SLOTS; ++i) {
+        if (!h->slots[i].used) {
+            h->slots[i].used = true;
+            strncpy(h->slots[i].name, name, TER_B200_MAX_NAME);
+            h->slots[i].name[TER_B200_MAX_NAME] = '\0';
+            h->slots[i].w = w;
+            return TER_B200_OK;
+        }
+    }
+    return TER_B200_E_FULL;
+}
+
+static int check_name(const char* name) {
+    if (!name) return TER_B200_E_NULL;
+    size_t n = strnlen(name, TER_B200_MAX_NAME + 1);
+    if (n == 0 || n > TER_B200_MAX_NAME) return TER_B200_E_NAME;
+    return TER_B200_OK;
+}
+
+static int ensure_host_staging(ter_b200_handle_t* h, size_t x_bytes, size_t out_floats) {
+    if (h->hx_cap < x_bytes) {
+        if (h->hx_dev) cudaFree(h->hx_dev);
+        h->hx_dev = nullptr;
+        h->hx_cap = 0;
+        TERB_CUDA(h, cudaMalloc((void**)&h->hx_dev, x_bytes));
+        h->hx_cap = x_bytes;
+    }
+    if (h->hout_cap < out_floats) {
+        if (h->hout_dev) cudaFree(h->hout_dev);
+        h->hout_dev = nullptr;
+        h->hout_cap = 0;
+        TERB_CUDA(h, cudaMalloc((void**)&h->hout_dev, out_floats * sizeof(float)));
+        h->hout_cap = out_floats;
+    }
+    return TER_B200_OK;
+}
+
+// One launch over up to kGemvMaxGroup weights sharing x.
+static int run_gemv(ter_b200_handle_t* h, const DevWeight* const* ws, int n, const int8_t* x_dev,
+                    const float* x_scale_dev, float x_scale_imm, float* const* outs, int32_t* const* accs,
+                    cudaStream_t st) {
+    if (n < 1 || n > kGemvMaxGroup) return TER_B200_E_SHAPE;
+    if (((uintptr_t)x_dev & 15u) != 0) return TER_B200_E_SHAPE;
+    GemvParams p;
+    memset(&p, 0, sizeof p);
+    p.K = ws[0]->K;
+    p.Kpad = ws[0]->Kpad;
+    int tiles = 0;
+    for (int i = 0; i < n; ++i) {
+        if (ws[i]->K != p.K) return TER_B200_E_SHAPE;
+        p.W[i] = ws[i]->data;
+        p.out[i] = outs ? outs[i] : nullptr;
+        p.acc_out[i] = accs ? accs[i] : nullptr;
+        p.w_scale[i] = ws[i]->scale;
+        p.N[i] = ws[i]->N;
+        p.tile_begin[i] = tiles;
+        tiles += ws[i]->tiles();
+    }
+    for (int i = n; i <= kGemvMaxGroup; ++i) p.tile_begin[i] = tiles;
+    p.x = x_dev;
+    p.x_scale = x_scale_dev;
+    p.x_scale_imm = x_scale_imm;
+    p.n_mats = n;
+    p.n_tiles = tiles;
+    p.status = h->status_dev;
+    GemvLaunchCfg cfg = h->gemv_cfg;
+    cfg.sm_count = h->sm_count;
+    TERB_CUDA(h, launch_gemv(p, cfg, st));
+    h->launches += 1;
+    for (int i = 0; i < n; ++i) count_gemv(h, ws[i]->K, ws[i]->N, 1);
+    return TER_B200_OK;
+}
+
+}  // namespace terb
+
+extern "C" {
+
+const char* ter_b200_strerror(int code) {
+    switch (code) {
+        case TER_B200_OK: return "ok";
+        case TER_B200_E_NULL: return "null handle, name or pointer";
+        case TER_B200_E_UNKNOWN: return "unknown slot or operator name";
+        case TER_B200_E_ALLOC: return "allocation failed";
+        case TER_B200_E_NARGS: return "more than 7 call arguments";
+        case TER_B200_E_SHAPE: return "unsupported shape, format or alignment";
+        case TER_B200_E_FULL: return "slot table full";
+        case TER_B200_E_NAME: return "name empty or longer than 31 characters";
+        case TER_B200_E_CUDA: return "CUDA call failed";
+        case TER_B200_E_NCCL: return "NCCL call failed";
+        case TER_B200_E_STATE: return "call made in the wrong state";
+        case TER_B200_E_TIMEOUT: return "bounded device wait ran out";
+        case TER_B200_E_VALUE: return "payload value outside {-1,0,+1}";
+        default: return "unknown error code";
+    }
+}
+
+ter_b200_handle_t* ter_b200_create(int device) {
+    int n_dev = 0;
+    if (cudaGetDeviceCount(&n_dev) != cudaSuccess || device < 0 || device >= n_dev) {
+        (void)cudaGetLastError();
+        return nullptr;
+    }
+    if (cudaSetDevice(device) != cudaSuccess) return nullptr;
+    ter_b200_handle_t* h = new (std::nothrow) ter_b200_handle_t();
+    if (!h) return nullptr;
+    h->device = device;
+    h->gemv_cfg = GemvLaunchCfg();
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) sms = 148;
+    h->sm_count = sms;
+    if (cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaMalloc((void**)&h->status_dev, sizeof(int)) != cudaSuccess ||
+        cudaMalloc((void**)&h->hscale_dev, sizeof(float)) != cudaSuccess ||
+        cudaMemset(h->status_dev, 0, sizeof(int)) != cudaSuccess) {
+        ter_b200_destroy(h);
+        return nullptr;
+    }
+    return h;
+}
+
+void ter_b200_model_free(ter_b200_handle_t* h);   // model.cpp
+
+void ter_b200_destroy(ter_b200_handle_t* h) {
+    if (!h) return;
+    cudaSetDevice(h->device);
+    if (h->stream) cudaStreamSynchronize(h->stream);
+    ter_b200_model_free(h);
+    for (int i = 0; i < TER_B200_MAX_SLOTS; ++i)
+        if (h->slots[i].used) free_weight(&h->slots[i].w);
+    if (h->status_dev) cudaFree(h->status_dev);
+    if (h->hscale_dev) cudaFree(h->hscale_dev);
+    if (h->hx_dev) cudaFree(h->hx_dev);
+    if (h->hout_dev) cudaFree(h->hout_dev);
+    if (h->stream) cudaStreamDestroy(h->stream);
+    delete h;
+}
+
+int ter_b200_install_weight_dev(ter_b200_handle_t* h, const char* name, const void* data_dev, int format, int K,
+                                int N, float scale, void* stream) {
+    if (!h || !data_dev) return TER_B200_E_NULL;
+    int rc = check_name(name);
+    if (rc) return rc;
+    TERB_CUDA(h, cudaSetDevice(h->device));
+    if (!find_slot(h, name)) {
+        int free_slots = 0;
+        for (int i = 0; i < TER_B200_MAX_SLOTS; ++i) free_slots += !h->slots[i].used;
+        if (!free_slots) return TER_B200_E_FULL;
+    }
+    DevWeight w;
+    rc = build_weight_from_dev(h, data_dev, format, K, N, scale, pick_stream(h, stream), &w);
+    if (rc) return rc;
+    rc = put_slot(h, name, w);
+    if (rc) free_weight(&w);
+    return rc;
+}
+
+int ter_b200_install_weight(ter_b200_handle_t* h, const char* name, const void* data, int format, int K, int N,
+                            float scale) {
+    if (!h || !data) return TER_B200_E_NULL;
+    int rc = check_name(name);
+    if (rc) return rc;
+    if (K <= 0 || N <= 0 || format < 0 || format > TER_B200_FMT_I32) return TER_B200_E_SHAPE;
+    if (format != TER_B200_FMT_I32 && N % 4 != 0) return TER_B200_E_SHAPE;
+    TERB_CUDA(h, cudaSetDevice(h->device));
+    const size_t bytes = boundary_bytes(format, K, N);
+    void* tmp = nullptr;
+    TERB_CUDA(h, cudaMalloc(&tmp, bytes));
+    cudaError_t e = cudaMemcpyAsync(tmp, data, bytes, cudaMemcpyHostToDevice, h->stream);
+    if (e != cudaSuccess) {
+        cudaFree(tmp);
+        return cuda_fail(h, e);
+    }
+    rc = ter_b200_install_weight_dev(h, name, tmp, format, K, N, scale, h->stream);
+    cudaFree(tmp);
+    return rc;
+}
+
+int ter_b200_install_kernel(ter_b200_handle_t* h, const char* name, const void* blob_bytes, size_t blob_n_words) {
+    if (!h || !name || !blob_bytes) return TER_B200_E_NULL;
+    if (blob_n_words * 4u < sizeof(ter_b200_blob_hdr_t)) return TER_B200_E_SHAPE;
+    ter_b200_blob_hdr_t hdr;
+    memcpy(&hdr, blob_bytes, sizeof hdr);
+    if (hdr.magic != TER_B200_BLOB_MAGIC || hdr.format > TER_B200_FMT_I32) return TER_B200_E_SHAPE;
+    if (hdr.K == 0 || hdr.N == 0 || hdr.K > (uint32_t)kGemvMaxK || hdr.N > (1u << 28)) return TER_B200_E_SHAPE;
+    if (hdr.format != TER_B200_FMT_I32 && hdr.N % 4u != 0) return TER_B200_E_SHAPE;
+    const size_t need = sizeof hdr + boundary_bytes((int)hdr.format, (int)hdr.K, (int)hdr.N);
+    if (blob_n_words * 4u < need) return TER_B200_E_SHAPE;
+    return ter_b200_install_weight(h, name, (const uint8_t*)blob_bytes + sizeof hdr, (int)hdr.format, (int)hdr.K,
+                                   (int)hdr.N, hdr.scale);
+}
+
+int ter_b200_remove_weight(ter_b200_handle_t* h, const char* name) {
+    if (!h || !name) return TER_B200_E_NULL;
+    TerbSlot* s = find_slot(h, name);
+    if (!s) return TER_B200_E_UNKNOWN;
+    cudaSetDevice(h->device);
+    cudaStreamSynchronize(h->stream);
+    free_weight(&s->w);
+    s->used = false;
+    s->name[0] = '\0';
+    return TER_B200_OK;
+}
+
+int ter_b200_weight_info(const ter_b200_handle_t* h, const char* name, int* K, int* N, float* scale) {
+    if (!h || !name) return TER_B200_E_NULL;
+    const TerbSlot* s = find_slot(h, name);
+    if (!s) return TER_B200_E_UNKNOWN;
+    if (K) *K = s->w.K;
+    if (N) *N = s->w.N;
+    if (scale) *scale = s->w.scale;
+    return TER_B200_OK;
+}
+
+void ter_b200_op_counts(const ter_b200_handle_t* h, ter_b200_op_counts_t* out) {
+    if (!h || !out) return;
+    *out = h->counts;
+}
+void ter_b200_reset_counters(ter_b200_handle_t* h) {
+    if (!h) return;
+    memset(&h->counts, 0, sizeof h->counts);
+    h->launches = 0;
+}
+uint64_t ter_b200_launch_count(const ter_b200_handle_t* h) { return h ? h->launches : 0; }
+
+int ter_b200_gemv(ter_b200_handle_t* h, const char* slot, const int8_t* x_dev, const float* x_scale_dev,
+                  float* out_dev, void* stream) {
+    if (!h || !slot || !x_dev || !x_scale_dev || !out_dev) return TER_B200_E_NULL;
+    TerbSlot* s = find_slot(h, slot);
+    if (!s) return TER_B200_E_UNKNOWN;
+    TERB_CUDA(h, cudaSetDevice(h->device));
+    const DevWeight* ws[1] = {&s->w};
+    float* outs[1] = {out_dev};
+    return run_gemv(h, ws, 1, x_dev, x_scale_dev, 1.0f, outs, nullptr, pick_stream(h, stream));
+}
+
+int ter_b200_gemv_acc(ter_b200_handle_t* h, const char* slot, const int8_t* x_dev, int32_t* acc_dev,
+                      void* stream) {
+    if (!h || !slot || !x_dev || !acc_dev) return TER_B200_E_NULL;
+    TerbSlot* s = find_slot(h, slot);
+    if (!s) return TER_B200_E_UNKNOWN;
+    TERB_CUDA(h, cudaSetDevice(h->device));
+    const DevWeight* ws[1] = {&s->w};
+    int32_t* accs[1] = {acc_dev};
+    return run_gemv(h, ws, 1, x_dev, nullptr, 1.0f, nullptr, accs, pick_stream(h, stream));
+}
+
+int ter_b200_gemv_group(ter_b200_handle_t* h, const char* const* slots, int n_slots, const int8_t* x_dev,
+                        const float* x_scale_dev, float* const* outs_dev, void* stream) {
+    if (!h || !slots || !x_dev || !x_scale_dev || !outs_dev) return TER_B200_E_NULL;
+    if (n_slots < 1 || n_slots > kGemvMaxGroup) return TER_B200_E_SHAPE;
+    const DevWeight* ws[kGemvMaxGroup];
+    for (int i = 0; i < n_slots; ++i) {
+        if (!slots[i] || !outs_dev[i]) return TER_B200_E_NULL;
+        TerbSlot* s = find_slot(h, slots[i]);
+        if (!s) return TER_B200_E_UNKNOWN;
+        ws[i] = &s->w;
+    }
+    TERB_CUDA(h, cudaSetDevice(h->device));
+    return run_gemv(h, ws, n_slots, x_dev, x_scale_dev, 1.0f, outs_dev, nullptr, pick_stream(h, stream));
+}
+
+int ter_b200_gemv_host(ter_b200_handle_t* h, const char* slot, const int8_t* x_host, float x_scale,
+                       float* out_host, void* stream) {
+    if (!h || !slot || !x_host || !out_host) return TER_B200_E_NULL;
+    TerbSlot* s = find_slot(h, slot);
+    if (!s) return TER_B200_E_UNKNOWN;
+    TERB_CUDA(h, cudaSetDevice(h->device));
+    int rc = ensure_host_staging(h, (size_t)s->w.Kpad, (size_t)s->w.Npad);
+    if (rc) return rc;
+    cudaStream_t st = pick_stream(h, stream);
+    TERB_CUDA(h, cudaMemcpyAsync(h->hx_dev, x_host, (size_t)s->w.K, cudaMemcpyHostToDevice, st));
+    const DevWeight* ws[1] = {&s->w};
+    float* outs[1] = {h->hout_dev};
+    rc = run_gemv(h, ws, 1, h->hx_dev, nullptr, x_scale, outs, nullptr, st);
+    if (rc) return rc;
+    TERB_CUDA(h, cudaMemcpyAsync(out_host, h->hout_dev, (size_t)s->w.N * sizeof(float), cudaMemcpyDeviceToHost, st));
+    return TER_B200_OK;
+}
+
+int ter_b200_sync(ter_b200_handle_t* h, void* stream) {
+    if (!h) return TER_B200_E_NULL;
+    TERB_CUDA(h, cudaSetDevice(h->device));
+    TERB_CUDA(h, cudaStreamSynchronize(pick_stream(h, stream)));
+    return TER_B200_OK;
+}
+
+int ter_b200_device_status(ter_b200_handle_t* h) {
+    if (!h) return TER_B200_E_NULL;
+    TERB_CUDA(h, cudaSetDevice(h->device));
+    TERB_CUDA(h, cudaDeviceSynchronize());
+    int st = 0;
+    TERB_CUDA(h, cudaMemcpy(&st, h->status_dev, sizeof(int), cudaMemcpyDeviceToHost));
+    if (st != 0) {
+        cudaMemset(h->status_dev, 0, sizeof(int));
+        return TER_B200_E_TIMEOUT;
+    }
+    return TER_B200_OK;
+}
+
+int ter_b200_last_cuda_error(const ter_b200_handle_t* h) { return h ? h->last_cuda : 0; }
+
+int ter_b200_set_option(ter_b200_handle_t* h, const char* key, int value) {
+    if (!h || !key) return TER_B200_E_NULL;
+    if (strcmp(key, "gemv_ctas_per_sm") == 0) {
+        if (value < 1 || value > 8) return TER_B200_E_SHAPE;
+        h->gemv_cfg.ctas_per_sm = value;
+    } else if (strcmp(key, "gemv_stages") == 0) {
+        if (value < 0 || value > 8) return TER_B200_E_SHAPE;
+        h->gemv_cfg.stages = value;
+    } else if (strcmp(key, "pdl") == 0) {
+        h->gemv_cfg.pdl = value ? 1 : 0;
+    } else {
+        return TER_B200_E_UNKNOWN;
+    }
+    return TER_B200_OK;
+}
+
+}  // extern "C"

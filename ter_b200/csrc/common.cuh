@@ -1,0 +1,77 @@
+// Shared device helpers for the sm_100a kernels: mbarrier, 1-D TMA bulk copies,
+// programmatic dependent launch, mixed-sign dp4a.  Inline PTX only; no library code.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace terb {
+
+// Device-side error codes written to the handle's status word.
+enum : int { DEV_OK = 0, DEV_TIMEOUT_MBAR = 1, DEV_TIMEOUT_FLAG = 2 };
+
+// Upper bound on mbarrier polls.  Each try_wait suspends for a hardware-defined
+// interval, so this is of the order of a second before a kernel gives up.
+constexpr uint32_t kMbarSpinLimit = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+// Make barrier initialisation visible to the async (TMA) proxy.
+__device__ __forceinline__ void mbar_fence_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  On expiry records DEV_TIMEOUT_MBAR in *status and returns false;
+// the caller carries on (its results are then meaningless, and the host sees the code).
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, int* status) {
+    for (uint32_t i = 0; i < kMbarSpinLimit; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    if (status) atomicExch(status, DEV_TIMEOUT_MBAR);
+    // Second bounded chance for copies still in flight before the CTA moves on.
+    for (uint32_t i = 0; i < kMbarSpinLimit; ++i)
+        if (mbar_try_wait(bar, parity)) return false;
+    return false;
+}
+
+// 1-D TMA bulk copy global -> shared, completion counted on an mbarrier.
+// dst, src 16-byte aligned; bytes a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+            smem_u32(dst)),
+        "l"(src), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
+
+// Programmatic dependent launch: let the next kernel in the stream start its
+// prologue; wait until the kernels this one depends on have finished and flushed.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// d = c + sum_i s8(a.byte[i]) * u8(b.byte[i])
+__device__ __forceinline__ int dp4a_su(int a, uint32_t b, int c) {
+    int d;
+    asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+}  // namespace terb

@@ -1,0 +1,78 @@
+// Internal definition of the opaque handle behind include/ter_b200.h.
+// Plain arrays and explicit error codes only: no exceptions cross the C boundary
+// (the reference builds its wrapper the same way, CMakeLists.txt:52-57).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string.h>
+
+#include "../../include/ter_b200.h"
+#include "kernels.h"
+
+struct TerbSlot {
+    char name[TER_B200_MAX_NAME + 1];
+    bool used;
+    terb::DevWeight w;
+};
+
+struct TerbModel;   // decode-forward state (model.cpp)
+
+struct ter_b200_handle_t {
+    int device;
+    int sm_count;
+    cudaStream_t stream;
+    TerbSlot slots[TER_B200_MAX_SLOTS];
+    ter_b200_op_counts_t counts;
+    int* status_dev;          // device status word written by bounded waits
+    int last_cuda;
+    uint64_t launches;
+    terb::GemvLaunchCfg gemv_cfg;
+    // staging for the host-buffer entry points
+    int8_t* hx_dev;
+    size_t hx_cap;
+    float* hout_dev;
+    size_t hout_cap;
+    float* hscale_dev;
+    TerbModel* model;
+};
+
+namespace terb {
+
+inline int cuda_fail(ter_b200_handle_t* h, cudaError_t e) {
+    if (e == cudaSuccess) return TER_B200_OK;
+    if (h) h->last_cuda = (int)e;
+    (void)cudaGetLastError();   // clear the sticky-free error state
+    return e == cudaErrorMemoryAllocation ? TER_B200_E_ALLOC : TER_B200_E_CUDA;
+}
+
+#define TERB_CUDA(h, call)                                   \
+    do {                                                     \
+        cudaError_t e__ = (call);                            \
+        if (e__ != cudaSuccess) return terb::cuda_fail((h), e__); \
+    } while (0)
+
+inline cudaStream_t pick_stream(ter_b200_handle_t* h, void* stream) {
+    return stream ? (cudaStream_t)stream : h->stream;
+}
+
+inline TerbSlot* find_slot(ter_b200_handle_t* h, const char* name) {
+    for (int i = 0; i < TER_B200_MAX_SLOTS; ++i)
+        if (h->slots[i].used && strncmp(h->slots[i].name, name, TER_B200_MAX_NAME + 1) == 0) return &h->slots[i];
+    return nullptr;
+}
+inline const TerbSlot* find_slot(const ter_b200_handle_t* h, const char* name) {
+    return find_slot(const_cast<ter_b200_handle_t*>(h), name);
+}
+
+inline void count_gemv(ter_b200_handle_t* h, int K, int N, int rows) {
+    const uint64_t n = (uint64_t)((K + 26) / 27) * (uint64_t)N * (uint64_t)rows;
+    h->counts.tvmac += n;
+    h->counts.total_ops += n;
+}
+
+// Allocates and fills a DevWeight from a DEVICE pointer in one of the boundary formats.
+int build_weight_from_dev(ter_b200_handle_t* h, const void* data_dev, int format, int K, int N, float scale,
+                          cudaStream_t st, DevWeight* out);
+void free_weight(DevWeight* w);
+
+}  // namespace terb
