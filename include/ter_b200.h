@@ -150,6 +150,15 @@ int ter_b200_gemm(ter_b200_handle_t* h, const char* slot, const int8_t* X_dev,
 int ter_b200_gemm_acc(ter_b200_handle_t* h, const char* slot, const int8_t* X_dev, int M,
                       int32_t* acc_dev, void* stream);
 
+/* ---- CUDA graphs ------------------------------------------------------------
+ * Record every launch made through this handle on `stream` between begin and end into a
+ * CUDA graph and replay it with one call, as the reference's decode loop does
+ * (cuda/ter_cuda_forward_packed.cu:729-747).  Up to 16 graphs per handle. */
+int ter_b200_capture_begin(ter_b200_handle_t* h, void* stream);
+int ter_b200_capture_end(ter_b200_handle_t* h, void* stream, int* graph_id);
+int ter_b200_graph_launch(ter_b200_handle_t* h, int graph_id, void* stream);
+int ter_b200_graph_destroy(ter_b200_handle_t* h, int graph_id);
+
 /* ---- device status ---------------------------------------------------------
  * Kernels never spin without a bound; a wait that ran out records a code that this call
  * returns (TER_B200_E_TIMEOUT) after synchronising the handle's streams. */

@@ -62,6 +62,10 @@ SIGNATURES = {
     "ter_b200_sync": (_I, [_VP, _VP]),
     "ter_b200_gemm": (_I, [_VP, _CP, _VP, _VP, _I, _VP, _VP]),
     "ter_b200_gemm_acc": (_I, [_VP, _CP, _VP, _I, _VP, _VP]),
+    "ter_b200_capture_begin": (_I, [_VP, _VP]),
+    "ter_b200_capture_end": (_I, [_VP, _VP, C.POINTER(_I)]),
+    "ter_b200_graph_launch": (_I, [_VP, _I, _VP]),
+    "ter_b200_graph_destroy": (_I, [_VP, _I]),
     "ter_b200_device_status": (_I, [_VP]),
     "ter_b200_last_cuda_error": (_I, [_VP]),
     "ter_b200_set_option": (_I, [_VP, _CP, _I]),
@@ -100,11 +104,17 @@ def _check(rc: int, what: str = ""):
         raise TerB200Error(rc, what)
 
 
+_CUDA_STREAM_LEGACY = 0x1   # cudaStreamLegacy: the NULL stream named explicitly
+
+
 def _stream_ptr(stream=None):
+    """cudaStream_t of a torch stream (default: torch's current stream).  torch reports its default
+    stream as 0, which the C ABI reads as "the handle's own stream"; name the legacy stream
+    explicitly so that the library's launches stay ordered with torch's work."""
     import torch
     if stream is None:
         stream = torch.cuda.current_stream()
-    return C.c_void_p(stream.cuda_stream)
+    return C.c_void_p(stream.cuda_stream or _CUDA_STREAM_LEGACY)
 
 
 class TerB200:
@@ -238,6 +248,27 @@ class TerB200:
     def call(self, op: str, args):
         arr = (C.c_int64 * len(args))(*[int(a) for a in args])
         return self.L.ter_b200_call(self.h, op.encode(), arr, len(args))
+
+    # ---- CUDA graphs
+    def capture(self, fn, stream=None):
+        """Record the launches fn() makes through this handle into a CUDA graph; returns its id."""
+        import torch
+        s = stream or torch.cuda.Stream()
+        gid = C.c_int(-1)
+        with torch.cuda.stream(s):
+            _check(self.L.ter_b200_capture_begin(self.h, _stream_ptr(s)), "capture_begin")
+            try:
+                fn()
+            finally:
+                rc = self.L.ter_b200_capture_end(self.h, _stream_ptr(s), C.byref(gid))
+            _check(rc, "capture_end")
+        return gid.value
+
+    def graph_launch(self, gid: int, stream=None):
+        _check(self.L.ter_b200_graph_launch(self.h, gid, _stream_ptr(stream)), "graph_launch")
+
+    def graph_destroy(self, gid: int):
+        _check(self.L.ter_b200_graph_destroy(self.h, gid))
 
     # ---- counters / status
     def op_counts(self) -> dict:

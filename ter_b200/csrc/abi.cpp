@@ -203,6 +203,8 @@ void ter_b200_destroy(ter_b200_handle_t* h) {
     cudaSetDevice(h->device);
     if (h->stream) cudaStreamSynchronize(h->stream);
     ter_b200_model_free(h);
+    for (int i = 0; i < 16; ++i)
+        if (h->graphs[i]) cudaGraphExecDestroy(h->graphs[i]);
     for (int i = 0; i < TER_B200_MAX_SLOTS; ++i)
         if (h->slots[i].used) free_weight(&h->slots[i].w);
     if (h->status_dev) cudaFree(h->status_dev);
@@ -362,6 +364,59 @@ int ter_b200_sync(ter_b200_handle_t* h, void* stream) {
     return TER_B200_OK;
 }
 
+int ter_b200_capture_begin(ter_b200_handle_t* h, void* stream) {
+    if (!h) return TER_B200_E_NULL;
+    if (h->capturing) return TER_B200_E_STATE;
+    TERB_CUDA(h, cudaSetDevice(h->device));
+    TERB_CUDA(h, cudaStreamBeginCapture(pick_stream(h, stream), cudaStreamCaptureModeThreadLocal));
+    h->capturing = true;
+    h->capture_mark = h->launches;
+    return TER_B200_OK;
+}
+
+int ter_b200_capture_end(ter_b200_handle_t* h, void* stream, int* graph_id) {
+    if (!h || !graph_id) return TER_B200_E_NULL;
+    if (!h->capturing) return TER_B200_E_STATE;
+    h->capturing = false;
+    cudaGraph_t g = nullptr;
+    TERB_CUDA(h, cudaStreamEndCapture(pick_stream(h, stream), &g));
+    int id = -1;
+    for (int i = 0; i < 16; ++i)
+        if (!h->graphs[i]) { id = i; break; }
+    if (id < 0) {
+        cudaGraphDestroy(g);
+        return TER_B200_E_FULL;
+    }
+    cudaError_t e = cudaGraphInstantiate(&h->graphs[id], g, 0);
+    cudaGraphDestroy(g);
+    if (e != cudaSuccess) {
+        h->graphs[id] = nullptr;
+        return cuda_fail(h, e);
+    }
+    h->graph_launches[id] = h->launches - h->capture_mark;
+    h->launches = h->capture_mark;   // recording a launch is not running it
+    *graph_id = id;
+    return TER_B200_OK;
+}
+
+int ter_b200_graph_launch(ter_b200_handle_t* h, int graph_id, void* stream) {
+    if (!h) return TER_B200_E_NULL;
+    if (graph_id < 0 || graph_id >= 16 || !h->graphs[graph_id]) return TER_B200_E_UNKNOWN;
+    TERB_CUDA(h, cudaSetDevice(h->device));
+    TERB_CUDA(h, cudaGraphLaunch(h->graphs[graph_id], pick_stream(h, stream)));
+    h->launches += h->graph_launches[graph_id];
+    return TER_B200_OK;
+}
+
+int ter_b200_graph_destroy(ter_b200_handle_t* h, int graph_id) {
+    if (!h) return TER_B200_E_NULL;
+    if (graph_id < 0 || graph_id >= 16 || !h->graphs[graph_id]) return TER_B200_E_UNKNOWN;
+    cudaSetDevice(h->device);
+    cudaGraphExecDestroy(h->graphs[graph_id]);
+    h->graphs[graph_id] = nullptr;
+    return TER_B200_OK;
+}
+
 int ter_b200_device_status(ter_b200_handle_t* h) {
     if (!h) return TER_B200_E_NULL;
     TERB_CUDA(h, cudaSetDevice(h->device));
@@ -385,6 +440,9 @@ int ter_b200_set_option(ter_b200_handle_t* h, const char* key, int value) {
     } else if (strcmp(key, "gemv_stages") == 0) {
         if (value < 0 || value > 8) return TER_B200_E_SHAPE;
         h->gemv_cfg.stages = value;
+    } else if (strcmp(key, "gemv_split_max_strips") == 0) {
+        if (value < 0) return TER_B200_E_SHAPE;
+        h->gemv_cfg.split_max_strips = value;
     } else if (strcmp(key, "pdl") == 0) {
         h->gemv_cfg.pdl = value ? 1 : 0;
     } else {

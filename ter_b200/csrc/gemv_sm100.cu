@@ -6,22 +6,24 @@
 //     out[j] = (float)(sum_k x[k] * trit(k, j)) * (x_scale[0] * w_scale)
 // with the integer sum exact.
 //
-// Design (bandwidth kernel; the weights are read exactly once):
-//   * a tile = 16 output columns x all of K = 4*Kpad contiguous bytes of the internal
-//     layout (kernels.h).  One thread issues ONE 1-D TMA bulk copy per tile into a
-//     ring of shared-memory stages; an mbarrier per stage counts the bytes in.
-//   * CTAs are persistent over tiles (tile = blockIdx.x + i*gridDim.x); the copies
-//     for the first `stages` tiles are issued BEFORE griddepcontrol.wait, so under
-//     programmatic dependent launch the weight stream of this GEMV overlaps the
-//     kernel that is still producing x.
-//   * 8 warps split K in 128-byte chunks; lane = (byte-column 0..3, 16-byte segment
-//     0..7): one LDS.128 of weights + one LDS.128 of x feed 16 AND + 16 dp4a.
-//     Field i of every byte is column i, so  dp4a(x4, w & (0x03030303 << 2i))  adds
-//     4^i * sum x*u  for column i: no shifts, no sign decode.  u = trit + 1, so the
-//     true dot product is (acc >> 2i) - sum_k x[k].
-//   * int32 partials are reduced by shuffles over the 8 segment lanes and through
-//     shared memory over the 8 warps; integer addition is associative, so the result
-//     is bit-exact whatever the grid.
+// Design (bandwidth kernel; every weight byte is read exactly once):
+//   * Work unit: a strip = 16 output columns x all of K, stored as contiguous blocks of
+//     [4 byte-columns][<=1024 k] (kernels.h).  Each WARP owns whole strips and streams
+//     their blocks through its own ring of shared-memory stages: lane 0 issues one 1-D
+//     TMA bulk copy per block, an mbarrier per stage counts the bytes in.  Warps never
+//     synchronise with each other after the prologue, so there is no per-strip
+//     __syncthreads and no cross-warp reduction.
+//   * The copies for the first `stages` blocks are issued BEFORE griddepcontrol.wait:
+//     under programmatic dependent launch the weight stream of this GEMV starts while
+//     the kernel that produces x is still running.  x (int8[K]) is then staged once per
+//     CTA in shared memory and shared by the 8 warps.
+//   * lane = (byte-column c = lane/8, 16-byte segment s = lane%8); per 128 k a lane does
+//     one LDS.128 of weights + one LDS.128 of x feeding 16 AND + 16 dp4a.  Field i of
+//     every weight byte is column i, so dp4a(x4, w & (0x03030303 << 2i)) accumulates
+//     4^i * sum x*u for column i: no shifts, no sign decode.  u = trit + 1, so the true
+//     dot product is (acc >> 2i) - sum_k x[k].
+//   * The 8 segment lanes of a byte-column are reduced with 3 xor-shuffles per strip.
+//     Integer addition is associative: the result is bit-exact whatever the grid.
 #include "common.cuh"
 #include "kernels.h"
 
@@ -32,32 +34,39 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
 constexpr int kMaxStages = 8;
-// Fixed shared-memory header: barriers, reduction scratch, sum of x.
-constexpr int kBarOff = 0;                       // 8 x u64
-constexpr int kRedOff = 64;                      // int[2][8][16]
-constexpr int kXsumOff = kRedOff + 2 * kWarps * 16 * 4;   // 1088
-constexpr int kHdrBytes = 1152;                  // multiple of 128
+constexpr int kStageBytes = 4 * kGemvKC;
+// Fixed shared-memory header.
+constexpr int kBarOff = 0;                          // u64[kWarps][kMaxStages] = 512 B
+constexpr int kXsumOff = kWarps * kMaxStages * 8;   // 512
+constexpr int kHdrBytes = 640;                      // multiple of 128
 
-__device__ __forceinline__ void mac16(uint32_t w, int x, int& a0, int& a1, int& a2, int& a3) {
-    a0 = dp4a_su(x, w & 0x03030303u, a0);
+// Accumulates one 32-bit word of weights (4 k x 4 columns) against 4 int8 activations.
+// t collects the UNMASKED product  S0 + 4*S1 + 16*S2 + 64*S3  (no AND needed); a1..a3 collect
+// 4*S1, 16*S2, 64*S3 from masked words; column 0 is recovered as t - a1 - a2 - a3.
+__device__ __forceinline__ void mac16(uint32_t w, int x, int& t, int& a1, int& a2, int& a3) {
+    t = dp4a_su(x, w, t);
     a1 = dp4a_su(x, w & 0x0C0C0C0Cu, a1);
     a2 = dp4a_su(x, w & 0x30303030u, a2);
     a3 = dp4a_su(x, w & 0xC0C0C0C0u, a3);
 }
+__device__ __forceinline__ void mac64(const uint4& w, const int4& xv, int& t, int& a1, int& a2, int& a3) {
+    mac16(w.x, xv.x, t, a1, a2, a3);
+    mac16(w.y, xv.y, t, a1, a2, a3);
+    mac16(w.z, xv.z, t, a1, a2, a3);
+    mac16(w.w, xv.w, t, a1, a2, a3);
+}
 
-__device__ __forceinline__ const uint8_t* tile_src(const GemvParams& p, int tile, int& m, int& lt) {
+__device__ __forceinline__ void locate(const GemvParams& p, int strip, int& m, int& ls) {
     m = 0;
 #pragma unroll
     for (int i = 1; i < kGemvMaxGroup; ++i)
-        if (i < p.n_mats && tile >= p.tile_begin[i]) m = i;
-    lt = tile - p.tile_begin[m];
-    return p.W[m] + (size_t)lt * (size_t)(4 * p.Kpad);
+        if (i < p.n_mats && strip >= p.tile_begin[i]) m = i;
+    ls = strip - p.tile_begin[m];
 }
 
 __global__ void __launch_bounds__(kThreads) gemv_trit_kernel(const __grid_constant__ GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kBarOff);
-    int* red = reinterpret_cast<int*>(smem + kRedOff);
     int* xsum_s = reinterpret_cast<int*>(smem + kXsumOff);
     int8_t* xs = reinterpret_cast<int8_t*>(smem + kHdrBytes);
     uint8_t* wbuf = smem + kHdrBytes + p.Kpad;
@@ -65,31 +74,44 @@ __global__ void __launch_bounds__(kThreads) gemv_trit_kernel(const __grid_consta
     const int tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
     const int S = p.stages;
-    const uint32_t tile_bytes = 4u * (uint32_t)p.Kpad;
+    const int nb = (p.Kpad + kGemvKC - 1) / kGemvKC;          // blocks per strip
+    const int last_kc = p.Kpad - (nb - 1) * kGemvKC;
+    uint64_t* mybars = bars + warp * kMaxStages;
+    uint8_t* mybuf = wbuf + (size_t)warp * S * kStageBytes;
+    // strip t is handled by CTA t % gridDim, warp (t / gridDim) % 8: strips spread over SMs first
+    const int first = blockIdx.x + gridDim.x * warp;
+    const int stride = gridDim.x * kWarps;
 
-    if (tid == 0) {
-        for (int i = 0; i < S; ++i) mbar_init(&bars[i], 1);
-        *xsum_s = 0;
+    if (lane == 0) {
+        for (int i = 0; i < S; ++i) mbar_init(&mybars[i], 1);
         mbar_fence_init();
     }
-    __syncthreads();
+    if (tid == 0) *xsum_s = 0;
+    __syncwarp();
 
-    // Weights are immutable: start streaming them before waiting on the producer of x.
-    if (tid == 0) {
-        for (int i = 0; i < S; ++i) {
-            int tile = blockIdx.x + i * gridDim.x;
-            if (tile < p.n_tiles) {
-                int m, lt;
-                const uint8_t* src = tile_src(p, tile, m, lt);
-                mbar_arrive_expect_tx(&bars[i], tile_bytes);
-                bulk_g2s(wbuf + (size_t)i * tile_bytes, src, tile_bytes, &bars[i]);
+    // Producer cursor over this warp's (strip, block) items; uniform across the warp.
+    int p_strip = first, p_q = 0, p_stage = 0;
+    auto issue = [&]() {
+        if (p_strip < p.n_tiles) {
+            if (lane == 0) {
+                int m, ls;
+                locate(p, p_strip, m, ls);
+                const int kc = (p_q == nb - 1) ? last_kc : kGemvKC;
+                const uint8_t* src = p.W[m] + (size_t)ls * 4u * (size_t)p.Kpad + (size_t)p_q * kStageBytes;
+                mbar_arrive_expect_tx(&mybars[p_stage], 4u * (uint32_t)kc);
+                bulk_g2s(mybuf + (size_t)p_stage * kStageBytes, src, 4u * (uint32_t)kc, &mybars[p_stage]);
             }
+            if (++p_q == nb) { p_q = 0; p_strip += stride; }
+            if (++p_stage == S) p_stage = 0;
         }
-    }
+    };
+    // Weights are immutable: start streaming them before waiting on the producer of x.
+    for (int i = 0; i < S; ++i) issue();
+
     pdl_launch_dependents();
     pdl_wait();
 
-    // Stage x (int8[K], zero-padded to Kpad) and sum it.
+    // Stage x (int8[K], zero-padded to Kpad) once per CTA and sum it.
     {
         int local = 0;
         for (int i = tid * 16; i < p.Kpad; i += kThreads * 16) {
@@ -110,25 +132,28 @@ __global__ void __launch_bounds__(kThreads) gemv_trit_kernel(const __grid_consta
     const float xscale = p.x_scale ? p.x_scale[0] : p.x_scale_imm;
 
     const int c = lane >> 3, sgm = lane & 7;
-    const int n_chunks = p.Kpad >> 7;
-    const int8_t* xp = xs + sgm * 16;
-
-    int it = 0;
-    for (int tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x, ++it) {
-        const int stage = it % S;
-        const uint32_t parity = (uint32_t)(it / S) & 1u;
-        mbar_wait_bounded(&bars[stage], parity, p.status);
-
-        const uint8_t* wt = wbuf + (size_t)stage * tile_bytes + (size_t)c * p.Kpad + sgm * 16;
+    int stage = 0;
+    uint32_t parity = 0;
+    for (int strip = first; strip < p.n_tiles; strip += stride) {
         int a0 = 0, a1 = 0, a2 = 0, a3 = 0;
-#pragma unroll 2
-        for (int ch = warp; ch < n_chunks; ch += kWarps) {
-            const uint4 w = *reinterpret_cast<const uint4*>(wt + ch * 128);
-            const int4 xv = *reinterpret_cast<const int4*>(xp + ch * 128);
-            mac16(w.x, xv.x, a0, a1, a2, a3);
-            mac16(w.y, xv.y, a0, a1, a2, a3);
-            mac16(w.z, xv.z, a0, a1, a2, a3);
-            mac16(w.w, xv.w, a0, a1, a2, a3);
+        for (int q = 0; q < nb; ++q) {
+            const int kc = (q == nb - 1) ? last_kc : kGemvKC;
+            mbar_wait_bounded(&mybars[stage], parity, p.status);
+            const uint8_t* wt = mybuf + (size_t)stage * kStageBytes + c * kc + sgm * 16;
+            const int8_t* xp = xs + q * kGemvKC + sgm * 16;
+            if (kc == kGemvKC) {
+#pragma unroll
+                for (int j = 0; j < kGemvKC / 128; ++j)
+                    mac64(*reinterpret_cast<const uint4*>(wt + j * 128), *reinterpret_cast<const int4*>(xp + j * 128),
+                          a0, a1, a2, a3);
+            } else {
+                for (int j = 0; j < (kc >> 7); ++j)
+                    mac64(*reinterpret_cast<const uint4*>(wt + j * 128), *reinterpret_cast<const int4*>(xp + j * 128),
+                          a0, a1, a2, a3);
+            }
+            __syncwarp();          // every lane has finished reading this stage
+            issue();               // refill it with the block `S` items ahead
+            if (++stage == S) { stage = 0; parity ^= 1u; }
         }
 #pragma unroll
         for (int o = 1; o < 8; o <<= 1) {
@@ -137,33 +162,133 @@ __global__ void __launch_bounds__(kThreads) gemv_trit_kernel(const __grid_consta
             a2 += __shfl_xor_sync(0xffffffffu, a2, o);
             a3 += __shfl_xor_sync(0xffffffffu, a3, o);
         }
-        int* rbuf = red + (it & 1) * (kWarps * 16);
         if (sgm == 0) {
-            int* r = rbuf + warp * 16 + c * 4;
-            r[0] = a0; r[1] = a1; r[2] = a2; r[3] = a3;
-        }
-        __syncthreads();   // every read of this stage is done; partials are visible
-
-        if (tid == 0) {    // refill the stage with the tile `S` rounds ahead
-            int nt = tile + S * gridDim.x;
-            if (nt < p.n_tiles) {
-                int m, lt;
-                const uint8_t* src = tile_src(p, nt, m, lt);
-                mbar_arrive_expect_tx(&bars[stage], tile_bytes);
-                bulk_g2s(wbuf + (size_t)stage * tile_bytes, src, tile_bytes, &bars[stage]);
+            int m, ls;
+            locate(p, strip, m, ls);
+            const int col = ls * 16 + c * 4;
+            const int v0 = (a0 - a1 - a2 - a3) - xsum, v1 = (a1 >> 2) - xsum, v2 = (a2 >> 4) - xsum, v3 = (a3 >> 6) - xsum;
+            const int N = p.N[m];
+            if (int32_t* ao = p.acc_out[m]) {
+                if (col + 3 < N && ((reinterpret_cast<uintptr_t>(ao) & 15u) == 0)) {
+                    *reinterpret_cast<int4*>(ao + col) = make_int4(v0, v1, v2, v3);
+                } else {
+                    if (col < N) ao[col] = v0;
+                    if (col + 1 < N) ao[col + 1] = v1;
+                    if (col + 2 < N) ao[col + 2] = v2;
+                    if (col + 3 < N) ao[col + 3] = v3;
+                }
+            }
+            if (float* fo = p.out[m]) {
+                const float sc = xscale * p.w_scale[m];
+                const float f0 = (float)v0 * sc, f1 = (float)v1 * sc, f2 = (float)v2 * sc, f3 = (float)v3 * sc;
+                if (col + 3 < N && ((reinterpret_cast<uintptr_t>(fo) & 15u) == 0)) {
+                    *reinterpret_cast<float4*>(fo + col) = make_float4(f0, f1, f2, f3);
+                } else {
+                    if (col < N) fo[col] = f0;
+                    if (col + 1 < N) fo[col + 1] = f1;
+                    if (col + 2 < N) fo[col + 2] = f2;
+                    if (col + 3 < N) fo[col + 3] = f3;
+                }
             }
         }
-        if (tid < 16) {
-            int sum = 0;
+    }
+}
+
+
+// ---------------------------------------------------------------------------------
+// Latency path for matrices with few strips (every projection except the lm_head).
+// One CTA per strip; the 8 warps split K in 128-byte chunks (chunk j -> warp j % 8).
+// Each lane fetches its weights with 16-byte read-only global loads straight into
+// registers BEFORE griddepcontrol.wait, so when the producer of x finishes the only
+// work left on the critical path is: load x (L2), 16 AND + 16 dp4a per chunk, a
+// shuffle + shared-memory reduction, one store.  No TMA ring, no staging of x.
+// ---------------------------------------------------------------------------------
+constexpr int kSplitBatch = 8;   // chunks per warp held in registers at once (covers K <= 8192)
+
+__device__ __forceinline__ uint4 ldg_stream(const uint8_t* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+__global__ void __launch_bounds__(kThreads) gemv_trit_split_kernel(const __grid_constant__ GemvParams p) {
+    __shared__ int red[kWarps][20];
+    const int tid = threadIdx.x;
+    const int lane = tid & 31, warp = tid >> 5;
+    const int c = lane >> 3, sgm = lane & 7;
+    const int n_chunks = p.Kpad >> 7;
+    const int nb = (p.Kpad + kGemvKC - 1) / kGemvKC;
+    const int last_kc = p.Kpad - (nb - 1) * kGemvKC;
+
+    const int strip = blockIdx.x;
+    int m, ls;
+    locate(p, strip, m, ls);
+    const uint8_t* base = p.W[m] + (size_t)ls * 4u * (size_t)p.Kpad;
+
+    auto waddr = [&](int j) -> const uint8_t* {
+        const int q = j >> 3;                                   // 8 chunks per 1024-k block
+        const int kc = (q == nb - 1) ? last_kc : kGemvKC;
+        return base + (size_t)q * kStageBytes + c * kc + (j & 7) * 128 + sgm * 16;
+    };
+
+    uint4 w[kSplitBatch];
 #pragma unroll
-            for (int w = 0; w < kWarps; ++w) sum += rbuf[w * 16 + tid];
-            const int v = (sum >> (2 * (tid & 3))) - xsum;
-            int m, lt;
-            (void)tile_src(p, tile, m, lt);
-            const int col = lt * 16 + tid;
-            if (col < p.N[m]) {
-                if (p.acc_out[m]) p.acc_out[m][col] = v;
-                if (p.out[m]) p.out[m][col] = (float)v * (xscale * p.w_scale[m]);
+    for (int i = 0; i < kSplitBatch; ++i) {
+        const int j = warp + kWarps * i;
+        w[i] = (j < n_chunks) ? ldg_stream(waddr(j)) : make_uint4(0, 0, 0, 0);
+    }
+    pdl_launch_dependents();
+    pdl_wait();
+
+    int a0 = 0, a1 = 0, a2 = 0, a3 = 0, xl = 0;
+    for (int b = 0; b * kSplitBatch * kWarps < n_chunks; ++b) {
+        if (b > 0) {
+#pragma unroll
+            for (int i = 0; i < kSplitBatch; ++i) {
+                const int j = warp + kWarps * (i + b * kSplitBatch);
+                w[i] = (j < n_chunks) ? ldg_stream(waddr(j)) : make_uint4(0, 0, 0, 0);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < kSplitBatch; ++i) {
+            const int j = warp + kWarps * (i + b * kSplitBatch);
+            const int k0 = j * 128 + sgm * 16;
+            int4 xv = make_int4(0, 0, 0, 0);
+            if (j < n_chunks && k0 < p.K) xv = *reinterpret_cast<const int4*>(p.x + k0);
+            mac64(w[i], xv, a0, a1, a2, a3);
+            xl = __dp4a(xv.x, 0x01010101, xl);
+            xl = __dp4a(xv.y, 0x01010101, xl);
+            xl = __dp4a(xv.z, 0x01010101, xl);
+            xl = __dp4a(xv.w, 0x01010101, xl);
+        }
+    }
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) {
+        a0 += __shfl_xor_sync(0xffffffffu, a0, o);
+        a1 += __shfl_xor_sync(0xffffffffu, a1, o);
+        a2 += __shfl_xor_sync(0xffffffffu, a2, o);
+        a3 += __shfl_xor_sync(0xffffffffu, a3, o);
+        xl += __shfl_xor_sync(0xffffffffu, xl, o);
+    }
+    if (sgm == 0) {
+        int* r = &red[warp][c * 4];
+        r[0] = a0 - a1 - a2 - a3; r[1] = a1; r[2] = a2; r[3] = a3;
+        if (c == 0) red[warp][16] = xl;
+    }
+    __syncthreads();
+    if (tid < 16) {
+        int sum = 0, xsum = 0;
+#pragma unroll
+        for (int wi = 0; wi < kWarps; ++wi) { sum += red[wi][tid]; xsum += red[wi][16]; }
+        const int v = (sum >> (2 * (tid & 3))) - xsum;
+        const int col = ls * 16 + tid;
+        if (col < p.N[m]) {
+            if (p.acc_out[m]) p.acc_out[m][col] = v;
+            if (p.out[m]) {
+                const float xscale = p.x_scale ? p.x_scale[0] : p.x_scale_imm;
+                p.out[m][col] = (float)v * (xscale * p.w_scale[m]);
             }
         }
     }
@@ -172,7 +297,7 @@ __global__ void __launch_bounds__(kThreads) gemv_trit_kernel(const __grid_consta
 }  // namespace
 
 static size_t gemv_smem_bytes(int Kpad, int stages) {
-    return (size_t)kHdrBytes + (size_t)Kpad + (size_t)stages * 4u * (size_t)Kpad;
+    return (size_t)kHdrBytes + (size_t)Kpad + (size_t)kWarps * (size_t)stages * kStageBytes;
 }
 
 cudaError_t launch_gemv(const GemvParams& p_in, const GemvLaunchCfg& cfg, cudaStream_t st) {
@@ -186,25 +311,30 @@ cudaError_t launch_gemv(const GemvParams& p_in, const GemvLaunchCfg& cfg, cudaSt
         attr_set[dev] = true;
     }
     GemvParams p = p_in;
-    const size_t tile_bytes = 4u * (size_t)p.Kpad;
-    int stages = cfg.stages;
-    if (stages <= 0) {
-        // About 32 KB of weights in flight per CTA, at least a double buffer.
-        stages = (int)((32 * 1024) / tile_bytes);
+    if (cfg.split_max_strips > 0 && p.n_tiles <= cfg.split_max_strips) {
+        cudaLaunchConfig_t lc = {};
+        lc.gridDim = dim3((unsigned)p.n_tiles);
+        lc.blockDim = dim3(kThreads);
+        lc.dynamicSmemBytes = 0;
+        lc.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        lc.attrs = attr;
+        lc.numAttrs = cfg.pdl ? 1 : 0;
+        return cudaLaunchKernelEx(&lc, gemv_trit_split_kernel, p);
     }
-    if (stages < 2) stages = 2;
+    int per_sm = cfg.ctas_per_sm < 1 ? 1 : cfg.ctas_per_sm;
+    int stages = cfg.stages > 0 ? cfg.stages : 3;
     if (stages > kMaxStages) stages = kMaxStages;
+    // keep `per_sm` CTAs resident: shrink the ring first, then the residency
+    while (stages > 2 && gemv_smem_bytes(p.Kpad, stages) * per_sm > (size_t)kMaxSmem) --stages;
+    while (per_sm > 1 && gemv_smem_bytes(p.Kpad, stages) * per_sm > (size_t)kMaxSmem) --per_sm;
     while (stages > 1 && gemv_smem_bytes(p.Kpad, stages) > (size_t)kMaxSmem) --stages;
     if (gemv_smem_bytes(p.Kpad, stages) > (size_t)kMaxSmem) return cudaErrorInvalidValue;
     p.stages = stages;
     const size_t smem = gemv_smem_bytes(p.Kpad, stages);
 
-    int occ = 0;
-    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, gemv_trit_kernel, kThreads, smem);
-    if (e != cudaSuccess) return e;
-    if (occ < 1) return cudaErrorInvalidValue;
-    int per_sm = cfg.ctas_per_sm < occ ? cfg.ctas_per_sm : occ;
-    if (per_sm < 1) per_sm = 1;
     int grid = cfg.sm_count * per_sm;
     if (grid > p.n_tiles) grid = p.n_tiles;
     if (grid < 1) return cudaErrorInvalidValue;

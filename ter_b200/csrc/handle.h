@@ -34,6 +34,10 @@ struct ter_b200_handle_t {
     size_t hout_cap;
     float* hscale_dev;
     TerbModel* model;
+    cudaGraphExec_t graphs[16];
+    uint64_t graph_launches[16];   // kernels recorded in each graph
+    uint64_t capture_mark;
+    bool capturing;
 };
 
 namespace terb {

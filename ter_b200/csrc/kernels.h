@@ -7,19 +7,32 @@
 namespace terb {
 
 // ---- internal weight layout -------------------------------------------------
-// Bytes [Npad/4][Kpad]: byte-column jb holds columns 4*jb..4*jb+3 for consecutive k
-// (the reference's v11 arrangement, cuda/ter_cuda_forward_packed.cu:354-355), with
-//   * the 2-bit field re-coded to u = trit + 1 (0 -> -1, 1 -> 0, 2 -> +1), so that a
+// A "strip" is 16 output columns = 4 byte-columns of the reference's v11 arrangement
+// (byte-column jb holds columns 4*jb..4*jb+3, cuda/ter_cuda_forward_packed.cu:354-355)
+// over all of K.  A strip is stored as consecutive "blocks": block q covers
+// k in [q*kGemvKC, min((q+1)*kGemvKC, Kpad)) and is the contiguous byte array
+// [4 byte-columns][kc], so one 1-D TMA bulk copy fetches one block.  Also:
+//   * the 2-bit field is re-coded to u = trit + 1 (0 -> -1, 1 -> 0, 2 -> +1), so that a
 //     masked word is directly an unsigned dp4a operand,
-//   * K padded to a multiple of 128 with u = 1 (trit 0), N padded to a multiple of 16.
-// A "tile" is 4 consecutive byte-columns (16 output columns): 4*Kpad contiguous bytes.
+//   * K is padded to a multiple of 128 with u = 1 (trit 0), N to a multiple of 16.
+// Bytes per strip: 4*Kpad; strips: Npad/16; algorithmic bytes stay K*N/4.
+constexpr int kGemvKC = 1024;
+
 struct DevWeight {
     uint8_t* data = nullptr;
     int K = 0, N = 0, Kpad = 0, Npad = 0;
     float scale = 0.f;
     size_t bytes() const { return (size_t)(Npad / 4) * (size_t)Kpad; }
-    int tiles() const { return Npad / 16; }
+    int tiles() const { return Npad / 16; }   // strips
 };
+
+// Byte offset of (byte-column jb, k) in the internal layout.
+__host__ __device__ inline size_t weight_offset(int jb, int k, int Kpad) {
+    const int strip = jb >> 2, c = jb & 3;
+    const int q = k / kGemvKC;
+    const int kc = (Kpad - q * kGemvKC) < kGemvKC ? (Kpad - q * kGemvKC) : kGemvKC;
+    return (size_t)strip * 4u * (size_t)Kpad + (size_t)q * 4u * kGemvKC + (size_t)c * kc + (size_t)(k - q * kGemvKC);
+}
 
 constexpr int kGemvMaxGroup = 4;
 constexpr int kGemvMaxK = 32768;
@@ -40,9 +53,11 @@ struct GemvParams {
 };
 
 struct GemvLaunchCfg {
-    int ctas_per_sm = 4;
-    int stages = 0;      // 0 = choose from the tile size
+    int ctas_per_sm = 2;
+    int stages = 0;      // per-warp ring depth; 0 = default
     int pdl = 1;
+    // matrices (or groups) with at most this many strips take the register-prefetch split-K path
+    int split_max_strips = 148 * 8;
     int sm_count = 148;
 };
 

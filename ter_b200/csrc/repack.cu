@@ -28,7 +28,7 @@ __global__ void recode_v11_kernel(const uint8_t* __restrict__ src, uint8_t* __re
         const int jb = (int)(i / (size_t)Kpad), k = (int)(i % (size_t)Kpad);
         uint32_t v = 0x55u;
         if (jb < nbc && k < K) v = recode_byte(src[(size_t)jb * K + k]);
-        dst[i] = (uint8_t)v;
+        dst[weight_offset(jb, k, Kpad)] = (uint8_t)v;
     }
 }
 
@@ -39,7 +39,7 @@ __global__ void recode_rowmajor_kernel(const uint8_t* __restrict__ src, uint8_t*
         const int jb = (int)(i / (size_t)Kpad), k = (int)(i % (size_t)Kpad);
         uint32_t v = 0x55u;
         if (jb < nbc && k < K) v = recode_byte(src[(size_t)k * nbc + jb]);
-        dst[i] = (uint8_t)v;
+        dst[weight_offset(jb, k, Kpad)] = (uint8_t)v;
     }
 }
 
@@ -63,7 +63,7 @@ __global__ void pack_i32_kernel(const int32_t* __restrict__ src, uint8_t* __rest
                 v |= (uint32_t)(t + 1) << (2 * f);
             }
         }
-        dst[i] = (uint8_t)v;
+        dst[weight_offset(jb, k, Kpad)] = (uint8_t)v;
     }
     if (bad) atomicAdd(bad_count, bad);
 }
