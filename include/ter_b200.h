@@ -150,6 +150,53 @@ int ter_b200_gemm(ter_b200_handle_t* h, const char* slot, const int8_t* X_dev,
 int ter_b200_gemm_acc(ter_b200_handle_t* h, const char* slot, const int8_t* X_dev, int M,
                       int32_t* acc_dev, void* stream);
 
+/* ---- decode glue operators -------------------------------------------------
+ * All activations are fp32 device arrays; `rows`/`B` is the number of sequences.
+ *
+ * RMSNorm + absmax int8 quantisation: replaces rmsnorm_quant_fp16_in_k / rmsnorm_quant_f32_in_k
+ * (cuda/ter_cuda_forward_packed.cu:269-309, cuda/ter_cuda_forward_bitnet.cu:64-146):
+ *   n_i = (x_i * (1/sqrt(mean(x^2)+eps))) * gamma_i ; amax = max|n| + 1e-9 ; s = 127/amax ;
+ *   q_i = clamp(rint(n_i*s), -128, 127) ; scale[row] = 1/s.
+ * gamma_dev NULL: no normalisation = quant_int8_k (cuda/ter_cuda_forward_packed.cu:40-62).
+ * q_dev NULL with normed_dev set: RMSNorm only = rmsnorm_f32_in_k (cuda/ter_cuda_forward_bitnet.cu:149-159).
+ * normed_dev (optional) receives the fp32 values that were quantised. */
+int ter_b200_rmsnorm_quant(ter_b200_handle_t* h, const float* x_dev, const float* gamma_dev, int n, int rows,
+                           float eps, int8_t* q_dev, float* scale_dev, float* normed_dev, void* stream);
+/* Gated activation + quantisation.  act = SILU: silu_mul_quant_k
+ * (cuda/ter_cuda_forward_packed.cu:312-344), v = gate/(1+exp(-gate))*up.  act = RELU2:
+ * relu2_mul_rmsnorm_quant_k (cuda/ter_cuda_forward_bitnet.cu:258-309), v = max(gate,0)^2*up followed by
+ * RMSNorm with gamma_dev (the ffn sub-norm) when gamma_dev is not NULL. */
+#define TER_B200_ACT_SILU  1
+#define TER_B200_ACT_RELU2 2
+int ter_b200_act_quant(ter_b200_handle_t* h, int act, const float* gate_dev, const float* up_dev,
+                       const float* gamma_dev, int n, int rows, float eps, int8_t* q_dev, float* scale_dev,
+                       void* stream);
+/* Rotary embedding in place on q [B][Nh*Hd] and k [B][Nkv*Hd] at position pos_dev[b], then append of
+ * k and v, rounded to bf16, to one layer's cache laid out [B][Nkv][Smax][Hd]: rope_k + kv_copy_k
+ * (cuda/ter_cuda_forward_packed.cu:64-90).  neox = 0: pairs (2k,2k+1); neox = 1: pairs (k,k+Hd/2)
+ * (cuda/ter_cuda_forward_bitnet.cu:185-201).  Angles pos*theta^(-2k/Hd) come from a table evaluated
+ * in double on the host (src/tx/forward.cpp:78-88). */
+int ter_b200_rope_kv(ter_b200_handle_t* h, float* q_dev, float* k_dev, const float* v_dev, const int* pos_dev,
+                     int B, int Nh, int Nkv, int Hd, int Smax, double theta, int neox, uint16_t* kcache_dev,
+                     uint16_t* vcache_dev, void* stream);
+/* Causal GQA attention of one new token per sequence over the bf16 cache, seq_len = pos_dev[b]+1:
+ * attention_k (cuda/ter_cuda_forward_packed.cu:118-157), kv head = h*Nkv/Nh, scores/sqrt(Hd),
+ * max-subtracted softmax, sum p*V; evaluated as a split-KV online softmax over chunks of 256
+ * positions.  scratch_dev: ter_b200_attention_scratch_floats() floats of device memory that the
+ * call may overwrite.  Hd in {64,128}; Nh/Nkv <= 8. */
+size_t ter_b200_attention_scratch_floats(int B, int Nh, int Hd, int Smax);
+int ter_b200_attention(ter_b200_handle_t* h, const float* q_dev, const uint16_t* kcache_dev,
+                       const uint16_t* vcache_dev, const int* pos_dev, int B, int Nh, int Nkv, int Hd, int Smax,
+                       float* scratch_dev, size_t scratch_floats, float* out_dev, void* stream);
+/* logits[b][v] = sum_h bf16(table[v][h]) * x[b][h]: mm_fp16_lm_head_k
+ * (cuda/ter_cuda_forward_packed.cu:165-206) with a bf16 table and fp32 activations. */
+int ter_b200_lm_head_bf16(ter_b200_handle_t* h, const uint16_t* table_dev, const float* x_dev, float* logits_dev,
+                          int V, int H, int B, void* stream);
+/* out[b] = lowest index among the maxima of logits[b][0..V): argmax_local_k + argmax_final_k
+ * (cuda/ter_cuda_forward_packed.cu:209-241).  scratch_dev: B*256 floats. */
+int ter_b200_argmax(ter_b200_handle_t* h, const float* logits_dev, int V, int B, float* scratch_dev, int* out_dev,
+                    void* stream);
+
 /* ---- CUDA graphs ------------------------------------------------------------
  * Record every launch made through this handle on `stream` between begin and end into a
  * CUDA graph and replay it with one call, as the reference's decode loop does

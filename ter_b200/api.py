@@ -62,6 +62,13 @@ SIGNATURES = {
     "ter_b200_sync": (_I, [_VP, _VP]),
     "ter_b200_gemm": (_I, [_VP, _CP, _VP, _VP, _I, _VP, _VP]),
     "ter_b200_gemm_acc": (_I, [_VP, _CP, _VP, _I, _VP, _VP]),
+    "ter_b200_rmsnorm_quant": (_I, [_VP, _VP, _VP, _I, _I, _F, _VP, _VP, _VP, _VP]),
+    "ter_b200_act_quant": (_I, [_VP, _I, _VP, _VP, _VP, _I, _I, _F, _VP, _VP, _VP]),
+    "ter_b200_rope_kv": (_I, [_VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, C.c_double, _I, _VP, _VP, _VP]),
+    "ter_b200_attention_scratch_floats": (_SZ, [_I, _I, _I, _I]),
+    "ter_b200_attention": (_I, [_VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _VP, _SZ, _VP, _VP]),
+    "ter_b200_lm_head_bf16": (_I, [_VP, _VP, _VP, _VP, _I, _I, _I, _VP]),
+    "ter_b200_argmax": (_I, [_VP, _VP, _I, _I, _VP, _VP, _VP]),
     "ter_b200_capture_begin": (_I, [_VP, _VP]),
     "ter_b200_capture_end": (_I, [_VP, _VP, C.POINTER(_I)]),
     "ter_b200_graph_launch": (_I, [_VP, _I, _VP]),
@@ -248,6 +255,72 @@ class TerB200:
     def call(self, op: str, args):
         arr = (C.c_int64 * len(args))(*[int(a) for a in args])
         return self.L.ter_b200_call(self.h, op.encode(), arr, len(args))
+
+    # ---- decode glue operators (fp32 torch CUDA tensors; rows = leading dimension)
+    def rmsnorm_quant(self, x, gamma, eps, quant=True, want_normed=False, stream=None):
+        import torch
+        x2 = x.reshape(-1, x.shape[-1])
+        rows, n = x2.shape
+        q = torch.empty((rows, n), dtype=torch.int8, device=x.device) if quant else None
+        sc = torch.empty(rows, dtype=torch.float32, device=x.device) if quant else None
+        normed = torch.empty((rows, n), dtype=torch.float32, device=x.device) if (want_normed or not quant) else None
+        ptr = lambda t: C.c_void_p(t.data_ptr()) if t is not None else None  # noqa: E731
+        _check(self.L.ter_b200_rmsnorm_quant(self.h, ptr(x2), ptr(gamma), n, rows, float(eps), ptr(q), ptr(sc),
+                                             ptr(normed), _stream_ptr(stream)), "rmsnorm_quant")
+        return q, sc, normed
+
+    def act_quant(self, act, gate, up, gamma, eps, stream=None):
+        import torch
+        g2 = gate.reshape(-1, gate.shape[-1])
+        rows, n = g2.shape
+        q = torch.empty((rows, n), dtype=torch.int8, device=gate.device)
+        sc = torch.empty(rows, dtype=torch.float32, device=gate.device)
+        _check(self.L.ter_b200_act_quant(self.h, act, C.c_void_p(g2.data_ptr()), C.c_void_p(up.data_ptr()),
+                                         C.c_void_p(gamma.data_ptr()) if gamma is not None else None, n, rows,
+                                         float(eps), C.c_void_p(q.data_ptr()), C.c_void_p(sc.data_ptr()),
+                                         _stream_ptr(stream)), "act_quant")
+        return q, sc
+
+    def rope_kv(self, q, k, v, pos, Nh, Nkv, Hd, Smax, theta, neox, kcache, vcache, stream=None):
+        B = pos.shape[0]
+        _check(self.L.ter_b200_rope_kv(self.h, C.c_void_p(q.data_ptr()), C.c_void_p(k.data_ptr()),
+                                       C.c_void_p(v.data_ptr()), C.c_void_p(pos.data_ptr()), B, Nh, Nkv, Hd, Smax,
+                                       float(theta), int(neox), C.c_void_p(kcache.data_ptr()),
+                                       C.c_void_p(vcache.data_ptr()), _stream_ptr(stream)), "rope_kv")
+
+    def attention(self, q, kcache, vcache, pos, Nh, Nkv, Hd, Smax, scratch=None, out=None, stream=None):
+        import torch
+        B = pos.shape[0]
+        need = self.L.ter_b200_attention_scratch_floats(B, Nh, Hd, Smax)
+        if scratch is None:
+            scratch = torch.empty(need, dtype=torch.float32, device=q.device)
+        if out is None:
+            out = torch.empty((B, Nh * Hd), dtype=torch.float32, device=q.device)
+        _check(self.L.ter_b200_attention(self.h, C.c_void_p(q.data_ptr()), C.c_void_p(kcache.data_ptr()),
+                                         C.c_void_p(vcache.data_ptr()), C.c_void_p(pos.data_ptr()), B, Nh, Nkv, Hd,
+                                         Smax, C.c_void_p(scratch.data_ptr()), scratch.numel(),
+                                         C.c_void_p(out.data_ptr()), _stream_ptr(stream)), "attention")
+        return out
+
+    def lm_head_bf16(self, table, x, stream=None):
+        import torch
+        x2 = x.reshape(-1, x.shape[-1])
+        B, H = x2.shape
+        V = table.shape[0]
+        logits = torch.empty((B, V), dtype=torch.float32, device=x.device)
+        _check(self.L.ter_b200_lm_head_bf16(self.h, C.c_void_p(table.data_ptr()), C.c_void_p(x2.data_ptr()),
+                                            C.c_void_p(logits.data_ptr()), V, H, B, _stream_ptr(stream)), "lm_head")
+        return logits
+
+    def argmax(self, logits, stream=None):
+        import torch
+        l2 = logits.reshape(-1, logits.shape[-1])
+        B, V = l2.shape
+        scratch = torch.empty(B * 256, dtype=torch.float32, device=logits.device)
+        out = torch.empty(B, dtype=torch.int32, device=logits.device)
+        _check(self.L.ter_b200_argmax(self.h, C.c_void_p(l2.data_ptr()), V, B, C.c_void_p(scratch.data_ptr()),
+                                      C.c_void_p(out.data_ptr()), _stream_ptr(stream)), "argmax")
+        return out
 
     # ---- CUDA graphs
     def capture(self, fn, stream=None):

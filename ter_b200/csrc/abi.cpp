@@ -207,6 +207,8 @@ void ter_b200_destroy(ter_b200_handle_t* h) {
         if (h->graphs[i]) cudaGraphExecDestroy(h->graphs[i]);
     for (int i = 0; i < TER_B200_MAX_SLOTS; ++i)
         if (h->slots[i].used) free_weight(&h->slots[i].w);
+    for (int i = 0; i < 4; ++i)
+        if (h->rope[i].data) cudaFree(h->rope[i].data);
     if (h->status_dev) cudaFree(h->status_dev);
     if (h->hscale_dev) cudaFree(h->hscale_dev);
     if (h->hx_dev) cudaFree(h->hx_dev);

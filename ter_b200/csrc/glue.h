@@ -1,0 +1,67 @@
+// Host-side declarations of the decode glue launchers (glue_sm100.cu).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace terb {
+
+enum PreOp : int { PRE_NONE = 0, PRE_SILU_MUL = 1, PRE_RELU2_MUL = 2 };
+
+// v = pre(x, u) ; optional RMSNorm(gamma, eps) ; optional absmax int8 quantisation.
+// Row r of a batch of `rows` uses x + r*n (and u, q, normed likewise), scale_out[r].
+struct NormQuantParams {
+    const float* x;        // [rows][n]  (gate for the SILU/RELU2 pre-ops)
+    const float* u;        // [rows][n]  up-projection, or null
+    const float* gamma;    // [n] or null (no normalisation)
+    int8_t* q;             // [rows][n] or null (no quantisation)
+    float* scale_out;      // [rows]
+    float* normed;         // [rows][n] or null: the fp32 values before quantisation
+    int n, rows, pre;
+    float eps;
+};
+cudaError_t launch_norm_quant(const NormQuantParams& p, bool pdl, cudaStream_t st);
+
+// Rotary embedding of q [B][Nh*Hd] and k [B][Nkv*Hd] in place at position pos[b], then
+// append of k, v (rounded to bf16) to the cache of one layer, laid out
+// [B][Nkv][Smax][Hd].  table: [Smax][Hd/2][2] (cos, sin).
+struct RopeKvParams {
+    float* q;
+    float* k;
+    const float* v;
+    const float* table;
+    const int* pos;        // [B] device
+    uint16_t* kcache;
+    uint16_t* vcache;
+    int B, Nh, Nkv, Hd, Smax, neox;
+};
+cudaError_t launch_rope_kv(const RopeKvParams& p, bool pdl, cudaStream_t st);
+
+constexpr int kAttnChunk = 256;
+// Partial record per (b, head, chunk): m, l, o[Hd]  -> Hd + 2 floats.
+struct AttnParams {
+    const float* q;          // [B][Nh*Hd] (after rotary)
+    const uint16_t* kcache;  // [B][Nkv][Smax][Hd] bf16
+    const uint16_t* vcache;
+    const int* pos;          // [B]: seq_len = pos[b] + 1
+    float* scratch;          // [B][Nh][max_chunks][Hd+2]
+    float* out;              // [B][Nh*Hd]
+    int B, Nh, Nkv, Hd, Smax, max_chunks;
+};
+cudaError_t launch_attention(const AttnParams& p, bool pdl, cudaStream_t st);
+size_t attention_scratch_floats(int B, int Nh, int Hd, int Smax);
+
+// logits[b][v] = sum_h bf16(table[v][h]) * x[b][h], fp32 accumulate.
+cudaError_t launch_lm_head_bf16(const uint16_t* table, const float* x, float* logits, int V, int H, int B,
+                                int sm_count, bool pdl, cudaStream_t st);
+// out[b] = lowest index among the maxima of logits[b][0..V).  scratch: [B][kArgmaxParts][2] floats.
+constexpr int kArgmaxParts = 128;
+cudaError_t launch_argmax(const float* logits, int V, int B, float* scratch, int* out, bool pdl, cudaStream_t st);
+// hidden[b][:] = float(table[token[b]][:])
+cudaError_t launch_embed(const uint16_t* table, const int* tokens, float* hidden, int H, int B, int V, bool pdl,
+                         cudaStream_t st);
+// x[i] += y[i]
+cudaError_t launch_add(float* x, const float* y, size_t n, bool pdl, cudaStream_t st);
+// pos[b] += 1
+cudaError_t launch_inc(int* pos, int B, bool pdl, cudaStream_t st);
+
+}  // namespace terb

@@ -1,0 +1,573 @@
+// Decode glue kernels for sm_100a: fused RMSNorm / activation + absmax int8 quantisation,
+// rotary embedding + KV-cache append, split-KV GQA attention over a bf16 cache, bf16
+// lm_head, argmax, embedding gather, residual add.  Each is a single-pass bandwidth kernel.
+//
+// Numerics: this file is compiled with -fmad=false; every fused multiply-add below is an
+// explicit fmaf().  Floating-point reductions use one fixed order that depends on the
+// problem only ("block order"): 256 lane partials over elements 1024*r + 4*t + e, an xor
+// butterfly (16,8,4,2,1) inside each warp, then the 8 warp sums added left to right.  The
+// result therefore does not depend on the grid, the batch size or the number of GPUs, and
+// the CPU checker reproduces it bit for bit.
+//
+// Reference kernels restated here (formulas, not code): rmsnorm_quant_*_in_k,
+// quant_int8_k, silu_mul_quant_k (cuda/ter_cuda_forward_packed.cu:40-62,269-344),
+// relu2_mul_rmsnorm_quant_k (cuda/ter_cuda_forward_bitnet.cu:258-309), rope_k / kv_copy_k /
+// attention_k (cuda/ter_cuda_forward_packed.cu:64-90,118-157; NEOX variant
+// cuda/ter_cuda_forward_bitnet.cu:185-201), mm_fp16_lm_head_k and argmax_*_k
+// (cuda/ter_cuda_forward_packed.cu:165-259).
+#include <cuda_bf16.h>
+#include <math_constants.h>
+
+#include "common.cuh"
+#include "glue.h"
+
+namespace terb {
+
+namespace {
+
+constexpr int kT = 256;   // threads per CTA in every glue kernel
+
+// exp(x) in fp32: n = rint(x*log2e); r = x - n*ln2 (two steps); degree-5 polynomial; * 2^n.
+// Arguments are clamped to [-87, 88]; below -87 the result is 0.  Same operations, in the
+// same order, as the CPU checker.
+__device__ __forceinline__ float exp_fixed(float x) {
+    if (!(x >= -87.0f)) return 0.0f;
+    if (x > 88.0f) x = 88.0f;
+    const float n = rintf(x * 1.44269504088896341f);
+    float r = fmaf(n, -0.693145751953125f, x);
+    r = fmaf(n, -1.42860682030941723212e-6f, r);
+    float p = 1.9875691500e-4f;
+    p = fmaf(p, r, 1.3981999507e-3f);
+    p = fmaf(p, r, 8.3334519073e-3f);
+    p = fmaf(p, r, 4.1665795894e-2f);
+    p = fmaf(p, r, 1.6666665459e-1f);
+    p = fmaf(p, r, 5.0000001201e-1f);
+    const float r2 = r * r;
+    float y = fmaf(p, r2, r);
+    y = y + 1.0f;
+    const int ni = (int)n;
+    return y * __int_as_float((ni + 127) << 23);
+}
+
+__device__ __forceinline__ float bf16_bits_to_f32(uint32_t b) { return __uint_as_float(b << 16); }
+__device__ __forceinline__ uint16_t f32_to_bf16_bits(float f) {
+    return __bfloat16_as_ushort(__float2bfloat16_rn(f));
+}
+
+__device__ __forceinline__ float warp_sum_butterfly(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = v + __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+// Block order sum of one value per thread (256 threads).  red: 8 floats of shared memory.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    v = warp_sum_butterfly(v);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = red[0];
+#pragma unroll
+    for (int w = 1; w < kT / 32; ++w) t = t + red[w];
+    return t;
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+    v = warp_max(v);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = red[0];
+#pragma unroll
+    for (int w = 1; w < kT / 32; ++w) t = fmaxf(t, red[w]);
+    return t;
+}
+
+__device__ __forceinline__ int quant_one(float v, float scale) {
+    int q = __float2int_rn(v * scale);
+    return q > 127 ? 127 : (q < -128 ? -128 : q);
+}
+
+}  // namespace
+
+// ============================================================ norm / activation / quantise
+namespace {
+
+__device__ __forceinline__ float pre_op(int pre, float x, float u) {
+    if (pre == PRE_SILU_MUL) {
+        const float e = exp_fixed(-x);
+        const float sg = x / (1.0f + e);
+        return sg * u;
+    }
+    if (pre == PRE_RELU2_MUL) {
+        const float r = x > 0.0f ? x * x : 0.0f;
+        return r * u;
+    }
+    return x;
+}
+
+__global__ void __launch_bounds__(kT) norm_quant_kernel(const NormQuantParams p) {
+    extern __shared__ float vals[];   // n floats: the row after pre-op / normalisation
+    __shared__ float red[kT / 32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int tid = threadIdx.x;
+    const size_t off = (size_t)blockIdx.x * (size_t)p.n;
+    const float* x = p.x + off;
+    const float* u = p.u ? p.u + off : nullptr;
+    const int n = p.n;
+
+    float part = 0.0f;
+    for (int base = 4 * tid; base < n; base += 4 * kT) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int i = base + e;
+            if (i < n) {
+                const float v = pre_op(p.pre, x[i], u ? u[i] : 0.0f);
+                vals[i] = v;
+                part = fmaf(v, v, part);
+            }
+        }
+    }
+    float amax = 0.0f;
+    if (p.gamma) {
+        const float ss = block_sum(part, red);
+        const float mean = ss / (float)n;
+        const float ri = 1.0f / sqrtf(mean + p.eps);
+        for (int base = 4 * tid; base < n; base += 4 * kT) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int i = base + e;
+                if (i < n) {
+                    const float v = (vals[i] * ri) * p.gamma[i];
+                    vals[i] = v;
+                    amax = fmaxf(amax, fabsf(v));
+                }
+            }
+        }
+    } else {
+        for (int base = 4 * tid; base < n; base += 4 * kT)
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                if (base + e < n) amax = fmaxf(amax, fabsf(vals[base + e]));
+    }
+    if (p.normed) {
+        float* o = p.normed + off;
+        for (int base = 4 * tid; base < n; base += 4 * kT)
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                if (base + e < n) o[base + e] = vals[base + e];
+    }
+    if (p.q) {
+        amax = block_max(amax, red) + 1e-9f;
+        const float scale = 127.0f / amax;
+        if (tid == 0) p.scale_out[blockIdx.x] = 1.0f / scale;
+        int8_t* q = p.q + off;
+        for (int base = 4 * tid; base < n; base += 4 * kT) {
+            if (base + 3 < n && ((reinterpret_cast<uintptr_t>(q + base) & 3u) == 0)) {
+                const int q0 = quant_one(vals[base], scale), q1 = quant_one(vals[base + 1], scale);
+                const int q2 = quant_one(vals[base + 2], scale), q3 = quant_one(vals[base + 3], scale);
+                *reinterpret_cast<uint32_t*>(q + base) =
+                    (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) |
+                    ((uint32_t)(q3 & 0xff) << 24);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (base + e < n) q[base + e] = (int8_t)quant_one(vals[base + e], scale);
+            }
+        }
+    }
+}
+
+template <typename Kern, typename Params>
+cudaError_t launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, bool pdl, cudaStream_t st, const Params& p) {
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = grid;
+    lc.blockDim = block;
+    lc.dynamicSmemBytes = smem;
+    lc.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = attr;
+    lc.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&lc, kern, p);
+}
+
+}  // namespace
+
+cudaError_t launch_norm_quant(const NormQuantParams& p, bool pdl, cudaStream_t st) {
+    const size_t smem = (size_t)p.n * sizeof(float);
+    if (smem > 200 * 1024) return cudaErrorInvalidValue;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(norm_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+    }
+    return launch_pdl(norm_quant_kernel, dim3((unsigned)p.rows), dim3(kT), smem, pdl, st, p);
+}
+
+// ============================================================ rotary + KV append
+namespace {
+
+__global__ void __launch_bounds__(kT) rope_kv_kernel(const RopeKvParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int b = blockIdx.x;
+    const int pos = p.pos[b];
+    if (pos < 0 || pos >= p.Smax) return;
+    const int half = p.Hd / 2;
+    const float* row = p.table + (size_t)pos * p.Hd;   // [Hd/2][2]
+    float* q = p.q + (size_t)b * p.Nh * p.Hd;
+    float* k = p.k + (size_t)b * p.Nkv * p.Hd;
+    const float* v = p.v + (size_t)b * p.Nkv * p.Hd;
+    const int n_pairs = (p.Nh + p.Nkv) * half;
+    for (int idx = threadIdx.x; idx < n_pairs; idx += kT) {
+        const int head = idx / half, kk = idx % half;
+        const bool is_k = head >= p.Nh;
+        float* base = is_k ? k + (size_t)(head - p.Nh) * p.Hd : q + (size_t)head * p.Hd;
+        const int i0 = p.neox ? kk : 2 * kk;
+        const int i1 = p.neox ? kk + half : 2 * kk + 1;
+        const float c = row[2 * kk], s = row[2 * kk + 1];
+        const float v0 = base[i0], v1 = base[i1];
+        const float a = v0 * c, bb = v1 * s;
+        const float d = v0 * s, e = v1 * c;
+        const float o0 = a - bb, o1 = d + e;
+        base[i0] = o0;
+        base[i1] = o1;
+        if (is_k) {
+            const size_t co = (((size_t)b * p.Nkv + (head - p.Nh)) * p.Smax + pos) * p.Hd;
+            p.kcache[co + i0] = f32_to_bf16_bits(o0);
+            p.kcache[co + i1] = f32_to_bf16_bits(o1);
+        }
+    }
+    for (int idx = threadIdx.x; idx < p.Nkv * p.Hd; idx += kT) {
+        const int g = idx / p.Hd, d = idx % p.Hd;
+        const size_t co = (((size_t)b * p.Nkv + g) * p.Smax + pos) * p.Hd;
+        p.vcache[co + d] = f32_to_bf16_bits(v[idx]);
+    }
+}
+
+}  // namespace
+
+cudaError_t launch_rope_kv(const RopeKvParams& p, bool pdl, cudaStream_t st) {
+    return launch_pdl(rope_kv_kernel, dim3((unsigned)p.B), dim3(kT), 0, pdl, st, p);
+}
+
+// ============================================================ split-KV GQA attention
+// Chunked online softmax in a fixed order: the context is cut in chunks of 256 positions;
+// one CTA computes, for one (sequence, KV head, chunk) and every query head of the group,
+// the chunk maximum m, l = sum exp(s - m) (block order) and o[d] = sum_t exp(s_t - m) V[t][d]
+// (t ascending, fused multiply-adds).  A second kernel merges the chunks left to right.
+// Score of one position: 8 lanes each take 8 consecutive dims of every 64, fused
+// multiply-adds in ascending dim order, then an xor butterfly (4,2,1) over the 8 lanes.
+namespace {
+
+constexpr int kMaxGroup = 8;   // query heads per KV head
+
+template <int HD>
+__global__ void __launch_bounds__(kT) attn_partial_kernel(const AttnParams p) {
+    __shared__ __align__(16) float qs[kMaxGroup * HD];
+    __shared__ float sc[kMaxGroup][kAttnChunk];
+    __shared__ float red[kT / 32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int c = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
+    const int seq_len = p.pos[b] + 1;
+    const int s0 = c * kAttnChunk;
+    if (s0 >= seq_len || seq_len > p.Smax) return;
+    const int cnt = min(kAttnChunk, seq_len - s0);
+    const int G = p.Nh / p.Nkv;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint16_t* K = p.kcache + ((size_t)b * p.Nkv + g) * (size_t)p.Smax * HD;
+    const uint16_t* V = p.vcache + ((size_t)b * p.Nkv + g) * (size_t)p.Smax * HD;
+    const float* q = p.q + ((size_t)b * p.Nh + (size_t)g * G) * HD;
+    for (int i = tid; i < G * HD; i += kT) qs[i] = q[i];
+    __syncthreads();
+
+    const float inv_sqrt = 1.0f / sqrtf((float)HD);
+    const int sub = lane >> 3, j = lane & 7;
+#pragma unroll 1
+    for (int it = 0; it < 8; ++it) {
+        const int t = warp * 32 + it * 4 + sub;
+        const bool valid = t < cnt;
+        float kv[HD / 8];   // this lane's dims: 8 per 64-dim piece
+#pragma unroll
+        for (int pc = 0; pc < HD / 64; ++pc) {
+            uint4 raw = make_uint4(0, 0, 0, 0);
+            if (valid) raw = *reinterpret_cast<const uint4*>(K + (size_t)(s0 + t) * HD + pc * 64 + 8 * j);
+            kv[pc * 8 + 0] = bf16_bits_to_f32(raw.x & 0xffffu);
+            kv[pc * 8 + 1] = bf16_bits_to_f32(raw.x >> 16);
+            kv[pc * 8 + 2] = bf16_bits_to_f32(raw.y & 0xffffu);
+            kv[pc * 8 + 3] = bf16_bits_to_f32(raw.y >> 16);
+            kv[pc * 8 + 4] = bf16_bits_to_f32(raw.z & 0xffffu);
+            kv[pc * 8 + 5] = bf16_bits_to_f32(raw.z >> 16);
+            kv[pc * 8 + 6] = bf16_bits_to_f32(raw.w & 0xffffu);
+            kv[pc * 8 + 7] = bf16_bits_to_f32(raw.w >> 16);
+        }
+        for (int hh = 0; hh < G; ++hh) {
+            float acc = 0.0f;
+#pragma unroll
+            for (int pc = 0; pc < HD / 64; ++pc) {
+                const float4 qa = *reinterpret_cast<const float4*>(&qs[hh * HD + pc * 64 + 8 * j]);
+                const float4 qb = *reinterpret_cast<const float4*>(&qs[hh * HD + pc * 64 + 8 * j + 4]);
+                acc = fmaf(qa.x, kv[pc * 8 + 0], acc);
+                acc = fmaf(qa.y, kv[pc * 8 + 1], acc);
+                acc = fmaf(qa.z, kv[pc * 8 + 2], acc);
+                acc = fmaf(qa.w, kv[pc * 8 + 3], acc);
+                acc = fmaf(qb.x, kv[pc * 8 + 4], acc);
+                acc = fmaf(qb.y, kv[pc * 8 + 5], acc);
+                acc = fmaf(qb.z, kv[pc * 8 + 6], acc);
+                acc = fmaf(qb.w, kv[pc * 8 + 7], acc);
+            }
+            acc = acc + __shfl_xor_sync(0xffffffffu, acc, 4);
+            acc = acc + __shfl_xor_sync(0xffffffffu, acc, 2);
+            acc = acc + __shfl_xor_sync(0xffffffffu, acc, 1);
+            if (j == 0) sc[hh][t] = valid ? acc * inv_sqrt : -CUDART_INF_F;
+        }
+    }
+    __syncthreads();
+
+    float* rec0 = p.scratch + (((size_t)b * p.Nh + (size_t)g * G) * p.max_chunks + c) * (HD + 2);
+    const size_t rec_stride = (size_t)p.max_chunks * (HD + 2);
+    for (int hh = 0; hh < G; ++hh) {
+        const float s = sc[hh][tid];
+        const float m = block_max(s, red);
+        const float pt = tid < cnt ? exp_fixed(s - m) : 0.0f;
+        const float l = block_sum(pt, red);
+        sc[hh][tid] = pt;
+        if (tid == 0) {
+            rec0[hh * rec_stride + 0] = m;
+            rec0[hh * rec_stride + 1] = l;
+        }
+    }
+    __syncthreads();
+
+    for (int idx = tid; idx < G * HD; idx += kT) {
+        const int hh = idx / HD, d = idx % HD;
+        const float* pr = sc[hh];
+        const uint16_t* vp = V + (size_t)s0 * HD + d;
+        float acc = 0.0f;
+#pragma unroll 8
+        for (int t = 0; t < cnt; ++t) acc = fmaf(pr[t], bf16_bits_to_f32(vp[(size_t)t * HD]), acc);
+        rec0[hh * rec_stride + 2 + d] = acc;
+    }
+}
+
+template <int HD>
+__global__ void __launch_bounds__(HD) attn_combine_kernel(const AttnParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+    const int seq_len = p.pos[b] + 1;
+    if (seq_len < 1 || seq_len > p.Smax) return;
+    const int nc = (seq_len + kAttnChunk - 1) / kAttnChunk;
+    const float* rec = p.scratch + ((size_t)b * p.Nh + h) * (size_t)p.max_chunks * (HD + 2);
+    float M = rec[0], L = rec[1], O = rec[2 + d];
+    for (int c = 1; c < nc; ++c) {
+        const float* r = rec + (size_t)c * (HD + 2);
+        const float mc = r[0], lc = r[1], oc = r[2 + d];
+        const float Mn = fmaxf(M, mc);
+        const float a = exp_fixed(M - Mn), bb = exp_fixed(mc - Mn);
+        L = fmaf(lc, bb, L * a);
+        O = fmaf(oc, bb, O * a);
+        M = Mn;
+    }
+    p.out[((size_t)b * p.Nh + h) * HD + d] = O / L;
+}
+
+}  // namespace
+
+size_t attention_scratch_floats(int B, int Nh, int Hd, int Smax) {
+    const int mc = (Smax + kAttnChunk - 1) / kAttnChunk;
+    return (size_t)B * Nh * mc * (Hd + 2);
+}
+
+cudaError_t launch_attention(const AttnParams& p, bool pdl, cudaStream_t st) {
+    if (p.Nkv < 1 || p.Nh % p.Nkv != 0 || p.Nh / p.Nkv > kMaxGroup) return cudaErrorInvalidValue;
+    const dim3 grid((unsigned)p.max_chunks, (unsigned)p.Nkv, (unsigned)p.B);
+    cudaError_t e;
+    if (p.Hd == 64) {
+        e = launch_pdl(attn_partial_kernel<64>, grid, dim3(kT), 0, pdl, st, p);
+        if (e != cudaSuccess) return e;
+        return launch_pdl(attn_combine_kernel<64>, dim3((unsigned)p.Nh, (unsigned)p.B), dim3(64), 0, pdl, st, p);
+    }
+    if (p.Hd == 128) {
+        e = launch_pdl(attn_partial_kernel<128>, grid, dim3(kT), 0, pdl, st, p);
+        if (e != cudaSuccess) return e;
+        return launch_pdl(attn_combine_kernel<128>, dim3((unsigned)p.Nh, (unsigned)p.B), dim3(128), 0, pdl, st, p);
+    }
+    return cudaErrorInvalidValue;
+}
+
+// ============================================================ bf16 lm_head, argmax, small ops
+namespace {
+
+struct LmHeadParams {
+    const uint16_t* table;
+    const float* x;
+    float* logits;
+    int V, H;
+};
+
+__device__ __forceinline__ uint4 ldg_stream16(const void* ptr) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(ptr));
+    return v;
+}
+
+// One warp per vocabulary row; lane l takes elements 256*r + 8*l + e (e ascending), fused
+// multiply-adds, then an xor butterfly over the warp.  grid.y = batch row.
+__global__ void __launch_bounds__(kT) lm_head_bf16_kernel(const LmHeadParams p) {
+    extern __shared__ __align__(16) float xs[];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float* x = p.x + (size_t)blockIdx.y * p.H;
+    for (int i = tid; i < p.H; i += kT) xs[i] = x[i];
+    __syncthreads();
+    float* logits = p.logits + (size_t)blockIdx.y * p.V;
+    const int total_warps = gridDim.x * (kT / 32);
+    for (int v = blockIdx.x * (kT / 32) + warp; v < p.V; v += total_warps) {
+        const uint16_t* row = p.table + (size_t)v * p.H;
+        float acc = 0.0f;
+#pragma unroll 4
+        for (int base = 8 * lane; base < p.H; base += 256) {
+            const uint4 w = ldg_stream16(row + base);
+            const float4 xa = *reinterpret_cast<const float4*>(&xs[base]);
+            const float4 xb = *reinterpret_cast<const float4*>(&xs[base + 4]);
+            acc = fmaf(bf16_bits_to_f32(w.x & 0xffffu), xa.x, acc);
+            acc = fmaf(bf16_bits_to_f32(w.x >> 16), xa.y, acc);
+            acc = fmaf(bf16_bits_to_f32(w.y & 0xffffu), xa.z, acc);
+            acc = fmaf(bf16_bits_to_f32(w.y >> 16), xa.w, acc);
+            acc = fmaf(bf16_bits_to_f32(w.z & 0xffffu), xb.x, acc);
+            acc = fmaf(bf16_bits_to_f32(w.z >> 16), xb.y, acc);
+            acc = fmaf(bf16_bits_to_f32(w.w & 0xffffu), xb.z, acc);
+            acc = fmaf(bf16_bits_to_f32(w.w >> 16), xb.w, acc);
+        }
+        acc = warp_sum_butterfly(acc);
+        if (lane == 0) logits[v] = acc;
+    }
+}
+
+struct ArgmaxParams {
+    const float* logits;
+    float* scratch;   // [B][kArgmaxParts][2]: value, index bits
+    int* out;
+    int V;
+};
+
+__device__ __forceinline__ void argmax_merge(float& v, int& i, float v2, int i2) {
+    if (v2 > v || (v2 == v && i2 < i)) { v = v2; i = i2; }
+}
+__device__ __forceinline__ void argmax_block(float& v, int& i, float* sv, int* si) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float v2 = __shfl_xor_sync(0xffffffffu, v, o);
+        const int i2 = __shfl_xor_sync(0xffffffffu, i, o);
+        argmax_merge(v, i, v2, i2);
+    }
+    const int warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    if ((threadIdx.x & 31) == 0) { sv[warp] = v; si[warp] = i; }
+    __syncthreads();
+    if (threadIdx.x == 0)
+        for (int w = 1; w < nw; ++w) argmax_merge(v, i, sv[w], si[w]);
+}
+
+__global__ void __launch_bounds__(kT) argmax_part_kernel(const ArgmaxParams p) {
+    __shared__ float sv[kT / 32];
+    __shared__ int si[kT / 32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const float* lg = p.logits + (size_t)blockIdx.y * p.V;
+    float best = -CUDART_INF_F;
+    int bi = 0x7fffffff;
+    for (int i = blockIdx.x * kT + threadIdx.x; i < p.V; i += gridDim.x * kT) {
+        const float v = lg[i];
+        if (v > best) { best = v; bi = i; }
+    }
+    argmax_block(best, bi, sv, si);
+    if (threadIdx.x == 0) {
+        float* s = p.scratch + ((size_t)blockIdx.y * kArgmaxParts + blockIdx.x) * 2;
+        s[0] = best;
+        s[1] = __int_as_float(bi);
+    }
+}
+__global__ void __launch_bounds__(kArgmaxParts) argmax_final_kernel(const ArgmaxParams p) {
+    __shared__ float sv[kArgmaxParts / 32];
+    __shared__ int si[kArgmaxParts / 32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const float* s = p.scratch + ((size_t)blockIdx.x * kArgmaxParts + threadIdx.x) * 2;
+    float best = s[0];
+    int bi = __float_as_int(s[1]);
+    argmax_block(best, bi, sv, si);
+    if (threadIdx.x == 0) p.out[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;
+}
+
+struct EmbedParams { const uint16_t* table; const int* tokens; float* hidden; int H, V; };
+__global__ void __launch_bounds__(kT) embed_kernel(const EmbedParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
+    int t = p.tokens[blockIdx.y];
+    if (t < 0 || t >= p.V) t = 0;
+    const int i = blockIdx.x * kT + threadIdx.x;
+    if (i < p.H) p.hidden[(size_t)blockIdx.y * p.H + i] = bf16_bits_to_f32(p.table[(size_t)t * p.H + i]);
+}
+struct AddParams { float* x; const float* y; size_t n; };
+__global__ void __launch_bounds__(kT) add_kernel(const AddParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * kT + threadIdx.x;
+    if (i < p.n) p.x[i] = p.x[i] + p.y[i];
+}
+struct IncParams { int* pos; int B; };
+__global__ void inc_kernel(const IncParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
+    if ((int)threadIdx.x < p.B) p.pos[threadIdx.x] += 1;
+}
+
+}  // namespace
+
+cudaError_t launch_lm_head_bf16(const uint16_t* table, const float* x, float* logits, int V, int H, int B,
+                                int sm_count, bool pdl, cudaStream_t st) {
+    if (H % 8 != 0 || (size_t)H * 4 > 160 * 1024) return cudaErrorInvalidValue;
+    const size_t smem = (size_t)H * sizeof(float);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(lm_head_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+    }
+    int gx = sm_count * 4;
+    if (gx > (V + 7) / 8) gx = (V + 7) / 8;
+    LmHeadParams p{table, x, logits, V, H};
+    return launch_pdl(lm_head_bf16_kernel, dim3((unsigned)gx, (unsigned)B), dim3(kT), smem, pdl, st, p);
+}
+
+cudaError_t launch_argmax(const float* logits, int V, int B, float* scratch, int* out, bool pdl, cudaStream_t st) {
+    ArgmaxParams p{logits, scratch, out, V};
+    cudaError_t e = launch_pdl(argmax_part_kernel, dim3(kArgmaxParts, (unsigned)B), dim3(kT), 0, pdl, st, p);
+    if (e != cudaSuccess) return e;
+    return launch_pdl(argmax_final_kernel, dim3((unsigned)B), dim3(kArgmaxParts), 0, pdl, st, p);
+}
+
+cudaError_t launch_embed(const uint16_t* table, const int* tokens, float* hidden, int H, int B, int V, bool pdl,
+                         cudaStream_t st) {
+    EmbedParams p{table, tokens, hidden, H, V};
+    return launch_pdl(embed_kernel, dim3((unsigned)((H + kT - 1) / kT), (unsigned)B), dim3(kT), 0, pdl, st, p);
+}
+cudaError_t launch_add(float* x, const float* y, size_t n, bool pdl, cudaStream_t st) {
+    AddParams p{x, y, n};
+    return launch_pdl(add_kernel, dim3((unsigned)((n + kT - 1) / kT)), dim3(kT), 0, pdl, st, p);
+}
+cudaError_t launch_inc(int* pos, int B, bool pdl, cudaStream_t st) {
+    if (B > 1024) return cudaErrorInvalidValue;
+    IncParams p{pos, B};
+    return launch_pdl(inc_kernel, dim3(1), dim3(B < 32 ? 32 : ((B + 31) / 32 * 32)), 0, pdl, st, p);
+}
+
+}  // namespace terb

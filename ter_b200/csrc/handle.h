@@ -17,6 +17,12 @@ struct TerbSlot {
 
 struct TerbModel;   // decode-forward state (model.cpp)
 
+struct RopeTable {
+    float* data = nullptr;   // device [n_pos][head_dim/2][2]
+    int n_pos = 0, head_dim = 0;
+    double theta = 0.0;
+};
+
 struct ter_b200_handle_t {
     int device;
     int sm_count;
@@ -34,6 +40,7 @@ struct ter_b200_handle_t {
     size_t hout_cap;
     float* hscale_dev;
     TerbModel* model;
+    RopeTable rope[4];
     cudaGraphExec_t graphs[16];
     uint64_t graph_launches[16];   // kernels recorded in each graph
     uint64_t capture_mark;
@@ -78,5 +85,6 @@ inline void count_gemv(ter_b200_handle_t* h, int K, int N, int rows) {
 int build_weight_from_dev(ter_b200_handle_t* h, const void* data_dev, int format, int K, int N, float scale,
                           cudaStream_t st, DevWeight* out);
 void free_weight(DevWeight* w);
+int get_rope_table(ter_b200_handle_t* h, int n_pos, int head_dim, double theta, const float** out);
 
 }  // namespace terb

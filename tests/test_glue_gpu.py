@@ -1,0 +1,145 @@
+"""Parity of the decode glue kernels with the CPU checker, through the C ABI.
+int8 outputs and indices: bit-exact.  fp32 outputs: asserted within 1e-3 relative (the stated
+tolerance) and, because both sides use the same fixed reduction order, also bit-for-bit."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from ter_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def bits(a):
+    return np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+
+
+def close(a, b, rtol=1e-3, atol=1e-6):
+    return np.allclose(a, b, rtol=rtol, atol=atol)
+
+
+@pytest.mark.parametrize("n", [8, 100, 2048, 2560, 6912, 8192])
+def test_rmsnorm_quant(tb, n):
+    rng = np.random.default_rng(n)
+    x = (rng.standard_normal((3, n)) * rng.uniform(0.1, 20)).astype(np.float32)
+    g = rng.normal(1.0, 0.02, size=n).astype(np.float32)
+    q, sc, normed = tb.rmsnorm_quant(dev(x), dev(g), 1e-5, want_normed=True)
+    q, sc, normed = q.cpu().numpy(), sc.cpu().numpy(), normed.cpu().numpy()
+    for r in range(3):
+        oq, os_, on = oracle.rmsnorm_quant(x[r], g, 1e-5)
+        assert close(normed[r], on) and np.array_equal(bits(normed[r]), bits(on))
+        assert np.array_equal(q[r], oq)
+        assert bits(sc[r]) == bits(os_)
+    # RMSNorm only
+    _, _, only = tb.rmsnorm_quant(dev(x), dev(g), 1e-5, quant=False)
+    assert np.array_equal(bits(only.cpu().numpy()[1]), bits(oracle.rmsnorm(x[1], g, 1e-5)))
+    # absmax quantiser only (quant_int8_k)
+    q2, s2, _ = tb.rmsnorm_quant(dev(x), None, 0.0)
+    oq, os_ = oracle.quant_int8(x[2])
+    assert np.array_equal(q2.cpu().numpy()[2], oq) and bits(s2.cpu().numpy()[2]) == bits(os_)
+
+
+def test_quantiser_edge_cases(tb):
+    z = np.zeros((1, 64), np.float32)
+    q, s, _ = tb.rmsnorm_quant(dev(z), None, 0.0)
+    oq, os_ = oracle.quant_int8(z[0])
+    assert not q.cpu().numpy().any() and bits(s.cpu().numpy()[0]) == bits(os_)
+    one = np.zeros((1, 64), np.float32); one[0, 7] = -3.0
+    q, s, _ = tb.rmsnorm_quant(dev(one), None, 0.0)
+    assert q.cpu().numpy()[0, 7] == -127 and np.count_nonzero(q.cpu().numpy()) == 1
+
+
+@pytest.mark.parametrize("n", [64, 8192, 6912])
+def test_act_quant(tb, n):
+    rng = np.random.default_rng(n + 1)
+    g = (rng.standard_normal((2, n)) * 4).astype(np.float32)
+    u = (rng.standard_normal((2, n)) * 3).astype(np.float32)
+    gam = rng.normal(1.0, 0.02, size=n).astype(np.float32)
+    q, s = tb.act_quant(1, dev(g), dev(u), None, 0.0)
+    for r in range(2):
+        oq, os_ = oracle.silu_mul_quant(g[r], u[r])
+        assert np.array_equal(q.cpu().numpy()[r], oq) and bits(s.cpu().numpy()[r]) == bits(os_)
+    q, s = tb.act_quant(2, dev(g), dev(u), dev(gam), 1e-5)
+    for r in range(2):
+        oq, os_ = oracle.relu2_mul_rmsnorm_quant(g[r], u[r], gam, 1e-5)
+        assert np.array_equal(q.cpu().numpy()[r], oq) and bits(s.cpu().numpy()[r]) == bits(os_)
+
+
+def make_cache(rng, B, Nkv, Smax, Hd):
+    k = oracle.f32_to_bf16(rng.standard_normal((B, Nkv, Smax, Hd)).astype(np.float32))
+    v = oracle.f32_to_bf16(rng.standard_normal((B, Nkv, Smax, Hd)).astype(np.float32))
+    return k, v
+
+
+@pytest.mark.parametrize("Nh,Nkv,Hd,neox", [(32, 8, 64, 0), (20, 5, 128, 1), (4, 2, 64, 1)])
+def test_rope_and_kv_append(tb, Nh, Nkv, Hd, neox):
+    rng = np.random.default_rng(Nh)
+    B, Smax, theta = 3, 300, 500000.0
+    pos = np.array([0, 37, 299], np.int32)
+    q = rng.standard_normal((B, Nh * Hd)).astype(np.float32)
+    k = rng.standard_normal((B, Nkv * Hd)).astype(np.float32)
+    v = rng.standard_normal((B, Nkv * Hd)).astype(np.float32)
+    kc0, vc0 = make_cache(rng, B, Nkv, Smax, Hd)
+    qd, kd, vd, kcd, vcd = dev(q), dev(k), dev(v), dev(kc0.view(np.int16)), dev(vc0.view(np.int16))
+    tb.rope_kv(qd, kd, vd, dev(pos), Nh, Nkv, Hd, Smax, theta, neox, kcd, vcd)
+    tab = oracle.rope_table(Smax, Hd, theta)
+    kc, vc = kcd.cpu().numpy().view(np.uint16), vcd.cpu().numpy().view(np.uint16)
+    for b in range(B):
+        oq = oracle.rope(q[b], Nh, Hd, tab[pos[b]], neox)
+        ok = oracle.rope(k[b], Nkv, Hd, tab[pos[b]], neox)
+        assert np.array_equal(bits(qd.cpu().numpy()[b]), bits(oq))
+        assert np.array_equal(bits(kd.cpu().numpy()[b]), bits(ok))
+        want_k, want_v = kc0[b].copy(), vc0[b].copy()
+        want_k[:, pos[b], :] = oracle.f32_to_bf16(ok).reshape(Nkv, Hd)
+        want_v[:, pos[b], :] = oracle.f32_to_bf16(v[b]).reshape(Nkv, Hd)
+        assert np.array_equal(kc[b], want_k) and np.array_equal(vc[b], want_v)   # only row pos[b] changed
+
+
+@pytest.mark.parametrize("Nh,Nkv,Hd,Smax,lens", [
+    (32, 8, 64, 512, [1, 2, 255, 256, 257, 512]),
+    (20, 5, 128, 2176, [1, 300, 2048, 2176]),
+    (4, 1, 64, 700, [77, 700]),
+    (8, 1, 128, 64, [64]),
+])
+def test_attention(tb, Nh, Nkv, Hd, Smax, lens):
+    rng = np.random.default_rng(Smax)
+    B = len(lens)
+    q = rng.standard_normal((B, Nh * Hd)).astype(np.float32)
+    kc, vc = make_cache(rng, B, Nkv, Smax, Hd)
+    pos = np.array([n - 1 for n in lens], np.int32)
+    out = tb.attention(dev(q), dev(kc.view(np.int16)), dev(vc.view(np.int16)), dev(pos), Nh, Nkv, Hd, Smax)
+    out = out.cpu().numpy()
+    for b, n in enumerate(lens):
+        want = oracle.attention(q[b], kc[b], vc[b], Nh, Nkv, Hd, Smax, n)
+        spec = oracle.attention(q[b], kc[b], vc[b], Nh, Nkv, Hd, Smax, n, twopass=True)
+        assert close(out[b], spec, rtol=1e-3, atol=1e-5), (b, n)      # the reference's two-pass form
+        assert np.array_equal(bits(out[b]), bits(want)), (b, n)        # the chunked form, bit for bit
+
+
+@pytest.mark.parametrize("V,H,B", [(1000, 256, 1), (4099, 2048, 2), (128256, 2048, 1), (3000, 2560, 3)])
+def test_lm_head_and_argmax(tb, V, H, B):
+    rng = np.random.default_rng(V)
+    table = oracle.f32_to_bf16((rng.standard_normal((V, H)) * 0.02).astype(np.float32))
+    x = rng.standard_normal((B, H)).astype(np.float32)
+    logits = tb.lm_head_bf16(dev(table.view(np.int16)), dev(x))
+    lg = logits.cpu().numpy()
+    for b in range(B):
+        if V <= 5000:
+            want = oracle.lm_head_bf16(table, x[b])
+            assert np.array_equal(bits(lg[b]), bits(want))
+        ref = oracle.bf16_to_f32(table).astype(np.float64) @ x[b].astype(np.float64)
+        assert np.allclose(lg[b], ref, rtol=1e-3, atol=1e-4)
+    am = tb.argmax(logits).cpu().numpy()
+    for b in range(B):
+        assert am[b] == oracle.argmax(lg[b])
+    # ties resolve to the lowest index
+    t = torch.zeros((2, 70000), device="cuda")
+    t[0, 69999] = 5.0; t[0, 1234] = 5.0; t[0, 40000] = 5.0
+    t[1, :] = -3.0
+    am = tb.argmax(t).cpu().numpy()
+    assert am[0] == 1234 and am[1] == 0
