@@ -197,6 +197,56 @@ int ter_b200_lm_head_bf16(ter_b200_handle_t* h, const uint16_t* table_dev, const
 int ter_b200_argmax(ter_b200_handle_t* h, const float* logits_dev, int V, int B, float* scratch_dev, int* out_dev,
                     void* stream);
 
+/* ---- decode forward -----------------------------------------------------------
+ * One model per handle.  Replaces the Model/Scratch structs and forward_token_dev of the reference's
+ * CUDA forwards (cuda/ter_cuda_forward_packed.cu:399-421,505-563; cuda/ter_cuda_forward_bitnet.cu:850-913)
+ * and, on the CPU side, forward_token (src/tx/transformer.cpp:116-223).  arch 0 = Llama (interleaved
+ * rotary, SiLU gate, plain absmax quantisation before Wo); arch 1 = BitNet (NEOX rotary, ReLU^2 gate,
+ * attn_sub_norm / ffn_sub_norm).  Residual stream fp32, KV cache bf16, embeddings bf16. */
+typedef struct {
+    int32_t arch;
+    int32_t H, F, L, V, Nh, Nkv, Hd, Smax;
+    float   eps;
+    double  rope_theta;
+    int32_t lm_head_packed;   /* 1: packed-trit lm_head (K=H, N=V); 0: bf16 table tied to the embeddings */
+    int32_t max_batch;        /* sequences decoded together (KV cache is allocated for this many) */
+} ter_b200_model_cfg_t;
+#define TER_B200_ARCH_LLAMA  0
+#define TER_B200_ARCH_BITNET 1
+/* matrices of a layer, in the order of the packed-model files (tools/convert_llama_to_packed.py:13-43) */
+enum { TER_B200_WQ = 0, TER_B200_WK, TER_B200_WV, TER_B200_WO, TER_B200_WGATE, TER_B200_WUP, TER_B200_WDOWN };
+enum { TER_B200_ATTN_NORM = 0, TER_B200_FFN_NORM, TER_B200_ATTN_SUB_NORM, TER_B200_FFN_SUB_NORM };
+
+int ter_b200_model_create(ter_b200_handle_t* h, const ter_b200_model_cfg_t* cfg);
+/* data: HOST pointer in a TER_B200_FMT_* format; layer = -1 installs the packed lm_head. */
+int ter_b200_model_set_matrix(ter_b200_handle_t* h, int layer, int which, const void* data, int format, float scale);
+int ter_b200_model_set_matrix_dev(ter_b200_handle_t* h, int layer, int which, const void* data_dev, int format,
+                                  float scale);
+/* v: HOST fp32 vector; layer = -1 installs output_norm. */
+int ter_b200_model_set_vector(ter_b200_handle_t* h, int layer, int which, const float* v);
+/* bf16 [V][H] embedding table (also the lm_head when lm_head_packed = 0): host / device pointer. */
+int ter_b200_model_set_embd(ter_b200_handle_t* h, const uint16_t* table);
+int ter_b200_model_set_embd_dev(ter_b200_handle_t* h, const uint16_t* table_dev);
+/* Start `batch` sequences at position 0 (the KV cache content is simply overwritten as they grow). */
+int ter_b200_model_reset(ter_b200_handle_t* h, int batch);
+/* One decode step for every sequence: forward_token (cuda/ter_cuda_forward_packed.cu:671-678).
+ * tokens_host / pos_host ([batch], may be NULL: continue from the device-resident state, i.e. the
+ * greedy token and position left by the previous step).  next_host ([batch], may be NULL) receives
+ * the greedy next tokens after a stream synchronisation. */
+int ter_b200_decode_step(ter_b200_handle_t* h, const int32_t* tokens_host, const int32_t* pos_host,
+                         int32_t* next_host, void* stream);
+/* Copies of the state of the latest step: logits [batch][V], residual stream [batch][H]. */
+int ter_b200_model_logits(ter_b200_handle_t* h, float* logits_host);
+int ter_b200_model_hidden(ter_b200_handle_t* h, float* hidden_host);
+/* Greedy generation: feeds `n_prompt` prompt tokens per sequence one position at a time (the
+ * reference's only prefill method, cuda/ter_cuda_forward_packed.cu:706-712) and then `n_gen` greedy
+ * tokens, replaying ONE captured CUDA graph per step with no host round trip in between.
+ * prompts [batch][n_prompt], out [batch][n_gen]. */
+int ter_b200_generate(ter_b200_handle_t* h, const int32_t* prompts, int batch, int n_prompt, int n_gen,
+                      int32_t* out_tokens, void* stream);
+/* Milliseconds the device spent in the steps of the latest ter_b200_generate call (CUDA events). */
+float ter_b200_last_generate_ms(const ter_b200_handle_t* h);
+
 /* ---- CUDA graphs ------------------------------------------------------------
  * Record every launch made through this handle on `stream` between begin and end into a
  * CUDA graph and replay it with one call, as the reference's decode loop does

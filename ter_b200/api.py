@@ -32,6 +32,12 @@ class OpCounts(C.Structure):
                 ("tvsub", C.c_uint64), ("tvmul", C.c_uint64)]
 
 
+class ModelCfg(C.Structure):
+    _fields_ = [("arch", C.c_int32), ("H", C.c_int32), ("F", C.c_int32), ("L", C.c_int32), ("V", C.c_int32),
+                ("Nh", C.c_int32), ("Nkv", C.c_int32), ("Hd", C.c_int32), ("Smax", C.c_int32), ("eps", C.c_float),
+                ("rope_theta", C.c_double), ("lm_head_packed", C.c_int32), ("max_batch", C.c_int32)]
+
+
 class BlobHdr(C.Structure):
     _fields_ = [("magic", C.c_uint32), ("format", C.c_uint32), ("K", C.c_uint32), ("N", C.c_uint32),
                 ("scale", C.c_float), ("reserved", C.c_uint32 * 3)]
@@ -69,6 +75,18 @@ SIGNATURES = {
     "ter_b200_attention": (_I, [_VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _VP, _SZ, _VP, _VP]),
     "ter_b200_lm_head_bf16": (_I, [_VP, _VP, _VP, _VP, _I, _I, _I, _VP]),
     "ter_b200_argmax": (_I, [_VP, _VP, _I, _I, _VP, _VP, _VP]),
+    "ter_b200_model_create": (_I, [_VP, C.POINTER(ModelCfg)]),
+    "ter_b200_model_set_matrix": (_I, [_VP, _I, _I, _VP, _I, _F]),
+    "ter_b200_model_set_matrix_dev": (_I, [_VP, _I, _I, _VP, _I, _F]),
+    "ter_b200_model_set_vector": (_I, [_VP, _I, _I, _VP]),
+    "ter_b200_model_set_embd": (_I, [_VP, _VP]),
+    "ter_b200_model_set_embd_dev": (_I, [_VP, _VP]),
+    "ter_b200_model_reset": (_I, [_VP, _I]),
+    "ter_b200_decode_step": (_I, [_VP, _VP, _VP, _VP, _VP]),
+    "ter_b200_model_logits": (_I, [_VP, _VP]),
+    "ter_b200_model_hidden": (_I, [_VP, _VP]),
+    "ter_b200_generate": (_I, [_VP, _VP, _I, _I, _I, _VP, _VP]),
+    "ter_b200_last_generate_ms": (_F, [_VP]),
     "ter_b200_capture_begin": (_I, [_VP, _VP]),
     "ter_b200_capture_end": (_I, [_VP, _VP, C.POINTER(_I)]),
     "ter_b200_graph_launch": (_I, [_VP, _I, _VP]),
@@ -321,6 +339,85 @@ class TerB200:
         _check(self.L.ter_b200_argmax(self.h, C.c_void_p(l2.data_ptr()), V, B, C.c_void_p(scratch.data_ptr()),
                                       C.c_void_p(out.data_ptr()), _stream_ptr(stream)), "argmax")
         return out
+
+    # ---- decode forward
+    def model_create(self, cfg: dict, max_batch: int = 1):
+        c = ModelCfg(arch=cfg["arch"], H=cfg["H"], F=cfg["F"], L=cfg["L"], V=cfg["V"], Nh=cfg["Nh"], Nkv=cfg["Nkv"],
+                     Hd=cfg["Hd"], Smax=cfg["Smax"], eps=cfg["eps"], rope_theta=cfg["rope_theta"],
+                     lm_head_packed=int(cfg.get("lm_head_packed", 0)), max_batch=max_batch)
+        _check(self.L.ter_b200_model_create(self.h, C.byref(c)), "model_create")
+        self.model_cfg = dict(cfg, max_batch=max_batch)
+        self._batch = 1
+
+    def model_set_matrix(self, layer, which, data, fmt, scale):
+        import numpy as np
+        import torch
+        if isinstance(data, torch.Tensor) and data.is_cuda:
+            d = data.contiguous()
+            rc = self.L.ter_b200_model_set_matrix_dev(self.h, layer, which, C.c_void_p(d.data_ptr()), fmt, float(scale))
+        else:
+            a = np.ascontiguousarray(data)
+            rc = self.L.ter_b200_model_set_matrix(self.h, layer, which, C.c_void_p(a.ctypes.data), fmt, float(scale))
+        _check(rc, f"model_set_matrix {layer}/{which}")
+
+    def model_set_vector(self, layer, which, v):
+        import numpy as np
+        a = np.ascontiguousarray(v, dtype=np.float32)
+        _check(self.L.ter_b200_model_set_vector(self.h, layer, which, C.c_void_p(a.ctypes.data)), "model_set_vector")
+
+    def model_set_embd(self, table_bf16):
+        import numpy as np
+        import torch
+        if isinstance(table_bf16, torch.Tensor) and table_bf16.is_cuda:
+            rc = self.L.ter_b200_model_set_embd_dev(self.h, C.c_void_p(table_bf16.contiguous().data_ptr()))
+        else:
+            a = np.ascontiguousarray(table_bf16, dtype=np.uint16)
+            rc = self.L.ter_b200_model_set_embd(self.h, C.c_void_p(a.ctypes.data))
+        _check(rc, "model_set_embd")
+
+    def model_reset(self, batch=1):
+        _check(self.L.ter_b200_model_reset(self.h, batch), "model_reset")
+        self._batch = batch
+
+    def decode_step(self, tokens=None, pos=None, want_next=True, stream=None):
+        import numpy as np
+        B = self._batch
+        t = np.ascontiguousarray(tokens, dtype=np.int32) if tokens is not None else None
+        p = np.ascontiguousarray(pos, dtype=np.int32) if pos is not None else None
+        nxt = np.empty(B, dtype=np.int32) if want_next else None
+        _check(self.L.ter_b200_decode_step(self.h, C.c_void_p(t.ctypes.data) if t is not None else None,
+                                           C.c_void_p(p.ctypes.data) if p is not None else None,
+                                           C.c_void_p(nxt.ctypes.data) if want_next else None,
+                                           _stream_ptr(stream)), "decode_step")
+        return nxt
+
+    def model_logits(self):
+        import numpy as np
+        out = np.empty((self._batch, self.model_cfg["V"]), dtype=np.float32)
+        _check(self.L.ter_b200_model_logits(self.h, C.c_void_p(out.ctypes.data)), "model_logits")
+        return out
+
+    def model_hidden(self):
+        import numpy as np
+        out = np.empty((self._batch, self.model_cfg["H"]), dtype=np.float32)
+        _check(self.L.ter_b200_model_hidden(self.h, C.c_void_p(out.ctypes.data)), "model_hidden")
+        return out
+
+    def generate(self, prompts, n_gen, stream=None):
+        """prompts int32 [batch][n_prompt] -> int32 [batch][n_gen] greedy tokens."""
+        import numpy as np
+        p = np.ascontiguousarray(prompts, dtype=np.int32)
+        if p.ndim == 1:
+            p = p[None, :]
+        B, n_prompt = p.shape
+        out = np.empty((B, n_gen), dtype=np.int32)
+        _check(self.L.ter_b200_generate(self.h, C.c_void_p(p.ctypes.data), B, n_prompt, n_gen,
+                                        C.c_void_p(out.ctypes.data), _stream_ptr(stream)), "generate")
+        self._batch = B
+        return out
+
+    def last_generate_ms(self) -> float:
+        return float(self.L.ter_b200_last_generate_ms(self.h))
 
     # ---- CUDA graphs
     def capture(self, fn, stream=None):

@@ -114,9 +114,9 @@ static int ensure_host_staging(ter_b200_handle_t* h, size_t x_bytes, size_t out_
 }
 
 // One launch over up to kGemvMaxGroup weights sharing x.
-static int run_gemv(ter_b200_handle_t* h, const DevWeight* const* ws, int n, const int8_t* x_dev,
-                    const float* x_scale_dev, float x_scale_imm, float* const* outs, int32_t* const* accs,
-                    cudaStream_t st) {
+int run_gemv(ter_b200_handle_t* h, const DevWeight* const* ws, int n, const int8_t* x_dev,
+             const float* x_scale_dev, float x_scale_imm, float* const* outs, int32_t* const* accs,
+             bool accumulate, cudaStream_t st) {
     if (n < 1 || n > kGemvMaxGroup) return TER_B200_E_SHAPE;
     if (((uintptr_t)x_dev & 15u) != 0) return TER_B200_E_SHAPE;
     GemvParams p;
@@ -141,6 +141,7 @@ static int run_gemv(ter_b200_handle_t* h, const DevWeight* const* ws, int n, con
     p.n_mats = n;
     p.n_tiles = tiles;
     p.status = h->status_dev;
+    p.accumulate = accumulate ? 1 : 0;
     GemvLaunchCfg cfg = h->gemv_cfg;
     cfg.sm_count = h->sm_count;
     TERB_CUDA(h, launch_gemv(p, cfg, st));
@@ -312,7 +313,7 @@ int ter_b200_gemv(ter_b200_handle_t* h, const char* slot, const int8_t* x_dev, c
     TERB_CUDA(h, cudaSetDevice(h->device));
     const DevWeight* ws[1] = {&s->w};
     float* outs[1] = {out_dev};
-    return run_gemv(h, ws, 1, x_dev, x_scale_dev, 1.0f, outs, nullptr, pick_stream(h, stream));
+    return run_gemv(h, ws, 1, x_dev, x_scale_dev, 1.0f, outs, nullptr, false, pick_stream(h, stream));
 }
 
 int ter_b200_gemv_acc(ter_b200_handle_t* h, const char* slot, const int8_t* x_dev, int32_t* acc_dev,
@@ -323,7 +324,7 @@ int ter_b200_gemv_acc(ter_b200_handle_t* h, const char* slot, const int8_t* x_de
     TERB_CUDA(h, cudaSetDevice(h->device));
     const DevWeight* ws[1] = {&s->w};
     int32_t* accs[1] = {acc_dev};
-    return run_gemv(h, ws, 1, x_dev, nullptr, 1.0f, nullptr, accs, pick_stream(h, stream));
+    return run_gemv(h, ws, 1, x_dev, nullptr, 1.0f, nullptr, accs, false, pick_stream(h, stream));
 }
 
 int ter_b200_gemv_group(ter_b200_handle_t* h, const char* const* slots, int n_slots, const int8_t* x_dev,
@@ -338,7 +339,7 @@ int ter_b200_gemv_group(ter_b200_handle_t* h, const char* const* slots, int n_sl
         ws[i] = &s->w;
     }
     TERB_CUDA(h, cudaSetDevice(h->device));
-    return run_gemv(h, ws, n_slots, x_dev, x_scale_dev, 1.0f, outs_dev, nullptr, pick_stream(h, stream));
+    return run_gemv(h, ws, n_slots, x_dev, x_scale_dev, 1.0f, outs_dev, nullptr, false, pick_stream(h, stream));
 }
 
 int ter_b200_gemv_host(ter_b200_handle_t* h, const char* slot, const int8_t* x_host, float x_scale,
@@ -353,7 +354,7 @@ int ter_b200_gemv_host(ter_b200_handle_t* h, const char* slot, const int8_t* x_h
     TERB_CUDA(h, cudaMemcpyAsync(h->hx_dev, x_host, (size_t)s->w.K, cudaMemcpyHostToDevice, st));
     const DevWeight* ws[1] = {&s->w};
     float* outs[1] = {h->hout_dev};
-    rc = run_gemv(h, ws, 1, h->hx_dev, nullptr, x_scale, outs, nullptr, st);
+    rc = run_gemv(h, ws, 1, h->hx_dev, nullptr, x_scale, outs, nullptr, false, st);
     if (rc) return rc;
     TERB_CUDA(h, cudaMemcpyAsync(out_host, h->hout_dev, (size_t)s->w.N * sizeof(float), cudaMemcpyDeviceToHost, st));
     return TER_B200_OK;

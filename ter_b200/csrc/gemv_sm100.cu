@@ -180,7 +180,13 @@ __global__ void __launch_bounds__(kThreads) gemv_trit_kernel(const __grid_consta
             }
             if (float* fo = p.out[m]) {
                 const float sc = xscale * p.w_scale[m];
-                const float f0 = (float)v0 * sc, f1 = (float)v1 * sc, f2 = (float)v2 * sc, f3 = (float)v3 * sc;
+                float f0 = (float)v0 * sc, f1 = (float)v1 * sc, f2 = (float)v2 * sc, f3 = (float)v3 * sc;
+                if (p.accumulate) {
+                    if (col < N) f0 = fo[col] + f0;
+                    if (col + 1 < N) f1 = fo[col + 1] + f1;
+                    if (col + 2 < N) f2 = fo[col + 2] + f2;
+                    if (col + 3 < N) f3 = fo[col + 3] + f3;
+                }
                 if (col + 3 < N && ((reinterpret_cast<uintptr_t>(fo) & 15u) == 0)) {
                     *reinterpret_cast<float4*>(fo + col) = make_float4(f0, f1, f2, f3);
                 } else {
@@ -288,7 +294,8 @@ __global__ void __launch_bounds__(kThreads) gemv_trit_split_kernel(const __grid_
             if (p.acc_out[m]) p.acc_out[m][col] = v;
             if (p.out[m]) {
                 const float xscale = p.x_scale ? p.x_scale[0] : p.x_scale_imm;
-                p.out[m][col] = (float)v * (xscale * p.w_scale[m]);
+                const float f = (float)v * (xscale * p.w_scale[m]);
+                p.out[m][col] = p.accumulate ? p.out[m][col] + f : f;
             }
         }
     }

@@ -63,5 +63,17 @@ cudaError_t launch_embed(const uint16_t* table, const int* tokens, float* hidden
 cudaError_t launch_add(float* x, const float* y, size_t n, bool pdl, cudaStream_t st);
 // pos[b] += 1
 cudaError_t launch_inc(int* pos, int B, bool pdl, cudaStream_t st);
+// End of a decode step: next token = forced[b][pos+1] while pos+1 < ctl[0] (prompt feeding), else the
+// greedy token; logged to log[b][pos] when pos < ctl[1]; pos += 1.  ctl = {n_forced, log_len} on device.
+struct SelectParams {
+    const int* greedy;   // [B]
+    const int* forced;   // [B][forced_stride] or null
+    int* tokens;         // [B]
+    int* pos;            // [B]
+    int* log;            // [B][log_stride] or null
+    const int* ctl;
+    int B, forced_stride, log_stride;
+};
+cudaError_t launch_select(const SelectParams& p, bool pdl, cudaStream_t st);
 
 }  // namespace terb

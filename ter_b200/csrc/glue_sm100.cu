@@ -564,6 +564,24 @@ cudaError_t launch_add(float* x, const float* y, size_t n, bool pdl, cudaStream_
     AddParams p{x, y, n};
     return launch_pdl(add_kernel, dim3((unsigned)((n + kT - 1) / kT)), dim3(kT), 0, pdl, st, p);
 }
+namespace {
+__global__ void select_kernel(const SelectParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int b = threadIdx.x;
+    if (b >= p.B) return;
+    const int ps = p.pos[b];
+    int nxt = p.greedy[b];
+    if (p.forced && ps + 1 < p.ctl[0] && ps + 1 < p.forced_stride) nxt = p.forced[(size_t)b * p.forced_stride + ps + 1];
+    p.tokens[b] = nxt;
+    if (p.log && ps >= 0 && ps < p.ctl[1] && ps < p.log_stride) p.log[(size_t)b * p.log_stride + ps] = nxt;
+    p.pos[b] = ps + 1;
+}
+}  // namespace
+cudaError_t launch_select(const SelectParams& p, bool pdl, cudaStream_t st) {
+    if (p.B > 1024) return cudaErrorInvalidValue;
+    return launch_pdl(select_kernel, dim3(1), dim3(p.B < 32 ? 32 : ((p.B + 31) / 32 * 32)), 0, pdl, st, p);
+}
 cudaError_t launch_inc(int* pos, int B, bool pdl, cudaStream_t st) {
     if (B > 1024) return cudaErrorInvalidValue;
     IncParams p{pos, B};

@@ -85,6 +85,9 @@ inline void count_gemv(ter_b200_handle_t* h, int K, int N, int rows) {
 int build_weight_from_dev(ter_b200_handle_t* h, const void* data_dev, int format, int K, int N, float scale,
                           cudaStream_t st, DevWeight* out);
 void free_weight(DevWeight* w);
+// One launch over up to kGemvMaxGroup weights sharing x (abi.cpp).
+int run_gemv(ter_b200_handle_t* h, const DevWeight* const* ws, int n, const int8_t* x_dev, const float* x_scale_dev,
+             float x_scale_imm, float* const* outs, int32_t* const* accs, bool accumulate, cudaStream_t st);
 int get_rope_table(ter_b200_handle_t* h, int n_pos, int head_dim, double theta, const float** out);
 
 }  // namespace terb

@@ -49,6 +49,7 @@ struct GemvParams {
     float x_scale_imm;
     int K, Kpad;
     int n_mats, n_tiles, stages;
+    int accumulate;         // out[j] = out[j] + value (residual add fused in the epilogue)
     int* status;
 };
 

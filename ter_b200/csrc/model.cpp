@@ -1,0 +1,487 @@
+// Decode forward: model weights, per-sequence state and the per-token launch sequence, in host
+// C++ over the kernel launchers.  Stage order follows the reference's forward_token_dev
+// (cuda/ter_cuda_forward_packed.cu:505-563; BitNet: cuda/ter_cuda_forward_bitnet.cu:850-913) and
+// its NumPy statement (tools/llama_pyfwd.py:103-161, tools/bitnet_pyfwd.py:94-152).
+#include <new>
+#include <stdlib.h>
+
+#include "glue.h"
+#include "handle.h"
+
+using namespace terb;
+
+struct TerbModel {
+    ter_b200_model_cfg_t c;
+    DevWeight* mats;     // [L][7]
+    float** vecs;        // [L][4] device vectors
+    DevWeight lm_head;   // packed lm_head (optional)
+    uint16_t* embd;      // bf16 [V][H]
+    bool embd_owned;
+    float* out_norm;
+    const float* rope;   // owned by the handle's table cache
+    // state
+    int batch;
+    float *hidden, *q, *k, *v, *att, *gate, *up, *xnorm, *logits, *attn_scratch, *argmax_scratch, *xs;
+    int8_t* xq;
+    uint16_t *kcache, *vcache;   // [L][B][Nkv][Smax][Hd]
+    int *tokens, *pos, *greedy, *forced, *log, *ctl;
+    int forced_cap, log_cap;     // ints per sequence
+    cudaGraphExec_t graph;
+    int graph_batch;
+    bool graph_forced;
+    uint64_t graph_launches;
+    cudaEvent_t ev0, ev1;
+    float last_ms;
+};
+
+namespace {
+
+void mat_dims(const ter_b200_model_cfg_t& c, int which, int* K, int* N) {
+    const int Hq = c.Nh * c.Hd, Hkv = c.Nkv * c.Hd;
+    switch (which) {
+        case TER_B200_WQ: *K = c.H; *N = Hq; break;
+        case TER_B200_WK: case TER_B200_WV: *K = c.H; *N = Hkv; break;
+        case TER_B200_WO: *K = Hq; *N = c.H; break;
+        case TER_B200_WGATE: case TER_B200_WUP: *K = c.H; *N = c.F; break;
+        default: *K = c.F; *N = c.H; break;
+    }
+}
+int vec_len(const ter_b200_model_cfg_t& c, int which) {
+    return which == TER_B200_FFN_SUB_NORM ? c.F : (which == TER_B200_ATTN_SUB_NORM ? c.Nh * c.Hd : c.H);
+}
+size_t cache_elems(const ter_b200_model_cfg_t& c) {
+    return (size_t)c.L * c.max_batch * c.Nkv * (size_t)c.Smax * c.Hd;
+}
+void drop_graph(TerbModel* m) {
+    if (m->graph) cudaGraphExecDestroy(m->graph);
+    m->graph = nullptr;
+}
+template <typename T>
+cudaError_t dalloc(T** p, size_t n) { return cudaMalloc((void**)p, n * sizeof(T)); }
+
+// GEMV for every sequence of the batch (rows of X against the same weights).
+int mm(ter_b200_handle_t* h, const DevWeight* const* ws, int n, const int8_t* xq, int K, const float* xs,
+       float* const* outs, bool accumulate, int B, cudaStream_t st) {
+    for (int b = 0; b < B; ++b) {
+        float* o[kGemvMaxGroup];
+        for (int i = 0; i < n; ++i) o[i] = outs[i] + (size_t)b * ws[i]->N;
+        int rc = run_gemv(h, ws, n, xq + (size_t)b * K, xs + b, 1.0f, o, nullptr, accumulate, st);
+        if (rc) return rc;
+    }
+    return TER_B200_OK;
+}
+
+#define CK(call)                                              \
+    do {                                                      \
+        cudaError_t e__ = (call);                             \
+        if (e__ != cudaSuccess) return cuda_fail(h, e__);     \
+        h->launches += 1;                                     \
+    } while (0)
+
+// The launch sequence of one decode step for `B` sequences.
+int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st) {
+    const ter_b200_model_cfg_t& c = m->c;
+    const int B = m->batch, H = c.H, F = c.F, Hq = c.Nh * c.Hd;
+    const bool pdl = h->gemv_cfg.pdl != 0;
+    const bool bitnet = c.arch == TER_B200_ARCH_BITNET;
+    const size_t layer_cache = (size_t)c.max_batch * c.Nkv * (size_t)c.Smax * c.Hd;
+
+    CK(launch_embed(m->embd, m->tokens, m->hidden, H, B, c.V, pdl, st));
+    for (int L = 0; L < c.L; ++L) {
+        const DevWeight* W = m->mats + (size_t)L * 7;
+        float** vec = m->vecs + (size_t)L * 4;
+        // ---- attention block
+        NormQuantParams nq{m->hidden, nullptr, vec[TER_B200_ATTN_NORM], m->xq, m->xs, nullptr, H, B, PRE_NONE, c.eps};
+        CK(launch_norm_quant(nq, pdl, st));
+        {
+            const DevWeight* ws[3] = {&W[TER_B200_WQ], &W[TER_B200_WK], &W[TER_B200_WV]};
+            float* outs[3] = {m->q, m->k, m->v};
+            int rc = mm(h, ws, 3, m->xq, H, m->xs, outs, false, B, st);
+            if (rc) return rc;
+        }
+        RopeKvParams rp{m->q, m->k, m->v, m->rope, m->pos, m->kcache + L * layer_cache, m->vcache + L * layer_cache,
+                        B, c.Nh, c.Nkv, c.Hd, c.Smax, bitnet ? 1 : 0};
+        CK(launch_rope_kv(rp, pdl, st));
+        AttnParams ap{m->q, m->kcache + L * layer_cache, m->vcache + L * layer_cache, m->pos, m->attn_scratch, m->att,
+                      B, c.Nh, c.Nkv, c.Hd, c.Smax, (c.Smax + kAttnChunk - 1) / kAttnChunk};
+        CK(launch_attention(ap, pdl, st));
+        h->launches += 1;
+        NormQuantParams aq{m->att, nullptr, bitnet ? vec[TER_B200_ATTN_SUB_NORM] : nullptr, m->xq, m->xs, nullptr,
+                           Hq, B, PRE_NONE, c.eps};
+        CK(launch_norm_quant(aq, pdl, st));
+        {
+            const DevWeight* ws[1] = {&W[TER_B200_WO]};
+            float* outs[1] = {m->hidden};
+            int rc = mm(h, ws, 1, m->xq, Hq, m->xs, outs, true, B, st);   // hidden += Wo(attn)
+            if (rc) return rc;
+        }
+        // ---- FFN block
+        NormQuantParams fq{m->hidden, nullptr, vec[TER_B200_FFN_NORM], m->xq, m->xs, nullptr, H, B, PRE_NONE, c.eps};
+        CK(launch_norm_quant(fq, pdl, st));
+        {
+            const DevWeight* ws[2] = {&W[TER_B200_WGATE], &W[TER_B200_WUP]};
+            float* outs[2] = {m->gate, m->up};
+            int rc = mm(h, ws, 2, m->xq, H, m->xs, outs, false, B, st);
+            if (rc) return rc;
+        }
+        NormQuantParams gq{m->gate, m->up, bitnet ? vec[TER_B200_FFN_SUB_NORM] : nullptr, m->xq, m->xs, nullptr,
+                           F, B, bitnet ? PRE_RELU2_MUL : PRE_SILU_MUL, c.eps};
+        CK(launch_norm_quant(gq, pdl, st));
+        {
+            const DevWeight* ws[1] = {&W[TER_B200_WDOWN]};
+            float* outs[1] = {m->hidden};
+            int rc = mm(h, ws, 1, m->xq, F, m->xs, outs, true, B, st);    // hidden += Wdown(ffn)
+            if (rc) return rc;
+        }
+    }
+    if (c.lm_head_packed) {
+        // bench-mode packed lm_head: cuda/ter_cuda_forward_packed.cu:541-545
+        NormQuantParams oq{m->hidden, nullptr, m->out_norm, m->xq, m->xs, nullptr, H, B, PRE_NONE, c.eps};
+        CK(launch_norm_quant(oq, pdl, st));
+        const DevWeight* ws[1] = {&m->lm_head};
+        float* outs[1] = {m->logits};
+        int rc = mm(h, ws, 1, m->xq, H, m->xs, outs, false, B, st);
+        if (rc) return rc;
+    } else {
+        NormQuantParams on{m->hidden, nullptr, m->out_norm, nullptr, nullptr, m->xnorm, H, B, PRE_NONE, c.eps};
+        CK(launch_norm_quant(on, pdl, st));
+        CK(launch_lm_head_bf16(m->embd, m->xnorm, m->logits, c.V, H, B, h->sm_count, pdl, st));
+        const uint64_t n = (uint64_t)((H + 26) / 27) * (uint64_t)c.V * (uint64_t)B;
+        h->counts.tvmac += n;
+        h->counts.total_ops += n;
+    }
+    CK(launch_argmax(m->logits, c.V, B, m->argmax_scratch, m->greedy, pdl, st));
+    h->launches += 1;
+    SelectParams sp{m->greedy, use_forced ? m->forced : nullptr, m->tokens, m->pos, use_forced ? m->log : nullptr,
+                    m->ctl, B, m->forced_cap, m->log_cap};
+    CK(launch_select(sp, pdl, st));
+    return TER_B200_OK;
+}
+
+bool model_complete(const TerbModel* m) {
+    if (!m->embd || !m->out_norm) return false;
+    const bool bitnet = m->c.arch == TER_B200_ARCH_BITNET;
+    for (int L = 0; L < m->c.L; ++L) {
+        for (int w = 0; w < 7; ++w)
+            if (!m->mats[(size_t)L * 7 + w].data) return false;
+        if (!m->vecs[(size_t)L * 4 + TER_B200_ATTN_NORM] || !m->vecs[(size_t)L * 4 + TER_B200_FFN_NORM]) return false;
+        if (bitnet && (!m->vecs[(size_t)L * 4 + TER_B200_ATTN_SUB_NORM] || !m->vecs[(size_t)L * 4 + TER_B200_FFN_SUB_NORM]))
+            return false;
+    }
+    if (m->c.lm_head_packed && !m->lm_head.data) return false;
+    return true;
+}
+
+}  // namespace
+
+extern "C" {
+
+void ter_b200_model_free(ter_b200_handle_t* h) {
+    if (!h || !h->model) return;
+    TerbModel* m = h->model;
+    cudaSetDevice(h->device);
+    cudaDeviceSynchronize();
+    drop_graph(m);
+    if (m->mats) {
+        for (int i = 0; i < m->c.L * 7; ++i) free_weight(&m->mats[i]);
+        delete[] m->mats;
+    }
+    if (m->vecs) {
+        for (int i = 0; i < m->c.L * 4; ++i)
+            if (m->vecs[i]) cudaFree(m->vecs[i]);
+        delete[] m->vecs;
+    }
+    free_weight(&m->lm_head);
+    if (m->embd && m->embd_owned) cudaFree(m->embd);
+    void* bufs[] = {m->out_norm, m->hidden, m->q, m->k, m->v, m->att, m->gate, m->up, m->xnorm, m->logits,
+                    m->attn_scratch, m->argmax_scratch, m->xs, m->xq, m->kcache, m->vcache, m->tokens, m->pos,
+                    m->greedy, m->forced, m->log, m->ctl};
+    for (void* b : bufs)
+        if (b) cudaFree(b);
+    if (m->ev0) cudaEventDestroy(m->ev0);
+    if (m->ev1) cudaEventDestroy(m->ev1);
+    delete m;
+    h->model = nullptr;
+}
+
+int ter_b200_model_create(ter_b200_handle_t* h, const ter_b200_model_cfg_t* cfg) {
+    if (!h || !cfg) return TER_B200_E_NULL;
+    const ter_b200_model_cfg_t& c = *cfg;
+    if (c.H < 16 || c.F < 16 || c.L < 1 || c.V < 1 || c.Nh < 1 || c.Nkv < 1 || c.Smax < 1 || c.max_batch < 1 ||
+        c.max_batch > 1024)
+        return TER_B200_E_SHAPE;
+    if ((c.Hd != 64 && c.Hd != 128) || c.Nh % c.Nkv != 0 || c.Nh / c.Nkv > 8) return TER_B200_E_SHAPE;
+    if (c.H % 16 || c.F % 16 || (c.Nh * c.Hd) % 16 || c.H % 8) return TER_B200_E_SHAPE;
+    if (c.arch != TER_B200_ARCH_LLAMA && c.arch != TER_B200_ARCH_BITNET) return TER_B200_E_SHAPE;
+    TERB_CUDA(h, cudaSetDevice(h->device));
+    ter_b200_model_free(h);
+    TerbModel* m = new (std::nothrow) TerbModel();
+    if (!m) return TER_B200_E_ALLOC;
+    m->c = c;
+    m->batch = 1;
+    h->model = m;
+    m->mats = new (std::nothrow) DevWeight[(size_t)c.L * 7];
+    m->vecs = new (std::nothrow) float*[(size_t)c.L * 4]();
+    if (!m->mats || !m->vecs) { ter_b200_model_free(h); return TER_B200_E_ALLOC; }
+    const int B = c.max_batch, Hq = c.Nh * c.Hd, Hkv = c.Nkv * c.Hd;
+    const int wide = c.F > Hq ? (c.F > c.H ? c.F : c.H) : (Hq > c.H ? Hq : c.H);
+    cudaError_t e = cudaSuccess;
+    auto A = [&](cudaError_t r) { if (e == cudaSuccess) e = r; };
+    A(dalloc(&m->hidden, (size_t)B * c.H));
+    A(dalloc(&m->q, (size_t)B * Hq));
+    A(dalloc(&m->k, (size_t)B * Hkv));
+    A(dalloc(&m->v, (size_t)B * Hkv));
+    A(dalloc(&m->att, (size_t)B * Hq));
+    A(dalloc(&m->gate, (size_t)B * c.F));
+    A(dalloc(&m->up, (size_t)B * c.F));
+    A(dalloc(&m->xnorm, (size_t)B * c.H));
+    A(dalloc(&m->logits, (size_t)B * c.V));
+    A(dalloc(&m->attn_scratch, attention_scratch_floats(B, c.Nh, c.Hd, c.Smax)));
+    A(dalloc(&m->argmax_scratch, (size_t)B * kArgmaxParts * 2));
+    A(dalloc(&m->xs, (size_t)B));
+    A(dalloc(&m->xq, (size_t)B * wide));
+    A(dalloc(&m->kcache, cache_elems(c)));
+    A(dalloc(&m->vcache, cache_elems(c)));
+    A(dalloc(&m->tokens, (size_t)B));
+    A(dalloc(&m->pos, (size_t)B));
+    A(dalloc(&m->greedy, (size_t)B));
+    A(dalloc(&m->ctl, 2));
+    if (e == cudaSuccess) e = cudaMemset(m->kcache, 0, cache_elems(c) * 2);
+    if (e == cudaSuccess) e = cudaMemset(m->vcache, 0, cache_elems(c) * 2);
+    if (e == cudaSuccess) e = cudaMemset(m->tokens, 0, B * sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(m->pos, 0, B * sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(m->ctl, 0, 2 * sizeof(int));
+    if (e == cudaSuccess) e = cudaEventCreate(&m->ev0);
+    if (e == cudaSuccess) e = cudaEventCreate(&m->ev1);
+    if (e != cudaSuccess) { ter_b200_model_free(h); return cuda_fail(h, e); }
+    int rc = get_rope_table(h, c.Smax, c.Hd, c.rope_theta, &m->rope);
+    if (rc) { ter_b200_model_free(h); return rc; }
+    return TER_B200_OK;
+}
+
+static int set_matrix_common(ter_b200_handle_t* h, int layer, int which, const void* data, bool on_device,
+                             int format, float scale) {
+    if (!h || !data) return TER_B200_E_NULL;
+    TerbModel* m = h->model;
+    if (!m) return TER_B200_E_STATE;
+    int K, N;
+    DevWeight* dst;
+    if (layer < 0) {
+        K = m->c.H; N = m->c.V; dst = &m->lm_head;
+    } else {
+        if (layer >= m->c.L || which < 0 || which > TER_B200_WDOWN) return TER_B200_E_SHAPE;
+        mat_dims(m->c, which, &K, &N);
+        dst = &m->mats[(size_t)layer * 7 + which];
+    }
+    if (format < 0 || format > TER_B200_FMT_I32) return TER_B200_E_SHAPE;
+    if (format != TER_B200_FMT_I32 && N % 4 != 0) return TER_B200_E_SHAPE;
+    TERB_CUDA(h, cudaSetDevice(h->device));
+    drop_graph(m);
+    void* tmp = nullptr;
+    const void* src = data;
+    if (!on_device) {
+        const size_t bytes = format == TER_B200_FMT_I32 ? (size_t)K * N * 4u : (size_t)K * (size_t)(N / 4);
+        TERB_CUDA(h, cudaMalloc(&tmp, bytes));
+        cudaError_t e = cudaMemcpyAsync(tmp, data, bytes, cudaMemcpyHostToDevice, h->stream);
+        if (e != cudaSuccess) { cudaFree(tmp); return cuda_fail(h, e); }
+        src = tmp;
+    } else {
+        TERB_CUDA(h, cudaDeviceSynchronize());   // the caller's producer stream is unknown
+    }
+    DevWeight w;
+    int rc = build_weight_from_dev(h, src, format, K, N, scale, h->stream, &w);
+    if (tmp) cudaFree(tmp);
+    if (rc) return rc;
+    free_weight(dst);
+    *dst = w;
+    return TER_B200_OK;
+}
+
+int ter_b200_model_set_matrix(ter_b200_handle_t* h, int layer, int which, const void* data, int format, float scale) {
+    return set_matrix_common(h, layer, which, data, false, format, scale);
+}
+int ter_b200_model_set_matrix_dev(ter_b200_handle_t* h, int layer, int which, const void* data_dev, int format,
+                                  float scale) {
+    return set_matrix_common(h, layer, which, data_dev, true, format, scale);
+}
+
+int ter_b200_model_set_vector(ter_b200_handle_t* h, int layer, int which, const float* v) {
+    if (!h || !v) return TER_B200_E_NULL;
+    TerbModel* m = h->model;
+    if (!m) return TER_B200_E_STATE;
+    TERB_CUDA(h, cudaSetDevice(h->device));
+    float** slot;
+    int n;
+    if (layer < 0) {
+        slot = &m->out_norm; n = m->c.H;
+    } else {
+        if (layer >= m->c.L || which < 0 || which > TER_B200_FFN_SUB_NORM) return TER_B200_E_SHAPE;
+        slot = &m->vecs[(size_t)layer * 4 + which];
+        n = vec_len(m->c, which);
+    }
+    drop_graph(m);
+    if (!*slot) TERB_CUDA(h, dalloc(slot, (size_t)n));
+    TERB_CUDA(h, cudaMemcpy(*slot, v, (size_t)n * sizeof(float), cudaMemcpyHostToDevice));
+    return TER_B200_OK;
+}
+
+int ter_b200_model_set_embd(ter_b200_handle_t* h, const uint16_t* table) {
+    if (!h || !table) return TER_B200_E_NULL;
+    TerbModel* m = h->model;
+    if (!m) return TER_B200_E_STATE;
+    TERB_CUDA(h, cudaSetDevice(h->device));
+    drop_graph(m);
+    const size_t n = (size_t)m->c.V * m->c.H;
+    if (m->embd && !m->embd_owned) m->embd = nullptr;
+    if (!m->embd) TERB_CUDA(h, dalloc(&m->embd, n));
+    m->embd_owned = true;
+    TERB_CUDA(h, cudaMemcpy(m->embd, table, n * 2, cudaMemcpyHostToDevice));
+    return TER_B200_OK;
+}
+int ter_b200_model_set_embd_dev(ter_b200_handle_t* h, const uint16_t* table_dev) {
+    if (!h || !table_dev) return TER_B200_E_NULL;
+    TerbModel* m = h->model;
+    if (!m) return TER_B200_E_STATE;
+    TERB_CUDA(h, cudaSetDevice(h->device));
+    TERB_CUDA(h, cudaDeviceSynchronize());
+    drop_graph(m);
+    const size_t n = (size_t)m->c.V * m->c.H;
+    if (m->embd && !m->embd_owned) m->embd = nullptr;
+    if (!m->embd) TERB_CUDA(h, dalloc(&m->embd, n));
+    m->embd_owned = true;
+    TERB_CUDA(h, cudaMemcpy(m->embd, table_dev, n * 2, cudaMemcpyDeviceToDevice));
+    return TER_B200_OK;
+}
+
+int ter_b200_model_reset(ter_b200_handle_t* h, int batch) {
+    if (!h) return TER_B200_E_NULL;
+    TerbModel* m = h->model;
+    if (!m) return TER_B200_E_STATE;
+    if (batch < 1 || batch > m->c.max_batch) return TER_B200_E_SHAPE;
+    TERB_CUDA(h, cudaSetDevice(h->device));
+    TERB_CUDA(h, cudaDeviceSynchronize());
+    if (batch != m->batch) drop_graph(m);
+    m->batch = batch;
+    TERB_CUDA(h, cudaMemset(m->pos, 0, batch * sizeof(int)));
+    TERB_CUDA(h, cudaMemset(m->tokens, 0, batch * sizeof(int)));
+    return TER_B200_OK;
+}
+
+int ter_b200_decode_step(ter_b200_handle_t* h, const int32_t* tokens_host, const int32_t* pos_host,
+                         int32_t* next_host, void* stream) {
+    if (!h) return TER_B200_E_NULL;
+    TerbModel* m = h->model;
+    if (!m || !model_complete(m)) return TER_B200_E_STATE;
+    TERB_CUDA(h, cudaSetDevice(h->device));
+    cudaStream_t st = pick_stream(h, stream);
+    const int B = m->batch;
+    if (pos_host)
+        for (int b = 0; b < B; ++b)
+            if (pos_host[b] < 0 || pos_host[b] >= m->c.Smax) return TER_B200_E_SHAPE;
+    if (tokens_host) TERB_CUDA(h, cudaMemcpyAsync(m->tokens, tokens_host, B * sizeof(int), cudaMemcpyHostToDevice, st));
+    if (pos_host) TERB_CUDA(h, cudaMemcpyAsync(m->pos, pos_host, B * sizeof(int), cudaMemcpyHostToDevice, st));
+    int rc = forward(h, m, false, st);
+    if (rc) return rc;
+    if (next_host) {
+        TERB_CUDA(h, cudaMemcpyAsync(next_host, m->tokens, B * sizeof(int), cudaMemcpyDeviceToHost, st));
+        TERB_CUDA(h, cudaStreamSynchronize(st));
+    }
+    return TER_B200_OK;
+}
+
+int ter_b200_model_logits(ter_b200_handle_t* h, float* logits_host) {
+    if (!h || !logits_host) return TER_B200_E_NULL;
+    TerbModel* m = h->model;
+    if (!m) return TER_B200_E_STATE;
+    TERB_CUDA(h, cudaSetDevice(h->device));
+    TERB_CUDA(h, cudaDeviceSynchronize());
+    TERB_CUDA(h, cudaMemcpy(logits_host, m->logits, (size_t)m->batch * m->c.V * sizeof(float), cudaMemcpyDeviceToHost));
+    return TER_B200_OK;
+}
+int ter_b200_model_hidden(ter_b200_handle_t* h, float* hidden_host) {
+    if (!h || !hidden_host) return TER_B200_E_NULL;
+    TerbModel* m = h->model;
+    if (!m) return TER_B200_E_STATE;
+    TERB_CUDA(h, cudaSetDevice(h->device));
+    TERB_CUDA(h, cudaDeviceSynchronize());
+    TERB_CUDA(h, cudaMemcpy(hidden_host, m->hidden, (size_t)m->batch * m->c.H * sizeof(float), cudaMemcpyDeviceToHost));
+    return TER_B200_OK;
+}
+
+int ter_b200_generate(ter_b200_handle_t* h, const int32_t* prompts, int batch, int n_prompt, int n_gen,
+                      int32_t* out_tokens, void* stream) {
+    if (!h || !prompts || !out_tokens) return TER_B200_E_NULL;
+    TerbModel* m = h->model;
+    if (!m || !model_complete(m)) return TER_B200_E_STATE;
+    if (batch < 1 || batch > m->c.max_batch || n_prompt < 1 || n_gen < 1 || n_prompt + n_gen - 1 > m->c.Smax)
+        return TER_B200_E_SHAPE;
+    TERB_CUDA(h, cudaSetDevice(h->device));
+    // The steps are captured into a graph; the legacy default stream cannot be captured, so such a
+    // request runs on the handle's own stream (the call is synchronous either way).
+    cudaStream_t st = pick_stream(h, stream);
+    if (st == cudaStreamLegacy || st == cudaStreamPerThread) st = h->stream;
+    const int steps = n_prompt + n_gen - 1;
+    int rc = ter_b200_model_reset(h, batch);
+    if (rc) return rc;
+    if (m->forced_cap < n_prompt || m->log_cap < steps) {
+        drop_graph(m);
+        if (m->forced) cudaFree(m->forced);
+        if (m->log) cudaFree(m->log);
+        m->forced = m->log = nullptr;
+        m->forced_cap = m->log_cap = 0;
+        TERB_CUDA(h, dalloc(&m->forced, (size_t)m->c.max_batch * n_prompt));
+        m->forced_cap = n_prompt;
+        TERB_CUDA(h, dalloc(&m->log, (size_t)m->c.max_batch * steps));
+        m->log_cap = steps;
+    }
+    int* first = (int*)malloc(sizeof(int) * (size_t)batch);
+    if (!first) return TER_B200_E_ALLOC;
+    for (int b = 0; b < batch; ++b) {
+        first[b] = prompts[(size_t)b * n_prompt];
+        cudaError_t e = cudaMemcpy(m->forced + (size_t)b * m->forced_cap, prompts + (size_t)b * n_prompt,
+                                   n_prompt * sizeof(int), cudaMemcpyHostToDevice);
+        if (e != cudaSuccess) { free(first); return cuda_fail(h, e); }
+    }
+    cudaError_t e = cudaMemcpy(m->tokens, first, batch * sizeof(int), cudaMemcpyHostToDevice);
+    free(first);
+    if (e != cudaSuccess) return cuda_fail(h, e);
+    const int ctl[2] = {n_prompt, steps};
+    TERB_CUDA(h, cudaMemcpy(m->ctl, ctl, sizeof ctl, cudaMemcpyHostToDevice));
+
+    if (!m->graph || m->graph_batch != batch || !m->graph_forced) {
+        drop_graph(m);
+        const uint64_t mark = h->launches;
+        TERB_CUDA(h, cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+        rc = forward(h, m, true, st);
+        cudaGraph_t g = nullptr;
+        cudaError_t ce = cudaStreamEndCapture(st, &g);
+        if (rc) { if (g) cudaGraphDestroy(g); return rc; }
+        if (ce != cudaSuccess) return cuda_fail(h, ce);
+        ce = cudaGraphInstantiate(&m->graph, g, 0);
+        cudaGraphDestroy(g);
+        if (ce != cudaSuccess) { m->graph = nullptr; return cuda_fail(h, ce); }
+        m->graph_launches = h->launches - mark;
+        h->launches = mark;
+        m->graph_batch = batch;
+        m->graph_forced = true;
+    }
+    TERB_CUDA(h, cudaEventRecord(m->ev0, st));
+    for (int i = 0; i < steps; ++i) {
+        TERB_CUDA(h, cudaGraphLaunch(m->graph, st));
+        h->launches += m->graph_launches;
+    }
+    TERB_CUDA(h, cudaEventRecord(m->ev1, st));
+    TERB_CUDA(h, cudaStreamSynchronize(st));
+    TERB_CUDA(h, cudaEventElapsedTime(&m->last_ms, m->ev0, m->ev1));
+    for (int b = 0; b < batch; ++b)
+        TERB_CUDA(h, cudaMemcpy(out_tokens + (size_t)b * n_gen, m->log + (size_t)b * m->log_cap + (n_prompt - 1),
+                                n_gen * sizeof(int), cudaMemcpyDeviceToHost));
+    int dst = 0;
+    TERB_CUDA(h, cudaMemcpy(&dst, h->status_dev, sizeof(int), cudaMemcpyDeviceToHost));
+    if (dst != 0) { cudaMemset(h->status_dev, 0, sizeof(int)); return TER_B200_E_TIMEOUT; }
+    return TER_B200_OK;
+}
+
+float ter_b200_last_generate_ms(const ter_b200_handle_t* h) { return (h && h->model) ? h->model->last_ms : 0.0f; }
+
+}  // extern "C"

@@ -51,6 +51,4 @@ int ter_b200_call(ter_b200_handle_t* h, const char* name, const int64_t* args, s
     return TER_B200_E_UNKNOWN;
 }
 
-void ter_b200_model_free(ter_b200_handle_t* h) { (void)h; }
-
 }  // extern "C"

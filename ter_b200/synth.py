@@ -102,3 +102,48 @@ def packed_v11_cuda(K: int, N: int, seed: int, device="cuda"):
         code = (u >= 0.7).to(torch.uint8) + 2 * (u < 0.3).to(torch.uint8)   # +1 -> 1, -1 -> 2
         out |= code << (2 * f)
     return out
+
+
+MAT_ORDER = ["q", "k", "v", "o", "gate", "up", "down"]
+
+
+def model_shapes(cfg: dict) -> dict:
+    Hq, Hkv = cfg["Nh"] * cfg["Hd"], cfg["Nkv"] * cfg["Hd"]
+    return {"q": (cfg["H"], Hq), "k": (cfg["H"], Hkv), "v": (cfg["H"], Hkv), "o": (Hq, cfg["H"]),
+            "gate": (cfg["H"], cfg["F"]), "up": (cfg["H"], cfg["F"]), "down": (cfg["F"], cfg["H"])}
+
+
+def f32_to_bf16(a: np.ndarray) -> np.ndarray:
+    """Round-to-nearest-even fp32 -> bf16 bit patterns (uint16)."""
+    u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+    r = u + (np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1)))     # finite inputs: no wrap-around
+    return (r >> np.uint32(16)).astype(np.uint16)
+
+
+def model_weights(cfg: dict, seed: int = BASE_SEED):
+    """Random-init ternarised model of the given architecture, host side (numpy):
+    yields ("matrix", layer, which, packed_v11 bytes, scale), ("vector", layer, which, fp32),
+    ("embd", bf16 table [V][H]).  Embeddings ~ N(0, 0.02) in bf16; norm gains ~ N(1, 0.02)."""
+    shapes = model_shapes(cfg)
+    rng = np.random.default_rng(seed_for(seed, "vec"))
+    emb = np.random.default_rng(seed_for(seed, "embd")).standard_normal((cfg["V"], cfg["H"]), dtype=np.float32)
+    # N(0, 0.02), snapped to multiples of 2^-14 so that the bf16 values are also exact in fp16 (the
+    # reference's packed-model files store the table in fp16); in place to keep memory flat
+    emb *= np.float32(0.02 * 16384.0)
+    np.rint(emb, out=emb)
+    emb *= np.float32(1.0 / 16384.0)
+    yield ("embd", f32_to_bf16(emb))
+    del emb
+    yield ("vector", -1, 0, rng.normal(1.0, 0.02, cfg["H"]).astype(np.float32))
+    if cfg.get("lm_head_packed"):
+        s = seed_for(seed, "lm_head")
+        yield ("matrix", -1, 0, pack_v11(trits(cfg["H"], cfg["V"], s)), weight_scale(s))
+    for L in range(cfg["L"]):
+        for wi, nm in enumerate(MAT_ORDER):
+            K, N = shapes[nm]
+            s = seed_for(seed, L, nm)
+            yield ("matrix", L, wi, pack_v11(trits(K, N, s)), weight_scale(s))
+        n_vec = 4 if cfg["arch"] == 1 else 2
+        for vi in range(n_vec):
+            n = cfg["F"] if vi == 3 else (cfg["Nh"] * cfg["Hd"] if vi == 2 else cfg["H"])
+            yield ("vector", L, vi, rng.normal(1.0, 0.02, n).astype(np.float32))

@@ -1,0 +1,110 @@
+"""End-to-end parity of the CUDA decode forward with the CPU checker: logits within 1e-3 relative
+(asserted, and in fact bit-for-bit), greedy tokens identical."""
+import os
+import sys
+
+import numpy as np
+import pytest
+
+sys.path.insert(0, os.path.dirname(__file__))
+sys.path.insert(0, os.path.join(os.path.dirname(__file__), "golden"))
+import modelutil  # noqa: E402
+from ter_b200 import synth  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+SMALL_LLAMA = dict(arch=0, H=256, F=512, L=3, V=4096, Nh=4, Nkv=2, Hd=64, Smax=320, eps=1e-5, rope_theta=500000.0)
+SMALL_BITNET = dict(arch=1, H=512, F=768, L=2, V=3000, Nh=4, Nkv=1, Hd=128, Smax=300, eps=1e-5, rope_theta=500000.0)
+SMALL_PACKED_HEAD = dict(SMALL_LLAMA, lm_head_packed=1, L=2, Smax=64)
+
+
+def rel_err(a, b):
+    return np.max(np.abs(a - b) / (np.abs(b) + 1e-3 * np.max(np.abs(b))))
+
+
+@pytest.mark.parametrize("cfg,seed,n_prompt,n_gen", [
+    (SMALL_LLAMA, 11, 250, 40), (SMALL_BITNET, 12, 270, 20), (SMALL_PACKED_HEAD, 13, 5, 30)])
+def test_step_by_step_logits_and_tokens(tb, cfg, seed, n_prompt, n_gen):
+    modelutil.build_gpu(tb, cfg, seed)
+    om = modelutil.build_oracle(cfg, seed)
+    prompt = np.random.default_rng(seed).integers(0, cfg["V"], size=n_prompt).astype(np.int32)
+    want, want_logits = modelutil.oracle_generate(om, prompt, n_gen, want_logits=True)
+    tb.model_reset(1)
+    tok, got = int(prompt[0]), []
+    for pos in range(n_prompt + n_gen - 1):
+        nxt = int(tb.decode_step([tok], [pos])[0])
+        if pos in (0, 1, n_prompt - 1, n_prompt + n_gen - 2) or pos % 37 == 0:
+            lg = tb.model_logits()[0]
+            assert rel_err(lg, want_logits[pos]) < 1e-3, pos
+            assert np.array_equal(lg.view(np.uint32), want_logits[pos].view(np.uint32)), pos
+        if pos + 1 < n_prompt:
+            tok = int(prompt[pos + 1])
+        else:
+            tok = nxt
+            got.append(nxt)
+    assert got == want.tolist()
+    # the graph-replayed generate() gives the same tokens
+    out = tb.generate(prompt, n_gen)
+    assert out[0].tolist() == want.tolist()
+    assert tb.last_generate_ms() > 0
+    assert tb.device_status() == 0
+
+
+def test_batch_sequences_are_independent(tb):
+    cfg, seed = SMALL_LLAMA, 21
+    modelutil.build_gpu(tb, cfg, seed, max_batch=3)
+    om = modelutil.build_oracle(cfg, seed)
+    rng = np.random.default_rng(5)
+    prompts = rng.integers(0, cfg["V"], size=(3, 12)).astype(np.int32)
+    out = tb.generate(prompts, 10)
+    for b in range(3):
+        want, _ = modelutil.oracle_generate(om, prompts[b], 10)
+        assert out[b].tolist() == want.tolist(), b
+    # a smaller batch on the same handle, and position bounds
+    out1 = tb.generate(prompts[1], 10)
+    assert out1[0].tolist() == out[1].tolist()
+    from ter_b200 import TerB200Error, api
+    with pytest.raises(TerB200Error) as e:
+        tb.generate(prompts[0], cfg["Smax"])          # would run past Smax
+    assert e.value.code == api.E_SHAPE
+
+
+def test_reference_numpy_forward_tokens_on_gpu(tb, golden_dir):
+    """Greedy tokens printed by the reference's own tools/llama_pyfwd.py / bitnet_pyfwd.py."""
+    import make_pyfwd_golden as mk
+    g = np.load(os.path.join(golden_dir, "pyfwd_tokens.npz"))
+    for name in ("llama", "bitnet"):
+        case = mk.CASES[name]
+        cfg = {k: case[k] for k in ("arch", "H", "F", "L", "V", "Nh", "Nkv", "Hd", "Smax", "eps", "rope_theta")}
+        modelutil.build_gpu(tb, cfg, case["seed"])
+        want = g[f"{name}_tokens"]
+        out = tb.generate(np.array([128000], np.int32), len(want))
+        assert out[0].tolist() == want.tolist(), name
+
+
+@pytest.mark.parametrize("base,L", [(synth.LLAMA_1B_CFG, 3), (synth.BITNET_2B_CFG, 2)])
+def test_full_size_shapes_few_layers(tb, base, L):
+    """The real layer shapes and vocabulary of the two benchmark architectures, a few layers deep."""
+    cfg = dict(base, L=L, Smax=64)
+    modelutil.build_gpu(tb, cfg, 31)
+    om = modelutil.build_oracle(cfg, 31)
+    prompt = np.random.default_rng(1).integers(0, cfg["V"], size=6).astype(np.int32)
+    want, want_logits = modelutil.oracle_generate(om, prompt, 4, want_logits=True)
+    out = tb.generate(prompt, 4)
+    assert out[0].tolist() == want.tolist()
+    lg = tb.model_logits()[0]
+    assert rel_err(lg, want_logits[-1]) < 1e-3
+    assert np.array_equal(lg.view(np.uint32), want_logits[-1].view(np.uint32))
+
+
+def test_model_state_errors(tb):
+    from ter_b200 import TerB200, TerB200Error, api
+    h = TerB200(0)
+    try:
+        assert h.L.ter_b200_decode_step(h.h, None, None, None, None) == api.E_STATE      # no model yet
+        with pytest.raises(TerB200Error):
+            h.model_create(dict(SMALL_LLAMA, Hd=48))                                     # unsupported head_dim
+        h.model_create(SMALL_LLAMA)
+        assert h.L.ter_b200_decode_step(h.h, None, None, None, None) == api.E_STATE      # weights missing
+    finally:
+        h.close()
