@@ -188,6 +188,22 @@ size_t ter_b200_attention_scratch_floats(int B, int Nh, int Hd, int Smax);
 int ter_b200_attention(ter_b200_handle_t* h, const float* q_dev, const uint16_t* kcache_dev,
                        const uint16_t* vcache_dev, const int* pos_dev, int B, int Nh, int Nkv, int Hd, int Smax,
                        float* scratch_dev, size_t scratch_floats, float* out_dev, void* stream);
+/* The same attention for callers that cannot allocate device memory where they need it: code
+ * between cudaStreamBeginCapture and cudaStreamEndCapture, a decode loop that gave all of its
+ * memory out at start-up, a host whose allocator belongs to another runtime.  (No counterpart in
+ * the reference, which allocates its scratch once in alloc_scratch.)  The partial records go to
+ * a fixed 4 MiB array inside the library's device image instead of a caller buffer; every GPU
+ * that loads the library holds that array until the process exits.  Calls whose records do not
+ * fit -- ter_b200_attention_scratch_floats(B, Nh, Hd, Smax) > ter_b200_attention_noalloc_max_floats()
+ * -- return TER_B200_E_SHAPE.  The call itself makes no cudaMalloc / cudaFree.  The first call on
+ * a device looks the array's address up (cudaGetSymbolAddress); make that call before any stream
+ * capture.  All calls on a device share the one array and it keeps whatever the last call left:
+ * nothing in it needs clearing (every record that is read is written first by the same call), but
+ * two calls that overlap on the GPU (different streams) race on it -- serialise them. */
+size_t ter_b200_attention_noalloc_max_floats(void);
+int ter_b200_attention_noalloc(ter_b200_handle_t* h, const float* q_dev, const uint16_t* kcache_dev,
+                               const uint16_t* vcache_dev, const int* pos_dev, int B, int Nh, int Nkv, int Hd,
+                               int Smax, float* out_dev, void* stream);
 /* logits[b][v] = sum_h bf16(table[v][h]) * x[b][h]: mm_fp16_lm_head_k
  * (cuda/ter_cuda_forward_packed.cu:165-206) with a bf16 table and fp32 activations. */
 int ter_b200_lm_head_bf16(ter_b200_handle_t* h, const uint16_t* table_dev, const float* x_dev, float* logits_dev,

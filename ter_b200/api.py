@@ -73,6 +73,8 @@ SIGNATURES = {
     "ter_b200_rope_kv": (_I, [_VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, C.c_double, _I, _VP, _VP, _VP]),
     "ter_b200_attention_scratch_floats": (_SZ, [_I, _I, _I, _I]),
     "ter_b200_attention": (_I, [_VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _VP, _SZ, _VP, _VP]),
+    "ter_b200_attention_noalloc_max_floats": (_SZ, []),
+    "ter_b200_attention_noalloc": (_I, [_VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _VP, _VP]),
     "ter_b200_lm_head_bf16": (_I, [_VP, _VP, _VP, _VP, _I, _I, _I, _VP]),
     "ter_b200_argmax": (_I, [_VP, _VP, _I, _I, _VP, _VP, _VP]),
     "ter_b200_model_create": (_I, [_VP, C.POINTER(ModelCfg)]),
@@ -318,6 +320,19 @@ class TerB200:
                                          C.c_void_p(vcache.data_ptr()), C.c_void_p(pos.data_ptr()), B, Nh, Nkv, Hd,
                                          Smax, C.c_void_p(scratch.data_ptr()), scratch.numel(),
                                          C.c_void_p(out.data_ptr()), _stream_ptr(stream)), "attention")
+        return out
+
+    def attention_noalloc(self, q, kcache, vcache, pos, Nh, Nkv, Hd, Smax, out=None, stream=None):
+        """Attention through the entry point that brings its own fixed scratch (no allocation inside
+        the library; `out` is the caller's)."""
+        import torch
+        B = pos.shape[0]
+        if out is None:
+            out = torch.empty((B, Nh * Hd), dtype=torch.float32, device=q.device)
+        _check(self.L.ter_b200_attention_noalloc(self.h, C.c_void_p(q.data_ptr()), C.c_void_p(kcache.data_ptr()),
+                                                 C.c_void_p(vcache.data_ptr()), C.c_void_p(pos.data_ptr()), B, Nh,
+                                                 Nkv, Hd, Smax, C.c_void_p(out.data_ptr()), _stream_ptr(stream)),
+               "attention_noalloc")
         return out
 
     def lm_head_bf16(self, table, x, stream=None):

@@ -589,3 +589,50 @@ cudaError_t launch_inc(int* pos, int B, bool pdl, cudaStream_t st) {
 }
 
 }  // namespace terb
+
+// ============================================================ attention for callers that cannot allocate
+// Some hosts of this library may not allocate device memory at the point where they need
+// attention: code running between cudaStreamBeginCapture and cudaStreamEndCapture, a real-time
+// decode loop that has handed all of its memory budget out at start-up, or an embedding whose
+// allocator is owned by another runtime and must not see foreign cudaMalloc calls.  The regular
+// entry point asks them for a scratch buffer; this one brings its own, a fixed array that lives
+// in the library's device image.  Every GPU that loads the library holds these 4 MiB until the
+// process exits.
+#include "handle.h"
+
+#define TER_B200_STATIC_SCRATCH_FLOATS (1u << 20)   // 4 MiB; keep in step with include/ter_b200.h
+
+static __device__ __align__(256) float g_attn_static_scratch[TER_B200_STATIC_SCRATCH_FLOATS];
+
+// In host code `g_attn_static_scratch` is only a handle for the symbol, not a device address:
+// the address is looked up once per device, with that device current, and remembered here.
+static float* g_attn_static_ptr[64] = {};
+
+extern "C" size_t ter_b200_attention_noalloc_max_floats(void) { return TER_B200_STATIC_SCRATCH_FLOATS; }
+
+extern "C" int ter_b200_attention_noalloc(ter_b200_handle_t* h, const float* q_dev, const uint16_t* kcache_dev,
+                                          const uint16_t* vcache_dev, const int* pos_dev, int B, int Nh, int Nkv,
+                                          int Hd, int Smax, float* out_dev, void* stream) {
+    using namespace terb;
+    if (!h || !q_dev || !kcache_dev || !vcache_dev || !pos_dev || !out_dev) return TER_B200_E_NULL;
+    if (B < 1 || Nkv < 1 || Nh < 1 || Nh % Nkv != 0 || Nh / Nkv > 8 || (Hd != 64 && Hd != 128) || Smax < 1)
+        return TER_B200_E_SHAPE;
+    // the partial records of this problem must fit the fixed array
+    if (attention_scratch_floats(B, Nh, Hd, Smax) > (size_t)TER_B200_STATIC_SCRATCH_FLOATS) return TER_B200_E_SHAPE;
+    if (h->device < 0 || h->device >= 64) return TER_B200_E_SHAPE;
+    TERB_CUDA(h, cudaSetDevice(h->device));
+    float* scratch = g_attn_static_ptr[h->device];
+    if (!scratch) {
+        // First call on this device: resolve the symbol.  Do this before any stream capture.
+        void* ptr = nullptr;
+        TERB_CUDA(h, cudaGetSymbolAddress(&ptr, g_attn_static_scratch));
+        if (!ptr) return TER_B200_E_CUDA;
+        scratch = static_cast<float*>(ptr);
+        g_attn_static_ptr[h->device] = scratch;
+    }
+    AttnParams p{q_dev, kcache_dev, vcache_dev, pos_dev, scratch, out_dev, B, Nh, Nkv, Hd, Smax,
+                 (Smax + kAttnChunk - 1) / kAttnChunk};
+    TERB_CUDA(h, launch_attention(p, h->gemv_cfg.pdl != 0, pick_stream(h, stream)));
+    h->launches += 2;
+    return TER_B200_OK;
+}
