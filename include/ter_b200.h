@@ -134,6 +134,19 @@ int ter_b200_gemv_acc(ter_b200_handle_t* h, const char* slot, const int8_t* x_de
 int ter_b200_gemv_group(ter_b200_handle_t* h, const char* const* slots, int n_slots,
                         const int8_t* x_dev, const float* x_scale_dev,
                         float* const* outs_dev, void* stream);
+#define TER_B200_ACT_SILU  1
+#define TER_B200_ACT_RELU2 2
+/* Quantiser fused into the GEMV: y = W^T q(x) where q() is exactly ter_b200_rmsnorm_quant (act = 0:
+ * RMSNorm with gamma_dev, or plain absmax quantisation when gamma_dev is NULL) or ter_b200_act_quant
+ * (act = TER_B200_ACT_SILU / _RELU2 with up_dev, optional sub-norm gamma_dev) applied to the fp32 vector
+ * x_dev[K].  One launch replaces the reference's rmsnorm_quant / silu_mul_quant kernel plus the
+ * GEMVs that consume its output (cuda/ter_cuda_forward_packed.cu:514-518,531-536); every CTA derives
+ * the int8 vector itself, in the same fixed reduction order, so results are bit-identical to the
+ * two-step form.  accumulate != 0 adds into outs (the residual add, add_k, :529,:538).  Only for
+ * slot groups of at most 1184 strips (N total <= 18944), i.e. every projection but the lm_head. */
+int ter_b200_norm_gemv_group(ter_b200_handle_t* h, const char* const* slots, int n_slots, int act,
+                             const float* x_dev, const float* up_dev, const float* gamma_dev, float eps,
+                             float* const* outs_dev, int accumulate, void* stream);
 /* Host-buffer form: copies x (K bytes) and the scale in, the N floats out, on `stream`,
  * asynchronously; ter_b200_sync() completes it.  Buffers must stay valid until then
  * (pinned host memory makes the copies truly asynchronous). */
@@ -166,8 +179,6 @@ int ter_b200_rmsnorm_quant(ter_b200_handle_t* h, const float* x_dev, const float
  * (cuda/ter_cuda_forward_packed.cu:312-344), v = gate/(1+exp(-gate))*up.  act = RELU2:
  * relu2_mul_rmsnorm_quant_k (cuda/ter_cuda_forward_bitnet.cu:258-309), v = max(gate,0)^2*up followed by
  * RMSNorm with gamma_dev (the ffn sub-norm) when gamma_dev is not NULL. */
-#define TER_B200_ACT_SILU  1
-#define TER_B200_ACT_RELU2 2
 int ter_b200_act_quant(ter_b200_handle_t* h, int act, const float* gate_dev, const float* up_dev,
                        const float* gamma_dev, int n, int rows, float eps, int8_t* q_dev, float* scale_dev,
                        void* stream);

@@ -64,6 +64,7 @@ SIGNATURES = {
     "ter_b200_gemv": (_I, [_VP, _CP, _VP, _VP, _VP, _VP]),
     "ter_b200_gemv_acc": (_I, [_VP, _CP, _VP, _VP, _VP]),
     "ter_b200_gemv_group": (_I, [_VP, C.POINTER(_CP), _I, _VP, _VP, C.POINTER(_VP), _VP]),
+    "ter_b200_norm_gemv_group": (_I, [_VP, C.POINTER(_CP), _I, _I, _VP, _VP, _VP, _F, C.POINTER(_VP), _I, _VP]),
     "ter_b200_gemv_host": (_I, [_VP, _CP, _VP, _F, _VP, _VP]),
     "ter_b200_sync": (_I, [_VP, _VP]),
     "ter_b200_gemm": (_I, [_VP, _CP, _VP, _VP, _I, _VP, _VP]),
@@ -240,6 +241,19 @@ class TerB200:
         arr_o = (C.c_void_p * len(names))(*[o.data_ptr() for o in outs])
         _check(self.L.ter_b200_gemv_group(self.h, arr_n, len(names), C.c_void_p(x.data_ptr()),
                                           C.c_void_p(x_scale.data_ptr()), arr_o, _stream_ptr(stream)), "gemv_group")
+        return outs
+
+    def norm_gemv_group(self, names, x, gamma, eps, act=0, up=None, outs=None, accumulate=False, stream=None):
+        """Fused quantiser + GEMV: x fp32[K] (gate for act != 0), returns fp32 outputs."""
+        import torch
+        if outs is None:
+            outs = [torch.empty(self._shapes[n][1], dtype=torch.float32, device=x.device) for n in names]
+        arr_n = (C.c_char_p * len(names))(*[n.encode() for n in names])
+        arr_o = (C.c_void_p * len(names))(*[o.data_ptr() for o in outs])
+        ptr = lambda t: C.c_void_p(t.data_ptr()) if t is not None else None  # noqa: E731
+        _check(self.L.ter_b200_norm_gemv_group(self.h, arr_n, len(names), act, ptr(x), ptr(up), ptr(gamma),
+                                               float(eps), arr_o, int(accumulate), _stream_ptr(stream)),
+               "norm_gemv_group")
         return outs
 
     def gemv_host(self, name: str, x_host, x_scale: float, out_host, stream=None):

@@ -116,9 +116,9 @@ static int ensure_host_staging(ter_b200_handle_t* h, size_t x_bytes, size_t out_
 // One launch over up to kGemvMaxGroup weights sharing x.
 int run_gemv(ter_b200_handle_t* h, const DevWeight* const* ws, int n, const int8_t* x_dev,
              const float* x_scale_dev, float x_scale_imm, float* const* outs, int32_t* const* accs,
-             bool accumulate, cudaStream_t st) {
+             bool accumulate, cudaStream_t st, const NormQuantParams* fuse, int fuse_row, int act_pair, float* act_out) {
     if (n < 1 || n > kGemvMaxGroup) return TER_B200_E_SHAPE;
-    if (((uintptr_t)x_dev & 15u) != 0) return TER_B200_E_SHAPE;
+    if (!fuse && ((uintptr_t)x_dev & 15u) != 0) return TER_B200_E_SHAPE;
     GemvParams p;
     memset(&p, 0, sizeof p);
     p.K = ws[0]->K;
@@ -142,6 +142,14 @@ int run_gemv(ter_b200_handle_t* h, const DevWeight* const* ws, int n, const int8
     p.n_tiles = tiles;
     p.status = h->status_dev;
     p.accumulate = accumulate ? 1 : 0;
+    if (fuse) {
+        if (fuse->n != p.K) return TER_B200_E_SHAPE;
+        if (h->gemv_cfg.split_max_strips <= 0 || tiles > h->gemv_cfg.split_max_strips) return TER_B200_E_SHAPE;
+        p.fuse = *fuse;
+        p.fuse_row = fuse_row;
+    }
+    p.act_pair = act_pair;
+    p.act_out = act_out;
     GemvLaunchCfg cfg = h->gemv_cfg;
     cfg.sm_count = h->sm_count;
     TERB_CUDA(h, launch_gemv(p, cfg, st));
@@ -342,6 +350,28 @@ int ter_b200_gemv_group(ter_b200_handle_t* h, const char* const* slots, int n_sl
     return run_gemv(h, ws, n_slots, x_dev, x_scale_dev, 1.0f, outs_dev, nullptr, false, pick_stream(h, stream));
 }
 
+int ter_b200_norm_gemv_group(ter_b200_handle_t* h, const char* const* slots, int n_slots, int act,
+                             const float* x_dev, const float* up_dev, const float* gamma_dev, float eps,
+                             float* const* outs_dev, int accumulate, void* stream) {
+    if (!h || !slots || !x_dev || !outs_dev) return TER_B200_E_NULL;
+    if (n_slots < 1 || n_slots > kGemvMaxGroup) return TER_B200_E_SHAPE;
+    if (act != 0 && act != TER_B200_ACT_SILU && act != TER_B200_ACT_RELU2) return TER_B200_E_SHAPE;
+    if (act != 0 && !up_dev) return TER_B200_E_NULL;
+    const DevWeight* ws[kGemvMaxGroup];
+    for (int i = 0; i < n_slots; ++i) {
+        if (!slots[i] || !outs_dev[i]) return TER_B200_E_NULL;
+        TerbSlot* s = find_slot(h, slots[i]);
+        if (!s) return TER_B200_E_UNKNOWN;
+        ws[i] = &s->w;
+    }
+    TERB_CUDA(h, cudaSetDevice(h->device));
+    NormQuantParams nq{x_dev, act ? up_dev : nullptr, gamma_dev, nullptr, nullptr, nullptr, ws[0]->K, 1,
+                       act == TER_B200_ACT_SILU ? PRE_SILU_MUL : (act == TER_B200_ACT_RELU2 ? PRE_RELU2_MUL : PRE_NONE),
+                       eps};
+    return run_gemv(h, ws, n_slots, nullptr, nullptr, 1.0f, outs_dev, nullptr, accumulate != 0,
+                    pick_stream(h, stream), &nq, 0);
+}
+
 int ter_b200_gemv_host(ter_b200_handle_t* h, const char* slot, const int8_t* x_host, float x_scale,
                        float* out_host, void* stream) {
     if (!h || !slot || !x_host || !out_host) return TER_B200_E_NULL;
@@ -446,6 +476,8 @@ int ter_b200_set_option(ter_b200_handle_t* h, const char* key, int value) {
     } else if (strcmp(key, "gemv_split_max_strips") == 0) {
         if (value < 0) return TER_B200_E_SHAPE;
         h->gemv_cfg.split_max_strips = value;
+    } else if (strcmp(key, "fuse_quant") == 0) {
+        h->gemv_cfg.fuse_quant = value ? 1 : 0;
     } else if (strcmp(key, "pdl") == 0) {
         h->gemv_cfg.pdl = value ? 1 : 0;
     } else {

@@ -26,6 +26,7 @@
 //     Integer addition is associative: the result is bit-exact whatever the grid.
 #include "common.cuh"
 #include "kernels.h"
+#include "normq.cuh"
 
 namespace terb {
 
@@ -219,8 +220,18 @@ __device__ __forceinline__ uint4 ldg_stream(const uint8_t* p) {
     return v;
 }
 
+// SPC = strips handled by one CTA at once (1, 2 or 4); a strip then has at most 8/SPC chunks per
+// warp in registers (SPC = 1 loops over further batches for long K).  Fatter CTAs keep the grid
+// within one wave, so the per-CTA prologue (fused quantiser) is paid once per SM slot.
+// p.act_pair (needs SPC >= 2, exactly two matrices gate and up): the CTA takes the SAME strip
+// range of both matrices and writes act(gate, up) = silu(g)*u or relu(g)^2*u for its columns to
+// p.act_out instead of the two raw projections.
+template <int SPC>
 __global__ void __launch_bounds__(kThreads) gemv_trit_split_kernel(const __grid_constant__ GemvParams p) {
-    __shared__ int red[kWarps][20];
+    constexpr int CPW = kSplitBatch / SPC;            // register slots (chunks per warp) per strip
+    extern __shared__ __align__(16) uint8_t fsm[];    // fused prologue only: float vals[K] | int8 xq[Kpad]
+    __shared__ int red[kWarps][SPC * 16 + 4];
+    __shared__ float red_f[2 * kWarps];
     const int tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
     const int c = lane >> 3, sgm = lane & 7;
@@ -228,12 +239,25 @@ __global__ void __launch_bounds__(kThreads) gemv_trit_split_kernel(const __grid_
     const int nb = (p.Kpad + kGemvKC - 1) / kGemvKC;
     const int last_kc = p.Kpad - (nb - 1) * kGemvKC;
 
-    const int strip = blockIdx.x;
-    int m, ls;
-    locate(p, strip, m, ls);
-    const uint8_t* base = p.W[m] + (size_t)ls * 4u * (size_t)p.Kpad;
-
-    auto waddr = [&](int j) -> const uint8_t* {
+    // strips of this CTA
+    int sm[SPC], sls[SPC];
+    const uint8_t* sbase[SPC];
+#pragma unroll
+    for (int i = 0; i < SPC; ++i) {
+        int m, ls;
+        if (p.act_pair) {
+            constexpr int HALF = SPC >= 2 ? SPC / 2 : 1;
+            m = i / HALF;
+            ls = blockIdx.x * HALF + (i % HALF);
+            if (ls >= p.tile_begin[1]) ls = -1;               // both matrices have tile_begin[1] strips
+        } else {
+            const int strip = blockIdx.x * SPC + i;
+            if (strip < p.n_tiles) locate(p, strip, m, ls); else { m = 0; ls = -1; }
+        }
+        sm[i] = m; sls[i] = ls;
+        sbase[i] = ls >= 0 ? p.W[m] + (size_t)ls * 4u * (size_t)p.Kpad : nullptr;
+    }
+    auto waddr = [&](const uint8_t* base, int j) -> const uint8_t* {
         const int q = j >> 3;                                   // 8 chunks per 1024-k block
         const int kc = (q == nb - 1) ? last_kc : kGemvKC;
         return base + (size_t)q * kStageBytes + c * kc + (j & 7) * 128 + sgm * 16;
@@ -242,60 +266,107 @@ __global__ void __launch_bounds__(kThreads) gemv_trit_split_kernel(const __grid_
     uint4 w[kSplitBatch];
 #pragma unroll
     for (int i = 0; i < kSplitBatch; ++i) {
-        const int j = warp + kWarps * i;
-        w[i] = (j < n_chunks) ? ldg_stream(waddr(j)) : make_uint4(0, 0, 0, 0);
+        const int si = i / CPW, j = warp + kWarps * (i % CPW);
+        w[i] = (sbase[si] && j < n_chunks) ? ldg_stream(waddr(sbase[si], j)) : make_uint4(0, 0, 0, 0);
     }
+    if (p.fuse.x) norm_quant_prefetch_gamma(p.fuse);
     pdl_launch_dependents();
     pdl_wait();
 
-    int a0 = 0, a1 = 0, a2 = 0, a3 = 0, xl = 0;
-    for (int b = 0; b * kSplitBatch * kWarps < n_chunks; ++b) {
+    const int8_t* xsrc = p.x;
+    float xscale_f = 0.0f;
+    if (p.fuse.x) {
+        float* vals = reinterpret_cast<float*>(fsm);
+        int8_t* xq = reinterpret_cast<int8_t*>(fsm + 4 * (size_t)((p.K + 3) & ~3));
+        xscale_f = norm_quant_fast_ok(p.fuse, p.fuse_row, xq, nullptr)
+                       ? block_norm_quant_fast(p.fuse, p.fuse_row, red_f, xq, nullptr)
+                       : block_norm_quant(p.fuse, p.fuse_row, vals, red_f, xq, nullptr);
+        __syncthreads();
+        xsrc = xq;
+    }
+
+    int acc[SPC][4];
+#pragma unroll
+    for (int i = 0; i < SPC; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0;
+    int xl = 0;
+    const int n_batches = SPC == 1 ? (n_chunks + kSplitBatch * kWarps - 1) / (kSplitBatch * kWarps) : 1;
+    for (int b = 0; b < n_batches; ++b) {
         if (b > 0) {
 #pragma unroll
             for (int i = 0; i < kSplitBatch; ++i) {
                 const int j = warp + kWarps * (i + b * kSplitBatch);
-                w[i] = (j < n_chunks) ? ldg_stream(waddr(j)) : make_uint4(0, 0, 0, 0);
+                w[i] = (sbase[0] && j < n_chunks) ? ldg_stream(waddr(sbase[0], j)) : make_uint4(0, 0, 0, 0);
             }
         }
 #pragma unroll
         for (int i = 0; i < kSplitBatch; ++i) {
-            const int j = warp + kWarps * (i + b * kSplitBatch);
+            const int si = i / CPW;
+            const int j = warp + kWarps * ((i % CPW) + b * kSplitBatch);
             const int k0 = j * 128 + sgm * 16;
             int4 xv = make_int4(0, 0, 0, 0);
-            if (j < n_chunks && k0 < p.K) xv = *reinterpret_cast<const int4*>(p.x + k0);
-            mac64(w[i], xv, a0, a1, a2, a3);
-            xl = __dp4a(xv.x, 0x01010101, xl);
-            xl = __dp4a(xv.y, 0x01010101, xl);
-            xl = __dp4a(xv.z, 0x01010101, xl);
-            xl = __dp4a(xv.w, 0x01010101, xl);
+            if (j < n_chunks && k0 < p.K) xv = *reinterpret_cast<const int4*>(xsrc + k0);
+            mac64(w[i], xv, acc[si][0], acc[si][1], acc[si][2], acc[si][3]);
+            if (si == 0) {
+                xl = __dp4a(xv.x, 0x01010101, xl);
+                xl = __dp4a(xv.y, 0x01010101, xl);
+                xl = __dp4a(xv.z, 0x01010101, xl);
+                xl = __dp4a(xv.w, 0x01010101, xl);
+            }
         }
     }
 #pragma unroll
     for (int o = 1; o < 8; o <<= 1) {
-        a0 += __shfl_xor_sync(0xffffffffu, a0, o);
-        a1 += __shfl_xor_sync(0xffffffffu, a1, o);
-        a2 += __shfl_xor_sync(0xffffffffu, a2, o);
-        a3 += __shfl_xor_sync(0xffffffffu, a3, o);
+#pragma unroll
+        for (int i = 0; i < SPC; ++i) {
+            acc[i][0] += __shfl_xor_sync(0xffffffffu, acc[i][0], o);
+            acc[i][1] += __shfl_xor_sync(0xffffffffu, acc[i][1], o);
+            acc[i][2] += __shfl_xor_sync(0xffffffffu, acc[i][2], o);
+            acc[i][3] += __shfl_xor_sync(0xffffffffu, acc[i][3], o);
+        }
         xl += __shfl_xor_sync(0xffffffffu, xl, o);
     }
     if (sgm == 0) {
-        int* r = &red[warp][c * 4];
-        r[0] = a0 - a1 - a2 - a3; r[1] = a1; r[2] = a2; r[3] = a3;
-        if (c == 0) red[warp][16] = xl;
+#pragma unroll
+        for (int i = 0; i < SPC; ++i) {
+            int* r = &red[warp][i * 16 + c * 4];
+            r[0] = acc[i][0] - acc[i][1] - acc[i][2] - acc[i][3];
+            r[1] = acc[i][1]; r[2] = acc[i][2]; r[3] = acc[i][3];
+        }
+        if (c == 0) red[warp][SPC * 16] = xl;
     }
     __syncthreads();
-    if (tid < 16) {
+    const float xscale = p.fuse.x ? xscale_f : (p.x_scale ? p.x_scale[0] : p.x_scale_imm);
+    auto column_value = [&](int si, int lc) -> int {
         int sum = 0, xsum = 0;
 #pragma unroll
-        for (int wi = 0; wi < kWarps; ++wi) { sum += red[wi][tid]; xsum += red[wi][16]; }
-        const int v = (sum >> (2 * (tid & 3))) - xsum;
-        const int col = ls * 16 + tid;
-        if (col < p.N[m]) {
-            if (p.acc_out[m]) p.acc_out[m][col] = v;
-            if (p.out[m]) {
-                const float xscale = p.x_scale ? p.x_scale[0] : p.x_scale_imm;
-                const float f = (float)v * (xscale * p.w_scale[m]);
-                p.out[m][col] = p.accumulate ? p.out[m][col] + f : f;
+        for (int wi = 0; wi < kWarps; ++wi) { sum += red[wi][si * 16 + lc]; xsum += red[wi][SPC * 16]; }
+        return (sum >> (2 * (lc & 3))) - xsum;
+    };
+    if (p.act_pair) {
+        constexpr int HALF = SPC >= 2 ? SPC / 2 : 1;
+        if (tid < HALF * 16) {
+            const int si = tid >> 4, lc = tid & 15;
+            if (sls[si] >= 0) {
+                const int col = sls[si] * 16 + lc;
+                if (col < p.N[0]) {
+                    const float g = (float)column_value(si, lc) * (xscale * p.w_scale[0]);
+                    const float u = (float)column_value(si + HALF, lc) * (xscale * p.w_scale[1]);
+                    p.act_out[col] = pre_op(p.act_pair, g, u);
+                }
+            }
+        }
+    } else if (tid < SPC * 16) {
+        const int si = tid >> 4, lc = tid & 15;
+        if (sls[si] >= 0) {
+            const int m = sm[si];
+            const int col = sls[si] * 16 + lc;
+            if (col < p.N[m]) {
+                const int v = column_value(si, lc);
+                if (p.acc_out[m]) p.acc_out[m][col] = v;
+                if (p.out[m]) {
+                    const float f = (float)v * (xscale * p.w_scale[m]);
+                    p.out[m][col] = p.accumulate ? p.out[m][col] + f : f;
+                }
             }
         }
     }
@@ -319,18 +390,46 @@ cudaError_t launch_gemv(const GemvParams& p_in, const GemvLaunchCfg& cfg, cudaSt
     }
     GemvParams p = p_in;
     if (cfg.split_max_strips > 0 && p.n_tiles <= cfg.split_max_strips) {
+        size_t fsmem = 0;
+        if (p.fuse.x) {
+            fsmem = 4 * (size_t)((p.K + 3) & ~3) + (size_t)p.Kpad;
+            if (fsmem > (size_t)kMaxSmem - 4096) return cudaErrorInvalidValue;
+        }
+        // Strips per CTA: as few as keep the grid within one resident wave (about 3 CTAs per SM with the
+        // fused prologue), limited by the 8 register slots per warp.
+        const int cpw = ((p.Kpad >> 7) + kWarps - 1) / kWarps;
+        const int max_spc = cpw <= 2 ? 4 : (cpw <= 4 ? 2 : 1);
+        const int wave = cfg.sm_count * 2;   // 128 registers x 256 threads: two CTAs per SM
+        int spc = 1;
+        while (spc < max_spc && (p.n_tiles + spc - 1) / spc > wave) spc *= 2;
+        if (p.act_pair) {
+            if (p.n_mats != 2 || p.tile_begin[1] * 2 != p.n_tiles || max_spc < 2 || p.N[0] != p.N[1] || !p.act_out)
+                return cudaErrorInvalidValue;
+            if (spc < 2) spc = 2;
+        }
+        const int grid = p.act_pair ? (p.tile_begin[1] + spc / 2 - 1) / (spc / 2) : (p.n_tiles + spc - 1) / spc;
+        void (*kern)(GemvParams) = spc == 4 ? gemv_trit_split_kernel<4>
+                                  : (spc == 2 ? gemv_trit_split_kernel<2> : gemv_trit_split_kernel<1>);
+        static bool split_attr[64][3] = {};
+        const int ai = spc == 4 ? 2 : (spc == 2 ? 1 : 0);
+        if (fsmem > 48 * 1024 && !split_attr[dev][ai]) {
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem - 4096);
+            if (e != cudaSuccess) return e;
+            split_attr[dev][ai] = true;
+        }
         cudaLaunchConfig_t lc = {};
-        lc.gridDim = dim3((unsigned)p.n_tiles);
+        lc.gridDim = dim3((unsigned)grid);
         lc.blockDim = dim3(kThreads);
-        lc.dynamicSmemBytes = 0;
+        lc.dynamicSmemBytes = fsmem;
         lc.stream = st;
         cudaLaunchAttribute attr[1];
         attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         lc.attrs = attr;
         lc.numAttrs = cfg.pdl ? 1 : 0;
-        return cudaLaunchKernelEx(&lc, gemv_trit_split_kernel, p);
+        return cudaLaunchKernelEx(&lc, kern, p);
     }
+    if (p.fuse.x) return cudaErrorNotSupported;   // the streaming kernel takes a quantised x only
     int per_sm = cfg.ctas_per_sm < 1 ? 1 : cfg.ctas_per_sm;
     int stages = cfg.stages > 0 ? cfg.stages : 3;
     if (stages > kMaxStages) stages = kMaxStages;

@@ -46,6 +46,14 @@ struct AttnParams {
     float* scratch;          // [B][Nh][max_chunks][Hd+2]
     float* out;              // [B][Nh*Hd]
     int B, Nh, Nkv, Hd, Smax, max_chunks;
+    // Fused rotary + KV append (all null/0 when q is already rotated and the cache already appended):
+    const float* rope_table; // [Smax][Hd/2][2]
+    const float* k_new;      // [B][Nkv*Hd] un-rotated k of the new position
+    const float* v_new;      // [B][Nkv*Hd]
+    uint16_t* kcache_w;      // same buffers as kcache / vcache, writable
+    uint16_t* vcache_w;
+    int neox;
+    int* status;             // device status word for bounded waits (may be null)
 };
 cudaError_t launch_attention(const AttnParams& p, bool pdl, cudaStream_t st);
 size_t attention_scratch_floats(int B, int Nh, int Hd, int Smax);

@@ -113,7 +113,8 @@ int ter_b200_attention(ter_b200_handle_t* h, const float* q_dev, const uint16_t*
     if (scratch_floats < attention_scratch_floats(B, Nh, Hd, Smax)) return TER_B200_E_SHAPE;
     TERB_CUDA(h, cudaSetDevice(h->device));
     AttnParams p{q_dev, kcache_dev, vcache_dev, pos_dev, scratch_dev, out_dev, B, Nh, Nkv, Hd, Smax,
-                 (Smax + kAttnChunk - 1) / kAttnChunk};
+                 (Smax + kAttnChunk - 1) / kAttnChunk, nullptr, nullptr, nullptr, nullptr, nullptr, 0,
+                 h->status_dev};
     TERB_CUDA(h, launch_attention(p, h->gemv_cfg.pdl != 0, pick_stream(h, stream)));
     h->launches += 2;
     return TER_B200_OK;

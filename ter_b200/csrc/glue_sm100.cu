@@ -15,171 +15,26 @@
 // attention_k (cuda/ter_cuda_forward_packed.cu:64-90,118-157; NEOX variant
 // cuda/ter_cuda_forward_bitnet.cu:185-201), mm_fp16_lm_head_k and argmax_*_k
 // (cuda/ter_cuda_forward_packed.cu:165-259).
-#include <cuda_bf16.h>
-#include <math_constants.h>
-
-#include "common.cuh"
-#include "glue.h"
+#include "normq.cuh"
 
 namespace terb {
 
-namespace {
-
-constexpr int kT = 256;   // threads per CTA in every glue kernel
-
-// exp(x) in fp32: n = rint(x*log2e); r = x - n*ln2 (two steps); degree-5 polynomial; * 2^n.
-// Arguments are clamped to [-87, 88]; below -87 the result is 0.  Same operations, in the
-// same order, as the CPU checker.
-__device__ __forceinline__ float exp_fixed(float x) {
-    if (!(x >= -87.0f)) return 0.0f;
-    if (x > 88.0f) x = 88.0f;
-    const float n = rintf(x * 1.44269504088896341f);
-    float r = fmaf(n, -0.693145751953125f, x);
-    r = fmaf(n, -1.42860682030941723212e-6f, r);
-    float p = 1.9875691500e-4f;
-    p = fmaf(p, r, 1.3981999507e-3f);
-    p = fmaf(p, r, 8.3334519073e-3f);
-    p = fmaf(p, r, 4.1665795894e-2f);
-    p = fmaf(p, r, 1.6666665459e-1f);
-    p = fmaf(p, r, 5.0000001201e-1f);
-    const float r2 = r * r;
-    float y = fmaf(p, r2, r);
-    y = y + 1.0f;
-    const int ni = (int)n;
-    return y * __int_as_float((ni + 127) << 23);
-}
-
-__device__ __forceinline__ float bf16_bits_to_f32(uint32_t b) { return __uint_as_float(b << 16); }
-__device__ __forceinline__ uint16_t f32_to_bf16_bits(float f) {
-    return __bfloat16_as_ushort(__float2bfloat16_rn(f));
-}
-
-__device__ __forceinline__ float warp_sum_butterfly(float v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v = v + __shfl_xor_sync(0xffffffffu, v, o);
-    return v;
-}
-__device__ __forceinline__ float warp_max(float v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-    return v;
-}
-// Block order sum of one value per thread (256 threads).  red: 8 floats of shared memory.
-__device__ __forceinline__ float block_sum(float v, float* red) {
-    v = warp_sum_butterfly(v);
-    __syncthreads();
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
-    __syncthreads();
-    float t = red[0];
-#pragma unroll
-    for (int w = 1; w < kT / 32; ++w) t = t + red[w];
-    return t;
-}
-__device__ __forceinline__ float block_max(float v, float* red) {
-    v = warp_max(v);
-    __syncthreads();
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
-    __syncthreads();
-    float t = red[0];
-#pragma unroll
-    for (int w = 1; w < kT / 32; ++w) t = fmaxf(t, red[w]);
-    return t;
-}
-
-__device__ __forceinline__ int quant_one(float v, float scale) {
-    int q = __float2int_rn(v * scale);
-    return q > 127 ? 127 : (q < -128 ? -128 : q);
-}
-
-}  // namespace
-
 // ============================================================ norm / activation / quantise
 namespace {
-
-__device__ __forceinline__ float pre_op(int pre, float x, float u) {
-    if (pre == PRE_SILU_MUL) {
-        const float e = exp_fixed(-x);
-        const float sg = x / (1.0f + e);
-        return sg * u;
-    }
-    if (pre == PRE_RELU2_MUL) {
-        const float r = x > 0.0f ? x * x : 0.0f;
-        return r * u;
-    }
-    return x;
-}
 
 __global__ void __launch_bounds__(kT) norm_quant_kernel(const NormQuantParams p) {
     extern __shared__ float vals[];   // n floats: the row after pre-op / normalisation
     __shared__ float red[kT / 32];
     pdl_launch_dependents();
     pdl_wait();
-    const int tid = threadIdx.x;
     const size_t off = (size_t)blockIdx.x * (size_t)p.n;
-    const float* x = p.x + off;
-    const float* u = p.u ? p.u + off : nullptr;
-    const int n = p.n;
-
-    float part = 0.0f;
-    for (int base = 4 * tid; base < n; base += 4 * kT) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const int i = base + e;
-            if (i < n) {
-                const float v = pre_op(p.pre, x[i], u ? u[i] : 0.0f);
-                vals[i] = v;
-                part = fmaf(v, v, part);
-            }
-        }
-    }
-    float amax = 0.0f;
-    if (p.gamma) {
-        const float ss = block_sum(part, red);
-        const float mean = ss / (float)n;
-        const float ri = 1.0f / sqrtf(mean + p.eps);
-        for (int base = 4 * tid; base < n; base += 4 * kT) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int i = base + e;
-                if (i < n) {
-                    const float v = (vals[i] * ri) * p.gamma[i];
-                    vals[i] = v;
-                    amax = fmaxf(amax, fabsf(v));
-                }
-            }
-        }
-    } else {
-        for (int base = 4 * tid; base < n; base += 4 * kT)
-#pragma unroll
-            for (int e = 0; e < 4; ++e)
-                if (base + e < n) amax = fmaxf(amax, fabsf(vals[base + e]));
-    }
-    if (p.normed) {
-        float* o = p.normed + off;
-        for (int base = 4 * tid; base < n; base += 4 * kT)
-#pragma unroll
-            for (int e = 0; e < 4; ++e)
-                if (base + e < n) o[base + e] = vals[base + e];
-    }
-    if (p.q) {
-        amax = block_max(amax, red) + 1e-9f;
-        const float scale = 127.0f / amax;
-        if (tid == 0) p.scale_out[blockIdx.x] = 1.0f / scale;
-        int8_t* q = p.q + off;
-        for (int base = 4 * tid; base < n; base += 4 * kT) {
-            if (base + 3 < n && ((reinterpret_cast<uintptr_t>(q + base) & 3u) == 0)) {
-                const int q0 = quant_one(vals[base], scale), q1 = quant_one(vals[base + 1], scale);
-                const int q2 = quant_one(vals[base + 2], scale), q3 = quant_one(vals[base + 3], scale);
-                *reinterpret_cast<uint32_t*>(q + base) =
-                    (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) |
-                    ((uint32_t)(q3 & 0xff) << 24);
-            } else {
-#pragma unroll
-                for (int e = 0; e < 4; ++e)
-                    if (base + e < n) q[base + e] = (int8_t)quant_one(vals[base + e], scale);
-            }
-        }
-    }
+    int8_t* qo = p.q ? p.q + off : nullptr;
+    float* no = p.normed ? p.normed + off : nullptr;
+    __shared__ float red16[16];
+    const float stored = norm_quant_fast_ok(p, (int)blockIdx.x, qo, no)
+                             ? block_norm_quant_fast(p, (int)blockIdx.x, red16, qo, no)
+                             : block_norm_quant(p, (int)blockIdx.x, vals, red, qo, no);
+    if (p.q && threadIdx.x == 0) p.scale_out[blockIdx.x] = stored;
 }
 
 template <typename Kern, typename Params>
@@ -267,25 +122,126 @@ namespace {
 
 constexpr int kMaxGroup = 8;   // query heads per KV head
 
+// Shared memory of attn_partial_kernel<HD>: K chunk, V chunk (bf16 [256][HD] each, filled by one
+// 1-D TMA bulk copy each), the group's query heads, the score / probability rows, barriers.
+template <int HD>
+struct AttnSmem {
+    static constexpr int kKOff = 0;
+    static constexpr int kVOff = kAttnChunk * HD * 2;
+    static constexpr int kQOff = 2 * kAttnChunk * HD * 2;
+    static constexpr int kScOff = kQOff + kMaxGroup * HD * 4;
+    static constexpr int kRedOff = kScOff + kMaxGroup * kAttnChunk * 4;
+    static constexpr int kBarOff = kRedOff + 64;
+    static constexpr int kBytes = kBarOff + 16;
+};
+
+// When p.rope_table is set the kernel also does what rope_kv_kernel does, for its own data only:
+// it rotates the group's query heads on the fly (the q buffer is left untouched) and, in the CTA
+// whose chunk contains the new position, rotates k, rounds k and v to bf16, appends them to the
+// cache and uses them.  Otherwise q is taken as already rotated and the cache as already appended.
 template <int HD>
 __global__ void __launch_bounds__(kT) attn_partial_kernel(const AttnParams p) {
-    __shared__ __align__(16) float qs[kMaxGroup * HD];
-    __shared__ float sc[kMaxGroup][kAttnChunk];
-    __shared__ float red[kT / 32];
+    extern __shared__ __align__(128) uint8_t asmem[];
+    using L = AttnSmem<HD>;
+    uint16_t* Ks = reinterpret_cast<uint16_t*>(asmem + L::kKOff);
+    uint16_t* Vs = reinterpret_cast<uint16_t*>(asmem + L::kVOff);
+    float* qs = reinterpret_cast<float*>(asmem + L::kQOff);
+    float (*sc)[kAttnChunk] = reinterpret_cast<float (*)[kAttnChunk]>(asmem + L::kScOff);
+    float* red = reinterpret_cast<float*>(asmem + L::kRedOff);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(asmem + L::kBarOff);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) {
+        mbar_init(&bars[0], 1);
+        mbar_init(&bars[1], 1);
+        mbar_fence_init();
+    }
+    const int c = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
+    {
+        // Hints only, issued while the producer of q is still running: pull this CTA's K/V chunk and the
+        // rotary row towards L2.  The position read here may be one step stale; nothing depends on it.
+        const int pg = *reinterpret_cast<const volatile int*>(p.pos + b);
+        const int s0g = c * kAttnChunk;
+        if (pg >= 0 && pg < p.Smax && s0g <= pg + 1) {
+            const int rows = min(kAttnChunk, pg + 2 - s0g);
+            const size_t ho = ((size_t)b * p.Nkv + g) * (size_t)p.Smax * HD + (size_t)s0g * HD;
+            const int lines = rows * HD * 2 / 128;
+            for (int i = tid; i < lines; i += kT) {
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(p.kcache + ho) + (size_t)i * 128));
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(p.vcache + ho) + (size_t)i * 128));
+            }
+            if (p.rope_table && tid < 8) {
+                const int pr = min(pg + (tid >> 2), p.Smax - 1);
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(p.rope_table + (size_t)pr * HD) + (tid & 3) * 128));
+            }
+        }
+    }
     pdl_launch_dependents();
     pdl_wait();
-    const int c = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
-    const int seq_len = p.pos[b] + 1;
-    const int s0 = c * kAttnChunk;
-    if (s0 >= seq_len || seq_len > p.Smax) return;
-    const int cnt = min(kAttnChunk, seq_len - s0);
-    const int G = p.Nh / p.Nkv;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const uint16_t* K = p.kcache + ((size_t)b * p.Nkv + g) * (size_t)p.Smax * HD;
-    const uint16_t* V = p.vcache + ((size_t)b * p.Nkv + g) * (size_t)p.Smax * HD;
-    const float* q = p.q + ((size_t)b * p.Nh + (size_t)g * G) * HD;
-    for (int i = tid; i < G * HD; i += kT) qs[i] = q[i];
     __syncthreads();
+    const int pos = p.pos[b];
+    const int seq_len = pos + 1;
+    const int s0 = c * kAttnChunk;
+    if (s0 >= seq_len || seq_len > p.Smax || pos < 0) return;
+    const int cnt = min(kAttnChunk, seq_len - s0);
+    const bool fused = p.rope_table != nullptr;
+    const bool owner = fused && (pos >= s0) && (pos < s0 + kAttnChunk);   // this chunk holds the new row
+    const int n_copy = owner ? cnt - 1 : cnt;                             // rows already in the cache
+    const int G = p.Nh / p.Nkv;
+    const size_t head_off = ((size_t)b * p.Nkv + g) * (size_t)p.Smax * HD;
+    const uint16_t* K = p.kcache + head_off;
+    const uint16_t* V = p.vcache + head_off;
+
+    if (tid == 0 && n_copy > 0) {
+        const uint32_t bytes = (uint32_t)n_copy * HD * 2u;
+        mbar_arrive_expect_tx(&bars[0], bytes);
+        bulk_g2s(Ks, K + (size_t)s0 * HD, bytes, &bars[0]);
+        mbar_arrive_expect_tx(&bars[1], bytes);
+        bulk_g2s(Vs, V + (size_t)s0 * HD, bytes, &bars[1]);
+    }
+
+    // query heads of the group (rotated here when fused)
+    const float* q = p.q + ((size_t)b * p.Nh + (size_t)g * G) * HD;
+    if (fused) {
+        const float* row = p.rope_table + (size_t)pos * HD;
+        const int half = HD / 2;
+        for (int idx = tid; idx < G * half; idx += kT) {
+            const int hh = idx / half, kk = idx % half;
+            const int i0 = p.neox ? kk : 2 * kk, i1 = p.neox ? kk + half : 2 * kk + 1;
+            const float cs = row[2 * kk], sn = row[2 * kk + 1];
+            const float v0 = q[hh * HD + i0], v1 = q[hh * HD + i1];
+            const float a = v0 * cs, bb = v1 * sn;
+            const float d = v0 * sn, e = v1 * cs;
+            qs[hh * HD + i0] = a - bb;
+            qs[hh * HD + i1] = d + e;
+        }
+        if (owner) {
+            const float* kn = p.k_new + ((size_t)b * p.Nkv + g) * HD;
+            const float* vn = p.v_new + ((size_t)b * p.Nkv + g) * HD;
+            uint16_t* Kw = p.kcache_w + head_off + (size_t)pos * HD;
+            uint16_t* Vw = p.vcache_w + head_off + (size_t)pos * HD;
+            const int r = pos - s0;
+            for (int kk = tid; kk < half; kk += kT) {
+                const int i0 = p.neox ? kk : 2 * kk, i1 = p.neox ? kk + half : 2 * kk + 1;
+                const float cs = row[2 * kk], sn = row[2 * kk + 1];
+                const float v0 = kn[i0], v1 = kn[i1];
+                const float a = v0 * cs, bb = v1 * sn;
+                const float d = v0 * sn, e = v1 * cs;
+                const uint16_t k0 = f32_to_bf16_bits(a - bb), k1 = f32_to_bf16_bits(d + e);
+                Ks[r * HD + i0] = k0; Ks[r * HD + i1] = k1;
+                Kw[i0] = k0; Kw[i1] = k1;
+            }
+            for (int d = tid; d < HD; d += kT) {
+                const uint16_t vb = f32_to_bf16_bits(vn[d]);
+                Vs[r * HD + d] = vb;
+                Vw[d] = vb;
+            }
+        }
+    } else {
+        for (int i = tid; i < G * HD; i += kT) qs[i] = q[i];
+    }
+    __syncthreads();
+    if (n_copy > 0) mbar_wait_bounded(&bars[0], 0, p.status);
 
     const float inv_sqrt = 1.0f / sqrtf((float)HD);
     const int sub = lane >> 3, j = lane & 7;
@@ -297,7 +253,7 @@ __global__ void __launch_bounds__(kT) attn_partial_kernel(const AttnParams p) {
 #pragma unroll
         for (int pc = 0; pc < HD / 64; ++pc) {
             uint4 raw = make_uint4(0, 0, 0, 0);
-            if (valid) raw = *reinterpret_cast<const uint4*>(K + (size_t)(s0 + t) * HD + pc * 64 + 8 * j);
+            if (valid) raw = *reinterpret_cast<const uint4*>(Ks + t * HD + pc * 64 + 8 * j);
             kv[pc * 8 + 0] = bf16_bits_to_f32(raw.x & 0xffffu);
             kv[pc * 8 + 1] = bf16_bits_to_f32(raw.x >> 16);
             kv[pc * 8 + 2] = bf16_bits_to_f32(raw.y & 0xffffu);
@@ -344,14 +300,15 @@ __global__ void __launch_bounds__(kT) attn_partial_kernel(const AttnParams p) {
         }
     }
     __syncthreads();
+    if (n_copy > 0) mbar_wait_bounded(&bars[1], 0, p.status);
 
     for (int idx = tid; idx < G * HD; idx += kT) {
         const int hh = idx / HD, d = idx % HD;
         const float* pr = sc[hh];
-        const uint16_t* vp = V + (size_t)s0 * HD + d;
+        const uint16_t* vp = Vs + d;
         float acc = 0.0f;
 #pragma unroll 8
-        for (int t = 0; t < cnt; ++t) acc = fmaf(pr[t], bf16_bits_to_f32(vp[(size_t)t * HD]), acc);
+        for (int t = 0; t < cnt; ++t) acc = fmaf(pr[t], bf16_bits_to_f32(vp[t * HD]), acc);
         rec0[hh * rec_stride + 2 + d] = acc;
     }
 }
@@ -388,14 +345,29 @@ size_t attention_scratch_floats(int B, int Nh, int Hd, int Smax) {
 cudaError_t launch_attention(const AttnParams& p, bool pdl, cudaStream_t st) {
     if (p.Nkv < 1 || p.Nh % p.Nkv != 0 || p.Nh / p.Nkv > kMaxGroup) return cudaErrorInvalidValue;
     const dim3 grid((unsigned)p.max_chunks, (unsigned)p.Nkv, (unsigned)p.B);
+    static bool attr_set[64][2] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
     cudaError_t e;
     if (p.Hd == 64) {
-        e = launch_pdl(attn_partial_kernel<64>, grid, dim3(kT), 0, pdl, st, p);
+        if (!attr_set[dev][0]) {
+            e = cudaFuncSetAttribute(attn_partial_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     AttnSmem<64>::kBytes);
+            if (e != cudaSuccess) return e;
+            attr_set[dev][0] = true;
+        }
+        e = launch_pdl(attn_partial_kernel<64>, grid, dim3(kT), AttnSmem<64>::kBytes, pdl, st, p);
         if (e != cudaSuccess) return e;
         return launch_pdl(attn_combine_kernel<64>, dim3((unsigned)p.Nh, (unsigned)p.B), dim3(64), 0, pdl, st, p);
     }
     if (p.Hd == 128) {
-        e = launch_pdl(attn_partial_kernel<128>, grid, dim3(kT), 0, pdl, st, p);
+        if (!attr_set[dev][1]) {
+            e = cudaFuncSetAttribute(attn_partial_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     AttnSmem<128>::kBytes);
+            if (e != cudaSuccess) return e;
+            attr_set[dev][1] = true;
+        }
+        e = launch_pdl(attn_partial_kernel<128>, grid, dim3(kT), AttnSmem<128>::kBytes, pdl, st, p);
         if (e != cudaSuccess) return e;
         return launch_pdl(attn_combine_kernel<128>, dim3((unsigned)p.Nh, (unsigned)p.B), dim3(128), 0, pdl, st, p);
     }
@@ -631,7 +603,8 @@ extern "C" int ter_b200_attention_noalloc(ter_b200_handle_t* h, const float* q_d
         g_attn_static_ptr[h->device] = scratch;
     }
     AttnParams p{q_dev, kcache_dev, vcache_dev, pos_dev, scratch, out_dev, B, Nh, Nkv, Hd, Smax,
-                 (Smax + kAttnChunk - 1) / kAttnChunk};
+                 (Smax + kAttnChunk - 1) / kAttnChunk, nullptr, nullptr, nullptr, nullptr, nullptr, 0,
+                 h->status_dev};
     TERB_CUDA(h, launch_attention(p, h->gemv_cfg.pdl != 0, pick_stream(h, stream)));
     h->launches += 2;
     return TER_B200_OK;

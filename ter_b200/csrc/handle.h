@@ -87,7 +87,8 @@ int build_weight_from_dev(ter_b200_handle_t* h, const void* data_dev, int format
 void free_weight(DevWeight* w);
 // One launch over up to kGemvMaxGroup weights sharing x (abi.cpp).
 int run_gemv(ter_b200_handle_t* h, const DevWeight* const* ws, int n, const int8_t* x_dev, const float* x_scale_dev,
-             float x_scale_imm, float* const* outs, int32_t* const* accs, bool accumulate, cudaStream_t st);
+             float x_scale_imm, float* const* outs, int32_t* const* accs, bool accumulate, cudaStream_t st,
+             const NormQuantParams* fuse = nullptr, int fuse_row = 0, int act_pair = 0, float* act_out = nullptr);
 int get_rope_table(ter_b200_handle_t* h, int n_pos, int head_dim, double theta, const float** out);
 
 }  // namespace terb

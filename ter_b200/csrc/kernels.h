@@ -4,6 +4,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "glue.h"
+
 namespace terb {
 
 // ---- internal weight layout -------------------------------------------------
@@ -50,6 +52,15 @@ struct GemvParams {
     int K, Kpad;
     int n_mats, n_tiles, stages;
     int accumulate;         // out[j] = out[j] + value (residual add fused in the epilogue)
+    // Fused prologue (latency path only): when fuse.x is set, every CTA derives the int8 activation
+    // vector and its scale itself from fp32 inputs (pre-op -> RMSNorm -> absmax int8, row fuse_row)
+    // instead of reading x / x_scale.
+    NormQuantParams fuse;
+    int fuse_row;
+    // Paired activation epilogue (latency path, two matrices gate and up of equal N): instead of the
+    // two projections, write act(gate, up) (PRE_SILU_MUL / PRE_RELU2_MUL) for every column to act_out.
+    int act_pair;
+    float* act_out;
     int* status;
 };
 
@@ -59,6 +70,7 @@ struct GemvLaunchCfg {
     int pdl = 1;
     // matrices (or groups) with at most this many strips take the register-prefetch split-K path
     int split_max_strips = 148 * 8;
+    int fuse_quant = 1;   // decode forward: run the quantisers inside the GEMV launches
     int sm_count = 148;
 };
 

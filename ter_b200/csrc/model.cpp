@@ -59,16 +59,24 @@ void drop_graph(TerbModel* m) {
 template <typename T>
 cudaError_t dalloc(T** p, size_t n) { return cudaMalloc((void**)p, n * sizeof(T)); }
 
-// GEMV for every sequence of the batch (rows of X against the same weights).
+// GEMV for every sequence of the batch (rows of X against the same weights).  With `nq` the
+// quantiser runs inside the GEMV launch (fp32 rows in, no int8 round trip through memory).
 int mm(ter_b200_handle_t* h, const DevWeight* const* ws, int n, const int8_t* xq, int K, const float* xs,
-       float* const* outs, bool accumulate, int B, cudaStream_t st) {
+       float* const* outs, bool accumulate, int B, cudaStream_t st, const NormQuantParams* nq = nullptr) {
     for (int b = 0; b < B; ++b) {
         float* o[kGemvMaxGroup];
         for (int i = 0; i < n; ++i) o[i] = outs[i] + (size_t)b * ws[i]->N;
-        int rc = run_gemv(h, ws, n, xq + (size_t)b * K, xs + b, 1.0f, o, nullptr, accumulate, st);
+        int rc = nq ? run_gemv(h, ws, n, nullptr, nullptr, 1.0f, o, nullptr, accumulate, st, nq, b)
+                    : run_gemv(h, ws, n, xq + (size_t)b * K, xs + b, 1.0f, o, nullptr, accumulate, st);
         if (rc) return rc;
     }
     return TER_B200_OK;
+}
+
+bool can_fuse(const ter_b200_handle_t* h, const DevWeight* const* ws, int n) {
+    int tiles = 0;
+    for (int i = 0; i < n; ++i) tiles += ws[i]->tiles();
+    return h->gemv_cfg.fuse_quant && h->gemv_cfg.split_max_strips > 0 && tiles <= h->gemv_cfg.split_max_strips;
 }
 
 #define CK(call)                                              \
@@ -91,46 +99,60 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
         const DevWeight* W = m->mats + (size_t)L * 7;
         float** vec = m->vecs + (size_t)L * 4;
         // ---- attention block
-        NormQuantParams nq{m->hidden, nullptr, vec[TER_B200_ATTN_NORM], m->xq, m->xs, nullptr, H, B, PRE_NONE, c.eps};
-        CK(launch_norm_quant(nq, pdl, st));
         {
             const DevWeight* ws[3] = {&W[TER_B200_WQ], &W[TER_B200_WK], &W[TER_B200_WV]};
             float* outs[3] = {m->q, m->k, m->v};
-            int rc = mm(h, ws, 3, m->xq, H, m->xs, outs, false, B, st);
+            NormQuantParams nq{m->hidden, nullptr, vec[TER_B200_ATTN_NORM], m->xq, m->xs, nullptr, H, B, PRE_NONE, c.eps};
+            const bool fz = can_fuse(h, ws, 3);
+            if (!fz) CK(launch_norm_quant(nq, pdl, st));
+            int rc = mm(h, ws, 3, m->xq, H, m->xs, outs, false, B, st, fz ? &nq : nullptr);
             if (rc) return rc;
         }
-        RopeKvParams rp{m->q, m->k, m->v, m->rope, m->pos, m->kcache + L * layer_cache, m->vcache + L * layer_cache,
-                        B, c.Nh, c.Nkv, c.Hd, c.Smax, bitnet ? 1 : 0};
-        CK(launch_rope_kv(rp, pdl, st));
-        AttnParams ap{m->q, m->kcache + L * layer_cache, m->vcache + L * layer_cache, m->pos, m->attn_scratch, m->att,
-                      B, c.Nh, c.Nkv, c.Hd, c.Smax, (c.Smax + kAttnChunk - 1) / kAttnChunk};
+        // rotary, KV append and attention in one launch (+ the ordered merge of the chunks)
+        uint16_t* kc = m->kcache + L * layer_cache;
+        uint16_t* vc = m->vcache + L * layer_cache;
+        AttnParams ap{m->q, kc, vc, m->pos, m->attn_scratch, m->att, B, c.Nh, c.Nkv, c.Hd, c.Smax,
+                      (c.Smax + kAttnChunk - 1) / kAttnChunk, m->rope, m->k, m->v, kc, vc, bitnet ? 1 : 0,
+                      h->status_dev};
         CK(launch_attention(ap, pdl, st));
         h->launches += 1;
-        NormQuantParams aq{m->att, nullptr, bitnet ? vec[TER_B200_ATTN_SUB_NORM] : nullptr, m->xq, m->xs, nullptr,
-                           Hq, B, PRE_NONE, c.eps};
-        CK(launch_norm_quant(aq, pdl, st));
         {
             const DevWeight* ws[1] = {&W[TER_B200_WO]};
             float* outs[1] = {m->hidden};
-            int rc = mm(h, ws, 1, m->xq, Hq, m->xs, outs, true, B, st);   // hidden += Wo(attn)
+            NormQuantParams aq{m->att, nullptr, bitnet ? vec[TER_B200_ATTN_SUB_NORM] : nullptr, m->xq, m->xs, nullptr,
+                               Hq, B, PRE_NONE, c.eps};
+            const bool fz = can_fuse(h, ws, 1);
+            if (!fz) CK(launch_norm_quant(aq, pdl, st));
+            int rc = mm(h, ws, 1, m->xq, Hq, m->xs, outs, true, B, st, fz ? &aq : nullptr);   // hidden += Wo(attn)
             if (rc) return rc;
         }
-        // ---- FFN block
-        NormQuantParams fq{m->hidden, nullptr, vec[TER_B200_FFN_NORM], m->xq, m->xs, nullptr, H, B, PRE_NONE, c.eps};
-        CK(launch_norm_quant(fq, pdl, st));
+        // ---- FFN block: gate and up in one launch whose epilogue applies the gated activation, then
+        // the down projection whose prologue normalises (BitNet sub-norm) and quantises it.
         {
             const DevWeight* ws[2] = {&W[TER_B200_WGATE], &W[TER_B200_WUP]};
             float* outs[2] = {m->gate, m->up};
-            int rc = mm(h, ws, 2, m->xq, H, m->xs, outs, false, B, st);
-            if (rc) return rc;
-        }
-        NormQuantParams gq{m->gate, m->up, bitnet ? vec[TER_B200_FFN_SUB_NORM] : nullptr, m->xq, m->xs, nullptr,
-                           F, B, bitnet ? PRE_RELU2_MUL : PRE_SILU_MUL, c.eps};
-        CK(launch_norm_quant(gq, pdl, st));
-        {
-            const DevWeight* ws[1] = {&W[TER_B200_WDOWN]};
-            float* outs[1] = {m->hidden};
-            int rc = mm(h, ws, 1, m->xq, F, m->xs, outs, true, B, st);    // hidden += Wdown(ffn)
+            NormQuantParams fq{m->hidden, nullptr, vec[TER_B200_FFN_NORM], m->xq, m->xs, nullptr, H, B, PRE_NONE, c.eps};
+            const bool fz = can_fuse(h, ws, 2);
+            const DevWeight* wd[1] = {&W[TER_B200_WDOWN]};
+            const bool pair = fz && can_fuse(h, wd, 1) && (((ws[0]->Kpad >> 7) + 7) / 8) <= 4;
+            const int act = bitnet ? PRE_RELU2_MUL : PRE_SILU_MUL;
+            if (!fz) CK(launch_norm_quant(fq, pdl, st));
+            if (pair) {
+                for (int b = 0; b < B; ++b) {
+                    int rc = run_gemv(h, ws, 2, nullptr, nullptr, 1.0f, outs, nullptr, false, st, &fq, b, act,
+                                      m->gate + (size_t)b * F);
+                    if (rc) return rc;
+                }
+            } else {
+                int rc = mm(h, ws, 2, m->xq, H, m->xs, outs, false, B, st, fz ? &fq : nullptr);
+                if (rc) return rc;
+            }
+            float* outd[1] = {m->hidden};
+            NormQuantParams gq{m->gate, pair ? nullptr : m->up, bitnet ? vec[TER_B200_FFN_SUB_NORM] : nullptr, m->xq,
+                               m->xs, nullptr, F, B, pair ? PRE_NONE : act, c.eps};
+            const bool fd = can_fuse(h, wd, 1);
+            if (!fd) CK(launch_norm_quant(gq, pdl, st));
+            int rc = mm(h, wd, 1, m->xq, F, m->xs, outd, true, B, st, fd ? &gq : nullptr);    // hidden += Wdown(ffn)
             if (rc) return rc;
         }
     }

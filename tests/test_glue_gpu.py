@@ -143,3 +143,38 @@ def test_lm_head_and_argmax(tb, V, H, B):
     t[1, :] = -3.0
     am = tb.argmax(t).cpu().numpy()
     assert am[0] == 1234 and am[1] == 0
+
+
+def test_fused_quantiser_gemv_matches_two_step(tb):
+    """ter_b200_norm_gemv_group == rmsnorm_quant / act_quant followed by the GEMV, bit for bit."""
+    from ter_b200 import FMT_V11
+    rng = np.random.default_rng(77)
+    K = 2560
+    names = []
+    for nm, N in (("fz_a", 640), ("fz_b", 2560)):
+        tb.install(nm, synth.pack_v11(synth.trits(K, N, N)), FMT_V11, K, N, float(synth.weight_scale(N)))
+        names.append(nm)
+    x = (rng.standard_normal(K) * 3).astype(np.float32)
+    u = rng.standard_normal(K).astype(np.float32)
+    g = rng.normal(1.0, 0.02, size=K).astype(np.float32)
+    xd, ud, gd = dev(x), dev(u), dev(g)
+    for act, gamma in ((0, gd), (0, None), (1, None), (2, gd)):
+        if act == 0:
+            q, sc, _ = tb.rmsnorm_quant(xd, gamma, 1e-5)
+        else:
+            q, sc = tb.act_quant(act, xd, ud, gamma, 1e-5)
+        want = tb.gemv_group(names, q[0], sc)
+        got = tb.norm_gemv_group(names, xd, gamma, 1e-5, act=act, up=ud if act else None)
+        for a, b in zip(got, want):
+            assert torch.equal(a, b), (act, gamma is None)
+        # residual accumulate
+        base = torch.full_like(want[1], 0.25)
+        acc = tb.norm_gemv_group(names[1:], xd, gamma, 1e-5, act=act, up=ud if act else None,
+                                 outs=[base.clone()], accumulate=True)[0]
+        assert torch.equal(acc, base + want[1])
+    # and against the CPU checker for one case
+    oq, os_, _ = oracle.rmsnorm_quant(x, g, 1e-5)
+    t = synth.trits(K, 640, 640)
+    want = oracle.gemv_epilogue(oracle.gemv_acc_fast(oq, t), os_, synth.weight_scale(640))
+    got = tb.norm_gemv_group(names[:1], xd, gd, 1e-5)[0].cpu().numpy()
+    assert np.array_equal(bits(got), bits(want))
