@@ -153,6 +153,47 @@ def cpu_reference_run(steps: int, warmup: int, threads: int):
             "ms_per_step": dt / steps * 1e3}
 
 
+def decode_bench(tb, dev, rank, n_prompt=128, n_gen=256):
+    """Random-init ternarised Llama-3.2-1B architecture (16 layers, H 2048, 32/8 heads x 64, FFN 8192,
+    vocab 128256, tied bf16 lm_head, bf16 KV cache), batch 1: 128 random prompt ids fed one position at a
+    time, then 256 greedy tokens; every step is one replay of the captured decode graph."""
+    import torch
+    from ter_b200 import FMT_V11, synth
+    cfg = dict(synth.LLAMA_1B_CFG, Smax=512)
+    tb.model_create(cfg, max_batch=1)
+    g = torch.Generator(device=dev)
+    g.manual_seed(synth.seed_for(rank, "embd") & 0x7FFFFFFF)
+    emb = (torch.randn((cfg["V"], cfg["H"]), generator=g, device=dev) * 0.02).to(torch.bfloat16)
+    tb.model_set_embd(emb.view(torch.int16))
+    del emb
+    rng = np.random.default_rng(synth.seed_for(rank, "vec"))
+    tb.model_set_vector(-1, 0, rng.normal(1.0, 0.02, cfg["H"]).astype(np.float32))
+    shapes = synth.model_shapes(cfg)
+    for L in range(cfg["L"]):
+        for wi, nm in enumerate(synth.MAT_ORDER):
+            K, N = shapes[nm]
+            seed = synth.seed_for(rank, "dec", L, nm)
+            tb.model_set_matrix(L, wi, synth.packed_v11_cuda(K, N, seed, dev), FMT_V11, float(synth.weight_scale(seed)))
+        for vi in range(2):
+            tb.model_set_vector(L, vi, rng.normal(1.0, 0.02, cfg["H"]).astype(np.float32))
+    prompt = np.random.default_rng(synth.seed_for(rank, "prompt")).integers(0, cfg["V"], size=n_prompt).astype(np.int32)
+    tb.generate(prompt, n_gen)                 # captures the graph, warms up
+    t0 = time.perf_counter()
+    out = tb.generate(prompt, n_gen)           # host tokens in, host tokens out
+    wall = time.perf_counter() - t0
+    steps = n_prompt + n_gen - 1
+    ms = tb.last_generate_ms()
+    shapes_bytes = sum(K * N // 4 for K, N in shapes.values()) * cfg["L"]
+    step_bytes = shapes_bytes + 2 * cfg["V"] * cfg["H"]
+    peak, _ = peaks()
+    return {"workload": "llama-3.2-1b architecture decode, batch 1, prompt 128 + 256 greedy tokens, random-init",
+            "tokens_per_s": steps / ms * 1e3, "ms_per_token": ms / steps, "steps": steps,
+            "e2e_tokens_per_s": steps / wall, "first_tokens": [int(t) for t in out[0][:4]],
+            "roofline_frac_hbm": (step_bytes / (ms / steps * 1e-3) / 1e9) / peak,
+            "bytes_per_token": step_bytes,
+            "note": "device time of the graph replays (CUDA events); e2e = wall clock of the generate() call"}
+
+
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -177,6 +218,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--layers", type=int, default=16, help="layers of the fabric (profiling captures use fewer)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -301,6 +343,20 @@ def main():
     peak, peak_src = peaks()
     per_gpu = step_bytes * args.steps / (ms * 1e-3) / 1e9
 
+    # ---- decode tokens/s (BASELINE configs[3]: Llama-3.2-1B architecture, batch 1, prompt 128 + 256 greedy)
+    decode = None
+    if not args.no_decode:
+        tb.close()
+        torch.cuda.empty_cache()
+        tb = TerB200(local)
+        decode = decode_bench(tb, dev, rank)
+        if world > 1:
+            t = torch.tensor([decode["ms_per_token"]], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            decode["ms_per_token"] = float(t.item())
+            decode["tokens_per_s"] = 1e3 / decode["ms_per_token"] * world
+            decode["note"] += f"; {world} independent replicas, aggregate tokens/s"
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         try:
@@ -331,6 +387,7 @@ def main():
             "e2e": {"value": e2e_value, "unit": UNIT, "steps": e2e_steps,
                     "h2d_bytes_per_step": sum(K for _, K, _, _, _ in mats) * world,
                     "d2h_bytes_per_step": sum(4 * N for _, _, N, _, _ in mats) * world},
+            "decode": decode,
             "gpu_launches": launches,
             "clocks": clocks,
         }

@@ -97,7 +97,8 @@ static int check_name(const char* name) {
 
 static int ensure_host_staging(ter_b200_handle_t* h, size_t x_bytes, size_t out_floats) {
     if (h->hx_cap < x_bytes) {
-        if (h->hx_dev) cudaFree(h->hx_dev);
+        if (h->gemm_scratch) cudaFree(h->gemm_scratch);
+    if (h->hx_dev) cudaFree(h->hx_dev);
         h->hx_dev = nullptr;
         h->hx_cap = 0;
         TERB_CUDA(h, cudaMalloc((void**)&h->hx_dev, x_bytes));
@@ -192,6 +193,8 @@ ter_b200_handle_t* ter_b200_create(int device) {
     if (!h) return nullptr;
     h->device = device;
     h->gemv_cfg = GemvLaunchCfg();
+    h->gemm_min_m = 4;
+    h->gemm_split_k = 1;
     int sms = 0;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) sms = 148;
     h->sm_count = sms;
@@ -220,6 +223,7 @@ void ter_b200_destroy(ter_b200_handle_t* h) {
         if (h->rope[i].data) cudaFree(h->rope[i].data);
     if (h->status_dev) cudaFree(h->status_dev);
     if (h->hscale_dev) cudaFree(h->hscale_dev);
+    if (h->gemm_scratch) cudaFree(h->gemm_scratch);
     if (h->hx_dev) cudaFree(h->hx_dev);
     if (h->hout_dev) cudaFree(h->hout_dev);
     if (h->stream) cudaStreamDestroy(h->stream);
@@ -476,6 +480,11 @@ int ter_b200_set_option(ter_b200_handle_t* h, const char* key, int value) {
     } else if (strcmp(key, "gemv_split_max_strips") == 0) {
         if (value < 0) return TER_B200_E_SHAPE;
         h->gemv_cfg.split_max_strips = value;
+    } else if (strcmp(key, "gemm_min_m") == 0) {
+        if (value < 1) return TER_B200_E_SHAPE;
+        h->gemm_min_m = value;
+    } else if (strcmp(key, "gemm_split_k") == 0) {
+        h->gemm_split_k = value ? 1 : 0;
     } else if (strcmp(key, "fuse_quant") == 0) {
         h->gemv_cfg.fuse_quant = value ? 1 : 0;
     } else if (strcmp(key, "pdl") == 0) {

@@ -41,6 +41,10 @@ struct ter_b200_handle_t {
     float* hscale_dev;
     TerbModel* model;
     RopeTable rope[4];
+    int32_t* gemm_scratch;      // split-K partials of the tensor-core GEMM
+    size_t gemm_scratch_cap;    // ints
+    int gemm_min_m;             // batches below this go row by row through the GEMV kernel
+    int gemm_split_k;           // 0 = never split K
     cudaGraphExec_t graphs[16];
     uint64_t graph_launches[16];   // kernels recorded in each graph
     uint64_t capture_mark;
@@ -85,6 +89,9 @@ inline void count_gemv(ter_b200_handle_t* h, int K, int N, int rows) {
 int build_weight_from_dev(ter_b200_handle_t* h, const void* data_dev, int format, int K, int N, float scale,
                           cudaStream_t st, DevWeight* out);
 void free_weight(DevWeight* w);
+// Batched GEMM over one weight (tensor cores for M >= gemm_min_m, else GEMV per row).
+int run_gemm(ter_b200_handle_t* h, const DevWeight* w, const int8_t* X, const float* x_scales, int M, float* out,
+             int32_t* acc, cudaStream_t st);
 // One launch over up to kGemvMaxGroup weights sharing x (abi.cpp).
 int run_gemv(ter_b200_handle_t* h, const DevWeight* const* ws, int n, const int8_t* x_dev, const float* x_scale_dev,
              float x_scale_imm, float* const* outs, int32_t* const* accs, bool accumulate, cudaStream_t st,

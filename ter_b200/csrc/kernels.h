@@ -76,6 +76,23 @@ struct GemvLaunchCfg {
 
 cudaError_t launch_gemv(const GemvParams& p, const GemvLaunchCfg& cfg, cudaStream_t st);
 
+// ---- batched GEMM (tcgen05) ---------------------------------------------------
+struct GemmParams {
+    const uint8_t* W;         // internal layout (strips)
+    const int8_t* X;          // [M][K] row-major
+    const float* x_scales;    // [M]
+    float* out;               // [M][N] or null
+    int32_t* acc_out;         // [M][N] or null (raw int32 dot products)
+    int32_t* part;            // split-K scratch: gemm_scratch_ints(M, N) ints, or null (no split)
+    int32_t* part_xsum;       // set by the launcher
+    float w_scale;
+    int M, N, K, Kpad, n_strips;
+    int tokens, tmem_cols, ksplits, stages;   // set by the launcher
+    int* status;
+};
+size_t gemm_scratch_ints(int M, int N);
+cudaError_t launch_gemm(const GemmParams& p, int sm_count, bool pdl, cudaStream_t st);
+
 // ---- install-time re-pack (device side) --------------------------------------
 cudaError_t launch_recode_v11(const uint8_t* src, uint8_t* dst, int K, int N, int Kpad, int Npad, cudaStream_t st);
 cudaError_t launch_recode_rowmajor(const uint8_t* src, uint8_t* dst, int K, int N, int Kpad, int Npad, cudaStream_t st);

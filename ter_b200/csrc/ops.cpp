@@ -4,6 +4,58 @@
 
 using namespace terb;
 
+namespace terb {
+
+int run_gemm(ter_b200_handle_t* h, const DevWeight* w, const int8_t* X, const float* x_scales, int M, float* out,
+             int32_t* acc, cudaStream_t st) {
+    if (((uintptr_t)X & 15u) != 0) return TER_B200_E_SHAPE;
+    if (M < h->gemm_min_m) {
+        // small batches: one GEMV launch per row (exact; the weights are re-read M times)
+        for (int m = 0; m < M; ++m) {
+            const DevWeight* ws[1] = {w};
+            float* o[1] = {out ? out + (size_t)m * w->N : nullptr};
+            int32_t* a[1] = {acc ? acc + (size_t)m * w->N : nullptr};
+            int rc = run_gemv(h, ws, 1, X + (size_t)m * w->K, x_scales ? x_scales + m : nullptr, 1.0f, out ? o : nullptr,
+                              acc ? a : nullptr, false, st);
+            if (rc) return rc;
+        }
+        return TER_B200_OK;
+    }
+    if (!x_scales && out) return TER_B200_E_NULL;
+    GemmParams p;
+    memset(&p, 0, sizeof p);
+    p.W = w->data;
+    p.X = X;
+    p.x_scales = x_scales;
+    p.out = out;
+    p.acc_out = acc;
+    p.w_scale = w->scale;
+    p.M = M; p.N = w->N; p.K = w->K; p.Kpad = w->Kpad; p.n_strips = w->tiles();
+    p.status = h->status_dev;
+    if (h->gemm_split_k) {
+        const size_t need = gemm_scratch_ints(M, w->N);
+        if (h->gemm_scratch_cap < need) {
+            cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+            cudaStreamIsCapturing(st, &cs);
+            if (cs == cudaStreamCaptureStatusNone) {
+                TERB_CUDA(h, cudaDeviceSynchronize());
+                if (h->gemm_scratch) cudaFree(h->gemm_scratch);
+                h->gemm_scratch = nullptr;
+                h->gemm_scratch_cap = 0;
+                TERB_CUDA(h, cudaMalloc((void**)&h->gemm_scratch, need * sizeof(int)));
+                h->gemm_scratch_cap = need;
+            }
+        }
+        if (h->gemm_scratch_cap >= need) p.part = h->gemm_scratch;   // else: no split (still exact)
+    }
+    TERB_CUDA(h, launch_gemm(p, h->sm_count, h->gemv_cfg.pdl != 0, st));
+    h->launches += 1;
+    count_gemv(h, w->K, w->N, M);
+    return TER_B200_OK;
+}
+
+}  // namespace terb
+
 extern "C" {
 
 int ter_b200_gemm(ter_b200_handle_t* h, const char* slot, const int8_t* X_dev, const float* x_scales_dev, int M,
@@ -12,13 +64,8 @@ int ter_b200_gemm(ter_b200_handle_t* h, const char* slot, const int8_t* X_dev, c
     if (M < 1) return TER_B200_E_SHAPE;
     TerbSlot* s = find_slot(h, slot);
     if (!s) return TER_B200_E_UNKNOWN;
-    // Row-at-a-time through the GEMV kernel (exact; the tensor-core path replaces this for M >= 16).
-    for (int m = 0; m < M; ++m) {
-        int rc = ter_b200_gemv(h, slot, X_dev + (size_t)m * s->w.K, x_scales_dev + m,
-                               out_dev + (size_t)m * s->w.N, stream);
-        if (rc) return rc;
-    }
-    return TER_B200_OK;
+    TERB_CUDA(h, cudaSetDevice(h->device));
+    return run_gemm(h, &s->w, X_dev, x_scales_dev, M, out_dev, nullptr, pick_stream(h, stream));
 }
 
 int ter_b200_gemm_acc(ter_b200_handle_t* h, const char* slot, const int8_t* X_dev, int M, int32_t* acc_dev,
@@ -27,11 +74,8 @@ int ter_b200_gemm_acc(ter_b200_handle_t* h, const char* slot, const int8_t* X_de
     if (M < 1) return TER_B200_E_SHAPE;
     TerbSlot* s = find_slot(h, slot);
     if (!s) return TER_B200_E_UNKNOWN;
-    for (int m = 0; m < M; ++m) {
-        int rc = ter_b200_gemv_acc(h, slot, X_dev + (size_t)m * s->w.K, acc_dev + (size_t)m * s->w.N, stream);
-        if (rc) return rc;
-    }
-    return TER_B200_OK;
+    TERB_CUDA(h, cudaSetDevice(h->device));
+    return run_gemm(h, &s->w, X_dev, nullptr, M, nullptr, acc_dev, pick_stream(h, stream));
 }
 
 int ter_b200_call(ter_b200_handle_t* h, const char* name, const int64_t* args, size_t n_args) {
