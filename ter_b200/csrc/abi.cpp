@@ -483,6 +483,8 @@ int ter_b200_set_option(ter_b200_handle_t* h, const char* key, int value) {
     } else if (strcmp(key, "gemm_min_m") == 0) {
         if (value < 1) return TER_B200_E_SHAPE;
         h->gemm_min_m = value;
+    } else if (strcmp(key, "gemm_dbg") == 0) {
+        h->gemm_dbg = value;
     } else if (strcmp(key, "gemm_split_k") == 0) {
         h->gemm_split_k = value ? 1 : 0;
     } else if (strcmp(key, "fuse_quant") == 0) {

@@ -30,10 +30,21 @@ namespace terb {
 
 namespace {
 
-constexpr int kGemmThreads = 160;            // 4 producer/epilogue warps + 1 MMA warp
+constexpr int kProducerWarps = 8;
+constexpr int kGemmThreads = 32 * (kProducerWarps + 1);   // 8 producer/epilogue warps + 1 MMA warp
 constexpr int kTileN = 128;                  // output columns per CTA = MMA M
 constexpr int kKStep = 128;                  // k per pipeline stage = one 128-byte swizzle row
 constexpr int kAStageBytes = kTileN * kKStep;   // 16 KB
+constexpr int kRawStageBytes = 4096;            // the packed trits of one stage (128 columns x 128 k, 2 bits each)
+constexpr int kAhead = 2;                       // stages of cp.async copies in flight per producer thread (<= stages - 2,
+                                                // so a refill never waits on the MMA issued just before it)
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -80,9 +91,10 @@ struct GemmSmemLayout {
     __host__ __device__ int b_stage_bytes() const { return tokens * kKStep; }
     __host__ __device__ int a_off(int s) const { return s * kAStageBytes; }
     __host__ __device__ int b_off(int s) const { return stages * kAStageBytes + s * b_stage_bytes(); }
-    __host__ __device__ int tail_off() const { return stages * (kAStageBytes + b_stage_bytes()); }
-    // tail: full[8], empty[8], done (u64 each) | tmem base (u32) | abort (int) | xsum[256] (int)
-    __host__ __device__ int bytes() const { return tail_off() + 17 * 8 + 16 + 256 * 4 + 1024; }
+    __host__ __device__ int raw_off(int s) const { return stages * (kAStageBytes + b_stage_bytes()) + s * kRawStageBytes; }
+    __host__ __device__ int tail_off() const { return stages * (kAStageBytes + b_stage_bytes() + kRawStageBytes); }
+    // tail: full[8], empty[8], done (u64 each) | tmem base, abort (16 B) | scale[256] (float) | rowsum[256] (int)
+    __host__ __device__ int bytes() const { return tail_off() + 17 * 8 + 16 + 2 * 256 * 4 + 1024; }
 };
 
 __global__ void __launch_bounds__(kGemmThreads) gemm_trit_kernel(const __grid_constant__ GemmParams p) {
@@ -95,7 +107,8 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_trit_kernel(const __grid_co
     uint64_t* done = full + 16;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    int* xsum_s = reinterpret_cast<int*>(tmem_slot + 4);
+    float* tok_scale = reinterpret_cast<float*>(tmem_slot + 4);     // [256] x_scales[m] * w_scale
+    int* tok_sum = reinterpret_cast<int*>(tok_scale + 256);         // [256] sum_k X[m][k]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int tile = blockIdx.x;                       // 128-column tile
@@ -108,13 +121,12 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_trit_kernel(const __grid_co
     const int S = p.stages;
 
     if (tid == 0) {
-        for (int i = 0; i < S; ++i) { mbar_init(&full[i], 4); mbar_init(&empty[i], 1); }
+        for (int i = 0; i < S; ++i) { mbar_init(&full[i], kProducerWarps); mbar_init(&empty[i], 1); }
         mbar_init(done, 1);
         *abort_flag = 0;
         mbar_fence_init();
     }
-    for (int i = tid; i < 256; i += kGemmThreads) xsum_s[i] = 0;
-    if (warp == 4) {   // tensor memory for the accumulators: tmem_cols 32-bit columns x 128 lanes
+    if (warp == kProducerWarps) {   // tensor memory for the accumulators: tmem_cols 32-bit columns x 128 lanes
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
                      "r"((uint32_t)p.tmem_cols)
                      : "memory");
@@ -128,81 +140,78 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_trit_kernel(const __grid_co
     pdl_launch_dependents();
     pdl_wait();
 
-    if (warp < 4) {
-        // ------------------------------------------------------------------ producers
+    if (warp < kProducerWarps) {
+        // ------------------------------------------------------------------ producers (256 threads)
         const int nb = (p.Kpad + kGemvKC - 1) / kGemvKC;
         const int last_kc = p.Kpad - (nb - 1) * kGemvKC;
-        const int seg = tid >> 2, part = tid & 3;          // 32 segments (strip, byte-column) x 4 x 32 bytes
+        const int seg = tid >> 3, part = tid & 7;          // 32 segments (strip, byte-column) x 8 x 16 bytes
         const int strip_l = seg >> 2, bc = seg & 3;
         const int strip = tile * 8 + strip_l;
         const bool strip_ok = strip < p.n_strips;
         const uint8_t* sbase = p.W + (size_t)strip * 4u * (size_t)p.Kpad;
-        const int xr = tid >> 3, xci = tid & 7;            // activation copy: row xr + 16*i, 16-byte chunk xci
-        const int nt16 = p.tokens / 16;
-        int psum[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) psum[i] = 0;
+        const int xr = tid >> 3, xci = tid & 7;            // activation copy: row xr + 32*i, 16-byte chunk xci
+        const int nt32 = (p.tokens + 31) / 32;
+        // per-token epilogue constants
+        if (tid < p.tokens) {
+            const int m = m0 + tid;
+            tok_scale[tid] = (m < p.M && p.x_scales) ? p.x_scales[m] * p.w_scale : 0.0f;
+            tok_sum[tid] = (m < p.M) ? p.x_rowsum[m] : 0;
+        }
+        const int4 zero4 = make_int4(0, 0, 0, 0);
         bool ok = true;
-        for (int it = 0; it < n_steps && ok; ++it) {
-            const int s = it % S;
-            const uint32_t ph = (uint32_t)(it / S) & 1u;
-            if (it >= S) ok = mbar_wait_abortable(&empty[s], ph ^ 1u, abort_flag, p.status);
-            if (!ok) break;
-            const int ks = step_begin + it;
-            // ---- A: expand 32 packed bytes (32 k x 4 columns) of this thread's segment
-            uint8_t* A = gsm + L.a_off(s);
-            {
-                const int q = ks >> 3;
-                const int kc = (q == nb - 1) ? last_kc : kGemvKC;
-                const uint8_t* src = sbase + (size_t)q * (4 * kGemvKC) + (size_t)bc * kc + (ks & 7) * 128 + part * 32;
-                uint4 w0 = make_uint4(0x55555555u, 0x55555555u, 0x55555555u, 0x55555555u), w1 = w0;
+        // Asynchronous copies (cp.async) of stage `j`: this thread's 16 packed bytes and its 16-byte
+        // chunks of the activation slice, straight into shared memory; kAhead stages stay in flight.
+        auto issue = [&](int j) {
+            const int s = j % S;
+            if (j >= S) ok = ok && mbar_wait_abortable(&empty[s], ((uint32_t)(j / S) & 1u) ^ 1u, abort_flag, p.status);
+            if (ok) {
+                const int ks = step_begin + j;
+                uint8_t* raw = gsm + L.raw_off(s) + seg * 128 + part * 16;
                 if (strip_ok) {
-                    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                                 : "=r"(w0.x), "=r"(w0.y), "=r"(w0.z), "=r"(w0.w) : "l"(src));
-                    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                                 : "=r"(w1.x), "=r"(w1.y), "=r"(w1.z), "=r"(w1.w) : "l"(src + 16));
+                    const int q = ks >> 3;
+                    const int kc = (q == nb - 1) ? last_kc : kGemvKC;
+                    cp_async16(raw, sbase + (size_t)q * (4 * kGemvKC) + (size_t)bc * kc + (ks & 7) * 128 + part * 16);
+                } else {
+                    *reinterpret_cast<uint4*>(raw) = make_uint4(0x55555555u, 0x55555555u, 0x55555555u, 0x55555555u);
                 }
+                uint8_t* Bm = gsm + L.b_off(s);
+                const int kbyte = ks * kKStep + xci * 16;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    if (i >= nt32) break;
+                    const int ml = xr + 32 * i;
+                    if (ml >= p.tokens) break;
+                    uint8_t* dst = Bm + (ml >> 3) * 1024 + (ml & 7) * 128 + ((xci ^ (ml & 7)) * 16);
+                    if (m0 + ml < p.M && kbyte < p.K) cp_async16(dst, p.X + (size_t)(m0 + ml) * p.K + kbyte);
+                    else *reinterpret_cast<int4*>(dst) = zero4;
+                }
+            }
+            cp_async_commit();
+        };
+        for (int j = 0; j < kAhead; ++j)
+            if (j < n_steps) issue(j); else cp_async_commit();
+        for (int it = 0; it < n_steps; ++it) {
+            const int s = it % S;
+            if (it + kAhead < n_steps) issue(it + kAhead); else cp_async_commit();
+            cp_async_wait<kAhead>();         // this thread's copies of stage `it` have landed
+            if (!ok) break;
+            // ---- A: expand this thread's 16 packed bytes (16 k x 4 columns)
+            {
+                uint8_t* A = gsm + L.a_off(s);
+                const uint4 w = *reinterpret_cast<const uint4*>(gsm + L.raw_off(s) + seg * 128 + part * 16);
 #pragma unroll
                 for (int f = 0; f < 4; ++f) {
                     const uint32_t mk = 0x03030303u << (2 * f);
                     const int r = strip_l * 16 + bc * 4 + f;                     // A row = local output column
-                    uint8_t* rowp = A + (r >> 3) * 1024 + (r & 7) * 128;
-                    const int c0 = (part * 2) ^ (r & 7), c1 = (part * 2 + 1) ^ (r & 7);
-                    *reinterpret_cast<uint4*>(rowp + c0 * 16) = make_uint4(w0.x & mk, w0.y & mk, w0.z & mk, w0.w & mk);
-                    *reinterpret_cast<uint4*>(rowp + c1 * 16) = make_uint4(w1.x & mk, w1.y & mk, w1.z & mk, w1.w & mk);
+                    *reinterpret_cast<uint4*>(A + (r >> 3) * 1024 + (r & 7) * 128 + ((part ^ (r & 7)) * 16)) =
+                        make_uint4(w.x & mk, w.y & mk, w.z & mk, w.w & mk);
                 }
             }
-            // ---- B: the 128-k slice of the activations of this token tile
-            uint8_t* Bm = gsm + L.b_off(s);
-            const int kbyte = ks * kKStep + xci * 16;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                if (i >= nt16) break;
-                const int ml = xr + 16 * i;
-                int4 v = make_int4(0, 0, 0, 0);
-                if (m0 + ml < p.M && kbyte < p.K)
-                    v = *reinterpret_cast<const int4*>(p.X + (size_t)(m0 + ml) * p.K + kbyte);
-                *reinterpret_cast<int4*>(Bm + (ml >> 3) * 1024 + (ml & 7) * 128 + ((xci ^ (ml & 7)) * 16)) = v;
-                int sacc = psum[i];
-                sacc = __dp4a(v.x, 0x01010101, sacc);
-                sacc = __dp4a(v.y, 0x01010101, sacc);
-                sacc = __dp4a(v.z, 0x01010101, sacc);
-                sacc = __dp4a(v.w, 0x01010101, sacc);
-                psum[i] = sacc;
-            }
-            fence_async_smem();          // make the generic-proxy stores visible to the tensor core
+            fence_async_smem();          // make the generic-proxy writes visible to the tensor core
             __syncwarp();
             if (lane == 0) mbar_arrive(&full[s]);
         }
-        // row sums of X over this CTA's K range (8 lanes share a row)
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            int v = psum[i];
-            v += __shfl_xor_sync(0xffffffffu, v, 1);
-            v += __shfl_xor_sync(0xffffffffu, v, 2);
-            v += __shfl_xor_sync(0xffffffffu, v, 4);
-            if (xci == 0 && i < p.tokens / 16) xsum_s[xr + 16 * i] = v;
-        }
+        cp_async_wait<0>();
     } else if (lane == 0) {
         // ------------------------------------------------------------------ MMA issuer
         const uint32_t idesc = umma_idesc_i8(p.tokens);
@@ -235,64 +244,88 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_trit_kernel(const __grid_co
     }
     __syncwarp();
 
-    if (warp < 4) {
-        // ------------------------------------------------------------------ epilogue
-        asm volatile("bar.sync 1, 128;" ::: "memory");     // xsum_s complete (producer warps only)
+    if (warp < kProducerWarps) {
+        // ------------------------------------------------------------------ epilogue (8 warps)
+        asm volatile("bar.sync 1, 256;" ::: "memory");     // tok_scale / tok_sum visible to all producer warps
         const bool ok = n_steps > 0 && mbar_wait_abortable(done, 0, abort_flag, p.status);
         tc_fence_after();
-        const int nl = warp * 32 + lane;                   // TMEM lane = local output column
+        const int quarter = warp & 3;                      // the TMEM lanes this warp may read
+        const int nl = quarter * 32 + lane;                // TMEM lane = local output column
         const int n = tile * kTileN + nl;
         const int shift = 2 * (nl & 3);
+        // warps 0-3 take the even 32-token groups, warps 4-7 the odd ones
         if (ok) {
-            for (int c0 = 0; c0 < p.tokens; c0 += 16) {
-                uint32_t d[16];
-                const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0;
+            for (int c0 = (warp >> 2) * 32; c0 < p.tokens; c0 += 64) {
+                uint32_t d[32];
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
                 asm volatile(
-                    "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                    "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+                    "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
                     : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]), "=r"(d[4]), "=r"(d[5]), "=r"(d[6]), "=r"(d[7]),
-                      "=r"(d[8]), "=r"(d[9]), "=r"(d[10]), "=r"(d[11]), "=r"(d[12]), "=r"(d[13]), "=r"(d[14]), "=r"(d[15])
+                      "=r"(d[8]), "=r"(d[9]), "=r"(d[10]), "=r"(d[11]), "=r"(d[12]), "=r"(d[13]), "=r"(d[14]), "=r"(d[15]),
+                      "=r"(d[16]), "=r"(d[17]), "=r"(d[18]), "=r"(d[19]), "=r"(d[20]), "=r"(d[21]), "=r"(d[22]), "=r"(d[23]),
+                      "=r"(d[24]), "=r"(d[25]), "=r"(d[26]), "=r"(d[27]), "=r"(d[28]), "=r"(d[29]), "=r"(d[30]), "=r"(d[31])
                     : "r"(taddr));
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 if (n < p.N) {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
+                    for (int j = 0; j < 32; ++j) {
                         const int m = m0 + c0 + j;
-                        if (m >= p.M) break;
-                        const size_t o = (size_t)m * p.N + n;
-                        if (p.ksplits > 1) {
-                            atomicAdd(&p.part[o], (int)d[j]);
-                        } else {
-                            const int v = ((int)d[j] >> shift) - xsum_s[c0 + j];
-                            if (p.acc_out) p.acc_out[o] = v;
-                            if (p.out) p.out[o] = (float)v * (p.x_scales[m] * p.w_scale);
+                        if (c0 + j < p.tokens && m < p.M) {
+                            const size_t o = (size_t)m * p.N + n;
+                            if (p.ksplits > 1) {
+                                atomicAdd(&p.part[o], (int)d[j]);
+                            } else {
+                                const int v = ((int)d[j] >> shift) - tok_sum[c0 + j];
+                                if (p.acc_out) p.acc_out[o] = v;
+                                if (p.out) p.out[o] = (float)v * tok_scale[c0 + j];
+                            }
                         }
                     }
                 }
-            }
-            if (p.ksplits > 1 && tile == 0) {
-                // each K range contributes its part of the row sums once (tile 0 only)
-                for (int i = tid; i < p.tokens; i += 128)
-                    if (m0 + i < p.M) atomicAdd(&p.part_xsum[m0 + i], xsum_s[i]);
             }
         }
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 4) {
+    if (warp == kProducerWarps) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)p.tmem_cols)
                      : "memory");
     }
 }
 
-// Split-K second pass: out[m][n] = float((part[m][n] >> 2*(n%4)) - xsum[m]) * (x_scales[m] * w_scale).
+// Row sums of the activations: rowsum[m] = sum_k X[m][k] (one warp per row).  They remove the "+1" of
+// the unsigned weight bytes: sum_k x*(t+1) - sum_k x = sum_k x*t.
+__global__ void __launch_bounds__(256) gemm_rowsum_kernel(const GemmParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int m = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (m >= p.M) return;
+    const int8_t* row = p.X + (size_t)m * p.K;
+    int acc = 0;
+    for (int k = lane * 16; k < p.K; k += 512) {
+        const int4 v = *reinterpret_cast<const int4*>(row + k);
+        acc = __dp4a(v.x, 0x01010101, acc);
+        acc = __dp4a(v.y, 0x01010101, acc);
+        acc = __dp4a(v.z, 0x01010101, acc);
+        acc = __dp4a(v.w, 0x01010101, acc);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) p.x_rowsum_w[m] = acc;
+}
+
+// Split-K second pass: out[m][n] = float((part[m][n] >> 2*(n%4)) - rowsum[m]) * (x_scales[m] * w_scale).
 __global__ void __launch_bounds__(256) gemm_finalize_kernel(const GemmParams p) {
     pdl_launch_dependents();
     pdl_wait();
     const size_t total = (size_t)p.M * p.N;
     for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (size_t)gridDim.x * 256) {
         const int m = (int)(i / p.N), n = (int)(i % p.N);
-        const int v = (p.part[i] >> (2 * (n & 3))) - p.part_xsum[m];
+        const int v = (p.part[i] >> (2 * (n & 3))) - p.x_rowsum[m];
         if (p.acc_out) p.acc_out[i] = v;
         if (p.out) p.out[i] = (float)v * (p.x_scales[m] * p.w_scale);
     }
@@ -300,7 +333,8 @@ __global__ void __launch_bounds__(256) gemm_finalize_kernel(const GemmParams p) 
 
 }  // namespace
 
-size_t gemm_scratch_ints(int M, int N) { return (size_t)M * (size_t)N + (size_t)M; }
+// scratch = row sums [M] followed by the split-K partials [M][N]
+size_t gemm_scratch_ints(int M, int N, bool split) { return (size_t)M + (split ? (size_t)M * (size_t)N : 0); }
 
 cudaError_t launch_gemm(const GemmParams& p_in, int sm_count, bool pdl, cudaStream_t st) {
     GemmParams p = p_in;
@@ -317,14 +351,14 @@ cudaError_t launch_gemm(const GemmParams& p_in, int sm_count, bool pdl, cudaStre
     const int steps = p.Kpad / kKStep;
     // split K so that the grid covers the SMs (the weights are the traffic; every CTA streams its share)
     int ksplits = 1;
-    if (p.part) {
+    if (p.scratch && p.split_ok && p.M <= 256) {   // weight-bandwidth-bound regime only; larger batches have enough work per tile
         ksplits = sm_count / (n_tiles * m_tiles);
         if (ksplits > steps / 4) ksplits = steps / 4;
         if (ksplits < 1) ksplits = 1;
     }
     p.ksplits = ksplits;
     GemmSmemLayout L{4, tokens};
-    while (L.stages > 2 && L.bytes() > 200 * 1024) --L.stages;
+    if (L.bytes() > 220 * 1024) return cudaErrorInvalidValue;   // 4 stages are required (kAhead = 2 in flight + 2)
     p.stages = L.stages;
     const size_t smem = (size_t)L.bytes();
     static bool attr_set[64] = {};
@@ -336,19 +370,32 @@ cudaError_t launch_gemm(const GemmParams& p_in, int sm_count, bool pdl, cudaStre
         attr_set[dev] = true;
     }
     cudaError_t e;
-    if (ksplits > 1) {
-        e = cudaMemsetAsync(p.part, 0, gemm_scratch_ints(p.M, p.N) * sizeof(int), st);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    if (!p.x_rowsum) {   // the caller did not supply the row sums: compute them into the scratch
+        if (!p.scratch) return cudaErrorInvalidValue;
+        p.x_rowsum_w = p.scratch;
+        p.x_rowsum = p.scratch;
+        cudaLaunchConfig_t lr = {};
+        lr.gridDim = dim3((unsigned)((p.M + 7) / 8));
+        lr.blockDim = dim3(256);
+        lr.stream = st;
+        lr.attrs = attr;
+        lr.numAttrs = pdl ? 1 : 0;
+        e = cudaLaunchKernelEx(&lr, gemm_rowsum_kernel, p);
         if (e != cudaSuccess) return e;
-        p.part_xsum = p.part + (size_t)p.M * p.N;
+    }
+    if (ksplits > 1) {
+        p.part = p.scratch + p.M;
+        e = cudaMemsetAsync(p.part, 0, (size_t)p.M * p.N * sizeof(int), st);
+        if (e != cudaSuccess) return e;
     }
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3((unsigned)n_tiles, (unsigned)ksplits, (unsigned)m_tiles);
     lc.blockDim = dim3(kGemmThreads);
     lc.dynamicSmemBytes = smem;
     lc.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
     lc.attrs = attr;
     lc.numAttrs = (pdl && ksplits == 1) ? 1 : 0;   // after a memset node keep plain stream order
     e = cudaLaunchKernelEx(&lc, gemm_trit_kernel, p);

@@ -45,6 +45,7 @@ struct ter_b200_handle_t {
     size_t gemm_scratch_cap;    // ints
     int gemm_min_m;             // batches below this go row by row through the GEMV kernel
     int gemm_split_k;           // 0 = never split K
+    int gemm_dbg;
     cudaGraphExec_t graphs[16];
     uint64_t graph_launches[16];   // kernels recorded in each graph
     uint64_t capture_mark;

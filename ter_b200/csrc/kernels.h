@@ -83,14 +83,18 @@ struct GemmParams {
     const float* x_scales;    // [M]
     float* out;               // [M][N] or null
     int32_t* acc_out;         // [M][N] or null (raw int32 dot products)
-    int32_t* part;            // split-K scratch: gemm_scratch_ints(M, N) ints, or null (no split)
-    int32_t* part_xsum;       // set by the launcher
+    const int32_t* x_rowsum;  // [M] sum_k X[m][k], or null: computed into the scratch by a pre-kernel
+    int32_t* scratch;         // gemm_scratch_ints(M, N, split) ints: row sums, then split-K partials
+    int split_ok;             // the scratch has room for the split-K partials
+    int32_t* part;            // set by the launcher
+    int32_t* x_rowsum_w;      // set by the launcher
     float w_scale;
     int M, N, K, Kpad, n_strips;
     int tokens, tmem_cols, ksplits, stages;   // set by the launcher
+    int dbg;                  // timing experiments only: 1 = no activation copy, 2 = no MMA, 4 = no expansion, 8 = no row sums
     int* status;
 };
-size_t gemm_scratch_ints(int M, int N);
+size_t gemm_scratch_ints(int M, int N, bool split);
 cudaError_t launch_gemm(const GemmParams& p, int sm_count, bool pdl, cudaStream_t st);
 
 // ---- install-time re-pack (device side) --------------------------------------

@@ -32,11 +32,14 @@ int run_gemm(ter_b200_handle_t* h, const DevWeight* w, const int8_t* X, const fl
     p.w_scale = w->scale;
     p.M = M; p.N = w->N; p.K = w->K; p.Kpad = w->Kpad; p.n_strips = w->tiles();
     p.status = h->status_dev;
-    if (h->gemm_split_k) {
-        const size_t need = gemm_scratch_ints(M, w->N);
+    p.dbg = h->gemm_dbg;
+    {
+        const bool want_split = h->gemm_split_k && M <= 256;
+        const size_t need = gemm_scratch_ints(M, w->N, want_split);
         if (h->gemm_scratch_cap < need) {
             cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
             cudaStreamIsCapturing(st, &cs);
+            if (cs != cudaStreamCaptureStatusNone && h->gemm_scratch_cap < (size_t)M) return TER_B200_E_STATE;
             if (cs == cudaStreamCaptureStatusNone) {
                 TERB_CUDA(h, cudaDeviceSynchronize());
                 if (h->gemm_scratch) cudaFree(h->gemm_scratch);
@@ -46,10 +49,11 @@ int run_gemm(ter_b200_handle_t* h, const DevWeight* w, const int8_t* X, const fl
                 h->gemm_scratch_cap = need;
             }
         }
-        if (h->gemm_scratch_cap >= need) p.part = h->gemm_scratch;   // else: no split (still exact)
+        p.scratch = h->gemm_scratch;
+        p.split_ok = want_split && h->gemm_scratch_cap >= need;
     }
     TERB_CUDA(h, launch_gemm(p, h->sm_count, h->gemv_cfg.pdl != 0, st));
-    h->launches += 1;
+    h->launches += 2;
     count_gemv(h, w->K, w->N, M);
     return TER_B200_OK;
 }
