@@ -160,6 +160,11 @@ class TerB200:
             raise RuntimeError(f"ter_b200_create({device}) failed")
         self._shapes = {}
 
+    def _ck(self, rc: int, what: str = ""):
+        if rc != 0:
+            cu = self.L.ter_b200_last_cuda_error(self.h) if rc in (E_CUDA, E_ALLOC) else 0
+            raise TerB200Error(rc, what + (f" [cudaError {cu}]" if cu else ""))
+
     # ---- lifecycle
     def close(self):
         if getattr(self, "h", None):
@@ -205,12 +210,12 @@ class TerB200:
         self._shapes[name] = (K, N)
 
     def remove(self, name: str):
-        _check(self.L.ter_b200_remove_weight(self.h, name.encode()))
+        self._ck(self.L.ter_b200_remove_weight(self.h, name.encode()))
         self._shapes.pop(name, None)
 
     def weight_info(self, name: str):
         K, N, s = C.c_int(), C.c_int(), C.c_float()
-        _check(self.L.ter_b200_weight_info(self.h, name.encode(), C.byref(K), C.byref(N), C.byref(s)))
+        self._ck(self.L.ter_b200_weight_info(self.h, name.encode(), C.byref(K), C.byref(N), C.byref(s)))
         return K.value, N.value, s.value
 
     # ---- GEMV / GEMM
@@ -220,7 +225,7 @@ class TerB200:
         K, N = self._shapes[name]
         if out is None:
             out = torch.empty(N, dtype=torch.float32, device=x.device)
-        _check(self.L.ter_b200_gemv(self.h, name.encode(), C.c_void_p(x.data_ptr()), C.c_void_p(x_scale.data_ptr()),
+        self._ck(self.L.ter_b200_gemv(self.h, name.encode(), C.c_void_p(x.data_ptr()), C.c_void_p(x_scale.data_ptr()),
                                     C.c_void_p(out.data_ptr()), _stream_ptr(stream)), f"gemv {name}")
         return out
 
@@ -229,7 +234,7 @@ class TerB200:
         K, N = self._shapes[name]
         if out is None:
             out = torch.empty(N, dtype=torch.int32, device=x.device)
-        _check(self.L.ter_b200_gemv_acc(self.h, name.encode(), C.c_void_p(x.data_ptr()), C.c_void_p(out.data_ptr()),
+        self._ck(self.L.ter_b200_gemv_acc(self.h, name.encode(), C.c_void_p(x.data_ptr()), C.c_void_p(out.data_ptr()),
                                         _stream_ptr(stream)), f"gemv_acc {name}")
         return out
 
@@ -239,7 +244,7 @@ class TerB200:
             outs = [torch.empty(self._shapes[n][1], dtype=torch.float32, device=x.device) for n in names]
         arr_n = (C.c_char_p * len(names))(*[n.encode() for n in names])
         arr_o = (C.c_void_p * len(names))(*[o.data_ptr() for o in outs])
-        _check(self.L.ter_b200_gemv_group(self.h, arr_n, len(names), C.c_void_p(x.data_ptr()),
+        self._ck(self.L.ter_b200_gemv_group(self.h, arr_n, len(names), C.c_void_p(x.data_ptr()),
                                           C.c_void_p(x_scale.data_ptr()), arr_o, _stream_ptr(stream)), "gemv_group")
         return outs
 
@@ -251,7 +256,7 @@ class TerB200:
         arr_n = (C.c_char_p * len(names))(*[n.encode() for n in names])
         arr_o = (C.c_void_p * len(names))(*[o.data_ptr() for o in outs])
         ptr = lambda t: C.c_void_p(t.data_ptr()) if t is not None else None  # noqa: E731
-        _check(self.L.ter_b200_norm_gemv_group(self.h, arr_n, len(names), act, ptr(x), ptr(up), ptr(gamma),
+        self._ck(self.L.ter_b200_norm_gemv_group(self.h, arr_n, len(names), act, ptr(x), ptr(up), ptr(gamma),
                                                float(eps), arr_o, int(accumulate), _stream_ptr(stream)),
                "norm_gemv_group")
         return outs
@@ -260,11 +265,11 @@ class TerB200:
         """x_host int8[K], out_host float32[N]: (pinned) host torch tensors or numpy arrays. Asynchronous."""
         xp = x_host.data_ptr() if hasattr(x_host, "data_ptr") else x_host.ctypes.data
         op = out_host.data_ptr() if hasattr(out_host, "data_ptr") else out_host.ctypes.data
-        _check(self.L.ter_b200_gemv_host(self.h, name.encode(), C.c_void_p(xp), float(x_scale), C.c_void_p(op),
+        self._ck(self.L.ter_b200_gemv_host(self.h, name.encode(), C.c_void_p(xp), float(x_scale), C.c_void_p(op),
                                          _stream_ptr(stream)), f"gemv_host {name}")
 
     def sync(self, stream=None):
-        _check(self.L.ter_b200_sync(self.h, _stream_ptr(stream)))
+        self._ck(self.L.ter_b200_sync(self.h, _stream_ptr(stream)))
 
     def gemm(self, name: str, X, x_scales, out=None, stream=None):
         import torch
@@ -272,7 +277,7 @@ class TerB200:
         M = X.shape[0]
         if out is None:
             out = torch.empty((M, N), dtype=torch.float32, device=X.device)
-        _check(self.L.ter_b200_gemm(self.h, name.encode(), C.c_void_p(X.data_ptr()), C.c_void_p(x_scales.data_ptr()),
+        self._ck(self.L.ter_b200_gemm(self.h, name.encode(), C.c_void_p(X.data_ptr()), C.c_void_p(x_scales.data_ptr()),
                                     M, C.c_void_p(out.data_ptr()), _stream_ptr(stream)), f"gemm {name}")
         return out
 
@@ -282,7 +287,7 @@ class TerB200:
         M = X.shape[0]
         if out is None:
             out = torch.empty((M, N), dtype=torch.int32, device=X.device)
-        _check(self.L.ter_b200_gemm_acc(self.h, name.encode(), C.c_void_p(X.data_ptr()), M,
+        self._ck(self.L.ter_b200_gemm_acc(self.h, name.encode(), C.c_void_p(X.data_ptr()), M,
                                         C.c_void_p(out.data_ptr()), _stream_ptr(stream)), f"gemm_acc {name}")
         return out
 
@@ -299,7 +304,7 @@ class TerB200:
         sc = torch.empty(rows, dtype=torch.float32, device=x.device) if quant else None
         normed = torch.empty((rows, n), dtype=torch.float32, device=x.device) if (want_normed or not quant) else None
         ptr = lambda t: C.c_void_p(t.data_ptr()) if t is not None else None  # noqa: E731
-        _check(self.L.ter_b200_rmsnorm_quant(self.h, ptr(x2), ptr(gamma), n, rows, float(eps), ptr(q), ptr(sc),
+        self._ck(self.L.ter_b200_rmsnorm_quant(self.h, ptr(x2), ptr(gamma), n, rows, float(eps), ptr(q), ptr(sc),
                                              ptr(normed), _stream_ptr(stream)), "rmsnorm_quant")
         return q, sc, normed
 
@@ -309,7 +314,7 @@ class TerB200:
         rows, n = g2.shape
         q = torch.empty((rows, n), dtype=torch.int8, device=gate.device)
         sc = torch.empty(rows, dtype=torch.float32, device=gate.device)
-        _check(self.L.ter_b200_act_quant(self.h, act, C.c_void_p(g2.data_ptr()), C.c_void_p(up.data_ptr()),
+        self._ck(self.L.ter_b200_act_quant(self.h, act, C.c_void_p(g2.data_ptr()), C.c_void_p(up.data_ptr()),
                                          C.c_void_p(gamma.data_ptr()) if gamma is not None else None, n, rows,
                                          float(eps), C.c_void_p(q.data_ptr()), C.c_void_p(sc.data_ptr()),
                                          _stream_ptr(stream)), "act_quant")
@@ -317,7 +322,7 @@ class TerB200:
 
     def rope_kv(self, q, k, v, pos, Nh, Nkv, Hd, Smax, theta, neox, kcache, vcache, stream=None):
         B = pos.shape[0]
-        _check(self.L.ter_b200_rope_kv(self.h, C.c_void_p(q.data_ptr()), C.c_void_p(k.data_ptr()),
+        self._ck(self.L.ter_b200_rope_kv(self.h, C.c_void_p(q.data_ptr()), C.c_void_p(k.data_ptr()),
                                        C.c_void_p(v.data_ptr()), C.c_void_p(pos.data_ptr()), B, Nh, Nkv, Hd, Smax,
                                        float(theta), int(neox), C.c_void_p(kcache.data_ptr()),
                                        C.c_void_p(vcache.data_ptr()), _stream_ptr(stream)), "rope_kv")
@@ -330,7 +335,7 @@ class TerB200:
             scratch = torch.empty(need, dtype=torch.float32, device=q.device)
         if out is None:
             out = torch.empty((B, Nh * Hd), dtype=torch.float32, device=q.device)
-        _check(self.L.ter_b200_attention(self.h, C.c_void_p(q.data_ptr()), C.c_void_p(kcache.data_ptr()),
+        self._ck(self.L.ter_b200_attention(self.h, C.c_void_p(q.data_ptr()), C.c_void_p(kcache.data_ptr()),
                                          C.c_void_p(vcache.data_ptr()), C.c_void_p(pos.data_ptr()), B, Nh, Nkv, Hd,
                                          Smax, C.c_void_p(scratch.data_ptr()), scratch.numel(),
                                          C.c_void_p(out.data_ptr()), _stream_ptr(stream)), "attention")
@@ -343,7 +348,7 @@ class TerB200:
         B = pos.shape[0]
         if out is None:
             out = torch.empty((B, Nh * Hd), dtype=torch.float32, device=q.device)
-        _check(self.L.ter_b200_attention_noalloc(self.h, C.c_void_p(q.data_ptr()), C.c_void_p(kcache.data_ptr()),
+        self._ck(self.L.ter_b200_attention_noalloc(self.h, C.c_void_p(q.data_ptr()), C.c_void_p(kcache.data_ptr()),
                                                  C.c_void_p(vcache.data_ptr()), C.c_void_p(pos.data_ptr()), B, Nh,
                                                  Nkv, Hd, Smax, C.c_void_p(out.data_ptr()), _stream_ptr(stream)),
                "attention_noalloc")
@@ -355,7 +360,7 @@ class TerB200:
         B, H = x2.shape
         V = table.shape[0]
         logits = torch.empty((B, V), dtype=torch.float32, device=x.device)
-        _check(self.L.ter_b200_lm_head_bf16(self.h, C.c_void_p(table.data_ptr()), C.c_void_p(x2.data_ptr()),
+        self._ck(self.L.ter_b200_lm_head_bf16(self.h, C.c_void_p(table.data_ptr()), C.c_void_p(x2.data_ptr()),
                                             C.c_void_p(logits.data_ptr()), V, H, B, _stream_ptr(stream)), "lm_head")
         return logits
 
@@ -365,7 +370,7 @@ class TerB200:
         B, V = l2.shape
         scratch = torch.empty(B * 256, dtype=torch.float32, device=logits.device)
         out = torch.empty(B, dtype=torch.int32, device=logits.device)
-        _check(self.L.ter_b200_argmax(self.h, C.c_void_p(l2.data_ptr()), V, B, C.c_void_p(scratch.data_ptr()),
+        self._ck(self.L.ter_b200_argmax(self.h, C.c_void_p(l2.data_ptr()), V, B, C.c_void_p(scratch.data_ptr()),
                                       C.c_void_p(out.data_ptr()), _stream_ptr(stream)), "argmax")
         return out
 
@@ -374,7 +379,7 @@ class TerB200:
         c = ModelCfg(arch=cfg["arch"], H=cfg["H"], F=cfg["F"], L=cfg["L"], V=cfg["V"], Nh=cfg["Nh"], Nkv=cfg["Nkv"],
                      Hd=cfg["Hd"], Smax=cfg["Smax"], eps=cfg["eps"], rope_theta=cfg["rope_theta"],
                      lm_head_packed=int(cfg.get("lm_head_packed", 0)), max_batch=max_batch)
-        _check(self.L.ter_b200_model_create(self.h, C.byref(c)), "model_create")
+        self._ck(self.L.ter_b200_model_create(self.h, C.byref(c)), "model_create")
         self.model_cfg = dict(cfg, max_batch=max_batch)
         self._batch = 1
 
@@ -392,7 +397,7 @@ class TerB200:
     def model_set_vector(self, layer, which, v):
         import numpy as np
         a = np.ascontiguousarray(v, dtype=np.float32)
-        _check(self.L.ter_b200_model_set_vector(self.h, layer, which, C.c_void_p(a.ctypes.data)), "model_set_vector")
+        self._ck(self.L.ter_b200_model_set_vector(self.h, layer, which, C.c_void_p(a.ctypes.data)), "model_set_vector")
 
     def model_set_embd(self, table_bf16):
         import numpy as np
@@ -405,7 +410,7 @@ class TerB200:
         _check(rc, "model_set_embd")
 
     def model_reset(self, batch=1):
-        _check(self.L.ter_b200_model_reset(self.h, batch), "model_reset")
+        self._ck(self.L.ter_b200_model_reset(self.h, batch), "model_reset")
         self._batch = batch
 
     def decode_step(self, tokens=None, pos=None, want_next=True, stream=None):
@@ -414,7 +419,7 @@ class TerB200:
         t = np.ascontiguousarray(tokens, dtype=np.int32) if tokens is not None else None
         p = np.ascontiguousarray(pos, dtype=np.int32) if pos is not None else None
         nxt = np.empty(B, dtype=np.int32) if want_next else None
-        _check(self.L.ter_b200_decode_step(self.h, C.c_void_p(t.ctypes.data) if t is not None else None,
+        self._ck(self.L.ter_b200_decode_step(self.h, C.c_void_p(t.ctypes.data) if t is not None else None,
                                            C.c_void_p(p.ctypes.data) if p is not None else None,
                                            C.c_void_p(nxt.ctypes.data) if want_next else None,
                                            _stream_ptr(stream)), "decode_step")
@@ -423,13 +428,13 @@ class TerB200:
     def model_logits(self):
         import numpy as np
         out = np.empty((self._batch, self.model_cfg["V"]), dtype=np.float32)
-        _check(self.L.ter_b200_model_logits(self.h, C.c_void_p(out.ctypes.data)), "model_logits")
+        self._ck(self.L.ter_b200_model_logits(self.h, C.c_void_p(out.ctypes.data)), "model_logits")
         return out
 
     def model_hidden(self):
         import numpy as np
         out = np.empty((self._batch, self.model_cfg["H"]), dtype=np.float32)
-        _check(self.L.ter_b200_model_hidden(self.h, C.c_void_p(out.ctypes.data)), "model_hidden")
+        self._ck(self.L.ter_b200_model_hidden(self.h, C.c_void_p(out.ctypes.data)), "model_hidden")
         return out
 
     def generate(self, prompts, n_gen, stream=None):
@@ -440,7 +445,7 @@ class TerB200:
             p = p[None, :]
         B, n_prompt = p.shape
         out = np.empty((B, n_gen), dtype=np.int32)
-        _check(self.L.ter_b200_generate(self.h, C.c_void_p(p.ctypes.data), B, n_prompt, n_gen,
+        self._ck(self.L.ter_b200_generate(self.h, C.c_void_p(p.ctypes.data), B, n_prompt, n_gen,
                                         C.c_void_p(out.ctypes.data), _stream_ptr(stream)), "generate")
         self._batch = B
         return out
@@ -455,7 +460,7 @@ class TerB200:
         s = stream or torch.cuda.Stream()
         gid = C.c_int(-1)
         with torch.cuda.stream(s):
-            _check(self.L.ter_b200_capture_begin(self.h, _stream_ptr(s)), "capture_begin")
+            self._ck(self.L.ter_b200_capture_begin(self.h, _stream_ptr(s)), "capture_begin")
             try:
                 fn()
             finally:
@@ -464,10 +469,10 @@ class TerB200:
         return gid.value
 
     def graph_launch(self, gid: int, stream=None):
-        _check(self.L.ter_b200_graph_launch(self.h, gid, _stream_ptr(stream)), "graph_launch")
+        self._ck(self.L.ter_b200_graph_launch(self.h, gid, _stream_ptr(stream)), "graph_launch")
 
     def graph_destroy(self, gid: int):
-        _check(self.L.ter_b200_graph_destroy(self.h, gid))
+        self._ck(self.L.ter_b200_graph_destroy(self.h, gid))
 
     # ---- counters / status
     def op_counts(self) -> dict:
@@ -485,4 +490,4 @@ class TerB200:
         return self.L.ter_b200_device_status(self.h)
 
     def set_option(self, key: str, value: int):
-        _check(self.L.ter_b200_set_option(self.h, key.encode(), int(value)), f"set_option {key}")
+        self._ck(self.L.ter_b200_set_option(self.h, key.encode(), int(value)), f"set_option {key}")

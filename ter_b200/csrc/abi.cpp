@@ -97,8 +97,7 @@ static int check_name(const char* name) {
 
 static int ensure_host_staging(ter_b200_handle_t* h, size_t x_bytes, size_t out_floats) {
     if (h->hx_cap < x_bytes) {
-        if (h->gemm_scratch) cudaFree(h->gemm_scratch);
-    if (h->hx_dev) cudaFree(h->hx_dev);
+        if (h->hx_dev) cudaFree(h->hx_dev);
         h->hx_dev = nullptr;
         h->hx_cap = 0;
         TERB_CUDA(h, cudaMalloc((void**)&h->hx_dev, x_bytes));

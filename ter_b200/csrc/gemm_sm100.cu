@@ -279,7 +279,10 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_trit_kernel(const __grid_co
                             } else {
                                 const int v = ((int)d[j] >> shift) - tok_sum[c0 + j];
                                 if (p.acc_out) p.acc_out[o] = v;
-                                if (p.out) p.out[o] = (float)v * tok_scale[c0 + j];
+                                if (p.out) {
+                                    const float f = (float)v * tok_scale[c0 + j];
+                                    p.out[o] = p.accumulate ? p.out[o] + f : f;
+                                }
                             }
                         }
                     }
@@ -298,24 +301,29 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_trit_kernel(const __grid_co
 
 // Row sums of the activations: rowsum[m] = sum_k X[m][k] (one warp per row).  They remove the "+1" of
 // the unsigned weight bytes: sum_k x*(t+1) - sum_k x = sum_k x*t.
-__global__ void __launch_bounds__(256) gemm_rowsum_kernel(const GemmParams p) {
+__global__ void __launch_bounds__(256) gemm_prep_kernel(const GemmParams p) {
     pdl_launch_dependents();
     pdl_wait();
-    const int lane = threadIdx.x & 31;
-    const int m = blockIdx.x * 8 + (threadIdx.x >> 5);
-    if (m >= p.M) return;
-    const int8_t* row = p.X + (size_t)m * p.K;
-    int acc = 0;
-    for (int k = lane * 16; k < p.K; k += 512) {
-        const int4 v = *reinterpret_cast<const int4*>(row + k);
-        acc = __dp4a(v.x, 0x01010101, acc);
-        acc = __dp4a(v.y, 0x01010101, acc);
-        acc = __dp4a(v.z, 0x01010101, acc);
-        acc = __dp4a(v.w, 0x01010101, acc);
+    if (p.part) {   // split-K partials start at zero
+        const size_t total = (size_t)p.M * p.N;
+        for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (size_t)gridDim.x * 256) p.part[i] = 0;
     }
+    if (!p.x_rowsum_w) return;
+    const int lane = threadIdx.x & 31;
+    for (int m = blockIdx.x * 8 + (threadIdx.x >> 5); m < p.M; m += gridDim.x * 8) {
+        const int8_t* row = p.X + (size_t)m * p.K;
+        int acc = 0;
+        for (int k = lane * 16; k < p.K; k += 512) {
+            const int4 v = *reinterpret_cast<const int4*>(row + k);
+            acc = __dp4a(v.x, 0x01010101, acc);
+            acc = __dp4a(v.y, 0x01010101, acc);
+            acc = __dp4a(v.z, 0x01010101, acc);
+            acc = __dp4a(v.w, 0x01010101, acc);
+        }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (lane == 0) p.x_rowsum_w[m] = acc;
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0) p.x_rowsum_w[m] = acc;
+    }
 }
 
 // Split-K second pass: out[m][n] = float((part[m][n] >> 2*(n%4)) - rowsum[m]) * (x_scales[m] * w_scale).
@@ -327,7 +335,10 @@ __global__ void __launch_bounds__(256) gemm_finalize_kernel(const GemmParams p) 
         const int m = (int)(i / p.N), n = (int)(i % p.N);
         const int v = (p.part[i] >> (2 * (n & 3))) - p.x_rowsum[m];
         if (p.acc_out) p.acc_out[i] = v;
-        if (p.out) p.out[i] = (float)v * (p.x_scales[m] * p.w_scale);
+        if (p.out) {
+            const float f = (float)v * (p.x_scales[m] * p.w_scale);
+            p.out[i] = p.accumulate ? p.out[i] + f : f;
+        }
     }
 }
 
@@ -373,22 +384,25 @@ cudaError_t launch_gemm(const GemmParams& p_in, int sm_count, bool pdl, cudaStre
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
+    p.part = nullptr;
+    p.x_rowsum_w = nullptr;
+    if (ksplits > 1) p.part = p.scratch + p.M;
     if (!p.x_rowsum) {   // the caller did not supply the row sums: compute them into the scratch
         if (!p.scratch) return cudaErrorInvalidValue;
         p.x_rowsum_w = p.scratch;
         p.x_rowsum = p.scratch;
+    }
+    if (p.part || p.x_rowsum_w) {
         cudaLaunchConfig_t lr = {};
-        lr.gridDim = dim3((unsigned)((p.M + 7) / 8));
+        size_t g = p.part ? ((size_t)p.M * p.N + 1023) / 1024 : (size_t)(p.M + 7) / 8;
+        if (g < (size_t)(p.M + 7) / 8) g = (size_t)(p.M + 7) / 8;
+        if (g > (size_t)sm_count * 8) g = (size_t)sm_count * 8;
+        lr.gridDim = dim3((unsigned)g);
         lr.blockDim = dim3(256);
         lr.stream = st;
         lr.attrs = attr;
         lr.numAttrs = pdl ? 1 : 0;
-        e = cudaLaunchKernelEx(&lr, gemm_rowsum_kernel, p);
-        if (e != cudaSuccess) return e;
-    }
-    if (ksplits > 1) {
-        p.part = p.scratch + p.M;
-        e = cudaMemsetAsync(p.part, 0, (size_t)p.M * p.N * sizeof(int), st);
+        e = cudaLaunchKernelEx(&lr, gemm_prep_kernel, p);
         if (e != cudaSuccess) return e;
     }
     cudaLaunchConfig_t lc = {};
@@ -397,7 +411,7 @@ cudaError_t launch_gemm(const GemmParams& p_in, int sm_count, bool pdl, cudaStre
     lc.dynamicSmemBytes = smem;
     lc.stream = st;
     lc.attrs = attr;
-    lc.numAttrs = (pdl && ksplits == 1) ? 1 : 0;   // after a memset node keep plain stream order
+    lc.numAttrs = pdl ? 1 : 0;   // after a memset node keep plain stream order
     e = cudaLaunchKernelEx(&lc, gemm_trit_kernel, p);
     if (e != cudaSuccess || ksplits == 1) return e;
     cudaLaunchConfig_t lf = {};

@@ -381,7 +381,7 @@ struct LmHeadParams {
     const uint16_t* table;
     const float* x;
     float* logits;
-    int V, H;
+    int V, H, B;
 };
 
 __device__ __forceinline__ uint4 ldg_stream16(const void* ptr) {
@@ -393,36 +393,52 @@ __device__ __forceinline__ uint4 ldg_stream16(const void* ptr) {
 }
 
 // One warp per vocabulary row; lane l takes elements 256*r + 8*l + e (e ascending), fused
-// multiply-adds, then an xor butterfly over the warp.  grid.y = batch row.
+// multiply-adds, then an xor butterfly over the warp.  A CTA serves up to kLmRows batch rows per
+// table row it reads (grid.y = groups of kLmRows batch rows), each with its own accumulator in the
+// same order, so the result per (batch row, vocabulary row) does not depend on the batch size.
+constexpr int kLmRows = 8;
 __global__ void __launch_bounds__(kT) lm_head_bf16_kernel(const LmHeadParams p) {
-    extern __shared__ __align__(16) float xs[];
+    extern __shared__ __align__(16) float xs[];       // [rows][H]
     pdl_launch_dependents();
     pdl_wait();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const float* x = p.x + (size_t)blockIdx.y * p.H;
-    for (int i = tid; i < p.H; i += kT) xs[i] = x[i];
+    const int b0 = blockIdx.y * kLmRows;
+    const int rows = min(kLmRows, p.B - b0);
+    for (int i = tid; i < rows * p.H; i += kT) xs[i] = p.x[(size_t)b0 * p.H + i];
     __syncthreads();
-    float* logits = p.logits + (size_t)blockIdx.y * p.V;
     const int total_warps = gridDim.x * (kT / 32);
     for (int v = blockIdx.x * (kT / 32) + warp; v < p.V; v += total_warps) {
         const uint16_t* row = p.table + (size_t)v * p.H;
-        float acc = 0.0f;
-#pragma unroll 4
+        float acc[kLmRows];
+#pragma unroll
+        for (int r = 0; r < kLmRows; ++r) acc[r] = 0.0f;
+#pragma unroll 2
         for (int base = 8 * lane; base < p.H; base += 256) {
             const uint4 w = ldg_stream16(row + base);
-            const float4 xa = *reinterpret_cast<const float4*>(&xs[base]);
-            const float4 xb = *reinterpret_cast<const float4*>(&xs[base + 4]);
-            acc = fmaf(bf16_bits_to_f32(w.x & 0xffffu), xa.x, acc);
-            acc = fmaf(bf16_bits_to_f32(w.x >> 16), xa.y, acc);
-            acc = fmaf(bf16_bits_to_f32(w.y & 0xffffu), xa.z, acc);
-            acc = fmaf(bf16_bits_to_f32(w.y >> 16), xa.w, acc);
-            acc = fmaf(bf16_bits_to_f32(w.z & 0xffffu), xb.x, acc);
-            acc = fmaf(bf16_bits_to_f32(w.z >> 16), xb.y, acc);
-            acc = fmaf(bf16_bits_to_f32(w.w & 0xffffu), xb.z, acc);
-            acc = fmaf(bf16_bits_to_f32(w.w >> 16), xb.w, acc);
+            float wf[8];
+            wf[0] = bf16_bits_to_f32(w.x & 0xffffu); wf[1] = bf16_bits_to_f32(w.x >> 16);
+            wf[2] = bf16_bits_to_f32(w.y & 0xffffu); wf[3] = bf16_bits_to_f32(w.y >> 16);
+            wf[4] = bf16_bits_to_f32(w.z & 0xffffu); wf[5] = bf16_bits_to_f32(w.z >> 16);
+            wf[6] = bf16_bits_to_f32(w.w & 0xffffu); wf[7] = bf16_bits_to_f32(w.w >> 16);
+#pragma unroll
+            for (int r = 0; r < kLmRows; ++r) {
+                if (r < rows) {
+                    const float4 xa = *reinterpret_cast<const float4*>(&xs[r * p.H + base]);
+                    const float4 xb = *reinterpret_cast<const float4*>(&xs[r * p.H + base + 4]);
+                    float a = acc[r];
+                    a = fmaf(wf[0], xa.x, a); a = fmaf(wf[1], xa.y, a); a = fmaf(wf[2], xa.z, a); a = fmaf(wf[3], xa.w, a);
+                    a = fmaf(wf[4], xb.x, a); a = fmaf(wf[5], xb.y, a); a = fmaf(wf[6], xb.z, a); a = fmaf(wf[7], xb.w, a);
+                    acc[r] = a;
+                }
+            }
         }
-        acc = warp_sum_butterfly(acc);
-        if (lane == 0) logits[v] = acc;
+#pragma unroll
+        for (int r = 0; r < kLmRows; ++r) {
+            if (r < rows) {
+                const float t = warp_sum_butterfly(acc[r]);
+                if (lane == 0) p.logits[(size_t)(b0 + r) * p.V + v] = t;
+            }
+        }
     }
 }
 
@@ -508,16 +524,18 @@ __global__ void inc_kernel(const IncParams p) {
 
 cudaError_t launch_lm_head_bf16(const uint16_t* table, const float* x, float* logits, int V, int H, int B,
                                 int sm_count, bool pdl, cudaStream_t st) {
-    if (H % 8 != 0 || (size_t)H * 4 > 160 * 1024) return cudaErrorInvalidValue;
-    const size_t smem = (size_t)H * sizeof(float);
+    if (H % 8 != 0) return cudaErrorInvalidValue;
+    const int rows = B < kLmRows ? B : kLmRows;
+    const size_t smem = (size_t)rows * H * sizeof(float);
+    if (smem > 200 * 1024) return cudaErrorInvalidValue;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(lm_head_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
-    int gx = sm_count * 4;
+    int gx = sm_count * (smem > 100 * 1024 ? 1 : (smem > 48 * 1024 ? 2 : 4));
     if (gx > (V + 7) / 8) gx = (V + 7) / 8;
-    LmHeadParams p{table, x, logits, V, H};
-    return launch_pdl(lm_head_bf16_kernel, dim3((unsigned)gx, (unsigned)B), dim3(kT), smem, pdl, st, p);
+    LmHeadParams p{table, x, logits, V, H, B};
+    return launch_pdl(lm_head_bf16_kernel, dim3((unsigned)gx, (unsigned)((B + kLmRows - 1) / kLmRows)), dim3(kT), smem, pdl, st, p);
 }
 
 cudaError_t launch_argmax(const float* logits, int V, int B, float* scratch, int* out, bool pdl, cudaStream_t st) {

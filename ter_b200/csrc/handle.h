@@ -90,9 +90,10 @@ inline void count_gemv(ter_b200_handle_t* h, int K, int N, int rows) {
 int build_weight_from_dev(ter_b200_handle_t* h, const void* data_dev, int format, int K, int N, float scale,
                           cudaStream_t st, DevWeight* out);
 void free_weight(DevWeight* w);
+int ensure_gemm_scratch(ter_b200_handle_t* h, int M, int N);
 // Batched GEMM over one weight (tensor cores for M >= gemm_min_m, else GEMV per row).
 int run_gemm(ter_b200_handle_t* h, const DevWeight* w, const int8_t* X, const float* x_scales, int M, float* out,
-             int32_t* acc, cudaStream_t st);
+             int32_t* acc, cudaStream_t st, bool accumulate = false);
 // One launch over up to kGemvMaxGroup weights sharing x (abi.cpp).
 int run_gemv(ter_b200_handle_t* h, const DevWeight* const* ws, int n, const int8_t* x_dev, const float* x_scale_dev,
              float x_scale_imm, float* const* outs, int32_t* const* accs, bool accumulate, cudaStream_t st,

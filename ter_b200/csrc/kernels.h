@@ -86,6 +86,7 @@ struct GemmParams {
     const int32_t* x_rowsum;  // [M] sum_k X[m][k], or null: computed into the scratch by a pre-kernel
     int32_t* scratch;         // gemm_scratch_ints(M, N, split) ints: row sums, then split-K partials
     int split_ok;             // the scratch has room for the split-K partials
+    int accumulate;           // out[m][n] = out[m][n] + value (residual add)
     int32_t* part;            // set by the launcher
     int32_t* x_rowsum_w;      // set by the launcher
     float w_scale;

@@ -63,6 +63,13 @@ cudaError_t dalloc(T** p, size_t n) { return cudaMalloc((void**)p, n * sizeof(T)
 // quantiser runs inside the GEMV launch (fp32 rows in, no int8 round trip through memory).
 int mm(ter_b200_handle_t* h, const DevWeight* const* ws, int n, const int8_t* xq, int K, const float* xs,
        float* const* outs, bool accumulate, int B, cudaStream_t st, const NormQuantParams* nq = nullptr) {
+    if (!nq && B >= h->gemm_min_m) {   // token batch: one tensor-core GEMM per matrix over all rows
+        for (int i = 0; i < n; ++i) {
+            int rc = run_gemm(h, ws[i], xq, xs, B, outs[i], nullptr, st, accumulate);
+            if (rc) return rc;
+        }
+        return TER_B200_OK;
+    }
     for (int b = 0; b < B; ++b) {
         float* o[kGemvMaxGroup];
         for (int i = 0; i < n; ++i) o[i] = outs[i] + (size_t)b * ws[i]->N;
@@ -73,7 +80,8 @@ int mm(ter_b200_handle_t* h, const DevWeight* const* ws, int n, const int8_t* xq
     return TER_B200_OK;
 }
 
-bool can_fuse(const ter_b200_handle_t* h, const DevWeight* const* ws, int n) {
+bool can_fuse(const ter_b200_handle_t* h, const DevWeight* const* ws, int n, int B) {
+    if (B >= h->gemm_min_m) return false;   // batches go through the GEMM, which takes quantised rows
     int tiles = 0;
     for (int i = 0; i < n; ++i) tiles += ws[i]->tiles();
     return h->gemv_cfg.fuse_quant && h->gemv_cfg.split_max_strips > 0 && tiles <= h->gemv_cfg.split_max_strips;
@@ -103,7 +111,7 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
             const DevWeight* ws[3] = {&W[TER_B200_WQ], &W[TER_B200_WK], &W[TER_B200_WV]};
             float* outs[3] = {m->q, m->k, m->v};
             NormQuantParams nq{m->hidden, nullptr, vec[TER_B200_ATTN_NORM], m->xq, m->xs, nullptr, H, B, PRE_NONE, c.eps};
-            const bool fz = can_fuse(h, ws, 3);
+            const bool fz = can_fuse(h, ws, 3, B);
             if (!fz) CK(launch_norm_quant(nq, pdl, st));
             int rc = mm(h, ws, 3, m->xq, H, m->xs, outs, false, B, st, fz ? &nq : nullptr);
             if (rc) return rc;
@@ -121,7 +129,7 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
             float* outs[1] = {m->hidden};
             NormQuantParams aq{m->att, nullptr, bitnet ? vec[TER_B200_ATTN_SUB_NORM] : nullptr, m->xq, m->xs, nullptr,
                                Hq, B, PRE_NONE, c.eps};
-            const bool fz = can_fuse(h, ws, 1);
+            const bool fz = can_fuse(h, ws, 1, B);
             if (!fz) CK(launch_norm_quant(aq, pdl, st));
             int rc = mm(h, ws, 1, m->xq, Hq, m->xs, outs, true, B, st, fz ? &aq : nullptr);   // hidden += Wo(attn)
             if (rc) return rc;
@@ -132,9 +140,9 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
             const DevWeight* ws[2] = {&W[TER_B200_WGATE], &W[TER_B200_WUP]};
             float* outs[2] = {m->gate, m->up};
             NormQuantParams fq{m->hidden, nullptr, vec[TER_B200_FFN_NORM], m->xq, m->xs, nullptr, H, B, PRE_NONE, c.eps};
-            const bool fz = can_fuse(h, ws, 2);
+            const bool fz = can_fuse(h, ws, 2, B);
             const DevWeight* wd[1] = {&W[TER_B200_WDOWN]};
-            const bool pair = fz && can_fuse(h, wd, 1) && (((ws[0]->Kpad >> 7) + 7) / 8) <= 4;
+            const bool pair = fz && can_fuse(h, wd, 1, B) && (((ws[0]->Kpad >> 7) + 7) / 8) <= 4;
             const int act = bitnet ? PRE_RELU2_MUL : PRE_SILU_MUL;
             if (!fz) CK(launch_norm_quant(fq, pdl, st));
             if (pair) {
@@ -150,7 +158,7 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
             float* outd[1] = {m->hidden};
             NormQuantParams gq{m->gate, pair ? nullptr : m->up, bitnet ? vec[TER_B200_FFN_SUB_NORM] : nullptr, m->xq,
                                m->xs, nullptr, F, B, pair ? PRE_NONE : act, c.eps};
-            const bool fd = can_fuse(h, wd, 1);
+            const bool fd = can_fuse(h, wd, 1, B);
             if (!fd) CK(launch_norm_quant(gq, pdl, st));
             int rc = mm(h, wd, 1, m->xq, F, m->xs, outd, true, B, st, fd ? &gq : nullptr);    // hidden += Wdown(ffn)
             if (rc) return rc;
@@ -470,6 +478,13 @@ int ter_b200_generate(ter_b200_handle_t* h, const int32_t* prompts, int batch, i
     const int ctl[2] = {n_prompt, steps};
     TERB_CUDA(h, cudaMemcpy(m->ctl, ctl, sizeof ctl, cudaMemcpyHostToDevice));
 
+    if (batch >= h->gemm_min_m) {   // the GEMM scratch cannot grow while the step is being captured
+        int widest = m->c.F > m->c.H ? m->c.F : m->c.H;
+        if (m->c.Nh * m->c.Hd > widest) widest = m->c.Nh * m->c.Hd;
+        if (m->c.lm_head_packed && m->c.V > widest) widest = m->c.V;
+        rc = ensure_gemm_scratch(h, batch, widest);
+        if (rc) return rc;
+    }
     if (!m->graph || m->graph_batch != batch || !m->graph_forced) {
         drop_graph(m);
         const uint64_t mark = h->launches;

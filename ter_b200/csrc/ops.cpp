@@ -1,13 +1,29 @@
 // ter_b200_call: the named-operator entry point (ter_k4_call, src/k4/ter_k4.cpp:47-59),
 // plus the batched GEMM entry points.
+#include <stdio.h>
+
 #include "handle.h"
 
 using namespace terb;
 
 namespace terb {
 
+// Grows the handle's GEMM scratch (row sums + split-K partials) for M tokens x N columns.  Not for use
+// while a stream is capturing.
+int ensure_gemm_scratch(ter_b200_handle_t* h, int M, int N) {
+    const size_t need = gemm_scratch_ints(M, N, h->gemm_split_k && M <= 256);
+    if (h->gemm_scratch_cap >= need) return TER_B200_OK;
+    TERB_CUDA(h, cudaDeviceSynchronize());
+    if (h->gemm_scratch) cudaFree(h->gemm_scratch);
+    h->gemm_scratch = nullptr;
+    h->gemm_scratch_cap = 0;
+    TERB_CUDA(h, cudaMalloc((void**)&h->gemm_scratch, need * sizeof(int)));
+    h->gemm_scratch_cap = need;
+    return TER_B200_OK;
+}
+
 int run_gemm(ter_b200_handle_t* h, const DevWeight* w, const int8_t* X, const float* x_scales, int M, float* out,
-             int32_t* acc, cudaStream_t st) {
+             int32_t* acc, cudaStream_t st, bool accumulate) {
     if (((uintptr_t)X & 15u) != 0) return TER_B200_E_SHAPE;
     if (M < h->gemm_min_m) {
         // small batches: one GEMV launch per row (exact; the weights are re-read M times)
@@ -16,7 +32,7 @@ int run_gemm(ter_b200_handle_t* h, const DevWeight* w, const int8_t* X, const fl
             float* o[1] = {out ? out + (size_t)m * w->N : nullptr};
             int32_t* a[1] = {acc ? acc + (size_t)m * w->N : nullptr};
             int rc = run_gemv(h, ws, 1, X + (size_t)m * w->K, x_scales ? x_scales + m : nullptr, 1.0f, out ? o : nullptr,
-                              acc ? a : nullptr, false, st);
+                              acc ? a : nullptr, accumulate, st);
             if (rc) return rc;
         }
         return TER_B200_OK;
@@ -33,6 +49,7 @@ int run_gemm(ter_b200_handle_t* h, const DevWeight* w, const int8_t* X, const fl
     p.M = M; p.N = w->N; p.K = w->K; p.Kpad = w->Kpad; p.n_strips = w->tiles();
     p.status = h->status_dev;
     p.dbg = h->gemm_dbg;
+    p.accumulate = accumulate ? 1 : 0;
     {
         const bool want_split = h->gemm_split_k && M <= 256;
         const size_t need = gemm_scratch_ints(M, w->N, want_split);
@@ -41,12 +58,8 @@ int run_gemm(ter_b200_handle_t* h, const DevWeight* w, const int8_t* X, const fl
             cudaStreamIsCapturing(st, &cs);
             if (cs != cudaStreamCaptureStatusNone && h->gemm_scratch_cap < (size_t)M) return TER_B200_E_STATE;
             if (cs == cudaStreamCaptureStatusNone) {
-                TERB_CUDA(h, cudaDeviceSynchronize());
-                if (h->gemm_scratch) cudaFree(h->gemm_scratch);
-                h->gemm_scratch = nullptr;
-                h->gemm_scratch_cap = 0;
-                TERB_CUDA(h, cudaMalloc((void**)&h->gemm_scratch, need * sizeof(int)));
-                h->gemm_scratch_cap = need;
+                int rc = ensure_gemm_scratch(h, M, w->N);
+                if (rc) return rc;
             }
         }
         p.scratch = h->gemm_scratch;

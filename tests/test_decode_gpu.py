@@ -69,6 +69,24 @@ def test_batch_sequences_are_independent(tb):
     assert e.value.code == api.E_SHAPE
 
 
+@pytest.mark.parametrize("cfg,seed", [(SMALL_LLAMA, 41), (SMALL_BITNET, 42), (SMALL_PACKED_HEAD, 43)])
+def test_token_batch_through_tensor_core_gemm(tb, cfg, seed):
+    """Batches of at least 4 sequences take the tcgen05 GEMM for every projection; each sequence
+    must still reproduce its own single-sequence tokens and logits exactly."""
+    B = 9
+    modelutil.build_gpu(tb, cfg, seed, max_batch=B)
+    om = modelutil.build_oracle(cfg, seed)
+    rng = np.random.default_rng(seed)
+    prompts = rng.integers(0, cfg["V"], size=(B, 7)).astype(np.int32)
+    out = tb.generate(prompts, 6)
+    lg = tb.model_logits()
+    for b in range(B):
+        want, wl = modelutil.oracle_generate(om, prompts[b], 6, want_logits=True)
+        assert out[b].tolist() == want.tolist(), b
+        assert np.array_equal(lg[b].view(np.uint32), wl[-1].view(np.uint32)), b
+    assert tb.device_status() == 0
+
+
 def test_reference_numpy_forward_tokens_on_gpu(tb, golden_dir):
     """Greedy tokens printed by the reference's own tools/llama_pyfwd.py / bitnet_pyfwd.py."""
     import make_pyfwd_golden as mk
