@@ -274,6 +274,21 @@ int ter_b200_generate(ter_b200_handle_t* h, const int32_t* prompts, int batch, i
 /* Milliseconds the device spent in the steps of the latest ter_b200_generate call (CUDA events). */
 float ter_b200_last_generate_ms(const ter_b200_handle_t* h);
 
+/* ---- tensor parallelism (no counterpart in the reference, which is single-GPU) -------------
+ * One process per GPU, one handle per process.  Rank 0 creates a 128-byte id and hands it to the
+ * other ranks by any host channel; every rank then calls ter_b200_comm_init BEFORE
+ * ter_b200_model_create.  With a communicator of size G the model keeps columns
+ * [N*r/G, N*(r+1)/G) of every projection (output-dimension sharding: each output column is an
+ * independent exact dot product), the vocabulary rows [V*r/G, V*(r+1)/G) of the lm_head, and
+ * all-gathers the fp32 output slices over NCCL inside the captured step, so every rank holds the
+ * same bits as a single GPU would and greedy tokens are identical at every G.  Requirements:
+ * N/G a multiple of 16 for every projection, matrices given in TER_B200_FMT_V11. */
+int ter_b200_comm_unique_id(uint8_t* id128);
+int ter_b200_comm_init(ter_b200_handle_t* h, const uint8_t* id128, int rank, int size);
+void ter_b200_comm_destroy(ter_b200_handle_t* h);
+int ter_b200_comm_rank(const ter_b200_handle_t* h);
+int ter_b200_comm_size(const ter_b200_handle_t* h);
+
 /* ---- CUDA graphs ------------------------------------------------------------
  * Record every launch made through this handle on `stream` between begin and end into a
  * CUDA graph and replay it with one call, as the reference's decode loop does

@@ -90,6 +90,11 @@ SIGNATURES = {
     "ter_b200_model_hidden": (_I, [_VP, _VP]),
     "ter_b200_generate": (_I, [_VP, _VP, _I, _I, _I, _VP, _VP]),
     "ter_b200_last_generate_ms": (_F, [_VP]),
+    "ter_b200_comm_unique_id": (_I, [_VP]),
+    "ter_b200_comm_init": (_I, [_VP, _VP, _I, _I]),
+    "ter_b200_comm_destroy": (None, [_VP]),
+    "ter_b200_comm_rank": (_I, [_VP]),
+    "ter_b200_comm_size": (_I, [_VP]),
     "ter_b200_capture_begin": (_I, [_VP, _VP]),
     "ter_b200_capture_end": (_I, [_VP, _VP, C.POINTER(_I)]),
     "ter_b200_graph_launch": (_I, [_VP, _I, _VP]),
@@ -373,6 +378,21 @@ class TerB200:
         self._ck(self.L.ter_b200_argmax(self.h, C.c_void_p(l2.data_ptr()), V, B, C.c_void_p(scratch.data_ptr()),
                                       C.c_void_p(out.data_ptr()), _stream_ptr(stream)), "argmax")
         return out
+
+    # ---- tensor parallelism
+    def comm_init_from_torch(self):
+        """Builds the library's NCCL communicator over the ranks of the default torch.distributed group
+        (the id travels through torch's own broadcast; no data path goes through torch)."""
+        import torch
+        import torch.distributed as dist
+        rank, world = dist.get_rank(), dist.get_world_size()
+        buf = (C.c_uint8 * 128)()
+        if rank == 0:
+            _check(self.L.ter_b200_comm_unique_id(buf), "comm_unique_id")
+        t = torch.tensor(list(bytes(buf)), dtype=torch.uint8, device=f"cuda:{self.device}" if dist.get_backend() == "nccl" else "cpu")
+        dist.broadcast(t, 0)
+        raw = bytes(t.cpu().tolist())
+        self._ck(self.L.ter_b200_comm_init(self.h, raw, rank, world), "comm_init")
 
     # ---- decode forward
     def model_create(self, cfg: dict, max_batch: int = 1):

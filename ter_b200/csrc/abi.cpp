@@ -208,12 +208,14 @@ ter_b200_handle_t* ter_b200_create(int device) {
 }
 
 void ter_b200_model_free(ter_b200_handle_t* h);   // model.cpp
+void ter_b200_comm_destroy(ter_b200_handle_t* h); // comm.cpp
 
 void ter_b200_destroy(ter_b200_handle_t* h) {
     if (!h) return;
     cudaSetDevice(h->device);
     if (h->stream) cudaStreamSynchronize(h->stream);
     ter_b200_model_free(h);
+    ter_b200_comm_destroy(h);
     for (int i = 0; i < 16; ++i)
         if (h->graphs[i]) cudaGraphExecDestroy(h->graphs[i]);
     for (int i = 0; i < TER_B200_MAX_SLOTS; ++i)

@@ -16,6 +16,7 @@ struct TerbSlot {
 };
 
 struct TerbModel;   // decode-forward state (model.cpp)
+namespace terb { struct Comm; }
 
 struct RopeTable {
     float* data = nullptr;   // device [n_pos][head_dim/2][2]
@@ -41,6 +42,7 @@ struct ter_b200_handle_t {
     float* hscale_dev;
     TerbModel* model;
     RopeTable rope[4];
+    terb::Comm* comm;           // tensor-parallel communicator (comm.cpp), or null
     int32_t* gemm_scratch;      // split-K partials of the tensor-core GEMM
     size_t gemm_scratch_cap;    // ints
     int gemm_min_m;             // batches below this go row by row through the GEMV kernel
@@ -90,6 +92,11 @@ inline void count_gemv(ter_b200_handle_t* h, int K, int N, int rows) {
 int build_weight_from_dev(ter_b200_handle_t* h, const void* data_dev, int format, int K, int N, float scale,
                           cudaStream_t st, DevWeight* out);
 void free_weight(DevWeight* w);
+int comm_rank(const ter_b200_handle_t* h);
+int comm_size(const ter_b200_handle_t* h);
+int comm_all_gather_bytes(ter_b200_handle_t* h, void* buf, size_t bytes_per_rank, cudaStream_t st);
+int comm_group_start(ter_b200_handle_t* h);
+int comm_group_end(ter_b200_handle_t* h);
 int ensure_gemm_scratch(ter_b200_handle_t* h, int M, int N);
 // Batched GEMM over one weight (tensor cores for M >= gemm_min_m, else GEMV per row).
 int run_gemm(ter_b200_handle_t* h, const DevWeight* w, const int8_t* X, const float* x_scales, int M, float* out,

@@ -101,6 +101,15 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
     const bool pdl = h->gemv_cfg.pdl != 0;
     const bool bitnet = c.arch == TER_B200_ARCH_BITNET;
     const size_t layer_cache = (size_t)c.max_batch * c.Nkv * (size_t)c.Smax * c.Hd;
+    // Tensor parallelism (batch 1): this rank computes columns [N*R/G, N*(R+1)/G) of every projection into
+    // its slice of the full-size buffer; an in-place all-gather then gives every rank the whole vector.
+    const int G = comm_size(h), R = comm_rank(h);
+    const int Hkv = c.Nkv * c.Hd;
+    auto off = [&](int full_n) { return (size_t)(full_n / G) * (size_t)R; };
+    auto ag = [&](float* buf, int full_n) -> int {
+        return G > 1 ? comm_all_gather_bytes(h, buf, (size_t)(full_n / G) * sizeof(float), st) : TER_B200_OK;
+    };
+#define AG(buf, n) do { int rc__ = ag((buf), (n)); if (rc__) return rc__; } while (0)
 
     CK(launch_embed(m->embd, m->tokens, m->hidden, H, B, c.V, pdl, st));
     for (int L = 0; L < c.L; ++L) {
@@ -109,12 +118,17 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
         // ---- attention block
         {
             const DevWeight* ws[3] = {&W[TER_B200_WQ], &W[TER_B200_WK], &W[TER_B200_WV]};
-            float* outs[3] = {m->q, m->k, m->v};
+            float* outs[3] = {m->q + off(Hq), m->k + off(Hkv), m->v + off(Hkv)};
             NormQuantParams nq{m->hidden, nullptr, vec[TER_B200_ATTN_NORM], m->xq, m->xs, nullptr, H, B, PRE_NONE, c.eps};
             const bool fz = can_fuse(h, ws, 3, B);
             if (!fz) CK(launch_norm_quant(nq, pdl, st));
             int rc = mm(h, ws, 3, m->xq, H, m->xs, outs, false, B, st, fz ? &nq : nullptr);
             if (rc) return rc;
+            if (G > 1) {
+                if ((rc = comm_group_start(h))) return rc;
+                AG(m->q, Hq); AG(m->k, Hkv); AG(m->v, Hkv);
+                if ((rc = comm_group_end(h))) return rc;
+            }
         }
         // rotary, KV append and attention in one launch (+ the ordered merge of the chunks)
         uint16_t* kc = m->kcache + L * layer_cache;
@@ -126,19 +140,20 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
         h->launches += 1;
         {
             const DevWeight* ws[1] = {&W[TER_B200_WO]};
-            float* outs[1] = {m->hidden};
+            float* outs[1] = {m->hidden + off(H)};
             NormQuantParams aq{m->att, nullptr, bitnet ? vec[TER_B200_ATTN_SUB_NORM] : nullptr, m->xq, m->xs, nullptr,
                                Hq, B, PRE_NONE, c.eps};
             const bool fz = can_fuse(h, ws, 1, B);
             if (!fz) CK(launch_norm_quant(aq, pdl, st));
             int rc = mm(h, ws, 1, m->xq, Hq, m->xs, outs, true, B, st, fz ? &aq : nullptr);   // hidden += Wo(attn)
             if (rc) return rc;
+            AG(m->hidden, H);
         }
         // ---- FFN block: gate and up in one launch whose epilogue applies the gated activation, then
         // the down projection whose prologue normalises (BitNet sub-norm) and quantises it.
         {
             const DevWeight* ws[2] = {&W[TER_B200_WGATE], &W[TER_B200_WUP]};
-            float* outs[2] = {m->gate, m->up};
+            float* outs[2] = {m->gate + off(F), m->up + off(F)};
             NormQuantParams fq{m->hidden, nullptr, vec[TER_B200_FFN_NORM], m->xq, m->xs, nullptr, H, B, PRE_NONE, c.eps};
             const bool fz = can_fuse(h, ws, 2, B);
             const DevWeight* wd[1] = {&W[TER_B200_WDOWN]};
@@ -148,20 +163,23 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
             if (pair) {
                 for (int b = 0; b < B; ++b) {
                     int rc = run_gemv(h, ws, 2, nullptr, nullptr, 1.0f, outs, nullptr, false, st, &fq, b, act,
-                                      m->gate + (size_t)b * F);
+                                      m->gate + (size_t)b * F + off(F));
                     if (rc) return rc;
                 }
             } else {
                 int rc = mm(h, ws, 2, m->xq, H, m->xs, outs, false, B, st, fz ? &fq : nullptr);
                 if (rc) return rc;
             }
-            float* outd[1] = {m->hidden};
+            AG(m->gate, F);
+            if (!pair) AG(m->up, F);
+            float* outd[1] = {m->hidden + off(H)};
             NormQuantParams gq{m->gate, pair ? nullptr : m->up, bitnet ? vec[TER_B200_FFN_SUB_NORM] : nullptr, m->xq,
                                m->xs, nullptr, F, B, pair ? PRE_NONE : act, c.eps};
             const bool fd = can_fuse(h, wd, 1, B);
             if (!fd) CK(launch_norm_quant(gq, pdl, st));
             int rc = mm(h, wd, 1, m->xq, F, m->xs, outd, true, B, st, fd ? &gq : nullptr);    // hidden += Wdown(ffn)
             if (rc) return rc;
+            AG(m->hidden, H);
         }
     }
     if (c.lm_head_packed) {
@@ -169,13 +187,15 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
         NormQuantParams oq{m->hidden, nullptr, m->out_norm, m->xq, m->xs, nullptr, H, B, PRE_NONE, c.eps};
         CK(launch_norm_quant(oq, pdl, st));
         const DevWeight* ws[1] = {&m->lm_head};
-        float* outs[1] = {m->logits};
+        float* outs[1] = {m->logits + off(c.V)};
         int rc = mm(h, ws, 1, m->xq, H, m->xs, outs, false, B, st);
         if (rc) return rc;
+        AG(m->logits, c.V);
     } else {
         NormQuantParams on{m->hidden, nullptr, m->out_norm, nullptr, nullptr, m->xnorm, H, B, PRE_NONE, c.eps};
         CK(launch_norm_quant(on, pdl, st));
-        CK(launch_lm_head_bf16(m->embd, m->xnorm, m->logits, c.V, H, B, h->sm_count, pdl, st));
+        CK(launch_lm_head_bf16(m->embd + off(c.V) * H, m->xnorm, m->logits + off(c.V), c.V / G, H, B, h->sm_count, pdl, st));
+        AG(m->logits, c.V);
         const uint64_t n = (uint64_t)((H + 26) / 27) * (uint64_t)c.V * (uint64_t)B;
         h->counts.tvmac += n;
         h->counts.total_ops += n;
@@ -243,6 +263,15 @@ int ter_b200_model_create(ter_b200_handle_t* h, const ter_b200_model_cfg_t* cfg)
     if ((c.Hd != 64 && c.Hd != 128) || c.Nh % c.Nkv != 0 || c.Nh / c.Nkv > 8) return TER_B200_E_SHAPE;
     if (c.H % 16 || c.F % 16 || (c.Nh * c.Hd) % 16 || c.H % 8) return TER_B200_E_SHAPE;
     if (c.arch != TER_B200_ARCH_LLAMA && c.arch != TER_B200_ARCH_BITNET) return TER_B200_E_SHAPE;
+    {
+        const int G = comm_size(h);
+        if (G > 1) {   // every sharded width must split into whole 16-column strips per rank
+            const int widths[5] = {c.H, c.F, c.Nh * c.Hd, c.Nkv * c.Hd, c.V};
+            for (int w : widths)
+                if (w % (16 * G) != 0) return TER_B200_E_SHAPE;
+            if (c.max_batch != 1) return TER_B200_E_SHAPE;   // tensor parallelism serves one sequence; batches are sharded by sequence
+        }
+    }
     TERB_CUDA(h, cudaSetDevice(h->device));
     ter_b200_model_free(h);
     TerbModel* m = new (std::nothrow) TerbModel();
@@ -305,6 +334,16 @@ static int set_matrix_common(ter_b200_handle_t* h, int layer, int which, const v
     }
     if (format < 0 || format > TER_B200_FMT_I32) return TER_B200_E_SHAPE;
     if (format != TER_B200_FMT_I32 && N % 4 != 0) return TER_B200_E_SHAPE;
+    {
+        // tensor parallelism: keep this rank's column range.  In the v11 layout byte-column jb is a run of
+        // K bytes, so columns [N*R/G, N*(R+1)/G) are one contiguous byte range of the caller's matrix.
+        const int G = comm_size(h), R = comm_rank(h);
+        if (G > 1) {
+            if (format != TER_B200_FMT_V11 || N % (16 * G) != 0) return TER_B200_E_SHAPE;
+            data = (const uint8_t*)data + (size_t)(N / G) * R / 4 * (size_t)K;
+            N = N / G;
+        }
+    }
     TERB_CUDA(h, cudaSetDevice(h->device));
     drop_graph(m);
     void* tmp = nullptr;
