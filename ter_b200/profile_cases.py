@@ -1,0 +1,92 @@
+"""Small, self-contained workloads for profiling one kernel at a time:
+
+    python -m ter_b200.profile_cases gemv_stream      # 2048 x 513024 GEMV (263 MB of trits), 4 launches
+    python -m ter_b200.profile_cases gemm             # BitNet gate 2560 x 6912 GEMM at M = 16, 256, 1024
+    python -m ter_b200.profile_cases decode llama     # three decode steps at position ~300 (or: bitnet)
+
+Each holds at most a few GB on the device and finishes in seconds, so an `ncu` capture of it ends by itself.
+"""
+from __future__ import annotations
+
+import sys
+
+import numpy as np
+
+
+def build_random_model(tb, cfg, dev, max_batch=1, seed=1):
+    """Random-init ternarised model generated on the device (weights never visit the host)."""
+    import torch
+    from . import FMT_V11, synth
+    tb.model_create(cfg, max_batch=max_batch)
+    g = torch.Generator(device=dev)
+    g.manual_seed(seed)
+    emb = (torch.randn((cfg["V"], cfg["H"]), generator=g, device=dev) * 0.02).to(torch.bfloat16)
+    tb.model_set_embd(emb.view(torch.int16))
+    tb.model_set_vector(-1, 0, np.ones(cfg["H"], np.float32))
+    shapes = synth.model_shapes(cfg)
+    for L in range(cfg["L"]):
+        for wi, nm in enumerate(synth.MAT_ORDER):
+            K, N = shapes[nm]
+            tb.model_set_matrix(L, wi, synth.packed_v11_cuda(K, N, seed * 1000 + L * 7 + wi, dev), FMT_V11, 0.02)
+        for vi in range(4 if cfg["arch"] == 1 else 2):
+            n = cfg["F"] if vi == 3 else cfg["H"]
+            tb.model_set_vector(L, vi, np.ones(n, np.float32))
+
+
+def gemv_stream():
+    import torch
+    from . import FMT_V11, TerB200, synth
+    tb = TerB200(0)
+    dev = torch.device("cuda:0")
+    K, N = 2048, 128256 * 4
+    tb.install("big", synth.packed_v11_cuda(K, N, 1, dev), FMT_V11, K, N, 0.03)
+    x, xs = synth.activation(K, 4)
+    xd = torch.from_numpy(x).cuda()
+    sd = torch.tensor([xs], device=dev)
+    out = torch.empty(N, device=dev)
+    for _ in range(3):
+        tb.gemv("big", xd, sd, out)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    tb.gemv("big", xd, sd, out)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    print(f"gemv {K}x{N}: {ms * 1e3:.1f} us  {K * N // 4 / ms / 1e6:.0f} GB/s  status {tb.device_status()}")
+
+
+def gemm():
+    import torch
+    from . import FMT_V11, TerB200, synth
+    tb = TerB200(0)
+    dev = torch.device("cuda:0")
+    K, N = synth.BITNET_2B_SHAPES["gate"]
+    tb.install("gate", synth.packed_v11_cuda(K, N, 3, dev), FMT_V11, K, N, 0.02)
+    for M in (16, 256, 1024):
+        X = torch.randint(-127, 128, (M, K), dtype=torch.int8, device=dev)
+        xs = torch.rand(M, device=dev) * 0.05
+        out = torch.empty((M, N), device=dev)
+        for _ in range(2):
+            tb.gemm("gate", X, xs, out)
+        torch.cuda.synchronize()
+    print("gemm ok, status", tb.device_status())
+
+
+def decode(which="llama"):
+    import torch
+    from . import TerB200, synth
+    base, smax, pos0 = (synth.LLAMA_1B_CFG, 512, 300) if which == "llama" else (synth.BITNET_2B_CFG, 2304, 2100)
+    tb = TerB200(0)
+    build_random_model(tb, dict(base, Smax=smax), torch.device("cuda:0"))
+    tb.model_reset(1)
+    tok = 5
+    for i in range(3):
+        tok = int(tb.decode_step([tok], [pos0 + i])[0])
+    torch.cuda.synchronize()
+    print("decode ok", which, tok, tb.device_status())
+
+
+if __name__ == "__main__":
+    case = sys.argv[1] if len(sys.argv) > 1 else "gemv_stream"
+    {"gemv_stream": gemv_stream, "gemm": gemm, "decode": lambda: decode(*sys.argv[2:3])}[case]()
