@@ -193,6 +193,7 @@ ter_b200_handle_t* ter_b200_create(int device) {
     h->device = device;
     h->gemv_cfg = GemvLaunchCfg();
     h->gemm_min_m = 4;
+    h->attn_inline_merge = 1;
     h->gemm_split_k = 1;
     int sms = 0;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) sms = 148;
@@ -484,6 +485,8 @@ int ter_b200_set_option(ter_b200_handle_t* h, const char* key, int value) {
     } else if (strcmp(key, "gemm_min_m") == 0) {
         if (value < 1) return TER_B200_E_SHAPE;
         h->gemm_min_m = value;
+    } else if (strcmp(key, "attn_inline_merge") == 0) {
+        h->attn_inline_merge = value ? 1 : 0;
     } else if (strcmp(key, "gemm_dbg") == 0) {
         h->gemm_dbg = value;
     } else if (strcmp(key, "gemm_split_k") == 0) {
@@ -495,6 +498,7 @@ int ter_b200_set_option(ter_b200_handle_t* h, const char* key, int value) {
     } else {
         return TER_B200_E_UNKNOWN;
     }
+    model_invalidate_graph(h);
     return TER_B200_OK;
 }
 

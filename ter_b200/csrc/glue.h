@@ -54,6 +54,8 @@ struct AttnParams {
     uint16_t* vcache_w;
     int neox;
     int* status;             // device status word for bounded waits (may be null)
+    int* counters;           // [B][Nkv] arrival counters, zero between steps: the last CTA of a KV head merges
+                             // the chunks itself (no second kernel); null = merge in attn_combine_kernel
 };
 cudaError_t launch_attention(const AttnParams& p, bool pdl, cudaStream_t st);
 size_t attention_scratch_floats(int B, int Nh, int Hd, int Smax);

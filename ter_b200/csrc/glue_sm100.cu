@@ -149,6 +149,7 @@ __global__ void __launch_bounds__(kT) attn_partial_kernel(const AttnParams p) {
     float (*sc)[kAttnChunk] = reinterpret_cast<float (*)[kAttnChunk]>(asmem + L::kScOff);
     float* red = reinterpret_cast<float*>(asmem + L::kRedOff);
     uint64_t* bars = reinterpret_cast<uint64_t*>(asmem + L::kBarOff);
+    __shared__ float redg[kMaxGroup * 8];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (tid == 0) {
@@ -288,18 +289,50 @@ __global__ void __launch_bounds__(kT) attn_partial_kernel(const AttnParams p) {
 
     float* rec0 = p.scratch + (((size_t)b * p.Nh + (size_t)g * G) * p.max_chunks + c) * (HD + 2);
     const size_t rec_stride = (size_t)p.max_chunks * (HD + 2);
-    for (int hh = 0; hh < G; ++hh) {
-        const float s = sc[hh][tid];
-        const float m = block_max(s, red);
-        const float pt = tid < cnt ? exp_fixed(s - m) : 0.0f;
-        const float l = block_sum(pt, red);
-        sc[hh][tid] = pt;
-        if (tid == 0) {
-            rec0[hh * rec_stride + 0] = m;
-            rec0[hh * rec_stride + 1] = l;
+    // chunk maximum and sum of exponentials of every head of the group: same values, in the same
+    // order, as block_max / block_sum per head, with one barrier per reduction for all heads together
+    float sv[kMaxGroup], mv[kMaxGroup];
+#pragma unroll
+    for (int hh = 0; hh < kMaxGroup; ++hh) {
+        sv[hh] = -CUDART_INF_F;
+        if (hh < G) {
+            sv[hh] = sc[hh][tid];
+            const float w = warp_max(sv[hh]);
+            if (lane == 0) redg[hh * 8 + warp] = w;
         }
     }
     __syncthreads();
+#pragma unroll
+    for (int hh = 0; hh < kMaxGroup; ++hh) {
+        mv[hh] = 0.0f;
+        if (hh < G) {
+            float t = redg[hh * 8];
+#pragma unroll
+            for (int w = 1; w < kT / 32; ++w) t = fmaxf(t, redg[hh * 8 + w]);
+            mv[hh] = t;
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int hh = 0; hh < kMaxGroup; ++hh) {
+        if (hh < G) {
+            const float pt = tid < cnt ? exp_fixed(sv[hh] - mv[hh]) : 0.0f;
+            sc[hh][tid] = pt;
+            const float w = warp_sum_butterfly(pt);
+            if (lane == 0) redg[hh * 8 + warp] = w;
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int hh = 0; hh < kMaxGroup; ++hh) {
+        if (tid == hh && hh < G) {
+            float t = redg[hh * 8];
+#pragma unroll
+            for (int w = 1; w < kT / 32; ++w) t = t + redg[hh * 8 + w];
+            rec0[hh * rec_stride + 0] = mv[hh];
+            rec0[hh * rec_stride + 1] = t;
+        }
+    }
     if (n_copy > 0) mbar_wait_bounded(&bars[1], 0, p.status);
 
     for (int idx = tid; idx < G * HD; idx += kT) {
@@ -310,6 +343,40 @@ __global__ void __launch_bounds__(kT) attn_partial_kernel(const AttnParams p) {
 #pragma unroll 8
         for (int t = 0; t < cnt; ++t) acc = fmaf(pr[t], bf16_bits_to_f32(vp[t * HD]), acc);
         rec0[hh * rec_stride + 2 + d] = acc;
+    }
+
+    // Merge of the chunks by the last CTA of this (sequence, KV head) to finish, when the caller gave
+    // arrival counters; the order of the merge is fixed (chunk 0, 1, 2, ...) whoever performs it.
+    if (p.counters) {
+        __shared__ int is_last;
+        const int nc = (seq_len + kAttnChunk - 1) / kAttnChunk;
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            int* cnt_p = p.counters + (size_t)b * p.Nkv + g;
+            const int old = atomicAdd(cnt_p, 1);
+            is_last = (old == nc - 1);
+            if (is_last) *cnt_p = 0;          // ready for the next step
+        }
+        __syncthreads();
+        if (is_last) {
+            __threadfence();
+            for (int idx = tid; idx < G * HD; idx += kT) {
+                const int hh = idx / HD, d = idx % HD;
+                const float* rec = p.scratch + ((size_t)b * p.Nh + (size_t)g * G + hh) * rec_stride;
+                float M = __ldcg(rec), Lsum = __ldcg(rec + 1), O = __ldcg(rec + 2 + d);
+                for (int cc = 1; cc < nc; ++cc) {
+                    const float* r = rec + (size_t)cc * (HD + 2);
+                    const float mc = __ldcg(r), lc = __ldcg(r + 1), oc = __ldcg(r + 2 + d);
+                    const float Mn = fmaxf(M, mc);
+                    const float a = exp_fixed(M - Mn), bb = exp_fixed(mc - Mn);
+                    Lsum = fmaf(lc, bb, Lsum * a);
+                    O = fmaf(oc, bb, O * a);
+                    M = Mn;
+                }
+                p.out[((size_t)b * p.Nh + (size_t)g * G + hh) * HD + d] = O / Lsum;
+            }
+        }
     }
 }
 
@@ -357,7 +424,7 @@ cudaError_t launch_attention(const AttnParams& p, bool pdl, cudaStream_t st) {
             attr_set[dev][0] = true;
         }
         e = launch_pdl(attn_partial_kernel<64>, grid, dim3(kT), AttnSmem<64>::kBytes, pdl, st, p);
-        if (e != cudaSuccess) return e;
+        if (e != cudaSuccess || p.counters) return e;
         return launch_pdl(attn_combine_kernel<64>, dim3((unsigned)p.Nh, (unsigned)p.B), dim3(64), 0, pdl, st, p);
     }
     if (p.Hd == 128) {
@@ -368,7 +435,7 @@ cudaError_t launch_attention(const AttnParams& p, bool pdl, cudaStream_t st) {
             attr_set[dev][1] = true;
         }
         e = launch_pdl(attn_partial_kernel<128>, grid, dim3(kT), AttnSmem<128>::kBytes, pdl, st, p);
-        if (e != cudaSuccess) return e;
+        if (e != cudaSuccess || p.counters) return e;
         return launch_pdl(attn_combine_kernel<128>, dim3((unsigned)p.Nh, (unsigned)p.B), dim3(128), 0, pdl, st, p);
     }
     return cudaErrorInvalidValue;

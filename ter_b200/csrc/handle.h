@@ -48,6 +48,7 @@ struct ter_b200_handle_t {
     int gemm_min_m;             // batches below this go row by row through the GEMV kernel
     int gemm_split_k;           // 0 = never split K
     int gemm_dbg;
+    int attn_inline_merge;      // 1: the last attention CTA of a KV head merges the chunks (no second kernel)
     cudaGraphExec_t graphs[16];
     uint64_t graph_launches[16];   // kernels recorded in each graph
     uint64_t capture_mark;
@@ -97,6 +98,7 @@ int comm_size(const ter_b200_handle_t* h);
 int comm_all_gather_bytes(ter_b200_handle_t* h, void* buf, size_t bytes_per_rank, cudaStream_t st);
 int comm_group_start(ter_b200_handle_t* h);
 int comm_group_end(ter_b200_handle_t* h);
+void model_invalidate_graph(ter_b200_handle_t* h);
 int ensure_gemm_scratch(ter_b200_handle_t* h, int M, int N);
 // Batched GEMM over one weight (tensor cores for M >= gemm_min_m, else GEMV per row).
 int run_gemm(ter_b200_handle_t* h, const DevWeight* w, const int8_t* X, const float* x_scales, int M, float* out,

@@ -24,7 +24,7 @@ struct TerbModel {
     float *hidden, *q, *k, *v, *att, *gate, *up, *xnorm, *logits, *attn_scratch, *argmax_scratch, *xs;
     int8_t* xq;
     uint16_t *kcache, *vcache;   // [L][B][Nkv][Smax][Hd]
-    int *tokens, *pos, *greedy, *forced, *log, *ctl;
+    int *tokens, *pos, *greedy, *forced, *log, *ctl, *attn_counters;
     int forced_cap, log_cap;     // ints per sequence
     cudaGraphExec_t graph;
     int graph_batch;
@@ -135,9 +135,9 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
         uint16_t* vc = m->vcache + L * layer_cache;
         AttnParams ap{m->q, kc, vc, m->pos, m->attn_scratch, m->att, B, c.Nh, c.Nkv, c.Hd, c.Smax,
                       (c.Smax + kAttnChunk - 1) / kAttnChunk, m->rope, m->k, m->v, kc, vc, bitnet ? 1 : 0,
-                      h->status_dev};
+                      h->status_dev, h->attn_inline_merge ? m->attn_counters : nullptr};
         CK(launch_attention(ap, pdl, st));
-        h->launches += 1;
+        if (!h->attn_inline_merge) h->launches += 1;
         {
             const DevWeight* ws[1] = {&W[TER_B200_WO]};
             float* outs[1] = {m->hidden + off(H)};
@@ -224,6 +224,13 @@ bool model_complete(const TerbModel* m) {
 
 }  // namespace
 
+namespace terb {
+// A tuning knob changed: the captured decode step no longer matches the settings.
+void model_invalidate_graph(ter_b200_handle_t* h) {
+    if (h && h->model) drop_graph(h->model);
+}
+}  // namespace terb
+
 extern "C" {
 
 void ter_b200_model_free(ter_b200_handle_t* h) {
@@ -245,7 +252,7 @@ void ter_b200_model_free(ter_b200_handle_t* h) {
     if (m->embd && m->embd_owned) cudaFree(m->embd);
     void* bufs[] = {m->out_norm, m->hidden, m->q, m->k, m->v, m->att, m->gate, m->up, m->xnorm, m->logits,
                     m->attn_scratch, m->argmax_scratch, m->xs, m->xq, m->kcache, m->vcache, m->tokens, m->pos,
-                    m->greedy, m->forced, m->log, m->ctl};
+                    m->greedy, m->forced, m->log, m->ctl, m->attn_counters};
     for (void* b : bufs)
         if (b) cudaFree(b);
     if (m->ev0) cudaEventDestroy(m->ev0);
@@ -305,11 +312,13 @@ int ter_b200_model_create(ter_b200_handle_t* h, const ter_b200_model_cfg_t* cfg)
     A(dalloc(&m->pos, (size_t)B));
     A(dalloc(&m->greedy, (size_t)B));
     A(dalloc(&m->ctl, 2));
+    A(dalloc(&m->attn_counters, (size_t)B * c.Nkv));
     if (e == cudaSuccess) e = cudaMemset(m->kcache, 0, cache_elems(c) * 2);
     if (e == cudaSuccess) e = cudaMemset(m->vcache, 0, cache_elems(c) * 2);
     if (e == cudaSuccess) e = cudaMemset(m->tokens, 0, B * sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(m->pos, 0, B * sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(m->ctl, 0, 2 * sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(m->attn_counters, 0, (size_t)B * c.Nkv * sizeof(int));
     if (e == cudaSuccess) e = cudaEventCreate(&m->ev0);
     if (e == cudaSuccess) e = cudaEventCreate(&m->ev1);
     if (e != cudaSuccess) { ter_b200_model_free(h); return cuda_fail(h, e); }
