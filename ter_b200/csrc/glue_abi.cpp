@@ -108,7 +108,7 @@ int ter_b200_attention(ter_b200_handle_t* h, const float* q_dev, const uint16_t*
                        const uint16_t* vcache_dev, const int* pos_dev, int B, int Nh, int Nkv, int Hd, int Smax,
                        float* scratch_dev, size_t scratch_floats, float* out_dev, void* stream) {
     if (!h || !q_dev || !kcache_dev || !vcache_dev || !pos_dev || !scratch_dev || !out_dev) return TER_B200_E_NULL;
-    if (B < 1 || Nkv < 1 || Nh % Nkv != 0 || Nh / Nkv > 8 || (Hd != 64 && Hd != 128) || Smax < 1)
+    if (B < 1 || Nkv < 1 || Nh % Nkv != 0 || (Nh / Nkv != 1 && Nh / Nkv != 2 && Nh / Nkv != 4 && Nh / Nkv != 8) || (Hd != 64 && Hd != 128) || Smax < 1)
         return TER_B200_E_SHAPE;
     if (scratch_floats < attention_scratch_floats(B, Nh, Hd, Smax)) return TER_B200_E_SHAPE;
     TERB_CUDA(h, cudaSetDevice(h->device));

@@ -139,7 +139,7 @@ struct AttnSmem {
 // it rotates the group's query heads on the fly (the q buffer is left untouched) and, in the CTA
 // whose chunk contains the new position, rotates k, rounds k and v to bf16, appends them to the
 // cache and uses them.  Otherwise q is taken as already rotated and the cache as already appended.
-template <int HD>
+template <int HD, int G>
 __global__ void __launch_bounds__(kT) attn_partial_kernel(const AttnParams p) {
     extern __shared__ __align__(128) uint8_t asmem[];
     using L = AttnSmem<HD>;
@@ -188,7 +188,6 @@ __global__ void __launch_bounds__(kT) attn_partial_kernel(const AttnParams p) {
     const bool fused = p.rope_table != nullptr;
     const bool owner = fused && (pos >= s0) && (pos < s0 + kAttnChunk);   // this chunk holds the new row
     const int n_copy = owner ? cnt - 1 : cnt;                             // rows already in the cache
-    const int G = p.Nh / p.Nkv;
     const size_t head_off = ((size_t)b * p.Nkv + g) * (size_t)p.Smax * HD;
     const uint16_t* K = p.kcache + head_off;
     const uint16_t* V = p.vcache + head_off;
@@ -246,7 +245,7 @@ __global__ void __launch_bounds__(kT) attn_partial_kernel(const AttnParams p) {
 
     const float inv_sqrt = 1.0f / sqrtf((float)HD);
     const int sub = lane >> 3, j = lane & 7;
-#pragma unroll 1
+#pragma unroll 2
     for (int it = 0; it < 8; ++it) {
         const int t = warp * 32 + it * 4 + sub;
         const bool valid = t < cnt;
@@ -264,6 +263,7 @@ __global__ void __launch_bounds__(kT) attn_partial_kernel(const AttnParams p) {
             kv[pc * 8 + 6] = bf16_bits_to_f32(raw.w & 0xffffu);
             kv[pc * 8 + 7] = bf16_bits_to_f32(raw.w >> 16);
         }
+#pragma unroll
         for (int hh = 0; hh < G; ++hh) {
             float acc = 0.0f;
 #pragma unroll
@@ -409,35 +409,40 @@ size_t attention_scratch_floats(int B, int Nh, int Hd, int Smax) {
     return (size_t)B * Nh * mc * (Hd + 2);
 }
 
+namespace {
+template <int HD, int G>
+cudaError_t launch_attn_partial(const AttnParams& p, bool pdl, cudaStream_t st, int dev) {
+    static bool attr_set[64] = {};
+    if (!attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(attn_partial_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             AttnSmem<HD>::kBytes);
+        if (e != cudaSuccess) return e;
+        attr_set[dev] = true;
+    }
+    const dim3 grid((unsigned)p.max_chunks, (unsigned)p.Nkv, (unsigned)p.B);
+    return launch_pdl(attn_partial_kernel<HD, G>, grid, dim3(kT), AttnSmem<HD>::kBytes, pdl, st, p);
+}
+template <int HD>
+cudaError_t launch_attn_hd(const AttnParams& p, bool pdl, cudaStream_t st, int dev) {
+    cudaError_t e;
+    switch (p.Nh / p.Nkv) {
+        case 1: e = launch_attn_partial<HD, 1>(p, pdl, st, dev); break;
+        case 2: e = launch_attn_partial<HD, 2>(p, pdl, st, dev); break;
+        case 4: e = launch_attn_partial<HD, 4>(p, pdl, st, dev); break;
+        case 8: e = launch_attn_partial<HD, 8>(p, pdl, st, dev); break;
+        default: return cudaErrorInvalidValue;
+    }
+    if (e != cudaSuccess || p.counters) return e;
+    return launch_pdl(attn_combine_kernel<HD>, dim3((unsigned)p.Nh, (unsigned)p.B), dim3(HD), 0, pdl, st, p);
+}
+}  // namespace
+
 cudaError_t launch_attention(const AttnParams& p, bool pdl, cudaStream_t st) {
     if (p.Nkv < 1 || p.Nh % p.Nkv != 0 || p.Nh / p.Nkv > kMaxGroup) return cudaErrorInvalidValue;
-    const dim3 grid((unsigned)p.max_chunks, (unsigned)p.Nkv, (unsigned)p.B);
-    static bool attr_set[64][2] = {};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
-    cudaError_t e;
-    if (p.Hd == 64) {
-        if (!attr_set[dev][0]) {
-            e = cudaFuncSetAttribute(attn_partial_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     AttnSmem<64>::kBytes);
-            if (e != cudaSuccess) return e;
-            attr_set[dev][0] = true;
-        }
-        e = launch_pdl(attn_partial_kernel<64>, grid, dim3(kT), AttnSmem<64>::kBytes, pdl, st, p);
-        if (e != cudaSuccess || p.counters) return e;
-        return launch_pdl(attn_combine_kernel<64>, dim3((unsigned)p.Nh, (unsigned)p.B), dim3(64), 0, pdl, st, p);
-    }
-    if (p.Hd == 128) {
-        if (!attr_set[dev][1]) {
-            e = cudaFuncSetAttribute(attn_partial_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     AttnSmem<128>::kBytes);
-            if (e != cudaSuccess) return e;
-            attr_set[dev][1] = true;
-        }
-        e = launch_pdl(attn_partial_kernel<128>, grid, dim3(kT), AttnSmem<128>::kBytes, pdl, st, p);
-        if (e != cudaSuccess || p.counters) return e;
-        return launch_pdl(attn_combine_kernel<128>, dim3((unsigned)p.Nh, (unsigned)p.B), dim3(128), 0, pdl, st, p);
-    }
+    if (p.Hd == 64) return launch_attn_hd<64>(p, pdl, st, dev);
+    if (p.Hd == 128) return launch_attn_hd<128>(p, pdl, st, dev);
     return cudaErrorInvalidValue;
 }
 
@@ -672,7 +677,7 @@ extern "C" int ter_b200_attention_noalloc(ter_b200_handle_t* h, const float* q_d
                                           int Hd, int Smax, float* out_dev, void* stream) {
     using namespace terb;
     if (!h || !q_dev || !kcache_dev || !vcache_dev || !pos_dev || !out_dev) return TER_B200_E_NULL;
-    if (B < 1 || Nkv < 1 || Nh < 1 || Nh % Nkv != 0 || Nh / Nkv > 8 || (Hd != 64 && Hd != 128) || Smax < 1)
+    if (B < 1 || Nkv < 1 || Nh < 1 || Nh % Nkv != 0 || (Nh / Nkv != 1 && Nh / Nkv != 2 && Nh / Nkv != 4 && Nh / Nkv != 8) || (Hd != 64 && Hd != 128) || Smax < 1)
         return TER_B200_E_SHAPE;
     // the partial records of this problem must fit the fixed array
     if (attention_scratch_floats(B, Nh, Hd, Smax) > (size_t)TER_B200_STATIC_SCRATCH_FLOATS) return TER_B200_E_SHAPE;

@@ -267,7 +267,8 @@ int ter_b200_model_create(ter_b200_handle_t* h, const ter_b200_model_cfg_t* cfg)
     if (c.H < 16 || c.F < 16 || c.L < 1 || c.V < 1 || c.Nh < 1 || c.Nkv < 1 || c.Smax < 1 || c.max_batch < 1 ||
         c.max_batch > 1024)
         return TER_B200_E_SHAPE;
-    if ((c.Hd != 64 && c.Hd != 128) || c.Nh % c.Nkv != 0 || c.Nh / c.Nkv > 8) return TER_B200_E_SHAPE;
+    if ((c.Hd != 64 && c.Hd != 128) || c.Nh % c.Nkv != 0) return TER_B200_E_SHAPE;
+    { const int gq = c.Nh / c.Nkv; if (gq != 1 && gq != 2 && gq != 4 && gq != 8) return TER_B200_E_SHAPE; }
     if (c.H % 16 || c.F % 16 || (c.Nh * c.Hd) % 16 || c.H % 8) return TER_B200_E_SHAPE;
     if (c.arch != TER_B200_ARCH_LLAMA && c.arch != TER_B200_ARCH_BITNET) return TER_B200_E_SHAPE;
     {
