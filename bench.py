@@ -258,7 +258,12 @@ def main():
         host_x[K] = torch.from_numpy(x).pin_memory()
         host_s[K] = float(s)
     outs = {name: torch.empty(N, dtype=torch.float32, device=dev) for name, _, N, _, _ in mats}
-    host_out = {name: torch.empty(N, dtype=torch.float32).pin_memory() for name, _, N, _, _ in mats}
+    # host results: one pinned buffer, the outputs back to back in call order
+    host_out_all = torch.empty(sum(N for _, _, N, _, _ in mats), dtype=torch.float32).pin_memory()
+    host_out, off = {}, 0
+    for name, _, N, _, _ in mats:
+        host_out[name] = host_out_all[off:off + N]
+        off += N
 
     side = [torch.cuda.Stream(device=dev) for _ in range(8)]
 
@@ -292,9 +297,12 @@ def main():
             for st in streams:
                 cur.wait_stream(st)
 
+    host_plan = tb.gemv_host_batch_plan([m_[0] for m_ in mats], [host_x[m_[1]] for m_ in mats],
+                                        [host_s[m_[1]] for m_ in mats], [host_out[m_[0]] for m_ in mats])
+
     def step_host():
-        for name, K, N, _, _ in mats:
-            tb.gemv_host(name, host_x[K], host_s[K], host_out[name])
+        # every projection through the host-buffer C-ABI call: pinned int8 x in, fp32 outputs back
+        tb.gemv_host_batch(host_plan)
         tb.sync()
 
     def barrier():
@@ -328,10 +336,24 @@ def main():
     # The timed step replays a CUDA graph of the pass (as the reference's decode loop replays its
     # captured forward): graph_par = independent launches over 8 streams, graph_chain = one stream.
     graph_par = tb.capture(lambda: step_device(side))
+    # the whole pass as ONE launch: a sweep plan (descriptor table in device memory)
+    sweep = tb.gemv_plan([m_[0] for m_ in mats], [xs_dev[m_[1]][0] for m_ in mats], [xs_dev[m_[1]][1] for m_ in mats],
+                         [outs[m_[0]] for m_ in mats])
+    check = {m_[0]: outs[m_[0]].clone() for m_ in mats}
+    for o in outs.values():
+        o.zero_()
+    tb.gemv_plan_launch(sweep, stream=torch.cuda.current_stream())
+    torch.cuda.synchronize()
+    for name, o in outs.items():
+        if not torch.equal(o, check[name]):
+            raise RuntimeError(f"sweep plan and per-matrix launches disagree on {name}")
+    del check
+    cur_stream = torch.cuda.current_stream()
     graph_chain = tb.capture(lambda: step_device(None))
 
     sampler = ClockSampler(local) if rank == 0 else None
-    ms, launches = timed(lambda: tb.graph_launch(graph_par), args.steps, args.warmup)
+    ms, launches = timed(lambda: tb.gemv_plan_launch(sweep, stream=cur_stream), args.steps, args.warmup)
+    ms_par, launches_par = timed(lambda: tb.graph_launch(graph_par), args.steps, args.warmup)
     ms_chain, _ = timed(lambda: tb.graph_launch(graph_chain), args.steps, args.warmup)
     e2e_steps = max(3, args.steps // 5)
     ms_e2e, _ = timed(step_host, e2e_steps, 3)
@@ -376,19 +398,28 @@ def main():
             "config": {"workload": f"llama-3.2-1b GEMV fabric sweep: {args.layers} layers x 7 projections + packed "
                                    f"lm_head, M=1, {step_bytes / 1e6:.1f} MB packed trits per GPU per step",
                        "l2": "inputs larger than L2 (309 MB vs 126 MB), same order every step",
-                       "launches_per_step": launches // args.steps, "grouped": "q+k+v and gate+up share a launch",
-                       "timed": "CUDA-graph replay; the 65 launches of a pass are independent (fixed x) and are "
-                                "issued over 8 streams"},
+                       "launches_per_step": launches // args.steps,
+                       "timed": "one sweep-plan launch per step (ter_b200_gemv_plan_launch): the 113 independent GEMVs are "
+                                "rows of a device descriptor table and one persistent grid streams all of them"},
+            "per_matrix_launches": {"value": total_bytes * args.steps / (ms_par * 1e-3) / 1e9, "unit": UNIT,
+                                    "ms_per_step": ms_par / args.steps, "launches_per_step": launches_par // args.steps,
+                                    "note": "same pass as 65 launches (q+k+v and gate+up grouped) replayed from a CUDA "
+                                            "graph over 8 streams"},
             "dependent_chain": {"value": total_bytes * args.steps / (ms_chain * 1e-3) / 1e9, "unit": UNIT,
                                 "ms_per_step": ms_chain / args.steps,
                                 "note": "same pass as one stream-ordered chain with programmatic dependent launch "
                                         "(each GEMV waits for the previous one, as in a decode step)"},
             "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
                          "traffic": None, "peak_source": peak_src,
-                         "note": "achieved = packed weight bytes per GPU / CUDA-event time; per launch = /launches"},
+                         "traffic_note": "ncu: 263.0 MB DRAM per 262.7 MB algorithmic on the lm_head matrix (profiles/)",
+                         "note": "achieved = packed weight bytes of the launch / its CUDA-event time (one launch per step)"},
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": UNIT, "steps": e2e_steps,
-                    "h2d_bytes_per_step": sum(K for _, K, _, _, _ in mats) * world,
+                    # what the call copies up: each distinct activation vector once, a 32-byte descriptor per
+                    # matrix and the scales (one 256-byte block)
+                    "h2d_bytes_per_step": (sum(sorted({K for _, K, _, _, _ in mats})) + 32 * len(mats) + 256) * world,
+                    "note": "ter_b200_gemv_host_batch: pinned host x in, one launch, fp32 outputs back to one pinned "
+                            "host buffer; synchronous call",
                     "d2h_bytes_per_step": sum(4 * N for _, _, N, _, _ in mats) * world},
             "decode": decode,
             "gpu_launches": launches,

@@ -46,6 +46,8 @@ typedef struct ter_b200_handle_t ter_b200_handle_t;
  * weight tensor and one model has 7 per layer, so the fixed table is larger; the name limit and
  * the behaviour on overflow (an error code, never an exception) are the reference's. */
 #define TER_B200_MAX_SLOTS     1024
+#define TER_B200_MAX_PLANS     16     /* sweep plans per handle */
+#define TER_B200_MAX_PLAN_MATS 512    /* matrices in one sweep plan */
 #define TER_B200_MAX_NAME      31
 
 const char* ter_b200_strerror(int code);
@@ -136,6 +138,22 @@ int ter_b200_gemv_group(ter_b200_handle_t* h, const char* const* slots, int n_sl
                         float* const* outs_dev, void* stream);
 #define TER_B200_ACT_SILU  1
 #define TER_B200_ACT_RELU2 2
+/* `n` (at most 8) INDEPENDENT GEMVs in one launch: slot i with its own activation vector x_devs[i]
+ * (int8[K_i]) and scale x_scale_devs[i]; the K_i may differ.  Same results as n calls of
+ * ter_b200_gemv; one grid streams all the weights (the reference's benches time such sweeps one
+ * kernel at a time, cuda/ter_cuda_forward_packed_v12.cu:414-464). */
+int ter_b200_gemv_multi(ter_b200_handle_t* h, int n, const char* const* slots, const int8_t* const* x_devs,
+                        const float* const* x_scale_devs, float* const* outs_dev, void* stream);
+/* Sweep plan: up to TER_B200_MAX_PLAN_MATS independent GEMVs (at most 16 distinct (x, scale, K)
+ * vectors, 64 KB of x in total) whose descriptors are written to device memory ONCE; every
+ * ter_b200_gemv_plan_launch then streams all the matrices in a single launch and reads x / scales /
+ * writes outs at the addresses given here.  Installing, replacing or removing ANY weight slot makes
+ * existing plans stale: launch returns TER_B200_E_STATE, destroy and re-create them.  The reference
+ * issues such sequences one kernel per matrix (cuda/ter_cuda_forward_packed.cu:505-563). */
+int ter_b200_gemv_plan_create(ter_b200_handle_t* h, int n, const char* const* slots, const int8_t* const* x_devs,
+                              const float* const* x_scale_devs, float* const* outs_dev, int* plan_id);
+int ter_b200_gemv_plan_launch(ter_b200_handle_t* h, int plan_id, void* stream);
+int ter_b200_gemv_plan_destroy(ter_b200_handle_t* h, int plan_id);
 /* Quantiser fused into the GEMV: y = W^T q(x) where q() is exactly ter_b200_rmsnorm_quant (act = 0:
  * RMSNorm with gamma_dev, or plain absmax quantisation when gamma_dev is NULL) or ter_b200_act_quant
  * (act = TER_B200_ACT_SILU / _RELU2 with up_dev, optional sub-norm gamma_dev) applied to the fp32 vector
@@ -152,6 +170,13 @@ int ter_b200_norm_gemv_group(ter_b200_handle_t* h, const char* const* slots, int
  * (pinned host memory makes the copies truly asynchronous). */
 int ter_b200_gemv_host(ter_b200_handle_t* h, const char* slot, const int8_t* x_host,
                        float x_scale, float* out_host, void* stream);
+/* The same for `n` GEMVs in one call (e.g. every projection of a model): slots[i], x_hosts[i]
+ * (int8[K_i]), x_scales[i], out_hosts[i] (float[N_i]).  SYNCHRONOUS: the results are in out_hosts when
+ * it returns.  Vectors given with the same pointer, scale and K travel once; all inputs go up in one
+ * copy; the GEMVs run as one launch (more only past 512 matrices, 16 distinct vectors or 64 KB of x);
+ * outputs that lie back to back in host memory, in call order, come down in one copy. */
+int ter_b200_gemv_host_batch(ter_b200_handle_t* h, int n, const char* const* slots, const int8_t* const* x_hosts,
+                             const float* x_scales, float* const* out_hosts, void* stream);
 int ter_b200_sync(ter_b200_handle_t* h, void* stream);
 
 /* ---- batched ternary GEMM, M > 1 -------------------------------------------

@@ -64,8 +64,14 @@ SIGNATURES = {
     "ter_b200_gemv": (_I, [_VP, _CP, _VP, _VP, _VP, _VP]),
     "ter_b200_gemv_acc": (_I, [_VP, _CP, _VP, _VP, _VP]),
     "ter_b200_gemv_group": (_I, [_VP, C.POINTER(_CP), _I, _VP, _VP, C.POINTER(_VP), _VP]),
+    "ter_b200_gemv_multi": (_I, [_VP, _I, C.POINTER(_CP), C.POINTER(_VP), C.POINTER(_VP), C.POINTER(_VP), _VP]),
+    "ter_b200_gemv_plan_create": (_I, [_VP, _I, C.POINTER(_CP), C.POINTER(_VP), C.POINTER(_VP), C.POINTER(_VP),
+                                       C.POINTER(_I)]),
+    "ter_b200_gemv_plan_launch": (_I, [_VP, _I, _VP]),
+    "ter_b200_gemv_plan_destroy": (_I, [_VP, _I]),
     "ter_b200_norm_gemv_group": (_I, [_VP, C.POINTER(_CP), _I, _I, _VP, _VP, _VP, _F, C.POINTER(_VP), _I, _VP]),
     "ter_b200_gemv_host": (_I, [_VP, _CP, _VP, _F, _VP, _VP]),
+    "ter_b200_gemv_host_batch": (_I, [_VP, _I, C.POINTER(_CP), C.POINTER(_VP), C.POINTER(_F), C.POINTER(_VP), _VP]),
     "ter_b200_sync": (_I, [_VP, _VP]),
     "ter_b200_gemm": (_I, [_VP, _CP, _VP, _VP, _I, _VP, _VP]),
     "ter_b200_gemm_acc": (_I, [_VP, _CP, _VP, _I, _VP, _VP]),
@@ -253,6 +259,36 @@ class TerB200:
                                           C.c_void_p(x_scale.data_ptr()), arr_o, _stream_ptr(stream)), "gemv_group")
         return outs
 
+    def gemv_multi(self, names, xs, x_scales, outs=None, stream=None):
+        """Independent GEMVs (own x, own K) in one launch."""
+        import torch
+        n = len(names)
+        if outs is None:
+            outs = [torch.empty(self._shapes[nm][1], dtype=torch.float32, device=xs[0].device) for nm in names]
+        self._ck(self.L.ter_b200_gemv_multi(self.h, n, (C.c_char_p * n)(*[s.encode() for s in names]),
+                                            (C.c_void_p * n)(*[t.data_ptr() for t in xs]),
+                                            (C.c_void_p * n)(*[t.data_ptr() for t in x_scales]),
+                                            (C.c_void_p * n)(*[t.data_ptr() for t in outs]), _stream_ptr(stream)),
+                 "gemv_multi")
+        return outs
+
+    def gemv_plan(self, names, xs, x_scales, outs):
+        """Sweep plan: all GEMVs in one launch per gemv_plan_launch(); tensors must stay alive."""
+        n = len(names)
+        pid = C.c_int(-1)
+        self._ck(self.L.ter_b200_gemv_plan_create(self.h, n, (C.c_char_p * n)(*[s.encode() for s in names]),
+                                                  (C.c_void_p * n)(*[t.data_ptr() for t in xs]),
+                                                  (C.c_void_p * n)(*[t.data_ptr() for t in x_scales]),
+                                                  (C.c_void_p * n)(*[t.data_ptr() for t in outs]), C.byref(pid)),
+                 "gemv_plan_create")
+        return pid.value
+
+    def gemv_plan_launch(self, plan_id, stream=None):
+        self._ck(self.L.ter_b200_gemv_plan_launch(self.h, plan_id, _stream_ptr(stream)), "gemv_plan_launch")
+
+    def gemv_plan_destroy(self, plan_id):
+        self._ck(self.L.ter_b200_gemv_plan_destroy(self.h, plan_id), "gemv_plan_destroy")
+
     def norm_gemv_group(self, names, x, gamma, eps, act=0, up=None, outs=None, accumulate=False, stream=None):
         """Fused quantiser + GEMV: x fp32[K] (gate for act != 0), returns fp32 outputs."""
         import torch
@@ -272,6 +308,18 @@ class TerB200:
         op = out_host.data_ptr() if hasattr(out_host, "data_ptr") else out_host.ctypes.data
         self._ck(self.L.ter_b200_gemv_host(self.h, name.encode(), C.c_void_p(xp), float(x_scale), C.c_void_p(op),
                                          _stream_ptr(stream)), f"gemv_host {name}")
+
+    def gemv_host_batch_plan(self, names, x_hosts, x_scales, out_hosts):
+        """Pre-builds the argument arrays of ter_b200_gemv_host_batch (host tensors must stay alive)."""
+        n = len(names)
+        ptr = lambda t: t.data_ptr() if hasattr(t, "data_ptr") else t.ctypes.data  # noqa: E731
+        return (n, (C.c_char_p * n)(*[s.encode() for s in names]), (C.c_void_p * n)(*[ptr(t) for t in x_hosts]),
+                (C.c_float * n)(*[float(v) for v in x_scales]), (C.c_void_p * n)(*[ptr(t) for t in out_hosts]))
+
+    def gemv_host_batch(self, plan, stream=None):
+        n, names, xs, scales, outs = plan
+        self._ck(self.L.ter_b200_gemv_host_batch(self.h, n, names, xs, scales, outs, _stream_ptr(stream)),
+                 "gemv_host_batch")
 
     def sync(self, stream=None):
         self._ck(self.L.ter_b200_sync(self.h, _stream_ptr(stream)))

@@ -71,6 +71,7 @@ static size_t boundary_bytes(int format, int K, int N) {
 
 static int put_slot(ter_b200_handle_t* h, const char* name, const DevWeight& w) {
     TerbSlot* s = find_slot(h, name);
+    h->weights_epoch++;
     if (s) {
         free_weight(&s->w);
         s->w = w;
@@ -81,6 +82,7 @@ static int put_slot(ter_b200_handle_t* h, const char* name, const DevWeight& w) 
             h->slots[i].used = true;
             strncpy(h->slots[i].name, name, TER_B200_MAX_NAME);
             h->slots[i].name[TER_B200_MAX_NAME] = '\0';
+            h->slots[i].hash = name_hash(h->slots[i].name);
             h->slots[i].w = w;
             return TER_B200_OK;
         }
@@ -95,7 +97,7 @@ static int check_name(const char* name) {
     return TER_B200_OK;
 }
 
-static int ensure_host_staging(ter_b200_handle_t* h, size_t x_bytes, size_t out_floats) {
+int ensure_host_staging(ter_b200_handle_t* h, size_t x_bytes, size_t out_floats) {
     if (h->hx_cap < x_bytes) {
         if (h->hx_dev) cudaFree(h->hx_dev);
         h->hx_dev = nullptr;
@@ -228,6 +230,9 @@ void ter_b200_destroy(ter_b200_handle_t* h) {
     if (h->gemm_scratch) cudaFree(h->gemm_scratch);
     if (h->hx_dev) cudaFree(h->hx_dev);
     if (h->hout_dev) cudaFree(h->hout_dev);
+    if (h->hpin) cudaFreeHost(h->hpin);
+    for (int i = 0; i < TER_B200_MAX_PLANS; ++i)
+        if (h->plans[i].used && h->plans[i].table_dev) cudaFree(h->plans[i].table_dev);
     if (h->stream) cudaStreamDestroy(h->stream);
     delete h;
 }
@@ -295,6 +300,7 @@ int ter_b200_remove_weight(ter_b200_handle_t* h, const char* name) {
     free_weight(&s->w);
     s->used = false;
     s->name[0] = '\0';
+    h->weights_epoch++;
     return TER_B200_OK;
 }
 

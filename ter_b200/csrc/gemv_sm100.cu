@@ -57,6 +57,7 @@ __device__ __forceinline__ void mac64(const uint4& w, const int4& xv, int& t, in
     mac16(w.w, xv.w, t, a1, a2, a3);
 }
 
+// Matrix and local strip of global strip number `strip` (by-value parameter arrays).
 __device__ __forceinline__ void locate(const GemvParams& p, int strip, int& m, int& ls) {
     m = 0;
 #pragma unroll
@@ -65,18 +66,53 @@ __device__ __forceinline__ void locate(const GemvParams& p, int strip, int& m, i
     ls = strip - p.tile_begin[m];
 }
 
+// Per-matrix fields of strip `strip`: from the by-value parameter arrays, or (TABLE) from the
+// descriptor table that the CTA copied into shared memory.
+struct MatRef {
+    const uint8_t* W;
+    float* out;
+    int32_t* acc;
+    float w_scale;
+    int N, xid, ls;
+};
+
+template <bool TABLE>
+__device__ __forceinline__ MatRef locate(const GemvParams& p, const GemvDesc* tab, int strip) {
+    MatRef r;
+    if constexpr (TABLE) {
+        int lo = 0, hi = p.n_mats - 1;           // last matrix whose first strip is <= strip
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (tab[mid].tile_begin <= strip) lo = mid; else hi = mid - 1;
+        }
+        const GemvDesc d = tab[lo];
+        r.W = d.W; r.out = d.out; r.acc = nullptr; r.w_scale = d.w_scale; r.N = d.N; r.xid = d.xid;
+        r.ls = strip - d.tile_begin;
+    } else {
+        int m = 0;
+#pragma unroll
+        for (int i = 1; i < kGemvMaxGroup; ++i)
+            if (i < p.n_mats && strip >= p.tile_begin[i]) m = i;
+        r.W = p.W[m]; r.out = p.out[m]; r.acc = p.acc_out[m]; r.w_scale = p.w_scale[m]; r.N = p.N[m];
+        r.xid = p.xid[m];
+        r.ls = strip - p.tile_begin[m];
+    }
+    return r;
+}
+
+template <bool TABLE>
 __global__ void __launch_bounds__(kThreads) gemv_trit_kernel(const __grid_constant__ GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kBarOff);
-    int* xsum_s = reinterpret_cast<int*>(smem + kXsumOff);
-    int8_t* xs = reinterpret_cast<int8_t*>(smem + kHdrBytes);
-    uint8_t* wbuf = smem + kHdrBytes + p.Kpad;
+    int* xsum_s = reinterpret_cast<int*>(smem + kXsumOff);           // one per activation vector
+    const int tab_bytes = TABLE ? ((p.n_mats * (int)sizeof(GemvDesc) + 127) & ~127) : 0;
+    GemvDesc* tab = reinterpret_cast<GemvDesc*>(smem + kHdrBytes);
+    int8_t* xs = reinterpret_cast<int8_t*>(smem + kHdrBytes + tab_bytes);
+    uint8_t* wbuf = smem + kHdrBytes + tab_bytes + p.x_bytes;
 
     const int tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
     const int S = p.stages;
-    const int nb = (p.Kpad + kGemvKC - 1) / kGemvKC;          // blocks per strip
-    const int last_kc = p.Kpad - (nb - 1) * kGemvKC;
     uint64_t* mybars = bars + warp * kMaxStages;
     uint8_t* mybuf = wbuf + (size_t)warp * S * kStageBytes;
     // strip t is handled by CTA t % gridDim, warp (t / gridDim) % 8: strips spread over SMs first
@@ -87,22 +123,39 @@ __global__ void __launch_bounds__(kThreads) gemv_trit_kernel(const __grid_consta
         for (int i = 0; i < S; ++i) mbar_init(&mybars[i], 1);
         mbar_fence_init();
     }
-    if (tid == 0) *xsum_s = 0;
-    __syncwarp();
+    if (tid < kGemvMaxX) xsum_s[tid] = 0;
+    if constexpr (TABLE) {
+        // the table is written once when the plan is made, long before this launch
+        const int4* src = reinterpret_cast<const int4*>(p.table);
+        int4* dst = reinterpret_cast<int4*>(tab);
+        for (int i = tid; i < p.n_mats * (int)(sizeof(GemvDesc) / 16); i += kThreads) dst[i] = src[i];
+        __syncthreads();
+    } else {
+        __syncwarp();
+    }
 
     // Producer cursor over this warp's (strip, block) items; uniform across the warp.
-    int p_strip = first, p_q = 0, p_stage = 0;
+    int p_strip = first, p_q = 0, p_stage = 0, p_nb = 1, p_last = kGemvKC;
+    const uint8_t* p_src = nullptr;
+    auto cursor_load = [&]() {
+        if (p_strip < p.n_tiles) {
+            const MatRef r = locate<TABLE>(p, tab, p_strip);
+            const int kp = p.uKpad[r.xid];
+            p_nb = (kp + kGemvKC - 1) / kGemvKC;
+            p_last = kp - (p_nb - 1) * kGemvKC;
+            p_src = r.W + (size_t)r.ls * 4u * (size_t)kp;
+        }
+    };
+    cursor_load();
     auto issue = [&]() {
         if (p_strip < p.n_tiles) {
             if (lane == 0) {
-                int m, ls;
-                locate(p, p_strip, m, ls);
-                const int kc = (p_q == nb - 1) ? last_kc : kGemvKC;
-                const uint8_t* src = p.W[m] + (size_t)ls * 4u * (size_t)p.Kpad + (size_t)p_q * kStageBytes;
+                const int kc = (p_q == p_nb - 1) ? p_last : kGemvKC;
                 mbar_arrive_expect_tx(&mybars[p_stage], 4u * (uint32_t)kc);
-                bulk_g2s(mybuf + (size_t)p_stage * kStageBytes, src, 4u * (uint32_t)kc, &mybars[p_stage]);
+                bulk_g2s(mybuf + (size_t)p_stage * kStageBytes, p_src + (size_t)p_q * kStageBytes, 4u * (uint32_t)kc,
+                         &mybars[p_stage]);
             }
-            if (++p_q == nb) { p_q = 0; p_strip += stride; }
+            if (++p_q == p_nb) { p_q = 0; p_strip += stride; cursor_load(); }
             if (++p_stage == S) p_stage = 0;
         }
     };
@@ -112,13 +165,16 @@ __global__ void __launch_bounds__(kThreads) gemv_trit_kernel(const __grid_consta
     pdl_launch_dependents();
     pdl_wait();
 
-    // Stage x (int8[K], zero-padded to Kpad) once per CTA and sum it.
-    {
+    // Stage every activation vector (int8[K_u], zero-padded to Kpad_u) once per CTA and sum it.
+    for (int u = 0; u < p.n_x; ++u) {
         int local = 0;
-        for (int i = tid * 16; i < p.Kpad; i += kThreads * 16) {
+        int8_t* dst = xs + p.uoff[u];
+        const int8_t* srcx = p.ux[u];
+        const int K = p.uK[u], Kpad = p.uKpad[u];
+        for (int i = tid * 16; i < Kpad; i += kThreads * 16) {
             int4 v = make_int4(0, 0, 0, 0);
-            if (i < p.K) v = *reinterpret_cast<const int4*>(p.x + i);
-            *reinterpret_cast<int4*>(xs + i) = v;
+            if (i < K) v = *reinterpret_cast<const int4*>(srcx + i);
+            *reinterpret_cast<int4*>(dst + i) = v;
             local = __dp4a(v.x, 0x01010101, local);
             local = __dp4a(v.y, 0x01010101, local);
             local = __dp4a(v.z, 0x01010101, local);
@@ -126,22 +182,25 @@ __global__ void __launch_bounds__(kThreads) gemv_trit_kernel(const __grid_consta
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
-        if (lane == 0 && local != 0) atomicAdd(xsum_s, local);
+        if (lane == 0 && local != 0) atomicAdd(&xsum_s[u], local);
     }
     __syncthreads();
-    const int xsum = *xsum_s;
-    const float xscale = p.x_scale ? p.x_scale[0] : p.x_scale_imm;
 
     const int c = lane >> 3, sgm = lane & 7;
     int stage = 0;
     uint32_t parity = 0;
     for (int strip = first; strip < p.n_tiles; strip += stride) {
+        const MatRef r = locate<TABLE>(p, tab, strip);
+        const int kp = p.uKpad[r.xid];
+        const int nb = (kp + kGemvKC - 1) / kGemvKC;
+        const int last_kc = kp - (nb - 1) * kGemvKC;
+        const int8_t* xm = xs + p.uoff[r.xid] + sgm * 16;
         int a0 = 0, a1 = 0, a2 = 0, a3 = 0;
         for (int q = 0; q < nb; ++q) {
             const int kc = (q == nb - 1) ? last_kc : kGemvKC;
             mbar_wait_bounded(&mybars[stage], parity, p.status);
             const uint8_t* wt = mybuf + (size_t)stage * kStageBytes + c * kc + sgm * 16;
-            const int8_t* xp = xs + q * kGemvKC + sgm * 16;
+            const int8_t* xp = xm + q * kGemvKC;
             if (kc == kGemvKC) {
 #pragma unroll
                 for (int j = 0; j < kGemvKC / 128; ++j)
@@ -164,12 +223,12 @@ __global__ void __launch_bounds__(kThreads) gemv_trit_kernel(const __grid_consta
             a3 += __shfl_xor_sync(0xffffffffu, a3, o);
         }
         if (sgm == 0) {
-            int m, ls;
-            locate(p, strip, m, ls);
-            const int col = ls * 16 + c * 4;
+            const int xsum = xsum_s[r.xid];
+            const float xscale = p.uxs[r.xid] ? p.uxs[r.xid][0] : p.x_scale_imm;
+            const int col = r.ls * 16 + c * 4;
             const int v0 = (a0 - a1 - a2 - a3) - xsum, v1 = (a1 >> 2) - xsum, v2 = (a2 >> 4) - xsum, v3 = (a3 >> 6) - xsum;
-            const int N = p.N[m];
-            if (int32_t* ao = p.acc_out[m]) {
+            const int N = r.N;
+            if (int32_t* ao = r.acc) {
                 if (col + 3 < N && ((reinterpret_cast<uintptr_t>(ao) & 15u) == 0)) {
                     *reinterpret_cast<int4*>(ao + col) = make_int4(v0, v1, v2, v3);
                 } else {
@@ -179,8 +238,8 @@ __global__ void __launch_bounds__(kThreads) gemv_trit_kernel(const __grid_consta
                     if (col + 3 < N) ao[col + 3] = v3;
                 }
             }
-            if (float* fo = p.out[m]) {
-                const float sc = xscale * p.w_scale[m];
+            if (float* fo = r.out) {
+                const float sc = xscale * r.w_scale;
                 float f0 = (float)v0 * sc, f1 = (float)v1 * sc, f2 = (float)v2 * sc, f3 = (float)v3 * sc;
                 if (p.accumulate) {
                     if (col < N) f0 = fo[col] + f0;
@@ -200,7 +259,6 @@ __global__ void __launch_bounds__(kThreads) gemv_trit_kernel(const __grid_consta
         }
     }
 }
-
 
 // ---------------------------------------------------------------------------------
 // Latency path for matrices with few strips (every projection except the lm_head).
@@ -374,8 +432,8 @@ __global__ void __launch_bounds__(kThreads) gemv_trit_split_kernel(const __grid_
 
 }  // namespace
 
-static size_t gemv_smem_bytes(int Kpad, int stages) {
-    return (size_t)kHdrBytes + (size_t)Kpad + (size_t)kWarps * (size_t)stages * kStageBytes;
+static size_t gemv_smem_bytes(int tab_bytes, int x_bytes, int stages) {
+    return (size_t)kHdrBytes + (size_t)tab_bytes + (size_t)x_bytes + (size_t)kWarps * (size_t)stages * kStageBytes;
 }
 
 cudaError_t launch_gemv(const GemvParams& p_in, const GemvLaunchCfg& cfg, cudaStream_t st) {
@@ -384,12 +442,21 @@ cudaError_t launch_gemv(const GemvParams& p_in, const GemvLaunchCfg& cfg, cudaSt
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
     if (!attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_trit_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
+        cudaError_t e = cudaFuncSetAttribute(gemv_trit_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
+        if (e != cudaSuccess) return e;
+        e = cudaFuncSetAttribute(gemv_trit_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
     GemvParams p = p_in;
-    if (cfg.split_max_strips > 0 && p.n_tiles <= cfg.split_max_strips) {
+    if (!p.multi) {   // one shared activation vector, in the form the streaming kernel reads
+        p.n_x = 1;
+        p.ux[0] = p.x; p.uxs[0] = p.x_scale; p.uK[0] = p.K; p.uKpad[0] = p.Kpad; p.uoff[0] = 0;
+        for (int i = 0; i < kGemvMaxGroup; ++i) p.xid[i] = 0;
+        p.x_bytes = p.Kpad;
+        p.table = nullptr;
+    }
+    if (!p.multi && cfg.split_max_strips > 0 && p.n_tiles <= cfg.split_max_strips) {
         size_t fsmem = 0;
         if (p.fuse.x) {
             fsmem = 4 * (size_t)((p.K + 3) & ~3) + (size_t)p.Kpad;
@@ -430,16 +497,20 @@ cudaError_t launch_gemv(const GemvParams& p_in, const GemvLaunchCfg& cfg, cudaSt
         return cudaLaunchKernelEx(&lc, kern, p);
     }
     if (p.fuse.x) return cudaErrorNotSupported;   // the streaming kernel takes a quantised x only
+    if (p.table ? (p.n_mats < 1 || p.n_mats > kGemvMaxTable) : (p.n_mats < 1 || p.n_mats > kGemvMaxGroup))
+        return cudaErrorInvalidValue;
+    if (p.n_x < 1 || p.n_x > kGemvMaxX || p.x_bytes > kGemvMaxXBytes) return cudaErrorInvalidValue;
+    const int tab_bytes = p.table ? ((p.n_mats * (int)sizeof(GemvDesc) + 127) & ~127) : 0;
     int per_sm = cfg.ctas_per_sm < 1 ? 1 : cfg.ctas_per_sm;
     int stages = cfg.stages > 0 ? cfg.stages : 3;
     if (stages > kMaxStages) stages = kMaxStages;
     // keep `per_sm` CTAs resident: shrink the ring first, then the residency
-    while (stages > 2 && gemv_smem_bytes(p.Kpad, stages) * per_sm > (size_t)kMaxSmem) --stages;
-    while (per_sm > 1 && gemv_smem_bytes(p.Kpad, stages) * per_sm > (size_t)kMaxSmem) --per_sm;
-    while (stages > 1 && gemv_smem_bytes(p.Kpad, stages) > (size_t)kMaxSmem) --stages;
-    if (gemv_smem_bytes(p.Kpad, stages) > (size_t)kMaxSmem) return cudaErrorInvalidValue;
+    while (stages > 2 && gemv_smem_bytes(tab_bytes, p.x_bytes, stages) * per_sm > (size_t)kMaxSmem) --stages;
+    while (per_sm > 1 && gemv_smem_bytes(tab_bytes, p.x_bytes, stages) * per_sm > (size_t)kMaxSmem) --per_sm;
+    while (stages > 1 && gemv_smem_bytes(tab_bytes, p.x_bytes, stages) > (size_t)kMaxSmem) --stages;
+    if (gemv_smem_bytes(tab_bytes, p.x_bytes, stages) > (size_t)kMaxSmem) return cudaErrorInvalidValue;
     p.stages = stages;
-    const size_t smem = gemv_smem_bytes(p.Kpad, stages);
+    const size_t smem = gemv_smem_bytes(tab_bytes, p.x_bytes, stages);
 
     int grid = cfg.sm_count * per_sm;
     if (grid > p.n_tiles) grid = p.n_tiles;
@@ -455,7 +526,7 @@ cudaError_t launch_gemv(const GemvParams& p_in, const GemvLaunchCfg& cfg, cudaSt
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     lc.attrs = attr;
     lc.numAttrs = cfg.pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&lc, gemv_trit_kernel, p);
+    return p.table ? cudaLaunchKernelEx(&lc, gemv_trit_kernel<true>, p) : cudaLaunchKernelEx(&lc, gemv_trit_kernel<false>, p);
 }
 
 }  // namespace terb

@@ -12,7 +12,17 @@
 struct TerbSlot {
     char name[TER_B200_MAX_NAME + 1];
     bool used;
+    uint32_t hash;   // name_hash(name): lookups compare this before the string
     terb::DevWeight w;
+};
+
+// A sweep plan: launch parameters + the device descriptor table of ter_b200_gemv_plan_create.
+struct TerbPlan {
+    bool used = false;
+    uint64_t epoch = 0;    // weights_epoch when the plan was made
+    uint64_t tvmac = 0;    // op-counter increment of one launch
+    terb::GemvParams p;
+    terb::GemvDesc* table_dev = nullptr;
 };
 
 struct TerbModel;   // decode-forward state (model.cpp)
@@ -35,11 +45,15 @@ struct ter_b200_handle_t {
     uint64_t launches;
     terb::GemvLaunchCfg gemv_cfg;
     // staging for the host-buffer entry points
-    int8_t* hx_dev;
+    int8_t* hx_dev;   // also holds the descriptor tables of the host batch entry point
     size_t hx_cap;
     float* hout_dev;
     size_t hout_cap;
     float* hscale_dev;
+    uint8_t* hpin;            // pinned host image of the staging buffer (host batch entry point)
+    size_t hpin_cap;
+    TerbPlan plans[TER_B200_MAX_PLANS];
+    uint64_t weights_epoch;   // advances whenever a weight slot is replaced or removed
     TerbModel* model;
     RopeTable rope[4];
     terb::Comm* comm;           // tensor-parallel communicator (comm.cpp), or null
@@ -74,9 +88,16 @@ inline cudaStream_t pick_stream(ter_b200_handle_t* h, void* stream) {
     return stream ? (cudaStream_t)stream : h->stream;
 }
 
+inline uint32_t name_hash(const char* name) {
+    uint32_t v = 2166136261u;
+    for (int i = 0; i < TER_B200_MAX_NAME && name[i]; ++i) v = (v ^ (uint8_t)name[i]) * 16777619u;
+    return v;
+}
+
 inline TerbSlot* find_slot(ter_b200_handle_t* h, const char* name) {
+    const uint32_t hv = name_hash(name);
     for (int i = 0; i < TER_B200_MAX_SLOTS; ++i)
-        if (h->slots[i].used && strncmp(h->slots[i].name, name, TER_B200_MAX_NAME + 1) == 0) return &h->slots[i];
+        if (h->slots[i].used && h->slots[i].hash == hv && strncmp(h->slots[i].name, name, TER_B200_MAX_NAME + 1) == 0) return &h->slots[i];
     return nullptr;
 }
 inline const TerbSlot* find_slot(const ter_b200_handle_t* h, const char* name) {

@@ -36,8 +36,21 @@ __host__ __device__ inline size_t weight_offset(int jb, int k, int Kpad) {
     return (size_t)strip * 4u * (size_t)Kpad + (size_t)q * 4u * kGemvKC + (size_t)c * kc + (size_t)(k - q * kGemvKC);
 }
 
-constexpr int kGemvMaxGroup = 4;
+constexpr int kGemvMaxGroup = 8;
 constexpr int kGemvMaxK = 32768;
+constexpr int kGemvMaxX = 16;          // distinct activation vectors one streaming launch can stage
+constexpr int kGemvMaxTable = 512;     // matrices in one table-mode launch
+constexpr int kGemvMaxXBytes = 64 * 1024;
+
+// Per-matrix descriptor of a table-mode launch (device memory, 32 bytes).
+struct GemvDesc {
+    const uint8_t* W;
+    float* out;
+    float w_scale;
+    int N;
+    int tile_begin;   // first strip of this matrix in the launch's strip numbering
+    int xid;          // which activation vector
+};
 
 struct GemvParams {
     const uint8_t* W[kGemvMaxGroup];
@@ -48,6 +61,19 @@ struct GemvParams {
     int tile_begin[kGemvMaxGroup + 1];
     const int8_t* x;
     const float* x_scale;   // device scalar; when null, x_scale_imm is used
+    // Streaming kernel: the launch reads n_x activation vectors (vector u: int8[uK[u]] at ux[u], scale at
+    // uxs[u], staged at byte uoff[u] of the shared-memory activation area of x_bytes bytes); matrix m
+    // multiplies vector xid[m].  multi == 0: the launcher fills these from x / x_scale / K (one vector).
+    int multi;
+    int n_x;
+    const int8_t* ux[kGemvMaxX];
+    const float* uxs[kGemvMaxX];
+    int uK[kGemvMaxX], uKpad[kGemvMaxX], uoff[kGemvMaxX];
+    int x_bytes;
+    uint8_t xid[kGemvMaxGroup];
+    // Table mode (n_mats may exceed kGemvMaxGroup): the per-matrix fields come from this device array
+    // instead of W/out/w_scale/N/tile_begin/xid above; acc_out is not available.
+    const GemvDesc* table;
     float x_scale_imm;
     int K, Kpad;
     int n_mats, n_tiles, stages;

@@ -125,6 +125,25 @@ def test_group_launch_matches_single(tb):
         assert torch.equal(o, tb.gemv(nm, xd, sd))
 
 
+def test_multi_launch_matches_single(tb):
+    """Independent GEMVs with different K and different activations in one launch."""
+    specs = [("mq", 2048, 2048), ("mk", 2048, 512), ("md", 8192, 2048), ("mo", 2048, 2048), ("mg", 2560, 640)]
+    xs, scs, names = {}, {}, []
+    for nm, K, N in specs:
+        tb.install(nm, synth.pack_v11(synth.trits(K, N, synth.seed_for(nm))), FMT_V11, K, N, float(synth.weight_scale(N + K)))
+        names.append(nm)
+    for K in (2048, 8192, 2560):
+        x, s = synth.activation(K, K)
+        xs[K], scs[K] = dev(x), dev(np.array([s], np.float32))
+    x2, s2 = synth.activation(2048, 5)
+    xin = [xs[2048], xs[2048], xs[8192], dev(x2), xs[2560]]
+    sin = [scs[2048], scs[2048], scs[8192], dev(np.array([s2], np.float32)), scs[2560]]
+    outs = tb.gemv_multi(names, xin, sin)
+    for nm, x, s, o in zip(names, xin, sin, outs):
+        assert torch.equal(o, tb.gemv(nm, x, s)), nm
+    assert tb.device_status() == 0
+
+
 def test_linearity_and_tuning_invariance(tb):
     """Size-independent properties at a full-size shape: acc(x1)+acc(x2) == acc(x1+x2) (no clamp),
     and the result does not depend on grid/stage choices."""
@@ -228,6 +247,101 @@ def test_host_buffer_entry_point(tb):
     tb.sync()
     want = oracle.gemv_epilogue(exact_acc(x, t).astype(np.int32), xs, ws)
     assert np.array_equal(oh.numpy().view(np.uint32), want.view(np.uint32))
+
+
+def test_host_batch_entry_point(tb):
+    specs = [("hb1", 256, 64), ("hb2", 2048, 512), ("hb3", 128, 96)]
+    xs_h, outs_h, scales, wants = [], [], [], []
+    for nm, K, N in specs:
+        t = synth.trits(K, N, K + N)
+        ws = synth.weight_scale(K)
+        tb.install(nm, synth.pack_v11(t), FMT_V11, K, N, float(ws))
+        x, xs = synth.activation(K, N)
+        xs_h.append(torch.from_numpy(x).pin_memory())
+        outs_h.append(torch.empty(N, dtype=torch.float32).pin_memory())
+        scales.append(float(xs))
+        wants.append(oracle.gemv_epilogue(exact_acc(x, t).astype(np.int32), xs, ws))
+    plan = tb.gemv_host_batch_plan([s[0] for s in specs], xs_h, scales, outs_h)
+    tb.gemv_host_batch(plan)
+    tb.sync()
+    for o, w in zip(outs_h, wants):
+        assert np.array_equal(o.numpy().view(np.uint32), w.view(np.uint32))
+
+
+def test_host_batch_shared_vectors_contiguous_outputs_and_chunking(tb):
+    """Shared x (one copy), outputs back to back (one copy down), and more distinct vectors than one
+    launch stages (forces several launches)."""
+    specs = [(f"hc{i}", 256 if i % 3 else 384, 64 + 16 * (i % 4)) for i in range(40)]
+    shared = {K: synth.activation(K, K + 1) for K in (256, 384)}
+    total = sum(N for _, _, N in specs)
+    out_all = torch.full((total,), float("nan"), dtype=torch.float32).pin_memory()
+    xs_h, outs_h, scales, wants, off = [], [], [], [], 0
+    for i, (nm, K, N) in enumerate(specs):
+        t = synth.trits(K, N, 7 * i + 1)
+        ws = synth.weight_scale(i + 3)
+        tb.install(nm, synth.pack_v11(t), FMT_V11, K, N, float(ws))
+        if i < 12:
+            x, xsc = shared[K]                      # same pointer for every user of this K
+            key = ("s", K)
+        else:
+            x, xsc = synth.activation(K, 100 + i)   # its own vector: 28 distinct ones
+            key = ("o", i)
+        xs_h.append((key, x, xsc))
+        outs_h.append(out_all[off:off + N])
+        off += N
+        scales.append(float(xsc))
+        wants.append(oracle.gemv_epilogue(exact_acc(x, t).astype(np.int32), xsc, ws))
+    pinned = {}
+    for key, x, _ in xs_h:
+        if key not in pinned:
+            pinned[key] = torch.from_numpy(x).pin_memory()
+    plan = tb.gemv_host_batch_plan([s[0] for s in specs], [pinned[k] for k, _, _ in xs_h], scales, outs_h)
+    l0 = tb.launch_count()
+    tb.gemv_host_batch(plan)
+    assert tb.launch_count() - l0 == 2          # 2 shared + 28 own vectors: 16 per launch
+    for o, w in zip(outs_h, wants):
+        assert np.array_equal(o.numpy().view(np.uint32), w.view(np.uint32))
+    assert tb.device_status() == 0
+    for nm, _, _ in specs:
+        tb.remove(nm)
+
+
+def test_sweep_plan_matches_single_launches(tb):
+    specs = [(f"sp{i}", (2048, 8192, 2560, 128)[i % 4], (512, 2048, 640, 96, 4096)[i % 5]) for i in range(23)]
+    xs = {}
+    for K in (2048, 8192, 2560, 128):
+        x, s = synth.activation(K, K + 9)
+        xs[K] = (dev(x), dev(np.array([s], np.float32)))
+    names, xin, sin, outs = [], [], [], []
+    for i, (nm, K, N) in enumerate(specs):
+        tb.install(nm, synth.pack_v11(synth.trits(K, N, 11 * i + 2)), FMT_V11, K, N, float(synth.weight_scale(i)))
+        names.append(nm)
+        xin.append(xs[K][0])
+        sin.append(xs[K][1])
+        outs.append(torch.full((N,), float("nan"), dtype=torch.float32, device="cuda"))
+    pid = tb.gemv_plan(names, xin, sin, outs)
+    l0 = tb.launch_count()
+    tb.gemv_plan_launch(pid)
+    tb.sync()
+    assert tb.launch_count() - l0 == 1
+    for nm, x, s, o in zip(names, xin, sin, outs):
+        assert torch.equal(o, tb.gemv(nm, x, s)), nm
+    # the plan reads x where it lies: new activations, same plan
+    x2, s2 = synth.activation(2048, 77)
+    xs[2048][0].copy_(torch.from_numpy(x2))
+    xs[2048][1].fill_(float(s2))
+    tb.gemv_plan_launch(pid)
+    tb.sync()
+    for nm, x, s, o in zip(names, xin, sin, outs):
+        assert torch.equal(o, tb.gemv(nm, x, s)), nm
+    # any change of the weight slots makes the plan stale
+    tb.remove(names[-1])
+    with pytest.raises(RuntimeError):
+        tb.gemv_plan_launch(pid)
+    tb.gemv_plan_destroy(pid)
+    assert tb.device_status() == 0
+    for nm in names[:-1]:
+        tb.remove(nm)
 
 
 def test_gemm_rows_match_gemv(tb):
