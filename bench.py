@@ -71,7 +71,7 @@ class ClockSampler:
         self.p = None
         try:
             self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                       "-lms", "100", "-i", str(gpu_index)], stdout=self.f, stderr=subprocess.DEVNULL)
+                                       "-lms", "20", "-i", str(gpu_index)], stdout=self.f, stderr=subprocess.DEVNULL)
         except Exception:  # noqa: BLE001
             self.p = None
 
@@ -102,6 +102,63 @@ class ClockSampler:
             hot = [s for s in sm if s >= 0.5 * max(sm)]
             out.update(sm_mhz=statistics.median(hot), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
         return out
+
+
+def per_shape_bench(tb, dev, peak, reps=20):
+    """Packed-trit GEMV GB/s per projection shape (Llama-3.2-1B and BitNet-2B).  A single small matrix
+    would sit in the 126 MB L2, so every shape is measured over R distinct device copies (at least
+    256 MB in total, at most 512 copies) touched once each per pass, as a decode step touches a layer's
+    weights once per token: `sweep` = the R copies as ONE sweep-plan launch, `per_launch` = R separate
+    launches in stream order (CUDA-graph replay)."""
+    import torch
+    from ter_b200 import FMT_V11, synth
+    shapes = [("llama-1b", nm, *synth.LLAMA_1B_SHAPES[nm]) for nm in ("q", "k", "gate", "down", "lm_head")]
+    shapes += [("bitnet-2b", nm, *synth.BITNET_2B_SHAPES[nm]) for nm in ("q", "k", "gate", "down")]
+    rows = []
+    cur = torch.cuda.current_stream()
+    for model, nm, K, N in shapes:
+        nbytes = K * N // 4
+        R = max(2, min(512, -(-(256 << 20) // nbytes)))
+        seed = synth.seed_for("shape", K, N)
+        w = synth.packed_v11_cuda(K, N, seed, dev)
+        names = [f"ps{i}" for i in range(R)]
+        for n_ in names:
+            tb.install(n_, w, FMT_V11, K, N, float(synth.weight_scale(seed)))
+        del w
+        x, sc = synth.activation(K, synth.seed_for("x", K))
+        xd, sd = torch.from_numpy(x).to(dev), torch.tensor([sc], dtype=torch.float32, device=dev)
+        outs = [torch.empty(N, dtype=torch.float32, device=dev) for _ in range(R)]
+        plan = tb.gemv_plan(names, [xd] * R, [sd] * R, outs)
+
+        def run_single():
+            for n_, o in zip(names, outs):
+                tb.gemv(n_, xd, sd, o)
+        graph = tb.capture(run_single)
+
+        def t(fn):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / reps
+        ms_sweep = t(lambda: tb.gemv_plan_launch(plan, stream=cur))
+        ms_single = t(lambda: tb.graph_launch(graph, stream=cur))
+        sweep_gbs = R * nbytes / (ms_sweep * 1e-3) / 1e9
+        rows.append({"model": model, "proj": nm, "K": K, "N": N, "copies": R,
+                     "sweep_gbs": round(sweep_gbs, 1), "sweep_frac": round(sweep_gbs / peak, 3),
+                     "per_launch_gbs": round(R * nbytes / (ms_single * 1e-3) / 1e9, 1),
+                     "per_launch_us": round(ms_single * 1e3 / R, 2)})
+        tb.gemv_plan_destroy(plan)
+        tb.graph_destroy(graph)
+        for n_ in names:
+            tb.remove(n_)
+        del outs
+    return rows
 
 
 def cpu_reference_run(steps: int, warmup: int, threads: int):
@@ -219,6 +276,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true")
+    ap.add_argument("--no-per-shape", action="store_true")
     ap.add_argument("--layers", type=int, default=16, help="layers of the fabric (profiling captures use fewer)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -357,13 +415,19 @@ def main():
     ms_chain, _ = timed(lambda: tb.graph_launch(graph_chain), args.steps, args.warmup)
     e2e_steps = max(3, args.steps // 5)
     ms_e2e, _ = timed(step_host, e2e_steps, 3)
-    clocks = sampler.stop() if sampler else {}
+    clocks = {}
 
     total_bytes = step_bytes * world
     value = total_bytes * args.steps / (ms * 1e-3) / 1e9
     e2e_value = total_bytes * e2e_steps / (ms_e2e * 1e-3) / 1e9
     peak, peak_src = peaks()
     per_gpu = step_bytes * args.steps / (ms * 1e-3) / 1e9
+
+    per_shape = None
+    if not args.no_per_shape and rank == 0:
+        per_shape = per_shape_bench(tb, dev, peak)
+    if sampler:
+        clocks = sampler.stop()
 
     # ---- decode tokens/s (BASELINE configs[3]: Llama-3.2-1B architecture, batch 1, prompt 128 + 256 greedy)
     decode = None
@@ -413,6 +477,7 @@ def main():
                          "traffic": None, "peak_source": peak_src,
                          "traffic_note": "ncu: 263.0 MB DRAM per 262.7 MB algorithmic on the lm_head matrix (profiles/)",
                          "note": "achieved = packed weight bytes of the launch / its CUDA-event time (one launch per step)"},
+            "per_shape": per_shape,
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": UNIT, "steps": e2e_steps,
                     # what the call copies up: each distinct activation vector once, a 32-byte descriptor per
