@@ -13,6 +13,8 @@
 //     output layout allows.
 #include <stdlib.h>
 
+#include <algorithm>
+
 #include "handle.h"
 
 namespace terb {
@@ -67,6 +69,18 @@ struct SweepBuilder {
         tiles += w.tiles();
         ++n;
         return u;
+    }
+    // Table launches: longest strips first.  Strips go to warps round-robin, so equal strips in a row are
+    // spread evenly, and the long ones (large K) end up one per warp instead of clustering.
+    void sort_by_work() {
+        std::stable_sort(descs, descs + n, [&](const GemvDesc& a, const GemvDesc& b) {
+            return p.uKpad[a.xid] > p.uKpad[b.xid];
+        });
+        int t = 0;
+        for (int i = 0; i < n; ++i) {
+            descs[i].tile_begin = t;
+            t += (descs[i].N + 15) / 16;
+        }
     }
     void finish(int* status) {
         p.n_mats = n;
@@ -156,7 +170,9 @@ int ter_b200_gemv_plan_create(ter_b200_handle_t* h, int n, const char* const* sl
     GemvDesc* tab = nullptr;
     if (!rc) {
         cudaError_t e = cudaSetDevice(h->device);
-        if (e == cudaSuccess) e = cudaMalloc((void**)&tab, round256((size_t)n * sizeof(GemvDesc)));
+        const size_t tab_bytes = round256((size_t)n * sizeof(GemvDesc));
+        b->sort_by_work();
+        if (e == cudaSuccess) e = cudaMalloc((void**)&tab, tab_bytes);
         if (e == cudaSuccess) e = cudaMemcpy(tab, b->descs, (size_t)n * sizeof(GemvDesc), cudaMemcpyHostToDevice);
         if (e != cudaSuccess) {
             if (tab) cudaFree(tab);
@@ -274,6 +290,7 @@ int ter_b200_gemv_host_batch(ter_b200_handle_t* h, int n, const char* const* slo
             oo += (size_t)s->w.Npad;
             count_gemv(h, s->w.K, s->w.N, 1);
         }
+        b->sort_by_work();
         memcpy(h->hpin + tab_off, b->descs, sizeof(GemvDesc) * (size_t)cn);
         b->finish(h->status_dev);
         b->p.table = (const GemvDesc*)(h->hx_dev + tab_off);

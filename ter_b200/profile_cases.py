@@ -1,6 +1,7 @@
 """Small, self-contained workloads for profiling one kernel at a time:
 
     python -m ter_b200.profile_cases gemv_stream      # 2048 x 513024 GEMV (263 MB of trits), 4 launches
+    python -m ter_b200.profile_cases sweep            # Llama-1B fabric (113 matrices, 309 MB) as one sweep-plan launch, 4 launches
     python -m ter_b200.profile_cases gemm             # BitNet gate 2560 x 6912 GEMM at M = 16, 256, 1024
     python -m ter_b200.profile_cases decode llama     # three decode steps at position ~300 (or: bitnet)
 
@@ -56,6 +57,40 @@ def gemv_stream():
     print(f"gemv {K}x{N}: {ms * 1e3:.1f} us  {K * N // 4 / ms / 1e6:.0f} GB/s  status {tb.device_status()}")
 
 
+def sweep():
+    import torch
+    from . import FMT_V11, TerB200, synth
+    tb = TerB200(0)
+    dev = torch.device("cuda:0")
+    names, xs, ss, outs, nbytes = [], [], [], [], 0
+    acts = {}
+    for K in (2048, 8192):
+        x, sc = synth.activation(K, K)
+        acts[K] = (torch.from_numpy(x).cuda(), torch.tensor([sc], device=dev))
+    mats = [(f"L{L}.{nm}", *synth.LLAMA_1B_SHAPES[nm]) for L in range(16) for nm in synth.MAT_ORDER]
+    mats.append(("lm_head", *synth.LLAMA_1B_SHAPES["lm_head"]))
+    for i, (nm, K, N) in enumerate(mats):
+        tb.install(nm, synth.packed_v11_cuda(K, N, i + 1, dev), FMT_V11, K, N, 0.03)
+        names.append(nm)
+        xs.append(acts[K][0])
+        ss.append(acts[K][1])
+        outs.append(torch.empty(N, device=dev))
+        nbytes += K * N // 4
+    plan = tb.gemv_plan(names, xs, ss, outs)
+    cur = torch.cuda.current_stream()
+    for _ in range(3):
+        tb.gemv_plan_launch(plan, stream=cur)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    tb.gemv_plan_launch(plan, stream=cur)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    print(f"sweep of {len(mats)} matrices, {nbytes / 1e6:.1f} MB: {ms * 1e3:.1f} us  {nbytes / ms / 1e6:.0f} GB/s  "
+          f"status {tb.device_status()}")
+
+
 def gemm():
     import torch
     from . import FMT_V11, TerB200, synth
@@ -89,4 +124,4 @@ def decode(which="llama"):
 
 if __name__ == "__main__":
     case = sys.argv[1] if len(sys.argv) > 1 else "gemv_stream"
-    {"gemv_stream": gemv_stream, "gemm": gemm, "decode": lambda: decode(*sys.argv[2:3])}[case]()
+    {"gemv_stream": gemv_stream, "sweep": sweep, "gemm": gemm, "decode": lambda: decode(*sys.argv[2:3])}[case]()
