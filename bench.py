@@ -32,6 +32,8 @@ sys.path.insert(0, ROOT)
 
 METRIC = "packed-trit GEMV HBM GB/s (M=1, Llama-3.2-1B fabric sweep)"
 UNIT = "GB/s"
+# DRAM bytes of one sweep launch over the full fabric (ncu: 308,983,296 read + 5,458,688 written)
+NCU_TRAFFIC_BYTES = 314441984
 LAYER_MATS = ["q", "k", "v", "o", "gate", "up", "down"]
 
 
@@ -79,6 +81,11 @@ class ClockSampler:
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         if self.p is None:
             return out
+        for _ in range(30):                      # a very short timed region: wait for the first samples
+            self.f.flush()
+            if os.path.getsize(self.f.name) > 0:
+                break
+            time.sleep(0.02)
         self.p.terminate()
         try:
             self.p.wait(timeout=5)
@@ -474,8 +481,10 @@ def main():
                                 "note": "same pass as one stream-ordered chain with programmatic dependent launch "
                                         "(each GEMV waits for the previous one, as in a decode step)"},
             "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
-                         "traffic": None, "peak_source": peak_src,
-                         "traffic_note": "ncu: 263.0 MB DRAM per 262.7 MB algorithmic on the lm_head matrix (profiles/)",
+                         "traffic": NCU_TRAFFIC_BYTES if args.layers == 16 else None, "peak_source": peak_src,
+                         "algorithmic_bytes": step_bytes,
+                         "traffic_note": "dram__bytes_read.sum + dram__bytes_write.sum of one launch of this workload, from "
+                                         "the ncu capture summarised in profiles/gemv_trit_kernel_table_sweep_llama1b_fabric.md",
                          "note": "achieved = packed weight bytes of the launch / its CUDA-event time (one launch per step)"},
             "per_shape": per_shape,
             "cpu_baseline": cpu,

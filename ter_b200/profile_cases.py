@@ -1,7 +1,7 @@
 """Small, self-contained workloads for profiling one kernel at a time:
 
     python -m ter_b200.profile_cases gemv_stream      # 2048 x 513024 GEMV (263 MB of trits), 4 launches
-    python -m ter_b200.profile_cases sweep            # Llama-1B fabric (113 matrices, 309 MB) as one sweep-plan launch, 4 launches
+    python -m ter_b200.profile_cases sweep            # Llama-1B fabric (113 matrices, 309 MB) as one sweep-plan launch, 8 launches
     python -m ter_b200.profile_cases gemm             # BitNet gate 2560 x 6912 GEMM at M = 16, 256, 1024
     python -m ter_b200.profile_cases decode llama     # three decode steps at position ~300 (or: bitnet)
 
@@ -83,10 +83,11 @@ def sweep():
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    tb.gemv_plan_launch(plan, stream=cur)
+    for _ in range(4):
+        tb.gemv_plan_launch(plan, stream=cur)
     e1.record()
     torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1)
+    ms = e0.elapsed_time(e1) / 4
     print(f"sweep of {len(mats)} matrices, {nbytes / 1e6:.1f} MB: {ms * 1e3:.1f} us  {nbytes / ms / 1e6:.0f} GB/s  "
           f"status {tb.device_status()}")
 
