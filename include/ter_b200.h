@@ -40,6 +40,7 @@ typedef struct ter_b200_handle_t ter_b200_handle_t;
 #define TER_B200_E_STATE      (-10)  /* call made in the wrong state             */
 #define TER_B200_E_TIMEOUT    (-11)  /* a bounded device-side wait ran out       */
 #define TER_B200_E_VALUE      (-12)  /* payload value outside {-1,0,+1}          */
+#define TER_B200_E_IO         (-13)  /* file missing, short, or not a model file */
 
 /* The reference's KernelTable has 32 slots of 32-character names
  * (include/ter/kernels.hpp:21-38) because it holds five bytecode kernels.  Here a slot holds a
@@ -280,6 +281,17 @@ int ter_b200_model_set_vector(ter_b200_handle_t* h, int layer, int which, const 
 int ter_b200_model_set_embd(ter_b200_handle_t* h, const uint16_t* table);
 int ter_b200_model_set_embd_dev(ter_b200_handle_t* h, const uint16_t* table_dev);
 /* Start `batch` sequences at position 0 (the KV cache content is simply overwritten as they grow). */
+/* Creates the model from one of the reference's packed-model files and fills it: 'LLRT'
+ * (tools/convert_llama_to_packed.py:13-43; the reference reads it in load_model_from_bin,
+ * cuda/ter_cuda_forward_packed.cu:589-667) or 'TERT' (tools/convert_bitnet_to_packed.py:4-31,
+ * cuda/ter_cuda_forward_bitnet.cu:698-784).  smax > 0 overrides the file's context length (the
+ * reference's files say 64), max_batch as in the cfg.  The fp16 embeddings of the file are rounded
+ * to bf16.  cfg_out (may be NULL) receives the configuration.  Errors are return codes
+ * (TER_B200_E_IO for a missing / short / foreign file); nothing exits the process.
+ * ter_b200_model_file_info only reads the header and needs no handle and no GPU. */
+int ter_b200_model_load_file(ter_b200_handle_t* h, const char* path, int smax, int max_batch,
+                             ter_b200_model_cfg_t* cfg_out);
+int ter_b200_model_file_info(const char* path, ter_b200_model_cfg_t* cfg_out);
 int ter_b200_model_reset(ter_b200_handle_t* h, int batch);
 /* One decode step for every sequence: forward_token (cuda/ter_cuda_forward_packed.cu:671-678).
  * tokens_host / pos_host ([batch], may be NULL: continue from the device-resident state, i.e. the

@@ -16,8 +16,8 @@ _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "libter_b200.so")
 
 FMT_V11, FMT_ROWMAJOR, FMT_I32 = 0, 1, 2
-E_NULL, E_UNKNOWN, E_ALLOC, E_NARGS, E_SHAPE, E_FULL, E_NAME, E_CUDA, E_NCCL, E_STATE, E_TIMEOUT, E_VALUE = \
-    -1, -2, -3, -4, -5, -6, -7, -8, -9, -10, -11, -12
+E_NULL, E_UNKNOWN, E_ALLOC, E_NARGS, E_SHAPE, E_FULL, E_NAME, E_CUDA, E_NCCL, E_STATE, E_TIMEOUT, E_VALUE, E_IO = \
+    -1, -2, -3, -4, -5, -6, -7, -8, -9, -10, -11, -12, -13
 
 
 class TerB200Error(RuntimeError):
@@ -36,6 +36,13 @@ class ModelCfg(C.Structure):
     _fields_ = [("arch", C.c_int32), ("H", C.c_int32), ("F", C.c_int32), ("L", C.c_int32), ("V", C.c_int32),
                 ("Nh", C.c_int32), ("Nkv", C.c_int32), ("Hd", C.c_int32), ("Smax", C.c_int32), ("eps", C.c_float),
                 ("rope_theta", C.c_double), ("lm_head_packed", C.c_int32), ("max_batch", C.c_int32)]
+
+
+def model_file_info(path: str) -> dict:
+    """Header of an 'LLRT' / 'TERT' packed-model file (no GPU needed)."""
+    c = ModelCfg()
+    _check(load().ter_b200_model_file_info(os.fsencode(path), C.byref(c)), f"model_file_info {path}")
+    return {k: getattr(c, k) for k, _ in ModelCfg._fields_}
 
 
 class BlobHdr(C.Structure):
@@ -90,6 +97,8 @@ SIGNATURES = {
     "ter_b200_model_set_vector": (_I, [_VP, _I, _I, _VP]),
     "ter_b200_model_set_embd": (_I, [_VP, _VP]),
     "ter_b200_model_set_embd_dev": (_I, [_VP, _VP]),
+    "ter_b200_model_load_file": (_I, [_VP, _CP, _I, _I, C.POINTER(ModelCfg)]),
+    "ter_b200_model_file_info": (_I, [_CP, C.POINTER(ModelCfg)]),
     "ter_b200_model_reset": (_I, [_VP, _I]),
     "ter_b200_decode_step": (_I, [_VP, _VP, _VP, _VP, _VP]),
     "ter_b200_model_logits": (_I, [_VP, _VP]),
@@ -450,6 +459,16 @@ class TerB200:
         self._ck(self.L.ter_b200_model_create(self.h, C.byref(c)), "model_create")
         self.model_cfg = dict(cfg, max_batch=max_batch)
         self._batch = 1
+
+    def model_load_file(self, path: str, smax: int = 0, max_batch: int = 1) -> dict:
+        """Creates and fills the model from an 'LLRT' / 'TERT' packed-model file; returns its configuration."""
+        c = ModelCfg()
+        self._ck(self.L.ter_b200_model_load_file(self.h, os.fsencode(path), smax, max_batch, C.byref(c)),
+                 f"model_load_file {path}")
+        cfg = {k: getattr(c, k) for k, _ in ModelCfg._fields_}
+        self.model_cfg = dict(cfg)
+        self._batch = 1
+        return cfg
 
     def model_set_matrix(self, layer, which, data, fmt, scale):
         import numpy as np

@@ -14,7 +14,6 @@ reference.  Run from the repository root in a container that has the reference c
 import ast
 import os
 import re
-import struct
 import subprocess
 import sys
 
@@ -22,7 +21,7 @@ import numpy as np
 
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 sys.path.insert(0, ROOT)
-from ter_b200 import synth  # noqa: E402
+from ter_b200 import modelfile, synth  # noqa: E402
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 REF = os.environ.get("TER_REFERENCE", "/root/reference")
@@ -36,36 +35,8 @@ CASES = {
 }
 
 
-def bf16_to_f32(a):
-    return (a.astype(np.uint32) << 16).view(np.float32)
-
-
 def write_bin(case):
-    c = case
-    mats, vecs, embd = {}, {}, None
-    for item in synth.model_weights(c, c["seed"]):
-        if item[0] == "embd":
-            embd = item[1]
-        elif item[0] == "vector":
-            vecs[(item[1], item[2])] = item[3]
-        else:
-            mats[(item[1], item[2])] = (item[3], item[4])
-    e32 = bf16_to_f32(embd)
-    e16 = e32.astype(np.float16)
-    assert np.array_equal(e16.astype(np.float32), e32), "bf16 embeddings must be exact in fp16"
-    with open(c["bin"], "wb") as f:
-        hdr = struct.pack("<II8Iff", c["magic"], 1, c["H"], c["F"], c["L"], c["V"], c["Nh"], c["Nkv"], c["Hd"],
-                          c["Smax"], c["rope_theta"], c["eps"])
-        f.write(hdr + b"\0" * (64 - len(hdr)))
-        f.write(e16.tobytes())
-        f.write(vecs[(-1, 0)].astype(np.float32).tobytes())
-        for L in range(c["L"]):
-            for vi in range(4 if c["arch"] == 1 else 2):
-                f.write(vecs[(L, vi)].astype(np.float32).tobytes())
-            for wi in range(7):
-                packed, scale = mats[(L, wi)]
-                f.write(np.ascontiguousarray(packed).tobytes())
-                f.write(struct.pack("<f", float(scale)))
+    modelfile.write_packed_model(case["bin"], case, synth.model_weights(case, case["seed"]))
 
 
 def main():

@@ -68,3 +68,32 @@ def test_create_without_gpu_returns_null():
     assert L.ter_b200_create(0) is None
     with pytest.raises(RuntimeError):
         api.TerB200(0)
+
+
+def test_packed_model_file_header_round_trip(tmp_path):
+    """The writer and the library's header reader agree on the reference's 64-byte header
+    (tools/convert_llama_to_packed.py:13-24); foreign and short files are return codes."""
+    import numpy as np
+    from ter_b200 import modelfile, synth
+    cfg = dict(arch=1, H=128, F=256, L=1, V=512, Nh=2, Nkv=1, Hd=64, Smax=48, eps=1e-5, rope_theta=500000.0)
+    path = str(tmp_path / "tiny_tert.bin")
+    modelfile.write_packed_model(path, cfg, synth.model_weights(cfg, 5))
+    Hkv = cfg["Nkv"] * cfg["Hd"]
+    per_layer = 4 * (3 * cfg["H"] + cfg["F"]) + 7 * 4 + (2 * cfg["H"] * cfg["H"] + 2 * cfg["H"] * Hkv + 3 * cfg["H"] * cfg["F"]) // 4
+    assert os.path.getsize(path) == 64 + 2 * cfg["V"] * cfg["H"] + 4 * cfg["H"] + cfg["L"] * per_layer
+    got = api.model_file_info(path)
+    for k in ("arch", "H", "F", "L", "V", "Nh", "Nkv", "Hd", "Smax"):
+        assert got[k] == cfg[k], k
+    assert got["eps"] == np.float32(cfg["eps"]) and got["rope_theta"] == cfg["rope_theta"]
+    assert modelfile.read_header(path)["arch"] == 1
+    L = api.load()
+    c = api.ModelCfg()
+    assert L.ter_b200_model_file_info(None, C.byref(c)) == api.E_NULL
+    assert L.ter_b200_model_file_info(str(tmp_path / "missing.bin").encode(), C.byref(c)) == api.E_IO
+    bad = tmp_path / "bad.bin"
+    bad.write_bytes(b"GGUF" + b"\0" * 100)
+    assert L.ter_b200_model_file_info(str(bad).encode(), C.byref(c)) == api.E_IO
+    short = tmp_path / "short.bin"
+    short.write_bytes(open(path, "rb").read(40))
+    assert L.ter_b200_model_file_info(str(short).encode(), C.byref(c)) == api.E_IO
+    assert L.ter_b200_model_load_file(None, path.encode(), 0, 1, None) == api.E_NULL

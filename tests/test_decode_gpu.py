@@ -9,7 +9,7 @@ import pytest
 sys.path.insert(0, os.path.dirname(__file__))
 sys.path.insert(0, os.path.join(os.path.dirname(__file__), "golden"))
 import modelutil  # noqa: E402
-from ter_b200 import synth  # noqa: E402
+from ter_b200 import api, synth  # noqa: E402
 
 pytestmark = pytest.mark.gpu
 
@@ -98,6 +98,33 @@ def test_reference_numpy_forward_tokens_on_gpu(tb, golden_dir):
         want = g[f"{name}_tokens"]
         out = tb.generate(np.array([128000], np.int32), len(want))
         assert out[0].tolist() == want.tolist(), name
+
+
+def test_packed_model_files_load_and_reproduce_reference_tokens(tb, golden_dir, tmp_path):
+    """'LLRT' and 'TERT' files byte-identical to the ones the reference's scripts were run on, read by
+    the library's loader: the greedy tokens are the ones those scripts printed."""
+    import make_pyfwd_golden as mk
+    from ter_b200 import TerB200Error, modelfile
+    g = np.load(os.path.join(golden_dir, "pyfwd_tokens.npz"))
+    for name in ("llama", "bitnet"):
+        case = mk.CASES[name]
+        path = str(tmp_path / f"{name}.bin")
+        modelfile.write_packed_model(path, case, synth.model_weights(case, case["seed"]))
+        cfg = tb.model_load_file(path)
+        assert (cfg["arch"], cfg["H"], cfg["L"], cfg["Smax"]) == (case["arch"], case["H"], case["L"], case["Smax"])
+        want = g[f"{name}_tokens"]
+        out = tb.generate(np.array([128000], np.int32), len(want))
+        assert out[0].tolist() == want.tolist(), name
+        # a longer context than the file's, and a truncated file
+        cfg2 = tb.model_load_file(path, smax=96)
+        assert cfg2["Smax"] == 96
+        assert tb.generate(np.array([128000], np.int32), len(want))[0].tolist() == want.tolist()
+        cut = str(tmp_path / f"{name}_cut.bin")
+        with open(path, "rb") as f, open(cut, "wb") as o:
+            o.write(f.read(os.path.getsize(path) - 1000))
+        with pytest.raises(TerB200Error) as ei:
+            tb.model_load_file(cut)
+        assert ei.value.code == api.E_IO
 
 
 @pytest.mark.parametrize("base,L", [(synth.LLAMA_1B_CFG, 3), (synth.BITNET_2B_CFG, 2)])
