@@ -443,7 +443,8 @@ def main():
         torch.cuda.empty_cache()
         tb = TerB200(local)
         if world > 1:
-            tb.comm_init_from_torch()      # tensor parallel: output-dimension sharding + NCCL all-gathers
+            tb.comm_init_from_torch()      # tensor parallel: output-dimension sharding, slices exchanged over peer memory
+            tb.set_option("tp_p2p", int(os.environ.get("TER_TP_P2P", "1")))   # 0: NCCL all-gathers, for comparison
         decode = decode_bench(tb, dev, 0)  # the same model on every rank; the library keeps its slice
         if world > 1:
             t = torch.tensor([decode["ms_per_token"]], device=dev)
@@ -452,6 +453,7 @@ def main():
             decode["tokens_per_s"] = 1e3 / decode["ms_per_token"]
             decode["note"] += f"; tensor parallel over {world} GPUs (strong scaling, max over ranks)"
             decode["parallelism"] = f"tp{world}"
+            decode["exchange"] = "peer-memory kernel" if os.environ.get("TER_TP_P2P", "1") != "0" else "nccl all-gather"
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:

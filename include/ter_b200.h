@@ -317,9 +317,14 @@ float ter_b200_last_generate_ms(const ter_b200_handle_t* h);
  * ter_b200_model_create.  With a communicator of size G the model keeps columns
  * [N*r/G, N*(r+1)/G) of every projection (output-dimension sharding: each output column is an
  * independent exact dot product), the vocabulary rows [V*r/G, V*(r+1)/G) of the lm_head, and
- * all-gathers the fp32 output slices over NCCL inside the captured step, so every rank holds the
- * same bits as a single GPU would and greedy tokens are identical at every G.  Requirements:
- * N/G a multiple of 16 for every projection, matrices given in TER_B200_FMT_V11. */
+ * exchanges the fp32 output slices inside the captured step, so every rank holds the same bits as a
+ * single GPU would and greedy tokens are identical at every G.  The exchange is a kernel of peer
+ * stores over NVLink into buffers that every rank has mapped (CUDA IPC; NCCL only carries the
+ * set-up), or NCCL all-gathers when the GPUs have no peer access or option "tp_p2p" is 0.
+ * ter_b200_model_create, the destruction of a model and ter_b200_generate are then COLLECTIVE: every
+ * rank makes the same calls in the same order.  A rank that stops arriving makes the others' waits
+ * run out after 2 s (TER_B200_E_TIMEOUT), not hang.  Requirements: at most 8 ranks, N/G a multiple
+ * of 16 for every projection, matrices given in TER_B200_FMT_V11. */
 int ter_b200_comm_unique_id(uint8_t* id128);
 int ter_b200_comm_init(ter_b200_handle_t* h, const uint8_t* id128, int rank, int size);
 void ter_b200_comm_destroy(ter_b200_handle_t* h);
@@ -341,7 +346,10 @@ int ter_b200_graph_destroy(ter_b200_handle_t* h, int graph_id);
 int ter_b200_device_status(ter_b200_handle_t* h);
 /* Last CUDA error code seen by the handle (cudaError_t as int), 0 if none. */
 int ter_b200_last_cuda_error(const ter_b200_handle_t* h);
-/* Tuning knobs (integers): "gemv_ctas_per_sm", "gemv_stages", "pdl". Returns -2 if unknown. */
+/* Tuning knobs (integers): "gemv_ctas_per_sm", "gemv_stages", "gemv_split_max_strips", "pdl",
+ * "fuse_quant", "gemm_min_m", "gemm_split_k", "attn_inline_merge", and "tp_p2p" (1, default: tensor-
+ * parallel output slices travel by peer stores over NVLink inside one small kernel per exchange;
+ * 0: NCCL all-gathers; read by the next ter_b200_model_create).  Returns -2 if unknown. */
 int ter_b200_set_option(ter_b200_handle_t* h, const char* key, int value);
 /* Number of kernels this handle has launched since creation (or the last reset). */
 uint64_t ter_b200_launch_count(const ter_b200_handle_t* h);

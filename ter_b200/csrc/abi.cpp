@@ -196,6 +196,7 @@ ter_b200_handle_t* ter_b200_create(int device) {
     h->gemv_cfg = GemvLaunchCfg();
     h->gemm_min_m = 4;
     h->attn_inline_merge = 1;
+    h->tp_p2p = 1;
     h->gemm_split_k = 1;
     int sms = 0;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) sms = 148;
@@ -493,6 +494,8 @@ int ter_b200_set_option(ter_b200_handle_t* h, const char* key, int value) {
         h->gemm_min_m = value;
     } else if (strcmp(key, "attn_inline_merge") == 0) {
         h->attn_inline_merge = value ? 1 : 0;
+    } else if (strcmp(key, "tp_p2p") == 0) {
+        h->tp_p2p = value ? 1 : 0;      // read by the next ter_b200_model_create
     } else if (strcmp(key, "gemm_dbg") == 0) {
         h->gemm_dbg = value;
     } else if (strcmp(key, "gemm_split_k") == 0) {

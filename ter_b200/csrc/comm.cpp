@@ -27,6 +27,7 @@ struct Comm {
     fn_group group_start = nullptr, group_end = nullptr;
     void* comm = nullptr;
     int rank = 0, size = 1;
+    uint8_t* scratch = nullptr;   // device, kMaxRanks * 64 bytes: handle exchange and barriers
 };
 
 static void* open_nccl() {
@@ -65,6 +66,88 @@ int comm_all_gather_bytes(ter_b200_handle_t* h, void* buf, size_t bytes, cudaStr
     const int rc = c->all_gather((const char*)buf + (size_t)c->rank * bytes, buf, bytes, /*ncclInt8*/ 0, c->comm, st);
     return rc == 0 ? TER_B200_OK : TER_B200_E_NCCL;
 }
+// Host-level barrier over the communicator (a tiny all-gather followed by a stream synchronise).
+int comm_barrier(ter_b200_handle_t* h, cudaStream_t st) {
+    Comm* c = h->comm;
+    if (!c || c->size == 1) return TER_B200_OK;
+    int rc = comm_all_gather_bytes(h, c->scratch, 64, st);
+    if (rc) return rc;
+    TERB_CUDA(h, cudaStreamSynchronize(st));
+    return TER_B200_OK;
+}
+
+// Gathers one 64-byte record per rank (blocking).
+static int gather64(ter_b200_handle_t* h, const void* mine, void* all, cudaStream_t st) {
+    Comm* c = h->comm;
+    TERB_CUDA(h, cudaMemcpyAsync(c->scratch + (size_t)c->rank * 64, mine, 64, cudaMemcpyHostToDevice, st));
+    int rc = comm_all_gather_bytes(h, c->scratch, 64, st);
+    if (rc) return rc;
+    TERB_CUDA(h, cudaMemcpyAsync(all, c->scratch, (size_t)c->size * 64, cudaMemcpyDeviceToHost, st));
+    TERB_CUDA(h, cudaStreamSynchronize(st));
+    return TER_B200_OK;
+}
+
+// Allocates `bytes` of zeroed device memory that every peer maps (CUDA IPC, one process per GPU).
+// All ranks call this together.  Returns TER_B200_E_STATE on EVERY rank when any rank could not map
+// a peer (no peer access between the GPUs): the caller then stays on NCCL collectives.
+int comm_arena_create(ter_b200_handle_t* h, size_t bytes, PeerArena* a, cudaStream_t st) {
+    Comm* c = h->comm;
+    if (!c || c->size < 2 || c->size > kMaxRanks) return TER_B200_E_STATE;
+    memset(a, 0, sizeof *a);
+    TERB_CUDA(h, cudaMalloc((void**)&a->base, bytes));
+    a->bytes = bytes;
+    cudaError_t e = cudaMemset(a->base, 0, bytes);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    union { cudaIpcMemHandle_t hd; char raw[64]; } mine, all[kMaxRanks];
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    memset(&mine, 0, sizeof mine);
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&mine.hd, a->base);
+    int ok = e == cudaSuccess ? 1 : 0;
+    int rc = gather64(h, &mine, all, st);       // everybody's memset is done once this returns
+    if (rc) { cudaFree(a->base); a->base = nullptr; return rc; }
+    for (int r = 0; r < c->size && ok; ++r) {
+        if (r == c->rank) { a->peer[r] = a->base; continue; }
+        void* ptr = nullptr;
+        if (cudaIpcOpenMemHandle(&ptr, all[r].hd, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+            (void)cudaGetLastError();
+            ok = 0;
+        } else {
+            a->peer[r] = (uint8_t*)ptr;
+        }
+    }
+    // consensus: one rank without peer access turns the arena off everywhere
+    char vote[64] = {}, votes[kMaxRanks][64];
+    vote[0] = (char)ok;
+    rc = gather64(h, vote, votes, st);
+    int all_ok = rc == 0;
+    for (int r = 0; r < c->size && all_ok; ++r) all_ok = votes[r][0] != 0;
+    if (!all_ok) {
+        for (int r = 0; r < c->size; ++r)
+            if (r != c->rank && a->peer[r]) cudaIpcCloseMemHandle(a->peer[r]);
+        comm_barrier(h, st);                    // nobody frees while a peer may still be mapping
+        cudaFree(a->base);
+        memset(a, 0, sizeof *a);
+        return rc ? rc : TER_B200_E_STATE;
+    }
+    a->open = true;
+    return TER_B200_OK;
+}
+
+// All ranks call this together, between steps: waits until every rank has stopped using the arenas.
+void comm_arena_destroy(ter_b200_handle_t* h, PeerArena* a, cudaStream_t st) {
+    if (!a->base) return;
+    Comm* c = h->comm;
+    cudaDeviceSynchronize();
+    if (c && a->open) {
+        comm_barrier(h, st);
+        for (int r = 0; r < c->size; ++r)
+            if (r != c->rank && a->peer[r]) cudaIpcCloseMemHandle(a->peer[r]);
+        comm_barrier(h, st);
+    }
+    cudaFree(a->base);
+    memset(a, 0, sizeof *a);
+}
+
 int comm_group_start(ter_b200_handle_t* h) {
     return (h->comm && h->comm->size > 1 && h->comm->group_start() != 0) ? TER_B200_E_NCCL : TER_B200_OK;
 }
@@ -104,15 +187,27 @@ int ter_b200_comm_init(ter_b200_handle_t* h, const uint8_t* id128, int rank, int
         NcclId id;
         memcpy(id.bytes, id128, 128);
         if (c->comm_init_rank(&c->comm, size, id, rank) != 0) { delete c; return TER_B200_E_NCCL; }
+        if (cudaMalloc((void**)&c->scratch, (size_t)kMaxRanks * 64) != cudaSuccess ||
+            cudaMemset(c->scratch, 0, (size_t)kMaxRanks * 64) != cudaSuccess) {
+            (void)cudaGetLastError();
+            c->comm_destroy(c->comm);
+            if (c->scratch) cudaFree(c->scratch);
+            delete c;
+            return TER_B200_E_ALLOC;
+        }
     }
     h->comm = c;
     return TER_B200_OK;
 }
 
+void ter_b200_model_free(ter_b200_handle_t* h);   // model.cpp: a model may hold a peer arena of this communicator
+
 void ter_b200_comm_destroy(ter_b200_handle_t* h) {
     if (!h || !h->comm) return;
     cudaSetDevice(h->device);
+    if (h->comm->size > 1) ter_b200_model_free(h);
     cudaDeviceSynchronize();
+    if (h->comm->scratch) cudaFree(h->comm->scratch);
     if (h->comm->comm) h->comm->comm_destroy(h->comm->comm);
     delete h->comm;
     h->comm = nullptr;

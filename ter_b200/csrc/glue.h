@@ -86,4 +86,26 @@ struct SelectParams {
 };
 cudaError_t launch_select(const SelectParams& p, bool pdl, cudaStream_t st);
 
+// Tensor-parallel exchange of output slices over peer memory (exchange_sm100.cu).  base[r] = rank r's
+// arena as mapped in THIS process (base[rank] = the local one).  A segment is one exchanged buffer:
+// seg_buf_off = byte offset of the FULL buffer in the arena, seg_floats = floats per rank slice (rank
+// r's slice starts at float r*seg_floats).  recv_off: byte offset of this point's receive block,
+// uint4[size][words_total]; seq: this point's int[kMaxExchangeCtas] sequence words (local).
+constexpr int kMaxRanks = 8;
+constexpr int kMaxExchangeSegs = 3;
+constexpr int kMaxExchangePoints = 512;
+constexpr int kMaxExchangeCtas = 64;
+struct ExchangeParams {
+    uint8_t* base[kMaxRanks];
+    size_t seg_buf_off[kMaxExchangeSegs];
+    int seg_floats[kMaxExchangeSegs];
+    int n_seg, words_total;
+    int rank, size;
+    size_t recv_off;
+    int* seq;
+    int* status;
+    int point;
+};
+cudaError_t launch_peer_exchange(const ExchangeParams& p, bool pdl, cudaStream_t st);
+
 }  // namespace terb

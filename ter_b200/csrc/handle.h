@@ -25,6 +25,14 @@ struct TerbPlan {
     terb::GemvDesc* table_dev = nullptr;
 };
 
+// Device memory that every rank of the communicator has mapped (comm.cpp).
+struct PeerArena {
+    uint8_t* base;                  // local allocation
+    size_t bytes;
+    uint8_t* peer[terb::kMaxRanks]; // peer[r] = rank r's arena in this process's address space; peer[rank] = base
+    bool open;
+};
+
 struct TerbModel;   // decode-forward state (model.cpp)
 namespace terb { struct Comm; }
 
@@ -62,6 +70,7 @@ struct ter_b200_handle_t {
     int gemm_min_m;             // batches below this go row by row through the GEMV kernel
     int gemm_split_k;           // 0 = never split K
     int gemm_dbg;
+    int tp_p2p;                 // 1: tensor-parallel exchanges over peer memory (exchange_sm100.cu); 0: NCCL all-gathers
     int attn_inline_merge;      // 1: the last attention CTA of a KV head merges the chunks (no second kernel)
     cudaGraphExec_t graphs[16];
     uint64_t graph_launches[16];   // kernels recorded in each graph
@@ -117,6 +126,9 @@ void free_weight(DevWeight* w);
 int comm_rank(const ter_b200_handle_t* h);
 int comm_size(const ter_b200_handle_t* h);
 int comm_all_gather_bytes(ter_b200_handle_t* h, void* buf, size_t bytes_per_rank, cudaStream_t st);
+int comm_barrier(ter_b200_handle_t* h, cudaStream_t st);
+int comm_arena_create(ter_b200_handle_t* h, size_t bytes, PeerArena* a, cudaStream_t st);
+void comm_arena_destroy(ter_b200_handle_t* h, PeerArena* a, cudaStream_t st);
 int comm_group_start(ter_b200_handle_t* h);
 int comm_group_end(ter_b200_handle_t* h);
 void model_invalidate_graph(ter_b200_handle_t* h);

@@ -32,6 +32,11 @@ struct TerbModel {
     uint64_t graph_launches;
     cudaEvent_t ev0, ev1;
     float last_ms;
+    // tensor parallelism over peer memory: the exchanged buffers (hidden, q, k, v, gate, up, logits) and
+    // the flag words of the exchange points live in one arena that the peers have mapped
+    PeerArena arena;
+    size_t xrecv_off, xrecv_bytes;   // receive blocks of the exchange points, handed out in forward() order
+    int* xseq;                       // int[kMaxExchangePoints][kMaxExchangeCtas], inside the arena
 };
 
 namespace {
@@ -109,7 +114,45 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
     auto ag = [&](float* buf, int full_n) -> int {
         return G > 1 ? comm_all_gather_bytes(h, buf, (size_t)(full_n / G) * sizeof(float), st) : TER_B200_OK;
     };
-#define AG(buf, n) do { int rc__ = ag((buf), (n)); if (rc__) return rc__; } while (0)
+    // One exchange point: every rank's slices of up to three buffers reach every rank.  Peer memory path:
+    // one kernel of peer stores + flags; otherwise NCCL all-gathers in one group.
+    int point = 0;
+    size_t recv_cursor = 0;
+    auto exchange = [&](float* const* bufs, const int* full_n, int nb) -> int {
+        if (G == 1) return TER_B200_OK;
+        if (!m->arena.open) {
+            int rc = nb > 1 ? comm_group_start(h) : TER_B200_OK;
+            for (int i = 0; i < nb && !rc; ++i) rc = ag(bufs[i], full_n[i]);
+            if (!rc && nb > 1) rc = comm_group_end(h);
+            return rc;
+        }
+        if (point >= kMaxExchangePoints) return TER_B200_E_SHAPE;
+        ExchangeParams xp;
+        memset(&xp, 0, sizeof xp);
+        for (int r = 0; r < G; ++r) xp.base[r] = m->arena.peer[r];
+        for (int i = 0; i < nb; ++i) {
+            xp.seg_buf_off[i] = (size_t)((uint8_t*)bufs[i] - m->arena.base);
+            xp.seg_floats[i] = full_n[i] / G;
+            xp.words_total += full_n[i] / G / 2;
+        }
+        xp.n_seg = nb;
+        xp.rank = R;
+        xp.size = G;
+        // this point's receive block: one 16-byte word per pair of floats and per source rank
+        const size_t block = (size_t)xp.words_total * 16u * (size_t)G;
+        if (recv_cursor + block > m->xrecv_bytes) return TER_B200_E_SHAPE;
+        xp.recv_off = m->xrecv_off + recv_cursor;
+        recv_cursor += block;
+        xp.seq = m->xseq + (size_t)point * kMaxExchangeCtas;
+        xp.status = h->status_dev;
+        xp.point = point;
+        ++point;
+        cudaError_t e = launch_peer_exchange(xp, pdl, st);
+        if (e != cudaSuccess) return cuda_fail(h, e);
+        h->launches += 1;
+        return TER_B200_OK;
+    };
+#define XCHG1(buf, n) do { float* b__[1] = {(buf)}; int n__[1] = {(n)}; int rc__ = exchange(b__, n__, 1); if (rc__) return rc__; } while (0)
 
     CK(launch_embed(m->embd, m->tokens, m->hidden, H, B, c.V, pdl, st));
     for (int L = 0; L < c.L; ++L) {
@@ -124,11 +167,9 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
             if (!fz) CK(launch_norm_quant(nq, pdl, st));
             int rc = mm(h, ws, 3, m->xq, H, m->xs, outs, false, B, st, fz ? &nq : nullptr);
             if (rc) return rc;
-            if (G > 1) {
-                if ((rc = comm_group_start(h))) return rc;
-                AG(m->q, Hq); AG(m->k, Hkv); AG(m->v, Hkv);
-                if ((rc = comm_group_end(h))) return rc;
-            }
+            float* xb[3] = {m->q, m->k, m->v};
+            const int xn[3] = {Hq, Hkv, Hkv};
+            if ((rc = exchange(xb, xn, 3))) return rc;
         }
         // rotary, KV append and attention in one launch (+ the ordered merge of the chunks)
         uint16_t* kc = m->kcache + L * layer_cache;
@@ -147,7 +188,7 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
             if (!fz) CK(launch_norm_quant(aq, pdl, st));
             int rc = mm(h, ws, 1, m->xq, Hq, m->xs, outs, true, B, st, fz ? &aq : nullptr);   // hidden += Wo(attn)
             if (rc) return rc;
-            AG(m->hidden, H);
+            XCHG1(m->hidden, H);
         }
         // ---- FFN block: gate and up in one launch whose epilogue applies the gated activation, then
         // the down projection whose prologue normalises (BitNet sub-norm) and quantises it.
@@ -170,8 +211,14 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
                 int rc = mm(h, ws, 2, m->xq, H, m->xs, outs, false, B, st, fz ? &fq : nullptr);
                 if (rc) return rc;
             }
-            AG(m->gate, F);
-            if (!pair) AG(m->up, F);
+            if (pair) {
+                XCHG1(m->gate, F);
+            } else {
+                float* xb[2] = {m->gate, m->up};
+                const int xn[2] = {F, F};
+                int rc = exchange(xb, xn, 2);
+                if (rc) return rc;
+            }
             float* outd[1] = {m->hidden + off(H)};
             NormQuantParams gq{m->gate, pair ? nullptr : m->up, bitnet ? vec[TER_B200_FFN_SUB_NORM] : nullptr, m->xq,
                                m->xs, nullptr, F, B, pair ? PRE_NONE : act, c.eps};
@@ -179,7 +226,7 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
             if (!fd) CK(launch_norm_quant(gq, pdl, st));
             int rc = mm(h, wd, 1, m->xq, F, m->xs, outd, true, B, st, fd ? &gq : nullptr);    // hidden += Wdown(ffn)
             if (rc) return rc;
-            AG(m->hidden, H);
+            XCHG1(m->hidden, H);
         }
     }
     if (c.lm_head_packed) {
@@ -190,12 +237,12 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
         float* outs[1] = {m->logits + off(c.V)};
         int rc = mm(h, ws, 1, m->xq, H, m->xs, outs, false, B, st);
         if (rc) return rc;
-        AG(m->logits, c.V);
+        XCHG1(m->logits, c.V);
     } else {
         NormQuantParams on{m->hidden, nullptr, m->out_norm, nullptr, nullptr, m->xnorm, H, B, PRE_NONE, c.eps};
         CK(launch_norm_quant(on, pdl, st));
         CK(launch_lm_head_bf16(m->embd + off(c.V) * H, m->xnorm, m->logits + off(c.V), c.V / G, H, B, h->sm_count, pdl, st));
-        AG(m->logits, c.V);
+        XCHG1(m->logits, c.V);
         const uint64_t n = (uint64_t)((H + 26) / 27) * (uint64_t)c.V * (uint64_t)B;
         h->counts.tvmac += n;
         h->counts.total_ops += n;
@@ -249,6 +296,10 @@ void ter_b200_model_free(ter_b200_handle_t* h) {
         delete[] m->vecs;
     }
     free_weight(&m->lm_head);
+    if (m->arena.base) {   // the exchanged buffers are part of the arena (collective: every rank frees together)
+        m->hidden = m->q = m->k = m->v = m->gate = m->up = m->logits = nullptr;
+        comm_arena_destroy(h, &m->arena, h->stream);
+    }
     if (m->embd && m->embd_owned) cudaFree(m->embd);
     void* bufs[] = {m->out_norm, m->hidden, m->q, m->k, m->v, m->att, m->gate, m->up, m->xnorm, m->logits,
                     m->attn_scratch, m->argmax_scratch, m->xs, m->xq, m->kcache, m->vcache, m->tokens, m->pos,
@@ -294,15 +345,39 @@ int ter_b200_model_create(ter_b200_handle_t* h, const ter_b200_model_cfg_t* cfg)
     const int wide = c.F > Hq ? (c.F > c.H ? c.F : c.H) : (Hq > c.H ? Hq : c.H);
     cudaError_t e = cudaSuccess;
     auto A = [&](cudaError_t r) { if (e == cudaSuccess) e = r; };
-    A(dalloc(&m->hidden, (size_t)B * c.H));
-    A(dalloc(&m->q, (size_t)B * Hq));
-    A(dalloc(&m->k, (size_t)B * Hkv));
-    A(dalloc(&m->v, (size_t)B * Hkv));
+    // Buffers that ranks exchange.  With a communicator of more than one rank they are carved out of one
+    // arena that the peers map, followed by the words of the exchange points.
+    {
+        float** xb[7] = {&m->hidden, &m->q, &m->k, &m->v, &m->gate, &m->up, &m->logits};
+        const size_t xn[7] = {(size_t)B * c.H, (size_t)B * Hq, (size_t)B * Hkv, (size_t)B * Hkv, (size_t)B * c.F,
+                              (size_t)B * c.F, (size_t)B * c.V};
+        bool carved = false;
+        if (comm_size(h) > 1 && h->tp_p2p) {
+            size_t total = 0, offs[7];
+            for (int i = 0; i < 7; ++i) { offs[i] = total; total += (xn[i] * sizeof(float) + 255) & ~(size_t)255; }
+            // receive blocks: 16 bytes per pair of floats of every exchanged vector of a step (see forward())
+            const size_t recv_off = total;
+            const size_t recv_bytes = ((size_t)c.L * ((size_t)Hq + 2 * Hkv + 2 * (size_t)c.H + 2 * (size_t)c.F) + c.V) * 8u;
+            total += (recv_bytes + 255) & ~(size_t)255;
+            const size_t seq_off = total;
+            total += (size_t)kMaxExchangePoints * kMaxExchangeCtas * sizeof(int);
+            const int rc = comm_arena_create(h, total, &m->arena, h->stream);
+            if (rc == TER_B200_OK) {
+                for (int i = 0; i < 7; ++i) *xb[i] = (float*)(m->arena.base + offs[i]);
+                m->xrecv_off = recv_off;
+                m->xrecv_bytes = recv_bytes;
+                m->xseq = (int*)(m->arena.base + seq_off);
+                carved = true;
+            } else if (rc != TER_B200_E_STATE) {    // E_STATE: no peer access anywhere, stay on NCCL
+                ter_b200_model_free(h);
+                return rc;
+            }
+        }
+        if (!carved)
+            for (int i = 0; i < 7; ++i) A(dalloc(xb[i], xn[i]));
+    }
     A(dalloc(&m->att, (size_t)B * Hq));
-    A(dalloc(&m->gate, (size_t)B * c.F));
-    A(dalloc(&m->up, (size_t)B * c.F));
     A(dalloc(&m->xnorm, (size_t)B * c.H));
-    A(dalloc(&m->logits, (size_t)B * c.V));
     A(dalloc(&m->attn_scratch, attention_scratch_floats(B, c.Nh, c.Hd, c.Smax)));
     A(dalloc(&m->argmax_scratch, (size_t)B * kArgmaxParts * 2));
     A(dalloc(&m->xs, (size_t)B));
@@ -550,6 +625,10 @@ int ter_b200_generate(ter_b200_handle_t* h, const int32_t* prompts, int batch, i
         h->launches = mark;
         m->graph_batch = batch;
         m->graph_forced = true;
+    }
+    if (m->arena.open) {   // ranks enter the replay loop together: the peer exchanges wait with a time limit
+        rc = comm_barrier(h, st);
+        if (rc) return rc;
     }
     TERB_CUDA(h, cudaEventRecord(m->ev0, st));
     for (int i = 0; i < steps; ++i) {

@@ -1,6 +1,7 @@
 """Worker of the tensor-parallel test: run with torch.distributed.run, one rank per GPU.
 Every rank builds the same synthetic model (the library keeps its own column slice), generates
-greedy tokens with the output slices all-gathered over NCCL inside the captured step, and rank 0
+greedy tokens with the output slices exchanged inside the captured step (peer-memory kernel, or NCCL
+all-gathers with TER_TP_P2P=0), and rank 0
 checks tokens and final logits against the CPU checker (which knows nothing about sharding)."""
 import os
 import sys
@@ -24,6 +25,7 @@ def main():
     rank, world = dist.get_rank(), dist.get_world_size()
     tb = TerB200(local)
     tb.comm_init_from_torch()
+    tb.set_option("tp_p2p", int(os.environ.get("TER_TP_P2P", "1")))   # 1: peer-memory exchange kernel, 0: NCCL all-gathers
     ok = True
     cases = [
         (dict(arch=0, H=256, F=512, L=3, V=4096, Nh=4, Nkv=2, Hd=64, Smax=320, eps=1e-5, rope_theta=500000.0), 11, 260, 12),
@@ -49,7 +51,8 @@ def main():
     flag = torch.tensor([1 if ok else 0], device="cuda")
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0:
-        print("TP_OK" if int(flag.item()) == 1 else "TP_FAIL", "world", world, flush=True)
+        print("TP_OK" if int(flag.item()) == 1 else "TP_FAIL", "world", world, "p2p", os.environ.get("TER_TP_P2P", "1"),
+              flush=True)
     tb.close()
     dist.destroy_process_group()
 
