@@ -445,6 +445,8 @@ def main():
         if world > 1:
             tb.comm_init_from_torch()      # tensor parallel: output-dimension sharding, slices exchanged over peer memory
             tb.set_option("tp_p2p", int(os.environ.get("TER_TP_P2P", "1")))   # 0: NCCL all-gathers, for comparison
+            if "TER_TP_SHARD" in os.environ:                                  # else the library's default policy
+                tb.set_option("tp_shard", int(os.environ["TER_TP_SHARD"]))
         decode = decode_bench(tb, dev, 0)  # the same model on every rank; the library keeps its slice
         if world > 1:
             t = torch.tensor([decode["ms_per_token"]], device=dev)
@@ -453,6 +455,7 @@ def main():
             decode["tokens_per_s"] = 1e3 / decode["ms_per_token"]
             decode["note"] += f"; tensor parallel over {world} GPUs (strong scaling, max over ranks)"
             decode["parallelism"] = f"tp{world}"
+            decode["sharded_blocks"] = os.environ.get("TER_TP_SHARD", "library default")
             decode["exchange"] = "peer-memory kernel" if os.environ.get("TER_TP_P2P", "1") != "0" else "nccl all-gather"
 
     cpu = None

@@ -315,8 +315,9 @@ float ter_b200_last_generate_ms(const ter_b200_handle_t* h);
  * One process per GPU, one handle per process.  Rank 0 creates a 128-byte id and hands it to the
  * other ranks by any host channel; every rank then calls ter_b200_comm_init BEFORE
  * ter_b200_model_create.  With a communicator of size G the model keeps columns
- * [N*r/G, N*(r+1)/G) of every projection (output-dimension sharding: each output column is an
- * independent exact dot product), the vocabulary rows [V*r/G, V*(r+1)/G) of the lm_head, and
+ * [N*r/G, N*(r+1)/G) of every SHARDED projection (output-dimension sharding: each output column is
+ * an independent exact dot product; option "tp_shard" says which blocks), the vocabulary rows
+ * [V*r/G, V*(r+1)/G) of the lm_head, and
  * exchanges the fp32 output slices inside the captured step, so every rank holds the same bits as a
  * single GPU would and greedy tokens are identical at every G.  The exchange is a kernel of peer
  * stores over NVLink into buffers that every rank has mapped (CUDA IPC; NCCL only carries the
@@ -347,9 +348,13 @@ int ter_b200_device_status(ter_b200_handle_t* h);
 /* Last CUDA error code seen by the handle (cudaError_t as int), 0 if none. */
 int ter_b200_last_cuda_error(const ter_b200_handle_t* h);
 /* Tuning knobs (integers): "gemv_ctas_per_sm", "gemv_stages", "gemv_split_max_strips", "pdl",
- * "fuse_quant", "gemm_min_m", "gemm_split_k", "attn_inline_merge", and "tp_p2p" (1, default: tensor-
+ * "fuse_quant", "gemm_min_m", "gemm_split_k", "attn_inline_merge", "tp_p2p" (1, default: tensor-
  * parallel output slices travel by peer stores over NVLink inside one small kernel per exchange;
- * 0: NCCL all-gathers; read by the next ter_b200_model_create).  Returns -2 if unknown. */
+ * 0: NCCL all-gathers) and "tp_shard" (which blocks of a layer are column-sharded over the ranks:
+ * bit 0 the attention block q/k/v/o, bit 1 the FFN block gate/up/down; the lm_head always is.
+ * Default 0: at batch 1 a layer is bound by kernel-to-kernel latency, so sharding it only adds two
+ * exchanges per block; 3 shards everything).  Both are read by the next ter_b200_model_create.
+ * Returns -2 if unknown. */
 int ter_b200_set_option(ter_b200_handle_t* h, const char* key, int value);
 /* Number of kernels this handle has launched since creation (or the last reset). */
 uint64_t ter_b200_launch_count(const ter_b200_handle_t* h);

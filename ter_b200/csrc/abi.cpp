@@ -197,6 +197,7 @@ ter_b200_handle_t* ter_b200_create(int device) {
     h->gemm_min_m = 4;
     h->attn_inline_merge = 1;
     h->tp_p2p = 1;
+    h->tp_shard = 0;
     h->gemm_split_k = 1;
     int sms = 0;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) sms = 148;
@@ -494,6 +495,9 @@ int ter_b200_set_option(ter_b200_handle_t* h, const char* key, int value) {
         h->gemm_min_m = value;
     } else if (strcmp(key, "attn_inline_merge") == 0) {
         h->attn_inline_merge = value ? 1 : 0;
+    } else if (strcmp(key, "tp_shard") == 0) {
+        if (value < 0 || value > 3) return TER_B200_E_SHAPE;
+        h->tp_shard = value;            // read by the next ter_b200_model_create
     } else if (strcmp(key, "tp_p2p") == 0) {
         h->tp_p2p = value ? 1 : 0;      // read by the next ter_b200_model_create
     } else if (strcmp(key, "gemm_dbg") == 0) {

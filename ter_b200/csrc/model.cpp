@@ -37,6 +37,7 @@ struct TerbModel {
     PeerArena arena;
     size_t xrecv_off, xrecv_bytes;   // receive blocks of the exchange points, handed out in forward() order
     int* xseq;                       // int[kMaxExchangePoints][kMaxExchangeCtas], inside the arena
+    bool shard_attn, shard_ffn;      // which blocks are column-sharded over the ranks (the lm_head always is)
 };
 
 namespace {
@@ -110,7 +111,14 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
     // its slice of the full-size buffer; an in-place all-gather then gives every rank the whole vector.
     const int G = comm_size(h), R = comm_rank(h);
     const int Hkv = c.Nkv * c.Hd;
+    // Per block: sharded over the G ranks, or replicated (every rank computes all columns, no exchange).
+    // A batch-1 step is bound by kernel-to-kernel latency, not by weight bandwidth, so a replicated
+    // block costs the same time and saves its two exchanges; the lm_head (the one large matrix) is
+    // always split over the vocabulary.
+    const bool sa = G > 1 && m->shard_attn, sf = G > 1 && m->shard_ffn;
     auto off = [&](int full_n) { return (size_t)(full_n / G) * (size_t)R; };
+    auto offa = [&](int full_n) { return sa ? off(full_n) : (size_t)0; };
+    auto offf = [&](int full_n) { return sf ? off(full_n) : (size_t)0; };
     auto ag = [&](float* buf, int full_n) -> int {
         return G > 1 ? comm_all_gather_bytes(h, buf, (size_t)(full_n / G) * sizeof(float), st) : TER_B200_OK;
     };
@@ -118,8 +126,8 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
     // one kernel of peer stores + flags; otherwise NCCL all-gathers in one group.
     int point = 0;
     size_t recv_cursor = 0;
-    auto exchange = [&](float* const* bufs, const int* full_n, int nb) -> int {
-        if (G == 1) return TER_B200_OK;
+    auto exchange = [&](float* const* bufs, const int* full_n, int nb, bool sharded) -> int {
+        if (G == 1 || !sharded) return TER_B200_OK;
         if (!m->arena.open) {
             int rc = nb > 1 ? comm_group_start(h) : TER_B200_OK;
             for (int i = 0; i < nb && !rc; ++i) rc = ag(bufs[i], full_n[i]);
@@ -152,7 +160,7 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
         h->launches += 1;
         return TER_B200_OK;
     };
-#define XCHG1(buf, n) do { float* b__[1] = {(buf)}; int n__[1] = {(n)}; int rc__ = exchange(b__, n__, 1); if (rc__) return rc__; } while (0)
+#define XCHG1(buf, n, sharded) do { float* b__[1] = {(buf)}; int n__[1] = {(n)}; int rc__ = exchange(b__, n__, 1, (sharded)); if (rc__) return rc__; } while (0)
 
     CK(launch_embed(m->embd, m->tokens, m->hidden, H, B, c.V, pdl, st));
     for (int L = 0; L < c.L; ++L) {
@@ -161,7 +169,7 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
         // ---- attention block
         {
             const DevWeight* ws[3] = {&W[TER_B200_WQ], &W[TER_B200_WK], &W[TER_B200_WV]};
-            float* outs[3] = {m->q + off(Hq), m->k + off(Hkv), m->v + off(Hkv)};
+            float* outs[3] = {m->q + offa(Hq), m->k + offa(Hkv), m->v + offa(Hkv)};
             NormQuantParams nq{m->hidden, nullptr, vec[TER_B200_ATTN_NORM], m->xq, m->xs, nullptr, H, B, PRE_NONE, c.eps};
             const bool fz = can_fuse(h, ws, 3, B);
             if (!fz) CK(launch_norm_quant(nq, pdl, st));
@@ -169,7 +177,7 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
             if (rc) return rc;
             float* xb[3] = {m->q, m->k, m->v};
             const int xn[3] = {Hq, Hkv, Hkv};
-            if ((rc = exchange(xb, xn, 3))) return rc;
+            if ((rc = exchange(xb, xn, 3, sa))) return rc;
         }
         // rotary, KV append and attention in one launch (+ the ordered merge of the chunks)
         uint16_t* kc = m->kcache + L * layer_cache;
@@ -181,20 +189,20 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
         if (!h->attn_inline_merge) h->launches += 1;
         {
             const DevWeight* ws[1] = {&W[TER_B200_WO]};
-            float* outs[1] = {m->hidden + off(H)};
+            float* outs[1] = {m->hidden + offa(H)};
             NormQuantParams aq{m->att, nullptr, bitnet ? vec[TER_B200_ATTN_SUB_NORM] : nullptr, m->xq, m->xs, nullptr,
                                Hq, B, PRE_NONE, c.eps};
             const bool fz = can_fuse(h, ws, 1, B);
             if (!fz) CK(launch_norm_quant(aq, pdl, st));
             int rc = mm(h, ws, 1, m->xq, Hq, m->xs, outs, true, B, st, fz ? &aq : nullptr);   // hidden += Wo(attn)
             if (rc) return rc;
-            XCHG1(m->hidden, H);
+            XCHG1(m->hidden, H, sa);
         }
         // ---- FFN block: gate and up in one launch whose epilogue applies the gated activation, then
         // the down projection whose prologue normalises (BitNet sub-norm) and quantises it.
         {
             const DevWeight* ws[2] = {&W[TER_B200_WGATE], &W[TER_B200_WUP]};
-            float* outs[2] = {m->gate + off(F), m->up + off(F)};
+            float* outs[2] = {m->gate + offf(F), m->up + offf(F)};
             NormQuantParams fq{m->hidden, nullptr, vec[TER_B200_FFN_NORM], m->xq, m->xs, nullptr, H, B, PRE_NONE, c.eps};
             const bool fz = can_fuse(h, ws, 2, B);
             const DevWeight* wd[1] = {&W[TER_B200_WDOWN]};
@@ -204,7 +212,7 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
             if (pair) {
                 for (int b = 0; b < B; ++b) {
                     int rc = run_gemv(h, ws, 2, nullptr, nullptr, 1.0f, outs, nullptr, false, st, &fq, b, act,
-                                      m->gate + (size_t)b * F + off(F));
+                                      m->gate + (size_t)b * F + offf(F));
                     if (rc) return rc;
                 }
             } else {
@@ -212,21 +220,21 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
                 if (rc) return rc;
             }
             if (pair) {
-                XCHG1(m->gate, F);
+                XCHG1(m->gate, F, sf);
             } else {
                 float* xb[2] = {m->gate, m->up};
                 const int xn[2] = {F, F};
-                int rc = exchange(xb, xn, 2);
+                int rc = exchange(xb, xn, 2, sf);
                 if (rc) return rc;
             }
-            float* outd[1] = {m->hidden + off(H)};
+            float* outd[1] = {m->hidden + offf(H)};
             NormQuantParams gq{m->gate, pair ? nullptr : m->up, bitnet ? vec[TER_B200_FFN_SUB_NORM] : nullptr, m->xq,
                                m->xs, nullptr, F, B, pair ? PRE_NONE : act, c.eps};
             const bool fd = can_fuse(h, wd, 1, B);
             if (!fd) CK(launch_norm_quant(gq, pdl, st));
             int rc = mm(h, wd, 1, m->xq, F, m->xs, outd, true, B, st, fd ? &gq : nullptr);    // hidden += Wdown(ffn)
             if (rc) return rc;
-            XCHG1(m->hidden, H);
+            XCHG1(m->hidden, H, sf);
         }
     }
     if (c.lm_head_packed) {
@@ -237,12 +245,12 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
         float* outs[1] = {m->logits + off(c.V)};
         int rc = mm(h, ws, 1, m->xq, H, m->xs, outs, false, B, st);
         if (rc) return rc;
-        XCHG1(m->logits, c.V);
+        XCHG1(m->logits, c.V, true);
     } else {
         NormQuantParams on{m->hidden, nullptr, m->out_norm, nullptr, nullptr, m->xnorm, H, B, PRE_NONE, c.eps};
         CK(launch_norm_quant(on, pdl, st));
         CK(launch_lm_head_bf16(m->embd + off(c.V) * H, m->xnorm, m->logits + off(c.V), c.V / G, H, B, h->sm_count, pdl, st));
-        XCHG1(m->logits, c.V);
+        XCHG1(m->logits, c.V, true);
         const uint64_t n = (uint64_t)((H + 26) / 27) * (uint64_t)c.V * (uint64_t)B;
         h->counts.tvmac += n;
         h->counts.total_ops += n;
@@ -325,7 +333,8 @@ int ter_b200_model_create(ter_b200_handle_t* h, const ter_b200_model_cfg_t* cfg)
     {
         const int G = comm_size(h);
         if (G > 1) {   // every sharded width must split into whole 16-column strips per rank
-            const int widths[5] = {c.H, c.F, c.Nh * c.Hd, c.Nkv * c.Hd, c.V};
+            const bool sa = (h->tp_shard & 1) != 0, sf = (h->tp_shard & 2) != 0;
+            const int widths[5] = {(sa || sf) ? c.H : 0, sf ? c.F : 0, sa ? c.Nh * c.Hd : 0, sa ? c.Nkv * c.Hd : 0, c.V};
             for (int w : widths)
                 if (w % (16 * G) != 0) return TER_B200_E_SHAPE;
             if (c.max_batch != 1) return TER_B200_E_SHAPE;   // tensor parallelism serves one sequence; batches are sharded by sequence
@@ -337,6 +346,8 @@ int ter_b200_model_create(ter_b200_handle_t* h, const ter_b200_model_cfg_t* cfg)
     if (!m) return TER_B200_E_ALLOC;
     m->c = c;
     m->batch = 1;
+    m->shard_attn = (h->tp_shard & 1) != 0;
+    m->shard_ffn = (h->tp_shard & 2) != 0;
     h->model = m;
     m->mats = new (std::nothrow) DevWeight[(size_t)c.L * 7];
     m->vecs = new (std::nothrow) float*[(size_t)c.L * 4]();
@@ -423,7 +434,8 @@ static int set_matrix_common(ter_b200_handle_t* h, int layer, int which, const v
         // tensor parallelism: keep this rank's column range.  In the v11 layout byte-column jb is a run of
         // K bytes, so columns [N*R/G, N*(R+1)/G) are one contiguous byte range of the caller's matrix.
         const int G = comm_size(h), R = comm_rank(h);
-        if (G > 1) {
+        const bool sharded = layer < 0 || (which <= TER_B200_WO ? m->shard_attn : m->shard_ffn);
+        if (G > 1 && sharded) {
             if (format != TER_B200_FMT_V11 || N % (16 * G) != 0) return TER_B200_E_SHAPE;
             data = (const uint8_t*)data + (size_t)(N / G) * R / 4 * (size_t)K;
             N = N / G;

@@ -55,16 +55,17 @@ def test_sharding_arithmetic_on_two_cpu_ranks(tmp_path):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("p2p", [1, 0])
-def test_tensor_parallel_decode_matches_checker(p2p):
-    """p2p=1: slices exchanged by the peer-memory kernel; p2p=0: NCCL all-gathers."""
+@pytest.mark.parametrize("p2p,shard", [(1, 3), (0, 3), (1, 0), (1, 2)])
+def test_tensor_parallel_decode_matches_checker(p2p, shard):
+    """p2p=1: slices exchanged by the peer-memory kernel; p2p=0: NCCL all-gathers.  shard: which blocks are
+    column-sharded (bit 0 attention, bit 1 FFN; the lm_head always is)."""
     import torch
     n = torch.cuda.device_count()
     if n < 2:
         pytest.skip("needs two GPUs")
     world = 2
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TER_TP_P2P=str(p2p))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TER_TP_P2P=str(p2p), TER_TP_SHARD=str(shard))
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world),
-                        "--master-addr", "127.0.0.1", "--master-port", str(29618 + p2p),
+                        "--master-addr", "127.0.0.1", "--master-port", str(29618 + p2p + 2 * shard),
                         os.path.join(ROOT, "tests", "tp_worker.py")], capture_output=True, text=True, timeout=900, env=env)
     assert "TP_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]

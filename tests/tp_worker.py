@@ -25,6 +25,7 @@ def main():
     rank, world = dist.get_rank(), dist.get_world_size()
     tb = TerB200(local)
     tb.comm_init_from_torch()
+    tb.set_option("tp_shard", int(os.environ.get("TER_TP_SHARD", "3")))   # bit 0: attention block sharded, bit 1: FFN block
     tb.set_option("tp_p2p", int(os.environ.get("TER_TP_P2P", "1")))   # 1: peer-memory exchange kernel, 0: NCCL all-gathers
     ok = True
     cases = [
@@ -51,7 +52,7 @@ def main():
     flag = torch.tensor([1 if ok else 0], device="cuda")
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0:
-        print("TP_OK" if int(flag.item()) == 1 else "TP_FAIL", "world", world, "p2p", os.environ.get("TER_TP_P2P", "1"),
+        print("TP_OK" if int(flag.item()) == 1 else "TP_FAIL", "world", world, "p2p", os.environ.get("TER_TP_P2P", "1"), "shard", os.environ.get("TER_TP_SHARD", "3"),
               flush=True)
     tb.close()
     dist.destroy_process_group()
