@@ -168,6 +168,42 @@ def per_shape_bench(tb, dev, peak, reps=20):
     return rows
 
 
+def gemm_bench(tb, dev):
+    """Batched ternary GEMM (tcgen05 kind::i8) on the BitNet-2B projection shapes at M = 16, 64, 256, 1024
+    tokens: microseconds per call (CUDA events around a graph of 20 calls; includes the row-sum pre-kernel
+    and the split-K finalize kernel) and int8 TOPS = 2*M*K*N / time.  The 1-4 MB weight matrix stays in L2."""
+    import torch
+    from ter_b200 import FMT_V11, synth
+    rows = []
+    cur = torch.cuda.current_stream()
+    for nm in ("q", "k", "gate", "down"):
+        K, N = synth.BITNET_2B_SHAPES[nm]
+        tb.install("gm", synth.packed_v11_cuda(K, N, synth.seed_for("gemm", K, N), dev), FMT_V11, K, N, 0.02)
+        for M in (16, 64, 256, 1024):
+            g = torch.Generator(device=dev)
+            g.manual_seed(M)
+            X = torch.randint(-127, 128, (M, K), dtype=torch.int8, device=dev, generator=g)
+            xs = torch.rand(M, device=dev, generator=g) * 0.05 + 0.001
+            out = torch.empty((M, N), device=dev)
+            for _ in range(3):
+                tb.gemm("gm", X, xs, out)
+            torch.cuda.synchronize()
+            gid = tb.capture(lambda: [tb.gemm("gm", X, xs, out) for _ in range(20)])
+            tb.graph_launch(gid, stream=cur)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(3):
+                tb.graph_launch(gid, stream=cur)
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) / 60 * 1e3
+            tb.graph_destroy(gid)
+            rows.append({"proj": nm, "K": K, "N": N, "M": M, "us": round(us, 2), "tops": round(2 * M * K * N / us / 1e6, 1)})
+        tb.remove("gm")
+    return rows
+
+
 def cpu_reference_run(steps: int, warmup: int, threads: int):
     """Times the reference's CPU GEMV (mm_row, src/tx/forward.cpp:299-352) on the host cores:
     the unmodified reference when oracle/_ref was built, else the C restatement."""
@@ -284,6 +320,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--no-per-shape", action="store_true")
+    ap.add_argument("--no-gemm", action="store_true")
     ap.add_argument("--layers", type=int, default=16, help="layers of the fabric (profiling captures use fewer)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -433,6 +470,9 @@ def main():
     per_shape = None
     if not args.no_per_shape and rank == 0:
         per_shape = per_shape_bench(tb, dev, peak)
+    gemm = None
+    if not args.no_gemm and rank == 0:
+        gemm = gemm_bench(tb, dev)
     if sampler:
         clocks = sampler.stop()
 
@@ -492,6 +532,7 @@ def main():
                                          "the ncu capture summarised in profiles/gemv_trit_kernel_table_sweep_llama1b_fabric.md",
                          "note": "achieved = packed weight bytes of the launch / its CUDA-event time (one launch per step)"},
             "per_shape": per_shape,
+            "gemm": gemm,
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": UNIT, "steps": e2e_steps,
                     # what the call copies up: each distinct activation vector once, a 32-byte descriptor per

@@ -8,17 +8,19 @@
 // of 128 OUTPUT COLUMNS (weights), the N side of the MMA is the token batch (16..256), so a small
 // batch does not waste the 128-lane datapath.  Per CTA: one tile of 128 columns x a K range x one
 // token tile.
-//   * producers (warps 0-3): read the packed trits (2 bits) of the tile straight from global with
-//     16-byte read-only loads, expand them in registers to unsigned bytes and store them into the
-//     A stage in the 128-byte-swizzled K-major layout the tensor core reads; copy the matching
-//     128-k slice of the int8 activations into the B stage (same layout).  The expansion needs no
+//   * loader (warp 9, one lane): one TMA tensor copy (cp.async.bulk.tensor.2d, 128-byte swizzle) per
+//     stage brings the 128-k slice of the int8 activations of the token tile into the B stage, in the
+//     layout the tensor core reads; it runs as far ahead as there are free stages.
+//   * producers (warps 0-7): warp w owns k-steps w, w+8, ...: it reads the 4 KB of packed trits (2 bits)
+//     of the step with 16-byte read-only loads one step of its own ahead, expands them in registers to
+//     unsigned bytes and stores them into the A stage in the same 128-byte-swizzled layout.  The expansion needs no
 //     shift and no sign decode: row r of A holds column 4*b + f, whose bytes are (w & (3 << 2f)),
 //     i.e. 4^f * (trit + 1); the accumulator of row r is divided by 4^f in the epilogue (exact) and
 //     the "+1" is removed by subtracting sum_k X[m][k].
-//   * MMA warp (warp 4, one lane): tcgen05.mma kind::i8 (A unsigned, B signed), M=128, N=token
+//   * MMA warp (warp 8, one lane): tcgen05.mma kind::i8 (A unsigned, B signed), M=128, N=token
 //     tile, K=32 per instruction, int32 accumulators in tensor memory; tcgen05.commit releases a
 //     stage back to the producers through an mbarrier.
-//   * epilogue (warps 0-3): tcgen05.ld the accumulators (TMEM lane = output column), scale, store
+//   * epilogue (warps 0-7): tcgen05.ld the accumulators (TMEM lane = output column), scale, store
 //     out[m][n] coalesced over n.  With split-K the int32 partials are added into a scratch array
 //     with red.global.add.s32 (integer adds are exact and order-free) and a second kernel scales.
 // Every wait is bounded; on expiry a status code is recorded and all roles run to the end, so
@@ -31,20 +33,18 @@ namespace terb {
 namespace {
 
 constexpr int kProducerWarps = 8;
-constexpr int kGemmThreads = 32 * (kProducerWarps + 1);   // 8 producer/epilogue warps + 1 MMA warp
+constexpr int kGemmThreads = 32 * (kProducerWarps + 2);   // 8 producer/epilogue warps + MMA warp + loader warp
 constexpr int kTileN = 128;                  // output columns per CTA = MMA M
 constexpr int kKStep = 128;                  // k per pipeline stage = one 128-byte swizzle row
 constexpr int kAStageBytes = kTileN * kKStep;   // 16 KB
-constexpr int kRawStageBytes = 4096;            // the packed trits of one stage (128 columns x 128 k, 2 bits each)
-constexpr int kAhead = 2;                       // stages of cp.async copies in flight per producer thread (<= stages - 2,
-                                                // so a refill never waits on the MMA issued just before it)
 
-__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+__device__ __forceinline__ uint4 ldg_stream16(const uint8_t* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -91,8 +91,7 @@ struct GemmSmemLayout {
     __host__ __device__ int b_stage_bytes() const { return tokens * kKStep; }
     __host__ __device__ int a_off(int s) const { return s * kAStageBytes; }
     __host__ __device__ int b_off(int s) const { return stages * kAStageBytes + s * b_stage_bytes(); }
-    __host__ __device__ int raw_off(int s) const { return stages * (kAStageBytes + b_stage_bytes()) + s * kRawStageBytes; }
-    __host__ __device__ int tail_off() const { return stages * (kAStageBytes + b_stage_bytes() + kRawStageBytes); }
+    __host__ __device__ int tail_off() const { return stages * (kAStageBytes + b_stage_bytes()); }
     // tail: full[8], empty[8], done (u64 each) | tmem base, abort (16 B) | scale[256] (float) | rowsum[256] (int)
     __host__ __device__ int bytes() const { return tail_off() + 17 * 8 + 16 + 2 * 256 * 4 + 1024; }
 };
@@ -121,7 +120,7 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_trit_kernel(const __grid_co
     const int S = p.stages;
 
     if (tid == 0) {
-        for (int i = 0; i < S; ++i) { mbar_init(&full[i], kProducerWarps); mbar_init(&empty[i], 1); }
+        for (int i = 0; i < S; ++i) { mbar_init(&full[i], kProducerWarps / S + 1 /* its producer warps + the loader */); mbar_init(&empty[i], 1); }
         mbar_init(done, 1);
         *abort_flag = 0;
         mbar_fence_init();
@@ -141,77 +140,87 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_trit_kernel(const __grid_co
     pdl_wait();
 
     if (warp < kProducerWarps) {
-        // ------------------------------------------------------------------ producers (256 threads)
+        // ------------------------------------------------------------------ producers (8 warps)
+        // Stage s belongs to the 8 / S warps with warp % S == s; they fill it in EVERY round (steps s,
+        // s + S, ...), each expanding its share of the 128 rows, so a warp sees every phase of its stage's
+        // barrier in order (a parity wait must never skip a phase).  S steps are in the making at once:
+        // the latency of one step's chain (loads -> expand -> fence -> arrive) is spread over S MMA steps.
+        // Per step the tile's 4 KB of packed trits are 8 groups of 4 segments of 128 bytes (segment =
+        // (strip, byte-column), lane = (segment within the group, 16-byte part)): a warp load is a coalesced
+        // 4 x 128 bytes, and each 16 bytes become 4 rows of A; a warp store covers 4 whole 128-byte rows
+        // of the swizzled stage, i.e. no bank conflicts.
         const int nb = (p.Kpad + kGemvKC - 1) / kGemvKC;
         const int last_kc = p.Kpad - (nb - 1) * kGemvKC;
-        const int seg = tid >> 3, part = tid & 7;          // 32 segments (strip, byte-column) x 8 x 16 bytes
-        const int strip_l = seg >> 2, bc = seg & 3;
-        const int strip = tile * 8 + strip_l;
-        const bool strip_ok = strip < p.n_strips;
-        const uint8_t* sbase = p.W + (size_t)strip * 4u * (size_t)p.Kpad;
-        const int xr = tid >> 3, xci = tid & 7;            // activation copy: row xr + 32*i, 16-byte chunk xci
-        const int nt32 = (p.tokens + 31) / 32;
+        const int part = lane & 7, sub = lane >> 3;
+        const int my_stage = warp % S, share = warp / S, n_share = kProducerWarps / S;   // S is 2, 4 or 8
+        const int g_per = 8 / n_share, g0 = share * g_per;
         // per-token epilogue constants
         if (tid < p.tokens) {
             const int m = m0 + tid;
             tok_scale[tid] = (m < p.M && p.x_scales) ? p.x_scales[m] * p.w_scale : 0.0f;
             tok_sum[tid] = (m < p.M) ? p.x_rowsum[m] : 0;
         }
-        const int4 zero4 = make_int4(0, 0, 0, 0);
-        bool ok = true;
-        // Asynchronous copies (cp.async) of stage `j`: this thread's 16 packed bytes and its 16-byte
-        // chunks of the activation slice, straight into shared memory; kAhead stages stay in flight.
-        auto issue = [&](int j) {
-            const int s = j % S;
-            if (j >= S) ok = ok && mbar_wait_abortable(&empty[s], ((uint32_t)(j / S) & 1u) ^ 1u, abort_flag, p.status);
-            if (ok) {
-                const int ks = step_begin + j;
-                uint8_t* raw = gsm + L.raw_off(s) + seg * 128 + part * 16;
-                if (strip_ok) {
-                    const int q = ks >> 3;
-                    const int kc = (q == nb - 1) ? last_kc : kGemvKC;
-                    cp_async16(raw, sbase + (size_t)q * (4 * kGemvKC) + (size_t)bc * kc + (ks & 7) * 128 + part * 16);
-                } else {
-                    *reinterpret_cast<uint4*>(raw) = make_uint4(0x55555555u, 0x55555555u, 0x55555555u, 0x55555555u);
-                }
-                uint8_t* Bm = gsm + L.b_off(s);
-                const int kbyte = ks * kKStep + xci * 16;
+        uint4 raw[8];
+        auto load_raw = [&](int j) {
+            const int ks = step_begin + j;
+            const int q = ks >> 3;
+            const int kc = (q == nb - 1) ? last_kc : kGemvKC;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    if (i >= nt32) break;
-                    const int ml = xr + 32 * i;
-                    if (ml >= p.tokens) break;
-                    uint8_t* dst = Bm + (ml >> 3) * 1024 + (ml & 7) * 128 + ((xci ^ (ml & 7)) * 16);
-                    if (m0 + ml < p.M && kbyte < p.K) cp_async16(dst, p.X + (size_t)(m0 + ml) * p.K + kbyte);
-                    else *reinterpret_cast<int4*>(dst) = zero4;
+            for (int gi = 0; gi < 8; ++gi) {
+                if (gi < g_per) {
+                    const int seg = (g0 + gi) * 4 + sub, strip = tile * 8 + (seg >> 2), bc = seg & 3;
+                    if (strip < p.n_strips) {
+                        raw[gi] = ldg_stream16(p.W + (size_t)strip * 4u * (size_t)p.Kpad + (size_t)q * (4 * kGemvKC) +
+                                               (size_t)bc * kc + (ks & 7) * 128 + part * 16);
+                    } else {
+                        raw[gi] = make_uint4(0x55555555u, 0x55555555u, 0x55555555u, 0x55555555u);   // trit 0 everywhere
+                    }
                 }
             }
-            cp_async_commit();
         };
-        for (int j = 0; j < kAhead; ++j)
-            if (j < n_steps) issue(j); else cp_async_commit();
-        for (int it = 0; it < n_steps; ++it) {
-            const int s = it % S;
-            if (it + kAhead < n_steps) issue(it + kAhead); else cp_async_commit();
-            cp_async_wait<kAhead>();         // this thread's copies of stage `it` have landed
+        bool ok = true;
+        if (my_stage < n_steps) load_raw(my_stage);
+        for (int it = my_stage; it < n_steps; it += S) {
+            // the stage is free once the MMAs of step it - S have completed
+            if (it >= S) ok = ok && mbar_wait_abortable(&empty[my_stage], ((uint32_t)(it / S) & 1u) ^ 1u, abort_flag, p.status);
             if (!ok) break;
-            // ---- A: expand this thread's 16 packed bytes (16 k x 4 columns)
-            {
-                uint8_t* A = gsm + L.a_off(s);
-                const uint4 w = *reinterpret_cast<const uint4*>(gsm + L.raw_off(s) + seg * 128 + part * 16);
+            uint8_t* A = gsm + L.a_off(my_stage);
 #pragma unroll
-                for (int f = 0; f < 4; ++f) {
-                    const uint32_t mk = 0x03030303u << (2 * f);
-                    const int r = strip_l * 16 + bc * 4 + f;                     // A row = local output column
-                    *reinterpret_cast<uint4*>(A + (r >> 3) * 1024 + (r & 7) * 128 + ((part ^ (r & 7)) * 16)) =
-                        make_uint4(w.x & mk, w.y & mk, w.z & mk, w.w & mk);
+            for (int gi = 0; gi < 8; ++gi) {
+                if (gi < g_per) {
+                    const int seg = (g0 + gi) * 4 + sub;
+                    const uint4 w = raw[gi];
+#pragma unroll
+                    for (int f = 0; f < 4; ++f) {
+                        const uint32_t mk = 0x03030303u << (2 * f);
+                        const int r = (seg >> 2) * 16 + (seg & 3) * 4 + f;        // A row = local output column
+                        *reinterpret_cast<uint4*>(A + (r >> 3) * 1024 + (r & 7) * 128 + ((part ^ (r & 7)) * 16)) =
+                            make_uint4(w.x & mk, w.y & mk, w.z & mk, w.w & mk);
+                    }
                 }
             }
+            if (it + S < n_steps) load_raw(it + S);   // lands while the other stages are being filled
             fence_async_smem();          // make the generic-proxy writes visible to the tensor core
             __syncwarp();
-            if (lane == 0) mbar_arrive(&full[s]);
+            if (lane == 0) mbar_arrive(&full[my_stage]);
         }
-        cp_async_wait<0>();
+    } else if (warp == kProducerWarps + 1) {
+        // ------------------------------------------------------------------ activation loader (TMA)
+        if (lane == 0) {
+            const uint32_t bytes = (uint32_t)p.tokens * kKStep;
+            bool ok = true;
+            for (int j = 0; j < n_steps && ok; ++j) {
+                const int s = j % S;
+                if (j >= S) ok = mbar_wait_abortable(&empty[s], ((uint32_t)(j / S) & 1u) ^ 1u, abort_flag, p.status);
+                if (!ok) break;
+                mbar_arrive_expect_tx(&full[s], bytes);
+                asm volatile(
+                    "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                    ::"r"(smem_u32(gsm + L.b_off(s))), "l"(reinterpret_cast<uint64_t>(&p.xmap)),
+                      "r"((step_begin + j) * kKStep), "r"(m0), "r"(smem_u32(&full[s]))
+                    : "memory");
+            }
+        }
     } else if (lane == 0) {
         // ------------------------------------------------------------------ MMA issuer
         const uint32_t idesc = umma_idesc_i8(p.tokens);
@@ -344,6 +353,22 @@ __global__ void __launch_bounds__(256) gemm_finalize_kernel(const GemmParams p) 
 
 }  // namespace
 
+// cuTensorMapEncodeTiled, resolved through the runtime so that the library links against nothing but cudart.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)ptr;
+    }
+    return fn;
+}
+
 // scratch = row sums [M] followed by the split-K partials [M][N]
 size_t gemm_scratch_ints(int M, int N, bool split) { return (size_t)M + (split ? (size_t)M * (size_t)N : 0); }
 
@@ -368,9 +393,24 @@ cudaError_t launch_gemm(const GemmParams& p_in, int sm_count, bool pdl, cudaStre
         if (ksplits < 1) ksplits = 1;
     }
     p.ksplits = ksplits;
-    GemmSmemLayout L{4, tokens};
-    if (L.bytes() > 220 * 1024) return cudaErrorInvalidValue;   // 4 stages are required (kAhead = 2 in flight + 2)
+    GemmSmemLayout L{8, tokens};                                // 8, 4 or 2 stages: as many as fit
+    while (L.stages > 2 && L.bytes() > 220 * 1024) L.stages /= 2;
+    if (L.bytes() > 220 * 1024) return cudaErrorInvalidValue;
     p.stages = L.stages;
+    {
+        // X as a 2-D byte tensor: dim 0 = k (K bytes per row), dim 1 = token; one box = 128 k x the token tile
+        if ((reinterpret_cast<uintptr_t>(p.X) & 15u) != 0) return cudaErrorInvalidValue;
+        EncodeTiledFn enc = encode_tiled();
+        if (!enc) return cudaErrorNotSupported;
+        const cuuint64_t dims[2] = {(cuuint64_t)p.K, (cuuint64_t)p.M};
+        const cuuint64_t strides[1] = {(cuuint64_t)p.K};
+        const cuuint32_t box[2] = {(cuuint32_t)kKStep, (cuuint32_t)tokens};
+        const cuuint32_t estr[2] = {1, 1};
+        if (enc(&p.xmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(p.X), dims, strides, box, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return cudaErrorInvalidValue;
+    }
     const size_t smem = (size_t)L.bytes();
     static bool attr_set[64] = {};
     int dev = 0;

@@ -1,6 +1,7 @@
 // Host-side declarations of the kernel launchers (implemented in the .cu files).
 // Every launcher returns a cudaError_t and launches on the given stream.
 #pragma once
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -104,6 +105,9 @@ cudaError_t launch_gemv(const GemvParams& p, const GemvLaunchCfg& cfg, cudaStrea
 
 // ---- batched GEMM (tcgen05) ---------------------------------------------------
 struct GemmParams {
+    // TMA descriptor of X as a 2-D byte tensor {K, M}, box {128 k, token tile}, 128-byte swizzle: one copy
+    // lands a whole activation stage in the layout the tensor core reads.  Set by the launcher.
+    alignas(64) CUtensorMap xmap;
     const uint8_t* W;         // internal layout (strips)
     const int8_t* X;          // [M][K] row-major
     const float* x_scales;    // [M]
@@ -118,7 +122,7 @@ struct GemmParams {
     float w_scale;
     int M, N, K, Kpad, n_strips;
     int tokens, tmem_cols, ksplits, stages;   // set by the launcher
-    int dbg;                  // timing experiments only: 1 = no activation copy, 2 = no MMA, 4 = no expansion, 8 = no row sums
+    int dbg;                  // unused
     int* status;
 };
 size_t gemm_scratch_ints(int M, int N, bool split);
