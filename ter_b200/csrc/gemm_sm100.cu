@@ -11,9 +11,9 @@
 //   * loader (warp 9, one lane): one TMA tensor copy (cp.async.bulk.tensor.2d, 128-byte swizzle) per
 //     stage brings the 128-k slice of the int8 activations of the token tile into the B stage, in the
 //     layout the tensor core reads; it runs as far ahead as there are free stages.
-//   * producers (warps 0-7): warp w owns k-steps w, w+8, ...: it reads the 4 KB of packed trits (2 bits)
-//     of the step with 16-byte read-only loads one step of its own ahead, expands them in registers to
-//     unsigned bytes and stores them into the A stage in the same 128-byte-swizzled layout.  The expansion needs no
+//   * producers (warps 0-7): fetch the packed trits (2 bits) of the tile with 16-byte cp.async copies
+//     into a thread-private ring (6 steps deep, 4 in flight), expand them in registers to unsigned
+//     bytes and store them into the A stage in the same 128-byte-swizzled layout.  The expansion needs no
 //     shift and no sign decode: row r of A holds column 4*b + f, whose bytes are (w & (3 << 2f)),
 //     i.e. 4^f * (trit + 1); the accumulator of row r is divided by 4^f in the epilogue (exact) and
 //     the "+1" is removed by subtracting sum_k X[m][k].
@@ -37,14 +37,16 @@ constexpr int kGemmThreads = 32 * (kProducerWarps + 2);   // 8 producer/epilogue
 constexpr int kTileN = 128;                  // output columns per CTA = MMA M
 constexpr int kKStep = 128;                  // k per pipeline stage = one 128-byte swizzle row
 constexpr int kAStageBytes = kTileN * kKStep;   // 16 KB
+constexpr int kRawStageBytes = 4096;            // the packed trits of one step (128 columns x 128 k, 2 bits each)
+constexpr int kRawRing = 6;                     // thread-private ring of packed-trit steps
+constexpr int kRawAhead = 4;                    // cp.async copies in flight per producer thread (< kRawRing)
 
-__device__ __forceinline__ uint4 ldg_stream16(const uint8_t* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p));
-    return v;
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
 }
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -91,7 +93,8 @@ struct GemmSmemLayout {
     __host__ __device__ int b_stage_bytes() const { return tokens * kKStep; }
     __host__ __device__ int a_off(int s) const { return s * kAStageBytes; }
     __host__ __device__ int b_off(int s) const { return stages * kAStageBytes + s * b_stage_bytes(); }
-    __host__ __device__ int tail_off() const { return stages * (kAStageBytes + b_stage_bytes()); }
+    __host__ __device__ int raw_off(int s) const { return stages * (kAStageBytes + b_stage_bytes()) + s * kRawStageBytes; }
+    __host__ __device__ int tail_off() const { return stages * (kAStageBytes + b_stage_bytes()) + kRawRing * kRawStageBytes; }
     // tail: full[8], empty[8], done (u64 each) | tmem base, abort (16 B) | scale[256] (float) | rowsum[256] (int)
     __host__ __device__ int bytes() const { return tail_off() + 17 * 8 + 16 + 2 * 256 * 4 + 1024; }
 };
@@ -120,7 +123,7 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_trit_kernel(const __grid_co
     const int S = p.stages;
 
     if (tid == 0) {
-        for (int i = 0; i < S; ++i) { mbar_init(&full[i], kProducerWarps / S + 1 /* its producer warps + the loader */); mbar_init(&empty[i], 1); }
+        for (int i = 0; i < S; ++i) { mbar_init(&full[i], kProducerWarps + 1 /* the producer warps + the loader */); mbar_init(&empty[i], 1); }
         mbar_init(done, 1);
         *abort_flag = 0;
         mbar_fence_init();
@@ -140,70 +143,63 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_trit_kernel(const __grid_co
     pdl_wait();
 
     if (warp < kProducerWarps) {
-        // ------------------------------------------------------------------ producers (8 warps)
-        // Stage s belongs to the 8 / S warps with warp % S == s; they fill it in EVERY round (steps s,
-        // s + S, ...), each expanding its share of the 128 rows, so a warp sees every phase of its stage's
-        // barrier in order (a parity wait must never skip a phase).  S steps are in the making at once:
-        // the latency of one step's chain (loads -> expand -> fence -> arrive) is spread over S MMA steps.
-        // Per step the tile's 4 KB of packed trits are 8 groups of 4 segments of 128 bytes (segment =
-        // (strip, byte-column), lane = (segment within the group, 16-byte part)): a warp load is a coalesced
-        // 4 x 128 bytes, and each 16 bytes become 4 rows of A; a warp store covers 4 whole 128-byte rows
-        // of the swizzled stage, i.e. no bank conflicts.
+        // ------------------------------------------------------------------ producers (256 threads)
+        // Every thread owns 16 packed bytes of every step (segment = (strip, byte-column) of 128 bytes,
+        // part = 16 of them): it copies them with cp.async into its private slot of a ring (kRawAhead steps
+        // in flight, no barrier needed: the same thread reads them back), then expands them into 4 rows of
+        // the A stage.  All producer warps take part in every step, so each sees every phase of the stage
+        // barriers in order (a parity wait must never skip a phase).
         const int nb = (p.Kpad + kGemvKC - 1) / kGemvKC;
         const int last_kc = p.Kpad - (nb - 1) * kGemvKC;
-        const int part = lane & 7, sub = lane >> 3;
-        const int my_stage = warp % S, share = warp / S, n_share = kProducerWarps / S;   // S is 2, 4 or 8
-        const int g_per = 8 / n_share, g0 = share * g_per;
+        const int seg = tid >> 3, part = tid & 7;          // 32 segments x 8 x 16 bytes
+        const int strip_l = seg >> 2, bc = seg & 3;
+        const int strip = tile * 8 + strip_l;
+        const bool strip_ok = strip < p.n_strips;
+        const uint8_t* sbase = p.W + (size_t)strip * 4u * (size_t)p.Kpad;
         // per-token epilogue constants
         if (tid < p.tokens) {
             const int m = m0 + tid;
             tok_scale[tid] = (m < p.M && p.x_scales) ? p.x_scales[m] * p.w_scale : 0.0f;
             tok_sum[tid] = (m < p.M) ? p.x_rowsum[m] : 0;
         }
-        uint4 raw[8];
-        auto load_raw = [&](int j) {
-            const int ks = step_begin + j;
-            const int q = ks >> 3;
-            const int kc = (q == nb - 1) ? last_kc : kGemvKC;
-#pragma unroll
-            for (int gi = 0; gi < 8; ++gi) {
-                if (gi < g_per) {
-                    const int seg = (g0 + gi) * 4 + sub, strip = tile * 8 + (seg >> 2), bc = seg & 3;
-                    if (strip < p.n_strips) {
-                        raw[gi] = ldg_stream16(p.W + (size_t)strip * 4u * (size_t)p.Kpad + (size_t)q * (4 * kGemvKC) +
-                                               (size_t)bc * kc + (ks & 7) * 128 + part * 16);
-                    } else {
-                        raw[gi] = make_uint4(0x55555555u, 0x55555555u, 0x55555555u, 0x55555555u);   // trit 0 everywhere
-                    }
-                }
-            }
-        };
         bool ok = true;
-        if (my_stage < n_steps) load_raw(my_stage);
-        for (int it = my_stage; it < n_steps; it += S) {
-            // the stage is free once the MMAs of step it - S have completed
-            if (it >= S) ok = ok && mbar_wait_abortable(&empty[my_stage], ((uint32_t)(it / S) & 1u) ^ 1u, abort_flag, p.status);
+        auto issue = [&](int j) {
+            const int ks = step_begin + j;
+            uint8_t* raw = gsm + L.raw_off(j % kRawRing) + seg * 128 + part * 16;
+            if (strip_ok) {
+                const int q = ks >> 3;
+                const int kc = (q == nb - 1) ? last_kc : kGemvKC;
+                cp_async16(raw, sbase + (size_t)q * (4 * kGemvKC) + (size_t)bc * kc + (ks & 7) * 128 + part * 16);
+            } else {
+                *reinterpret_cast<uint4*>(raw) = make_uint4(0x55555555u, 0x55555555u, 0x55555555u, 0x55555555u);
+            }
+            cp_async_commit();
+        };
+        for (int j = 0; j < kRawAhead; ++j)
+            if (j < n_steps) issue(j); else cp_async_commit();
+        for (int it = 0; it < n_steps; ++it) {
+            const int s = it % S;
+            if (it + kRawAhead < n_steps) issue(it + kRawAhead); else cp_async_commit();
+            cp_async_wait<kRawAhead>();      // this thread's packed bytes of step `it` have landed
+            // the A stage is free once the MMAs of step it - S have completed
+            if (it >= S) ok = ok && mbar_wait_abortable(&empty[s], ((uint32_t)(it / S) & 1u) ^ 1u, abort_flag, p.status);
             if (!ok) break;
-            uint8_t* A = gsm + L.a_off(my_stage);
+            {
+                uint8_t* A = gsm + L.a_off(s);
+                const uint4 w = *reinterpret_cast<const uint4*>(gsm + L.raw_off(it % kRawRing) + seg * 128 + part * 16);
 #pragma unroll
-            for (int gi = 0; gi < 8; ++gi) {
-                if (gi < g_per) {
-                    const int seg = (g0 + gi) * 4 + sub;
-                    const uint4 w = raw[gi];
-#pragma unroll
-                    for (int f = 0; f < 4; ++f) {
-                        const uint32_t mk = 0x03030303u << (2 * f);
-                        const int r = (seg >> 2) * 16 + (seg & 3) * 4 + f;        // A row = local output column
-                        *reinterpret_cast<uint4*>(A + (r >> 3) * 1024 + (r & 7) * 128 + ((part ^ (r & 7)) * 16)) =
-                            make_uint4(w.x & mk, w.y & mk, w.z & mk, w.w & mk);
-                    }
+                for (int f = 0; f < 4; ++f) {
+                    const uint32_t mk = 0x03030303u << (2 * f);
+                    const int r = strip_l * 16 + bc * 4 + f;                     // A row = local output column
+                    *reinterpret_cast<uint4*>(A + (r >> 3) * 1024 + (r & 7) * 128 + ((part ^ (r & 7)) * 16)) =
+                        make_uint4(w.x & mk, w.y & mk, w.z & mk, w.w & mk);
                 }
             }
-            if (it + S < n_steps) load_raw(it + S);   // lands while the other stages are being filled
             fence_async_smem();          // make the generic-proxy writes visible to the tensor core
             __syncwarp();
-            if (lane == 0) mbar_arrive(&full[my_stage]);
+            if (lane == 0) mbar_arrive(&full[s]);
         }
+        cp_async_wait<0>();
     } else if (warp == kProducerWarps + 1) {
         // ------------------------------------------------------------------ activation loader (TMA)
         if (lane == 0) {
@@ -393,8 +389,8 @@ cudaError_t launch_gemm(const GemmParams& p_in, int sm_count, bool pdl, cudaStre
         if (ksplits < 1) ksplits = 1;
     }
     p.ksplits = ksplits;
-    GemmSmemLayout L{8, tokens};                                // 8, 4 or 2 stages: as many as fit
-    while (L.stages > 2 && L.bytes() > 220 * 1024) L.stages /= 2;
+    GemmSmemLayout L{8, tokens};                                // as many stages as fit, at most 8
+    while (L.stages > 2 && L.bytes() > 220 * 1024) --L.stages;
     if (L.bytes() > 220 * 1024) return cudaErrorInvalidValue;
     p.stages = L.stages;
     {
