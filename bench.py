@@ -253,14 +253,17 @@ def cpu_reference_run(steps: int, warmup: int, threads: int):
             "ms_per_step": dt / steps * 1e3}
 
 
-def decode_bench(tb, dev, rank, n_prompt=128, n_gen=256):
-    """Random-init ternarised Llama-3.2-1B architecture (16 layers, H 2048, 32/8 heads x 64, FFN 8192,
-    vocab 128256, tied bf16 lm_head, bf16 KV cache), batch 1: 128 random prompt ids fed one position at a
-    time, then 256 greedy tokens; every step is one replay of the captured decode graph."""
+def decode_bench(tb, dev, rank, which="llama", n_prompt=128, n_gen=256, batch=1, smax=512, warm=True):
+    """Random-init ternarised decode of one of the two benchmark architectures (tied bf16 lm_head, bf16 KV
+    cache): Llama-3.2-1B (16 layers, H 2048, 32/8 heads x 64, FFN 8192 SiLU) or BitNet-b1.58-2B (30 layers,
+    H 2560, 20/5 heads x 128, FFN 6912 squared-ReLU with sub-norms), vocab 128256.  n_prompt random prompt
+    ids are fed one position at a time (the reference's only method), then n_gen greedy tokens; every step
+    is one replay of the captured decode graph."""
     import torch
     from ter_b200 import FMT_V11, synth
-    cfg = dict(synth.LLAMA_1B_CFG, Smax=512)
-    tb.model_create(cfg, max_batch=1)
+    base = synth.LLAMA_1B_CFG if which == "llama" else synth.BITNET_2B_CFG
+    cfg = dict(base, Smax=smax)
+    tb.model_create(cfg, max_batch=batch)
     g = torch.Generator(device=dev)
     g.manual_seed(synth.seed_for(rank, "embd") & 0x7FFFFFFF)
     emb = (torch.randn((cfg["V"], cfg["H"]), generator=g, device=dev) * 0.02).to(torch.bfloat16)
@@ -272,26 +275,36 @@ def decode_bench(tb, dev, rank, n_prompt=128, n_gen=256):
     for L in range(cfg["L"]):
         for wi, nm in enumerate(synth.MAT_ORDER):
             K, N = shapes[nm]
-            seed = synth.seed_for(rank, "dec", L, nm)
+            seed = synth.seed_for(rank, "dec", which, L, nm)
             tb.model_set_matrix(L, wi, synth.packed_v11_cuda(K, N, seed, dev), FMT_V11, float(synth.weight_scale(seed)))
-        for vi in range(2):
-            tb.model_set_vector(L, vi, rng.normal(1.0, 0.02, cfg["H"]).astype(np.float32))
-    prompt = np.random.default_rng(synth.seed_for(rank, "prompt")).integers(0, cfg["V"], size=n_prompt).astype(np.int32)
-    tb.generate(prompt, n_gen)                 # captures the graph, warms up
+        for vi in range(4 if cfg["arch"] == 1 else 2):
+            n = cfg["F"] if vi == 3 else cfg["H"]
+            tb.model_set_vector(L, vi, rng.normal(1.0, 0.02, n).astype(np.float32))
+    prompt = np.random.default_rng(synth.seed_for(rank, "prompt", which)).integers(
+        0, cfg["V"], size=(batch, n_prompt)).astype(np.int32)
+    if batch == 1:
+        prompt = prompt[0]
+    if warm:
+        tb.generate(prompt, n_gen)             # captures the graph, warms up
     t0 = time.perf_counter()
     out = tb.generate(prompt, n_gen)           # host tokens in, host tokens out
     wall = time.perf_counter() - t0
     steps = n_prompt + n_gen - 1
     ms = tb.last_generate_ms()
     shapes_bytes = sum(K * N // 4 for K, N in shapes.values()) * cfg["L"]
-    step_bytes = shapes_bytes + 2 * cfg["V"] * cfg["H"]
+    # per step: packed layer weights + bf16 lm_head + the KV cache read (mean context over the run)
+    kv_bytes = batch * (steps / 2) * cfg["L"] * 2 * cfg["Nkv"] * cfg["Hd"] * 2
+    step_bytes = shapes_bytes + 2 * cfg["V"] * cfg["H"] + kv_bytes
     peak, _ = peaks()
-    return {"workload": "llama-3.2-1b architecture decode, batch 1, prompt 128 + 256 greedy tokens, random-init",
-            "tokens_per_s": steps / ms * 1e3, "ms_per_token": ms / steps, "steps": steps,
-            "e2e_tokens_per_s": steps / wall, "first_tokens": [int(t) for t in out[0][:4]],
+    name = "llama-3.2-1b" if which == "llama" else "bitnet-b1.58-2b"
+    return {"workload": f"{name} architecture decode, batch {batch}, prompt {n_prompt} + {n_gen} greedy tokens, random-init",
+            "tokens_per_s": batch * steps / ms * 1e3, "ms_per_step": ms / steps, "ms_per_token": ms / steps / batch,
+            "steps": steps, "batch": batch,
+            "e2e_tokens_per_s": batch * steps / wall, "first_tokens": [int(t) for t in out[0][:4]],
             "roofline_frac_hbm": (step_bytes / (ms / steps * 1e-3) / 1e9) / peak,
-            "bytes_per_token": step_bytes,
-            "note": "device time of the graph replays (CUDA events); e2e = wall clock of the generate() call"}
+            "bytes_per_step": int(step_bytes),
+            "note": "device time of the graph replays (CUDA events); e2e = wall clock of the generate() call"
+                    + ("" if warm else "; single call, includes the graph's first replays")}
 
 
 def run_reference_arm(args):
@@ -321,6 +334,8 @@ def main():
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--no-per-shape", action="store_true")
     ap.add_argument("--no-gemm", action="store_true")
+    ap.add_argument("--no-bitnet", action="store_true", help="skip the BitNet-2B decode runs")
+    ap.add_argument("--no-batch64", action="store_true", help="skip the batch-64 BitNet decode run (about 30 s)")
     ap.add_argument("--layers", type=int, default=16, help="layers of the fabric (profiling captures use fewer)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -478,6 +493,7 @@ def main():
 
     # ---- decode tokens/s (BASELINE configs[3]: Llama-3.2-1B architecture, batch 1, prompt 128 + 256 greedy)
     decode = None
+    decode_bitnet = None
     if not args.no_decode:
         tb.close()
         torch.cuda.empty_cache()
@@ -487,16 +503,26 @@ def main():
             tb.set_option("tp_p2p", int(os.environ.get("TER_TP_P2P", "1")))   # 0: NCCL all-gathers, for comparison
             if "TER_TP_SHARD" in os.environ:                                  # else the library's default policy
                 tb.set_option("tp_shard", int(os.environ["TER_TP_SHARD"]))
-        decode = decode_bench(tb, dev, 0)  # the same model on every rank; the library keeps its slice
-        if world > 1:
-            t = torch.tensor([decode["ms_per_token"]], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            decode["ms_per_token"] = float(t.item())
-            decode["tokens_per_s"] = 1e3 / decode["ms_per_token"]
-            decode["note"] += f"; tensor parallel over {world} GPUs (strong scaling, max over ranks)"
-            decode["parallelism"] = f"tp{world}"
-            decode["sharded_blocks"] = os.environ.get("TER_TP_SHARD", "library default")
-            decode["exchange"] = "peer-memory kernel" if os.environ.get("TER_TP_P2P", "1") != "0" else "nccl all-gather"
+        def tp_fix(d):
+            if world > 1:
+                t = torch.tensor([d["ms_per_step"]], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                d["ms_per_step"] = float(t.item())
+                d["ms_per_token"] = d["ms_per_step"] / d["batch"]
+                d["tokens_per_s"] = 1e3 / d["ms_per_token"]
+                d["note"] += f"; tensor parallel over {world} GPUs (strong scaling, max over ranks)"
+                d["parallelism"] = f"tp{world}"
+                d["sharded_blocks"] = os.environ.get("TER_TP_SHARD", "library default")
+                d["exchange"] = "peer-memory kernel" if os.environ.get("TER_TP_P2P", "1") != "0" else "nccl all-gather"
+            return d
+        decode = tp_fix(decode_bench(tb, dev, 0))  # the same model on every rank; the library keeps its slice
+        if not args.no_bitnet:
+            # BASELINE configs[4]: BitNet-2B architecture, context 2048 + 128 greedy tokens; batch 1 (tensor
+            # parallel at N > 1) and, on one GPU, batch 64 (token batch through the tensor-core GEMM)
+            decode_bitnet = [tp_fix(decode_bench(tb, dev, 0, "bitnet", n_prompt=2048, n_gen=128, smax=2176))]
+            if world == 1 and not args.no_batch64:
+                decode_bitnet.append(decode_bench(tb, dev, 0, "bitnet", n_prompt=2048, n_gen=128, batch=64, smax=2176,
+                                                  warm=False))
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -542,6 +568,7 @@ def main():
                             "host buffer; synchronous call",
                     "d2h_bytes_per_step": sum(4 * N for _, _, N, _, _ in mats) * world},
             "decode": decode,
+            "decode_bitnet": decode_bitnet,
             "gpu_launches": launches,
             "clocks": clocks,
         }
