@@ -289,22 +289,31 @@ def decode_bench(tb, dev, rank, which="llama", n_prompt=128, n_gen=256, batch=1,
     t0 = time.perf_counter()
     out = tb.generate(prompt, n_gen)           # host tokens in, host tokens out
     wall = time.perf_counter() - t0
-    steps = n_prompt + n_gen - 1
     ms = tb.last_generate_ms()
+    prompt_ms = tb.last_prompt_ms()
+    batched_prompt = tb.last_prefill_ms() > 0.0
+    # generation phase: the steps after the prompt has been consumed (the first generated token belongs to
+    # the prompt phase when the prompt ran as token batches)
+    gen_steps = n_gen - 1 if batched_prompt else n_gen
+    gen_ms = ms - prompt_ms
     shapes_bytes = sum(K * N // 4 for K, N in shapes.values()) * cfg["L"]
-    # per step: packed layer weights + bf16 lm_head + the KV cache read (mean context over the run)
-    kv_bytes = batch * (steps / 2) * cfg["L"] * 2 * cfg["Nkv"] * cfg["Hd"] * 2
+    # per generation step: packed layer weights + bf16 lm_head + the KV cache read at the mean context
+    kv_bytes = batch * (n_prompt + n_gen / 2) * cfg["L"] * 2 * cfg["Nkv"] * cfg["Hd"] * 2
     step_bytes = shapes_bytes + 2 * cfg["V"] * cfg["H"] + kv_bytes
     peak, _ = peaks()
     name = "llama-3.2-1b" if which == "llama" else "bitnet-b1.58-2b"
     return {"workload": f"{name} architecture decode, batch {batch}, prompt {n_prompt} + {n_gen} greedy tokens, random-init",
-            "tokens_per_s": batch * steps / ms * 1e3, "ms_per_step": ms / steps, "ms_per_token": ms / steps / batch,
-            "steps": steps, "batch": batch,
-            "e2e_tokens_per_s": batch * steps / wall, "first_tokens": [int(t) for t in out[0][:4]],
-            "roofline_frac_hbm": (step_bytes / (ms / steps * 1e-3) / 1e9) / peak,
+            "tokens_per_s": batch * gen_steps / gen_ms * 1e3, "ms_per_step": gen_ms / gen_steps,
+            "ms_per_token": gen_ms / gen_steps / batch, "steps": gen_steps, "batch": batch,
+            "prompt_ms": prompt_ms, "prompt_tokens_per_s": batch * n_prompt / prompt_ms * 1e3,
+            "prompt_mode": "token batches of up to 256 positions through the tensor-core GEMM" if batched_prompt
+                           else "one position per step (the reference's method)",
+            "e2e_tokens_per_s": batch * n_gen / wall, "first_tokens": [int(t) for t in out[0][:4]],
+            "roofline_frac_hbm": (step_bytes / (gen_ms / gen_steps * 1e-3) / 1e9) / peak,
             "bytes_per_step": int(step_bytes),
-            "note": "device time of the graph replays (CUDA events); e2e = wall clock of the generate() call"
-                    + ("" if warm else "; single call, includes the graph's first replays")}
+            "note": "tokens_per_s = generated tokens per second of device time (CUDA events) over the generation steps, "
+                    "at contexts n_prompt .. n_prompt + n_gen; e2e = generated tokens / wall clock of the whole generate() "
+                    "call (prompt included)" + ("" if warm else "; single call, includes the graph's first replays")}
 
 
 def run_reference_arm(args):

@@ -105,6 +105,8 @@ SIGNATURES = {
     "ter_b200_model_hidden": (_I, [_VP, _VP]),
     "ter_b200_generate": (_I, [_VP, _VP, _I, _I, _I, _VP, _VP]),
     "ter_b200_last_generate_ms": (_F, [_VP]),
+    "ter_b200_last_prefill_ms": (_F, [_VP]),
+    "ter_b200_last_prompt_ms": (_F, [_VP]),
     "ter_b200_comm_unique_id": (_I, [_VP]),
     "ter_b200_comm_init": (_I, [_VP, _VP, _I, _I]),
     "ter_b200_comm_destroy": (None, [_VP]),
@@ -539,6 +541,12 @@ class TerB200:
 
     def last_generate_ms(self) -> float:
         return float(self.L.ter_b200_last_generate_ms(self.h))
+
+    def last_prompt_ms(self) -> float:
+        return float(self.L.ter_b200_last_prompt_ms(self.h))
+
+    def last_prefill_ms(self) -> float:
+        return float(self.L.ter_b200_last_prefill_ms(self.h))
 
     # ---- CUDA graphs
     def capture(self, fn, stream=None):

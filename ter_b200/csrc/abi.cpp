@@ -198,6 +198,7 @@ ter_b200_handle_t* ter_b200_create(int device) {
     h->attn_inline_merge = 1;
     h->tp_p2p = 1;
     h->tp_shard = 0;
+    h->prefill = 1;
     h->gemm_split_k = 1;
     int sms = 0;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) sms = 148;
@@ -495,6 +496,8 @@ int ter_b200_set_option(ter_b200_handle_t* h, const char* key, int value) {
         h->gemm_min_m = value;
     } else if (strcmp(key, "attn_inline_merge") == 0) {
         h->attn_inline_merge = value ? 1 : 0;
+    } else if (strcmp(key, "prefill") == 0) {
+        h->prefill = value ? 1 : 0;     // buffers are sized by the next ter_b200_model_create
     } else if (strcmp(key, "tp_shard") == 0) {
         if (value < 0 || value > 3) return TER_B200_E_SHAPE;
         h->tp_shard = value;            // read by the next ter_b200_model_create

@@ -33,6 +33,7 @@ struct RopeKvParams {
     uint16_t* kcache;
     uint16_t* vcache;
     int B, Nh, Nkv, Hd, Smax, neox;
+    int shared_seq;        // 0: row b belongs to sequence b; s > 0: every row belongs to sequence s - 1 (prompt rows)
 };
 cudaError_t launch_rope_kv(const RopeKvParams& p, bool pdl, cudaStream_t st);
 
@@ -56,6 +57,8 @@ struct AttnParams {
     int* status;             // device status word for bounded waits (may be null)
     int* counters;           // [B][Nkv] arrival counters, zero between steps: the last CTA of a KV head merges
                              // the chunks itself (no second kernel); null = merge in attn_combine_kernel
+    int shared_seq;          // 0: row b reads the cache of sequence b; s > 0: every row reads sequence s - 1
+                             // (the rows are positions of one prompt, each with its own pos[b])
 };
 cudaError_t launch_attention(const AttnParams& p, bool pdl, cudaStream_t st);
 size_t attention_scratch_floats(int B, int Nh, int Hd, int Smax);

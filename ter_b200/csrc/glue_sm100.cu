@@ -71,6 +71,7 @@ __global__ void __launch_bounds__(kT) rope_kv_kernel(const RopeKvParams p) {
     pdl_launch_dependents();
     pdl_wait();
     const int b = blockIdx.x;
+    const int bs = p.shared_seq ? p.shared_seq - 1 : b;   // whose cache
     const int pos = p.pos[b];
     if (pos < 0 || pos >= p.Smax) return;
     const int half = p.Hd / 2;
@@ -93,14 +94,14 @@ __global__ void __launch_bounds__(kT) rope_kv_kernel(const RopeKvParams p) {
         base[i0] = o0;
         base[i1] = o1;
         if (is_k) {
-            const size_t co = (((size_t)b * p.Nkv + (head - p.Nh)) * p.Smax + pos) * p.Hd;
+            const size_t co = (((size_t)bs * p.Nkv + (head - p.Nh)) * p.Smax + pos) * p.Hd;
             p.kcache[co + i0] = f32_to_bf16_bits(o0);
             p.kcache[co + i1] = f32_to_bf16_bits(o1);
         }
     }
     for (int idx = threadIdx.x; idx < p.Nkv * p.Hd; idx += kT) {
         const int g = idx / p.Hd, d = idx % p.Hd;
-        const size_t co = (((size_t)b * p.Nkv + g) * p.Smax + pos) * p.Hd;
+        const size_t co = (((size_t)bs * p.Nkv + g) * p.Smax + pos) * p.Hd;
         p.vcache[co + d] = f32_to_bf16_bits(v[idx]);
     }
 }
@@ -158,6 +159,7 @@ __global__ void __launch_bounds__(kT) attn_partial_kernel(const AttnParams p) {
         mbar_fence_init();
     }
     const int c = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
+    const int bs = p.shared_seq ? p.shared_seq - 1 : b;   // whose cache
     {
         // Hints only, issued while the producer of q is still running: pull this CTA's K/V chunk and the
         // rotary row towards L2.  The position read here may be one step stale; nothing depends on it.
@@ -165,7 +167,7 @@ __global__ void __launch_bounds__(kT) attn_partial_kernel(const AttnParams p) {
         const int s0g = c * kAttnChunk;
         if (pg >= 0 && pg < p.Smax && s0g <= pg + 1) {
             const int rows = min(kAttnChunk, pg + 2 - s0g);
-            const size_t ho = ((size_t)b * p.Nkv + g) * (size_t)p.Smax * HD + (size_t)s0g * HD;
+            const size_t ho = ((size_t)bs * p.Nkv + g) * (size_t)p.Smax * HD + (size_t)s0g * HD;
             const int lines = rows * HD * 2 / 128;
             for (int i = tid; i < lines; i += kT) {
                 asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(p.kcache + ho) + (size_t)i * 128));
@@ -188,7 +190,7 @@ __global__ void __launch_bounds__(kT) attn_partial_kernel(const AttnParams p) {
     const bool fused = p.rope_table != nullptr;
     const bool owner = fused && (pos >= s0) && (pos < s0 + kAttnChunk);   // this chunk holds the new row
     const int n_copy = owner ? cnt - 1 : cnt;                             // rows already in the cache
-    const size_t head_off = ((size_t)b * p.Nkv + g) * (size_t)p.Smax * HD;
+    const size_t head_off = ((size_t)bs * p.Nkv + g) * (size_t)p.Smax * HD;
     const uint16_t* K = p.kcache + head_off;
     const uint16_t* V = p.vcache + head_off;
 

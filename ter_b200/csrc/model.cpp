@@ -38,7 +38,15 @@ struct TerbModel {
     size_t xrecv_off, xrecv_bytes;   // receive blocks of the exchange points, handed out in forward() order
     int* xseq;                       // int[kMaxExchangePoints][kMaxExchangeCtas], inside the arena
     bool shard_attn, shard_ffn;      // which blocks are column-sharded over the ranks (the lm_head always is)
+    // prompt processing (prefill): the activation buffers hold `rows_cap` rows; a tile of prompt positions
+    // goes through the layers as a token batch (tensor-core GEMM), all rows sharing sequence 0's cache
+    int rows_cap;
+    int *tok_rows, *pos_rows;        // [rows_cap] token ids and positions of the tile
+    cudaEvent_t ev_mid;
+    float last_prefill_ms, last_prompt_ms;
 };
+
+constexpr int kPrefillTile = 256;    // prompt positions per pass = the token tile of the GEMM
 
 namespace {
 
@@ -101,9 +109,15 @@ bool can_fuse(const ter_b200_handle_t* h, const DevWeight* const* ws, int n, int
     } while (0)
 
 // The launch sequence of one decode step for `B` sequences.
-int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st) {
+// prefill_rows > 0: the rows are `prefill_rows` consecutive positions of ONE prompt (tokens m->tok_rows,
+// positions m->pos_rows, all in sequence 0's cache): rotary + append for all rows first, then causal
+// attention per row; only the last row goes through the lm_head, and the step bookkeeping is left out.
+int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st, int prefill_rows = 0) {
     const ter_b200_model_cfg_t& c = m->c;
-    const int B = m->batch, H = c.H, F = c.F, Hq = c.Nh * c.Hd;
+    const bool pre = prefill_rows > 0;
+    const int B = pre ? prefill_rows : m->batch, H = c.H, F = c.F, Hq = c.Nh * c.Hd;
+    const int* posv = pre ? m->pos_rows : m->pos;
+    const int* tokv = pre ? m->tok_rows : m->tokens;
     const bool pdl = h->gemv_cfg.pdl != 0;
     const bool bitnet = c.arch == TER_B200_ARCH_BITNET;
     const size_t layer_cache = (size_t)c.max_batch * c.Nkv * (size_t)c.Smax * c.Hd;
@@ -162,7 +176,7 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
     };
 #define XCHG1(buf, n, sharded) do { float* b__[1] = {(buf)}; int n__[1] = {(n)}; int rc__ = exchange(b__, n__, 1, (sharded)); if (rc__) return rc__; } while (0)
 
-    CK(launch_embed(m->embd, m->tokens, m->hidden, H, B, c.V, pdl, st));
+    CK(launch_embed(m->embd, tokv, m->hidden, H, B, c.V, pdl, st));
     for (int L = 0; L < c.L; ++L) {
         const DevWeight* W = m->mats + (size_t)L * 7;
         float** vec = m->vecs + (size_t)L * 4;
@@ -182,10 +196,19 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
         // rotary, KV append and attention in one launch (+ the ordered merge of the chunks)
         uint16_t* kc = m->kcache + L * layer_cache;
         uint16_t* vc = m->vcache + L * layer_cache;
-        AttnParams ap{m->q, kc, vc, m->pos, m->attn_scratch, m->att, B, c.Nh, c.Nkv, c.Hd, c.Smax,
-                      (c.Smax + kAttnChunk - 1) / kAttnChunk, m->rope, m->k, m->v, kc, vc, bitnet ? 1 : 0,
-                      h->status_dev, h->attn_inline_merge ? m->attn_counters : nullptr};
-        CK(launch_attention(ap, pdl, st));
+        if (pre) {
+            RopeKvParams rp{m->q, m->k, m->v, m->rope, posv, kc, vc, B, c.Nh, c.Nkv, c.Hd, c.Smax, bitnet ? 1 : 0, 1};
+            CK(launch_rope_kv(rp, pdl, st));
+            AttnParams ap{m->q, kc, vc, posv, m->attn_scratch, m->att, B, c.Nh, c.Nkv, c.Hd, c.Smax,
+                          (c.Smax + kAttnChunk - 1) / kAttnChunk, nullptr, nullptr, nullptr, nullptr, nullptr, 0,
+                          h->status_dev, h->attn_inline_merge ? m->attn_counters : nullptr, 1};
+            CK(launch_attention(ap, pdl, st));
+        } else {
+            AttnParams ap{m->q, kc, vc, m->pos, m->attn_scratch, m->att, B, c.Nh, c.Nkv, c.Hd, c.Smax,
+                          (c.Smax + kAttnChunk - 1) / kAttnChunk, m->rope, m->k, m->v, kc, vc, bitnet ? 1 : 0,
+                          h->status_dev, h->attn_inline_merge ? m->attn_counters : nullptr, 0};
+            CK(launch_attention(ap, pdl, st));
+        }
         if (!h->attn_inline_merge) h->launches += 1;
         {
             const DevWeight* ws[1] = {&W[TER_B200_WO]};
@@ -237,26 +260,30 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
             XCHG1(m->hidden, H, sf);
         }
     }
+    // lm_head: every sequence of a decode step; of a prompt tile only its last position
+    const int Bh = pre ? 1 : B;
+    const float* hid = pre ? m->hidden + (size_t)(B - 1) * H : m->hidden;
     if (c.lm_head_packed) {
         // bench-mode packed lm_head: cuda/ter_cuda_forward_packed.cu:541-545
-        NormQuantParams oq{m->hidden, nullptr, m->out_norm, m->xq, m->xs, nullptr, H, B, PRE_NONE, c.eps};
+        NormQuantParams oq{hid, nullptr, m->out_norm, m->xq, m->xs, nullptr, H, Bh, PRE_NONE, c.eps};
         CK(launch_norm_quant(oq, pdl, st));
         const DevWeight* ws[1] = {&m->lm_head};
         float* outs[1] = {m->logits + off(c.V)};
-        int rc = mm(h, ws, 1, m->xq, H, m->xs, outs, false, B, st);
+        int rc = mm(h, ws, 1, m->xq, H, m->xs, outs, false, Bh, st);
         if (rc) return rc;
         XCHG1(m->logits, c.V, true);
     } else {
-        NormQuantParams on{m->hidden, nullptr, m->out_norm, nullptr, nullptr, m->xnorm, H, B, PRE_NONE, c.eps};
+        NormQuantParams on{hid, nullptr, m->out_norm, nullptr, nullptr, m->xnorm, H, Bh, PRE_NONE, c.eps};
         CK(launch_norm_quant(on, pdl, st));
-        CK(launch_lm_head_bf16(m->embd + off(c.V) * H, m->xnorm, m->logits + off(c.V), c.V / G, H, B, h->sm_count, pdl, st));
+        CK(launch_lm_head_bf16(m->embd + off(c.V) * H, m->xnorm, m->logits + off(c.V), c.V / G, H, Bh, h->sm_count, pdl, st));
         XCHG1(m->logits, c.V, true);
-        const uint64_t n = (uint64_t)((H + 26) / 27) * (uint64_t)c.V * (uint64_t)B;
+        const uint64_t n = (uint64_t)((H + 26) / 27) * (uint64_t)c.V * (uint64_t)Bh;
         h->counts.tvmac += n;
         h->counts.total_ops += n;
     }
-    CK(launch_argmax(m->logits, c.V, B, m->argmax_scratch, m->greedy, pdl, st));
+    CK(launch_argmax(m->logits, c.V, Bh, m->argmax_scratch, m->greedy, pdl, st));
     h->launches += 1;
+    if (pre) return TER_B200_OK;
     SelectParams sp{m->greedy, use_forced ? m->forced : nullptr, m->tokens, m->pos, use_forced ? m->log : nullptr,
                     m->ctl, B, m->forced_cap, m->log_cap};
     CK(launch_select(sp, pdl, st));
@@ -311,11 +338,12 @@ void ter_b200_model_free(ter_b200_handle_t* h) {
     if (m->embd && m->embd_owned) cudaFree(m->embd);
     void* bufs[] = {m->out_norm, m->hidden, m->q, m->k, m->v, m->att, m->gate, m->up, m->xnorm, m->logits,
                     m->attn_scratch, m->argmax_scratch, m->xs, m->xq, m->kcache, m->vcache, m->tokens, m->pos,
-                    m->greedy, m->forced, m->log, m->ctl, m->attn_counters};
+                    m->greedy, m->forced, m->log, m->ctl, m->attn_counters, m->tok_rows, m->pos_rows};
     for (void* b : bufs)
         if (b) cudaFree(b);
     if (m->ev0) cudaEventDestroy(m->ev0);
     if (m->ev1) cudaEventDestroy(m->ev1);
+    if (m->ev_mid) cudaEventDestroy(m->ev_mid);
     delete m;
     h->model = nullptr;
 }
@@ -352,7 +380,11 @@ int ter_b200_model_create(ter_b200_handle_t* h, const ter_b200_model_cfg_t* cfg)
     m->mats = new (std::nothrow) DevWeight[(size_t)c.L * 7];
     m->vecs = new (std::nothrow) float*[(size_t)c.L * 4]();
     if (!m->mats || !m->vecs) { ter_b200_model_free(h); return TER_B200_E_ALLOC; }
-    const int B = c.max_batch, Hq = c.Nh * c.Hd, Hkv = c.Nkv * c.Hd;
+    const int Hq = c.Nh * c.Hd, Hkv = c.Nkv * c.Hd;
+    // rows of the activation buffers: the decode batch, or a tile of prompt positions (prefill)
+    const int R = (h->prefill && c.max_batch < kPrefillTile) ? kPrefillTile : c.max_batch;
+    m->rows_cap = R;
+    const int B = c.max_batch;
     const int wide = c.F > Hq ? (c.F > c.H ? c.F : c.H) : (Hq > c.H ? Hq : c.H);
     cudaError_t e = cudaSuccess;
     auto A = [&](cudaError_t r) { if (e == cudaSuccess) e = r; };
@@ -360,8 +392,8 @@ int ter_b200_model_create(ter_b200_handle_t* h, const ter_b200_model_cfg_t* cfg)
     // arena that the peers map, followed by the words of the exchange points.
     {
         float** xb[7] = {&m->hidden, &m->q, &m->k, &m->v, &m->gate, &m->up, &m->logits};
-        const size_t xn[7] = {(size_t)B * c.H, (size_t)B * Hq, (size_t)B * Hkv, (size_t)B * Hkv, (size_t)B * c.F,
-                              (size_t)B * c.F, (size_t)B * c.V};
+        const size_t xn[7] = {(size_t)R * c.H, (size_t)R * Hq, (size_t)R * Hkv, (size_t)R * Hkv, (size_t)R * c.F,
+                              (size_t)R * c.F, (size_t)B * c.V};
         bool carved = false;
         if (comm_size(h) > 1 && h->tp_p2p) {
             size_t total = 0, offs[7];
@@ -387,27 +419,30 @@ int ter_b200_model_create(ter_b200_handle_t* h, const ter_b200_model_cfg_t* cfg)
         if (!carved)
             for (int i = 0; i < 7; ++i) A(dalloc(xb[i], xn[i]));
     }
-    A(dalloc(&m->att, (size_t)B * Hq));
+    A(dalloc(&m->att, (size_t)R * Hq));
     A(dalloc(&m->xnorm, (size_t)B * c.H));
-    A(dalloc(&m->attn_scratch, attention_scratch_floats(B, c.Nh, c.Hd, c.Smax)));
+    A(dalloc(&m->attn_scratch, attention_scratch_floats(R, c.Nh, c.Hd, c.Smax)));
     A(dalloc(&m->argmax_scratch, (size_t)B * kArgmaxParts * 2));
-    A(dalloc(&m->xs, (size_t)B));
-    A(dalloc(&m->xq, (size_t)B * wide));
+    A(dalloc(&m->xs, (size_t)R));
+    A(dalloc(&m->xq, (size_t)R * wide));
+    A(dalloc(&m->tok_rows, (size_t)R));
+    A(dalloc(&m->pos_rows, (size_t)R));
     A(dalloc(&m->kcache, cache_elems(c)));
     A(dalloc(&m->vcache, cache_elems(c)));
     A(dalloc(&m->tokens, (size_t)B));
     A(dalloc(&m->pos, (size_t)B));
     A(dalloc(&m->greedy, (size_t)B));
     A(dalloc(&m->ctl, 2));
-    A(dalloc(&m->attn_counters, (size_t)B * c.Nkv));
+    A(dalloc(&m->attn_counters, (size_t)R * c.Nkv));
     if (e == cudaSuccess) e = cudaMemset(m->kcache, 0, cache_elems(c) * 2);
     if (e == cudaSuccess) e = cudaMemset(m->vcache, 0, cache_elems(c) * 2);
     if (e == cudaSuccess) e = cudaMemset(m->tokens, 0, B * sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(m->pos, 0, B * sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(m->ctl, 0, 2 * sizeof(int));
-    if (e == cudaSuccess) e = cudaMemset(m->attn_counters, 0, (size_t)B * c.Nkv * sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(m->attn_counters, 0, (size_t)R * c.Nkv * sizeof(int));
     if (e == cudaSuccess) e = cudaEventCreate(&m->ev0);
     if (e == cudaSuccess) e = cudaEventCreate(&m->ev1);
+    if (e == cudaSuccess) e = cudaEventCreate(&m->ev_mid);
     if (e != cudaSuccess) { ter_b200_model_free(h); return cuda_fail(h, e); }
     int rc = get_rope_table(h, c.Smax, c.Hd, c.rope_theta, &m->rope);
     if (rc) { ter_b200_model_free(h); return rc; }
@@ -642,14 +677,54 @@ int ter_b200_generate(ter_b200_handle_t* h, const int32_t* prompts, int batch, i
         rc = comm_barrier(h, st);
         if (rc) return rc;
     }
+    // Prompt processing.  One sequence with a prompt of at least two tokens: the prompt goes through the
+    // layers in tiles of up to 256 positions as a token batch (tensor-core GEMM, causal attention per
+    // row over the shared cache), which leaves the cache, the position and the first generated token
+    // exactly as feeding the prompt one position at a time does.  Under tensor parallelism only with
+    // replicated layers (the default policy).  Otherwise: one graph replay per prompt position.
+    const bool use_prefill = h->prefill && batch == 1 && n_prompt >= 2 && m->rows_cap >= 2 &&
+                             (comm_size(h) == 1 || (!m->shard_attn && !m->shard_ffn));
     TERB_CUDA(h, cudaEventRecord(m->ev0, st));
-    for (int i = 0; i < steps; ++i) {
+    int replays = steps;
+    if (use_prefill) {
+        const int T = m->rows_cap < kPrefillTile ? m->rows_cap : kPrefillTile;
+        int widest = m->c.F > m->c.H ? m->c.F : m->c.H;
+        if (m->c.Nh * m->c.Hd > widest) widest = m->c.Nh * m->c.Hd;
+        rc = ensure_gemm_scratch(h, T, widest);
+        if (rc) return rc;
+        int* iota = (int*)malloc(sizeof(int) * (size_t)T);
+        if (!iota) return TER_B200_E_ALLOC;
+        for (int p0 = 0; p0 < n_prompt && !rc; p0 += T) {
+            const int rows = n_prompt - p0 < T ? n_prompt - p0 : T;
+            for (int r = 0; r < rows; ++r) iota[r] = p0 + r;
+            cudaError_t ce = cudaMemcpyAsync(m->tok_rows, prompts + p0, rows * sizeof(int), cudaMemcpyHostToDevice, st);
+            if (ce == cudaSuccess) ce = cudaMemcpyAsync(m->pos_rows, iota, rows * sizeof(int), cudaMemcpyHostToDevice, st);
+            if (ce != cudaSuccess) { rc = cuda_fail(h, ce); break; }
+            rc = forward(h, m, false, st, rows);
+        }
+        free(iota);
+        if (rc) return rc;
+        // bookkeeping of the last prompt position: log the first generated token, pos = n_prompt
+        const int last = n_prompt - 1;
+        TERB_CUDA(h, cudaMemcpyAsync(m->pos, &last, sizeof(int), cudaMemcpyHostToDevice, st));
+        SelectParams sp{m->greedy, m->forced, m->tokens, m->pos, m->log, m->ctl, 1, m->forced_cap, m->log_cap};
+        cudaError_t ce = launch_select(sp, h->gemv_cfg.pdl != 0, st);
+        if (ce != cudaSuccess) return cuda_fail(h, ce);
+        h->launches += 1;
+        replays = n_gen - 1;
+    }
+    if (use_prefill) TERB_CUDA(h, cudaEventRecord(m->ev_mid, st));
+    for (int i = 0; i < replays; ++i) {
+        // without prefill the first n_prompt - 1 replays feed the prompt; the mark splits prompt from generation
+        if (!use_prefill && i == n_prompt - 1) TERB_CUDA(h, cudaEventRecord(m->ev_mid, st));
         TERB_CUDA(h, cudaGraphLaunch(m->graph, st));
         h->launches += m->graph_launches;
     }
     TERB_CUDA(h, cudaEventRecord(m->ev1, st));
     TERB_CUDA(h, cudaStreamSynchronize(st));
     TERB_CUDA(h, cudaEventElapsedTime(&m->last_ms, m->ev0, m->ev1));
+    TERB_CUDA(h, cudaEventElapsedTime(&m->last_prompt_ms, m->ev0, m->ev_mid));
+    m->last_prefill_ms = use_prefill ? m->last_prompt_ms : 0.0f;
     for (int b = 0; b < batch; ++b)
         TERB_CUDA(h, cudaMemcpy(out_tokens + (size_t)b * n_gen, m->log + (size_t)b * m->log_cap + (n_prompt - 1),
                                 n_gen * sizeof(int), cudaMemcpyDeviceToHost));
@@ -660,5 +735,7 @@ int ter_b200_generate(ter_b200_handle_t* h, const int32_t* prompts, int batch, i
 }
 
 float ter_b200_last_generate_ms(const ter_b200_handle_t* h) { return (h && h->model) ? h->model->last_ms : 0.0f; }
+float ter_b200_last_prefill_ms(const ter_b200_handle_t* h) { return (h && h->model) ? h->model->last_prefill_ms : 0.0f; }
+float ter_b200_last_prompt_ms(const ter_b200_handle_t* h) { return (h && h->model) ? h->model->last_prompt_ms : 0.0f; }
 
 }  // extern "C"

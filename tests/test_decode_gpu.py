@@ -100,6 +100,30 @@ def test_reference_numpy_forward_tokens_on_gpu(tb, golden_dir):
         assert out[0].tolist() == want.tolist(), name
 
 
+@pytest.mark.parametrize("cfg,seed", [(SMALL_LLAMA, 41), (SMALL_BITNET, 42), (SMALL_PACKED_HEAD, 43)])
+def test_prompt_as_token_batches_equals_one_position_at_a_time(tb, cfg, seed):
+    """Prompt processing through the tensor-core GEMM (tiles of up to 256 positions, causal attention over
+    the shared cache) leaves tokens and logits bit-identical to feeding the prompt position by position."""
+    rng = np.random.default_rng(seed)
+    lengths = [2, 17, 40] if cfg["Smax"] < 300 else [2, 17, 255, 256, 290]
+    try:
+        for n_prompt in lengths:
+            n_gen = min(6, cfg["Smax"] - n_prompt + 1)
+            prompt = rng.integers(0, cfg["V"], size=n_prompt).astype(np.int32)
+            res = []
+            for prefill in (0, 1):
+                tb.set_option("prefill", prefill)
+                modelutil.build_gpu(tb, cfg, seed)
+                out = tb.generate(prompt, n_gen)
+                res.append((out[0].copy(), tb.model_logits()[0].copy(), tb.last_prefill_ms()))
+            assert res[0][2] == 0.0 and res[1][2] > 0.0
+            assert res[0][0].tolist() == res[1][0].tolist(), n_prompt
+            assert np.array_equal(res[0][1].view(np.uint32), res[1][1].view(np.uint32)), n_prompt
+            assert tb.device_status() == 0
+    finally:
+        tb.set_option("prefill", 1)
+
+
 def test_packed_model_files_load_and_reproduce_reference_tokens(tb, golden_dir, tmp_path):
     """'LLRT' and 'TERT' files byte-identical to the ones the reference's scripts were run on, read by
     the library's loader: the greedy tokens are the ones those scripts printed."""
