@@ -125,11 +125,14 @@ constexpr int kMaxGroup = 8;   // query heads per KV head
 
 // Shared memory of attn_partial_kernel<HD>: K chunk, V chunk (bf16 [256][HD] each, filled by one
 // 1-D TMA bulk copy each), the group's query heads, the score / probability rows, barriers.
-template <int HD>
+// COMPACT: K and V take turns in ONE chunk buffer (V is fetched once the scores are done), which
+// halves the footprint so that two to five CTAs fit an SM: for large grids (token batches, prompt
+// tiles), where throughput counts; the two-buffer form keeps both copies in flight for a lone step.
+template <int HD, bool COMPACT>
 struct AttnSmem {
     static constexpr int kKOff = 0;
-    static constexpr int kVOff = kAttnChunk * HD * 2;
-    static constexpr int kQOff = 2 * kAttnChunk * HD * 2;
+    static constexpr int kVOff = COMPACT ? 0 : kAttnChunk * HD * 2;
+    static constexpr int kQOff = (COMPACT ? 1 : 2) * kAttnChunk * HD * 2;
     static constexpr int kScOff = kQOff + kMaxGroup * HD * 4;
     static constexpr int kRedOff = kScOff + kMaxGroup * kAttnChunk * 4;
     static constexpr int kBarOff = kRedOff + 64;
@@ -140,10 +143,10 @@ struct AttnSmem {
 // it rotates the group's query heads on the fly (the q buffer is left untouched) and, in the CTA
 // whose chunk contains the new position, rotates k, rounds k and v to bf16, appends them to the
 // cache and uses them.  Otherwise q is taken as already rotated and the cache as already appended.
-template <int HD, int G>
+template <int HD, int G, bool COMPACT>
 __global__ void __launch_bounds__(kT) attn_partial_kernel(const AttnParams p) {
     extern __shared__ __align__(128) uint8_t asmem[];
-    using L = AttnSmem<HD>;
+    using L = AttnSmem<HD, COMPACT>;
     uint16_t* Ks = reinterpret_cast<uint16_t*>(asmem + L::kKOff);
     uint16_t* Vs = reinterpret_cast<uint16_t*>(asmem + L::kVOff);
     float* qs = reinterpret_cast<float*>(asmem + L::kQOff);
@@ -198,8 +201,10 @@ __global__ void __launch_bounds__(kT) attn_partial_kernel(const AttnParams p) {
         const uint32_t bytes = (uint32_t)n_copy * HD * 2u;
         mbar_arrive_expect_tx(&bars[0], bytes);
         bulk_g2s(Ks, K + (size_t)s0 * HD, bytes, &bars[0]);
-        mbar_arrive_expect_tx(&bars[1], bytes);
-        bulk_g2s(Vs, V + (size_t)s0 * HD, bytes, &bars[1]);
+        if (!COMPACT) {
+            mbar_arrive_expect_tx(&bars[1], bytes);
+            bulk_g2s(Vs, V + (size_t)s0 * HD, bytes, &bars[1]);
+        }
     }
 
     // query heads of the group (rotated here when fused)
@@ -235,7 +240,7 @@ __global__ void __launch_bounds__(kT) attn_partial_kernel(const AttnParams p) {
             }
             for (int d = tid; d < HD; d += kT) {
                 const uint16_t vb = f32_to_bf16_bits(vn[d]);
-                Vs[r * HD + d] = vb;
+                if (!COMPACT) Vs[r * HD + d] = vb;     // COMPACT: the buffer still holds K; written after the scores
                 Vw[d] = vb;
             }
         }
@@ -288,6 +293,20 @@ __global__ void __launch_bounds__(kT) attn_partial_kernel(const AttnParams p) {
         }
     }
     __syncthreads();
+    if (COMPACT) {
+        // every score is computed: the chunk buffer now takes V (rows already in the cache by TMA, the
+        // new row, in the CTA that owns it, from the projection output)
+        if (tid == 0 && n_copy > 0) {
+            const uint32_t bytes = (uint32_t)n_copy * HD * 2u;
+            mbar_arrive_expect_tx(&bars[1], bytes);
+            bulk_g2s(Vs, V + (size_t)s0 * HD, bytes, &bars[1]);
+        }
+        if (owner) {
+            const float* vn = p.v_new + ((size_t)b * p.Nkv + g) * HD;
+            const int r = pos - s0;
+            for (int d = tid; d < HD; d += kT) Vs[r * HD + d] = f32_to_bf16_bits(vn[d]);
+        }
+    }
 
     float* rec0 = p.scratch + (((size_t)b * p.Nh + (size_t)g * G) * p.max_chunks + c) * (HD + 2);
     const size_t rec_stride = (size_t)p.max_chunks * (HD + 2);
@@ -412,17 +431,23 @@ size_t attention_scratch_floats(int B, int Nh, int Hd, int Smax) {
 }
 
 namespace {
-template <int HD, int G>
-cudaError_t launch_attn_partial(const AttnParams& p, bool pdl, cudaStream_t st, int dev) {
+template <int HD, int G, bool COMPACT>
+cudaError_t launch_attn_variant(const AttnParams& p, bool pdl, cudaStream_t st, int dev) {
     static bool attr_set[64] = {};
     if (!attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(attn_partial_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             AttnSmem<HD>::kBytes);
+        cudaError_t e = cudaFuncSetAttribute(attn_partial_kernel<HD, G, COMPACT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             AttnSmem<HD, COMPACT>::kBytes);
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
     const dim3 grid((unsigned)p.max_chunks, (unsigned)p.Nkv, (unsigned)p.B);
-    return launch_pdl(attn_partial_kernel<HD, G>, grid, dim3(kT), AttnSmem<HD>::kBytes, pdl, st, p);
+    return launch_pdl(attn_partial_kernel<HD, G, COMPACT>, grid, dim3(kT), AttnSmem<HD, COMPACT>::kBytes, pdl, st, p);
+}
+template <int HD, int G>
+cudaError_t launch_attn_partial(const AttnParams& p, bool pdl, cudaStream_t st, int dev) {
+    // many CTAs (token batches, prompt tiles): the one-buffer form, several CTAs per SM
+    const bool compact = (long)p.max_chunks * p.Nkv * p.B >= 512;
+    return compact ? launch_attn_variant<HD, G, true>(p, pdl, st, dev) : launch_attn_variant<HD, G, false>(p, pdl, st, dev);
 }
 template <int HD>
 cudaError_t launch_attn_hd(const AttnParams& p, bool pdl, cudaStream_t st, int dev) {
