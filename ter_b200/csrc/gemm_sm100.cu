@@ -365,9 +365,6 @@ static EncodeTiledFn encode_tiled() {
     return fn;
 }
 
-// scratch = row sums [M] followed by the split-K partials [M][N]
-size_t gemm_scratch_ints(int M, int N, bool split) { return (size_t)M + (split ? (size_t)M * (size_t)N : 0); }
-
 cudaError_t launch_gemm(const GemmParams& p_in, int sm_count, bool pdl, cudaStream_t st) {
     GemmParams p = p_in;
     if (p.M < 1 || p.K % 16 != 0 || p.Kpad % kKStep != 0) return cudaErrorInvalidValue;
@@ -383,7 +380,7 @@ cudaError_t launch_gemm(const GemmParams& p_in, int sm_count, bool pdl, cudaStre
     const int steps = p.Kpad / kKStep;
     // split K so that the grid covers the SMs (the weights are the traffic; every CTA streams its share)
     int ksplits = 1;
-    if (p.scratch && p.split_ok && p.M <= 256) {   // weight-bandwidth-bound regime only; larger batches have enough work per tile
+    if (p.part_buf && p.M <= 256) {   // weight-bandwidth-bound regime only; larger batches have enough work per tile
         ksplits = sm_count / (n_tiles * m_tiles);
         if (ksplits > steps / 4) ksplits = steps / 4;
         if (ksplits < 1) ksplits = 1;
@@ -422,7 +419,7 @@ cudaError_t launch_gemm(const GemmParams& p_in, int sm_count, bool pdl, cudaStre
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     p.part = nullptr;
     p.x_rowsum_w = nullptr;
-    if (ksplits > 1) p.part = p.scratch + p.M;
+    if (ksplits > 1) p.part = p.part_buf;
     if (!p.x_rowsum) {   // the caller did not supply the row sums: compute them into the scratch
         if (!p.scratch) return cudaErrorInvalidValue;
         p.x_rowsum_w = p.scratch;
@@ -431,7 +428,7 @@ cudaError_t launch_gemm(const GemmParams& p_in, int sm_count, bool pdl, cudaStre
     if (p.part || p.x_rowsum_w) {
         cudaLaunchConfig_t lr = {};
         size_t g = p.part ? ((size_t)p.M * p.N + 1023) / 1024 : (size_t)(p.M + 7) / 8;
-        if (g < (size_t)(p.M + 7) / 8) g = (size_t)(p.M + 7) / 8;
+        if (p.x_rowsum_w && g < (size_t)(p.M + 7) / 8) g = (size_t)(p.M + 7) / 8;
         if (g > (size_t)sm_count * 8) g = (size_t)sm_count * 8;
         lr.gridDim = dim3((unsigned)g);
         lr.blockDim = dim3(256);

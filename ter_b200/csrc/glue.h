@@ -18,6 +18,8 @@ struct NormQuantParams {
     float* normed;         // [rows][n] or null: the fp32 values before quantisation
     int n, rows, pre;
     float eps;
+    int32_t* rowsum_out;   // [rows] or null: sum of the int8 values of each row (what the tensor-core GEMM
+                           // subtracts; stand-alone kernel only, n a multiple of 16)
 };
 cudaError_t launch_norm_quant(const NormQuantParams& p, bool pdl, cudaStream_t st);
 

@@ -35,6 +35,25 @@ __global__ void __launch_bounds__(kT) norm_quant_kernel(const NormQuantParams p)
                              ? block_norm_quant_fast(p, (int)blockIdx.x, red16, qo, no)
                              : block_norm_quant(p, (int)blockIdx.x, vals, red, qo, no);
     if (p.q && threadIdx.x == 0) p.scale_out[blockIdx.x] = stored;
+    if (p.rowsum_out && qo) {
+        // exact integer sum of the row just written (this CTA's own stores, visible after the barrier)
+        __shared__ int rs;
+        if (threadIdx.x == 0) rs = 0;
+        __syncthreads();
+        int local = 0;
+        for (int i = threadIdx.x * 16; i < p.n; i += kT * 16) {
+            const int4 v = *reinterpret_cast<const int4*>(qo + i);
+            local = __dp4a(v.x, 0x01010101, local);
+            local = __dp4a(v.y, 0x01010101, local);
+            local = __dp4a(v.z, 0x01010101, local);
+            local = __dp4a(v.w, 0x01010101, local);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
+        if ((threadIdx.x & 31) == 0 && local != 0) atomicAdd(&rs, local);
+        __syncthreads();
+        if (threadIdx.x == 0) p.rowsum_out[blockIdx.x] = rs;
+    }
 }
 
 template <typename Kern, typename Params>
@@ -57,6 +76,7 @@ cudaError_t launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, bool pdl, 
 cudaError_t launch_norm_quant(const NormQuantParams& p, bool pdl, cudaStream_t st) {
     const size_t smem = (size_t)p.n * sizeof(float);
     if (smem > 200 * 1024) return cudaErrorInvalidValue;
+    if (p.rowsum_out && (p.n % 16 != 0 || !p.q)) return cudaErrorInvalidValue;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(norm_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
@@ -491,51 +511,68 @@ __device__ __forceinline__ uint4 ldg_stream16(const void* ptr) {
     return v;
 }
 
-// One warp per vocabulary row; lane l takes elements 256*r + 8*l + e (e ascending), fused
-// multiply-adds, then an xor butterfly over the warp.  A CTA serves up to kLmRows batch rows per
-// table row it reads (grid.y = groups of kLmRows batch rows), each with its own accumulator in the
-// same order, so the result per (batch row, vocabulary row) does not depend on the batch size.
+// A warp takes kLmVoc consecutive vocabulary rows at a time; lane l takes elements 256*i + 8*l + e of
+// each (e ascending), fused multiply-adds, then an xor butterfly over the warp.  A CTA serves up to
+// kLmRows batch rows (grid.x = groups of kLmRows batch rows, the fastest-varying index, so that the
+// CTAs reading the same table rows for different batch groups run together and the table comes from
+// HBM once).  Every (batch row, vocabulary row) pair has its own accumulator and sees the same
+// sequence of operations whatever the batch size.  An activation value fetched from shared memory
+// feeds kLmVoc multiply-adds, which keeps the kernel off the shared-memory limit at large batches.
 constexpr int kLmRows = 8;
+constexpr int kLmVoc = 4;
+template <int ROWS>   // accumulator rows compiled in: 1 for a lone sequence (fewer registers), else kLmRows
 __global__ void __launch_bounds__(kT) lm_head_bf16_kernel(const LmHeadParams p) {
     extern __shared__ __align__(16) float xs[];       // [rows][H]
     pdl_launch_dependents();
     pdl_wait();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int b0 = blockIdx.y * kLmRows;
-    const int rows = min(kLmRows, p.B - b0);
+    const int b0 = blockIdx.x * ROWS;
+    const int rows = min(ROWS, p.B - b0);
     for (int i = tid; i < rows * p.H; i += kT) xs[i] = p.x[(size_t)b0 * p.H + i];
     __syncthreads();
-    const int total_warps = gridDim.x * (kT / 32);
-    for (int v = blockIdx.x * (kT / 32) + warp; v < p.V; v += total_warps) {
-        const uint16_t* row = p.table + (size_t)v * p.H;
-        float acc[kLmRows];
+    const int total_warps = gridDim.y * (kT / 32);
+    for (int v0 = (blockIdx.y * (kT / 32) + warp) * kLmVoc; v0 < p.V; v0 += total_warps * kLmVoc) {
+        const uint16_t* row[kLmVoc];
 #pragma unroll
-        for (int r = 0; r < kLmRows; ++r) acc[r] = 0.0f;
-#pragma unroll 2
+        for (int i = 0; i < kLmVoc; ++i) row[i] = p.table + (size_t)min(v0 + i, p.V - 1) * p.H;
+        float acc[kLmVoc][ROWS];
+#pragma unroll
+        for (int i = 0; i < kLmVoc; ++i)
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) acc[i][r] = 0.0f;
         for (int base = 8 * lane; base < p.H; base += 256) {
-            const uint4 w = ldg_stream16(row + base);
-            float wf[8];
-            wf[0] = bf16_bits_to_f32(w.x & 0xffffu); wf[1] = bf16_bits_to_f32(w.x >> 16);
-            wf[2] = bf16_bits_to_f32(w.y & 0xffffu); wf[3] = bf16_bits_to_f32(w.y >> 16);
-            wf[4] = bf16_bits_to_f32(w.z & 0xffffu); wf[5] = bf16_bits_to_f32(w.z >> 16);
-            wf[6] = bf16_bits_to_f32(w.w & 0xffffu); wf[7] = bf16_bits_to_f32(w.w >> 16);
+            float wf[kLmVoc][8];
 #pragma unroll
-            for (int r = 0; r < kLmRows; ++r) {
+            for (int i = 0; i < kLmVoc; ++i) {
+                const uint4 w = ldg_stream16(row[i] + base);
+                wf[i][0] = bf16_bits_to_f32(w.x & 0xffffu); wf[i][1] = bf16_bits_to_f32(w.x >> 16);
+                wf[i][2] = bf16_bits_to_f32(w.y & 0xffffu); wf[i][3] = bf16_bits_to_f32(w.y >> 16);
+                wf[i][4] = bf16_bits_to_f32(w.z & 0xffffu); wf[i][5] = bf16_bits_to_f32(w.z >> 16);
+                wf[i][6] = bf16_bits_to_f32(w.w & 0xffffu); wf[i][7] = bf16_bits_to_f32(w.w >> 16);
+            }
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) {
                 if (r < rows) {
                     const float4 xa = *reinterpret_cast<const float4*>(&xs[r * p.H + base]);
                     const float4 xb = *reinterpret_cast<const float4*>(&xs[r * p.H + base + 4]);
-                    float a = acc[r];
-                    a = fmaf(wf[0], xa.x, a); a = fmaf(wf[1], xa.y, a); a = fmaf(wf[2], xa.z, a); a = fmaf(wf[3], xa.w, a);
-                    a = fmaf(wf[4], xb.x, a); a = fmaf(wf[5], xb.y, a); a = fmaf(wf[6], xb.z, a); a = fmaf(wf[7], xb.w, a);
-                    acc[r] = a;
+#pragma unroll
+                    for (int i = 0; i < kLmVoc; ++i) {
+                        float a = acc[i][r];
+                        a = fmaf(wf[i][0], xa.x, a); a = fmaf(wf[i][1], xa.y, a); a = fmaf(wf[i][2], xa.z, a); a = fmaf(wf[i][3], xa.w, a);
+                        a = fmaf(wf[i][4], xb.x, a); a = fmaf(wf[i][5], xb.y, a); a = fmaf(wf[i][6], xb.z, a); a = fmaf(wf[i][7], xb.w, a);
+                        acc[i][r] = a;
+                    }
                 }
             }
         }
 #pragma unroll
-        for (int r = 0; r < kLmRows; ++r) {
-            if (r < rows) {
-                const float t = warp_sum_butterfly(acc[r]);
-                if (lane == 0) p.logits[(size_t)(b0 + r) * p.V + v] = t;
+        for (int i = 0; i < kLmVoc; ++i) {
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) {
+                if (r < rows) {
+                    const float t = warp_sum_butterfly(acc[i][r]);
+                    if (lane == 0 && v0 + i < p.V) p.logits[(size_t)(b0 + r) * p.V + v0 + i] = t;
+                }
             }
         }
     }
@@ -624,17 +661,21 @@ __global__ void inc_kernel(const IncParams p) {
 cudaError_t launch_lm_head_bf16(const uint16_t* table, const float* x, float* logits, int V, int H, int B,
                                 int sm_count, bool pdl, cudaStream_t st) {
     if (H % 8 != 0) return cudaErrorInvalidValue;
-    const int rows = B < kLmRows ? B : kLmRows;
+    const int rows = B == 1 ? 1 : kLmRows;
     const size_t smem = (size_t)rows * H * sizeof(float);
     if (smem > 200 * 1024) return cudaErrorInvalidValue;
+    auto kern = B == 1 ? lm_head_bf16_kernel<1> : lm_head_bf16_kernel<kLmRows>;
     if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(lm_head_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
-    int gx = sm_count * (smem > 100 * 1024 ? 1 : (smem > 48 * 1024 ? 2 : 4));
-    if (gx > (V + 7) / 8) gx = (V + 7) / 8;
+    const int groups = (B + rows - 1) / rows;
+    int gy = sm_count * (smem > 100 * 1024 ? 1 : (smem > 48 * 1024 ? 2 : 4)) / groups;   // CTAs per batch group
+    const int need = (V + 8 * kLmVoc - 1) / (8 * kLmVoc);
+    if (gy > need) gy = need;
+    if (gy < 1) gy = 1;
     LmHeadParams p{table, x, logits, V, H, B};
-    return launch_pdl(lm_head_bf16_kernel, dim3((unsigned)gx, (unsigned)((B + kLmRows - 1) / kLmRows)), dim3(kT), smem, pdl, st, p);
+    return launch_pdl(kern, dim3((unsigned)groups, (unsigned)gy), dim3(kT), smem, pdl, st, p);
 }
 
 cudaError_t launch_argmax(const float* logits, int V, int B, float* scratch, int* out, bool pdl, cudaStream_t st) {

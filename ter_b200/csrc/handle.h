@@ -65,8 +65,10 @@ struct ter_b200_handle_t {
     TerbModel* model;
     RopeTable rope[4];
     terb::Comm* comm;           // tensor-parallel communicator (comm.cpp), or null
-    int32_t* gemm_scratch;      // split-K partials of the tensor-core GEMM
+    int32_t* gemm_scratch;      // row sums of the activations of the tensor-core GEMM (one int per token)
     size_t gemm_scratch_cap;    // ints
+    int32_t* gemm_part;         // split-K partials
+    size_t gemm_part_cap;       // ints
     int gemm_min_m;             // batches below this go row by row through the GEMV kernel
     int gemm_split_k;           // 0 = never split K
     int gemm_dbg;
@@ -136,8 +138,9 @@ int comm_group_end(ter_b200_handle_t* h);
 void model_invalidate_graph(ter_b200_handle_t* h);
 int ensure_gemm_scratch(ter_b200_handle_t* h, int M, int N);
 // Batched GEMM over one weight (tensor cores for M >= gemm_min_m, else GEMV per row).
+// x_rowsum: sum_k X[m][k] per token when the caller has it (the quantiser kernel can produce it), else null
 int run_gemm(ter_b200_handle_t* h, const DevWeight* w, const int8_t* X, const float* x_scales, int M, float* out,
-             int32_t* acc, cudaStream_t st, bool accumulate = false);
+             int32_t* acc, cudaStream_t st, bool accumulate = false, const int32_t* x_rowsum = nullptr);
 // One launch over up to kGemvMaxGroup weights sharing x (abi.cpp).
 int run_gemv(ter_b200_handle_t* h, const DevWeight* const* ws, int n, const int8_t* x_dev, const float* x_scale_dev,
              float x_scale_imm, float* const* outs, int32_t* const* accs, bool accumulate, cudaStream_t st,

@@ -114,8 +114,8 @@ struct GemmParams {
     float* out;               // [M][N] or null
     int32_t* acc_out;         // [M][N] or null (raw int32 dot products)
     const int32_t* x_rowsum;  // [M] sum_k X[m][k], or null: computed into the scratch by a pre-kernel
-    int32_t* scratch;         // gemm_scratch_ints(M, N, split) ints: row sums, then split-K partials
-    int split_ok;             // the scratch has room for the split-K partials
+    int32_t* scratch;         // M ints: row sums computed by the pre-kernel when x_rowsum is null
+    int32_t* part_buf;        // M*N ints or null: split-K partials (zeroed by the pre-kernel)
     int accumulate;           // out[m][n] = out[m][n] + value (residual add)
     int32_t* part;            // set by the launcher
     int32_t* x_rowsum_w;      // set by the launcher
@@ -125,7 +125,6 @@ struct GemmParams {
     int dbg;                  // unused
     int* status;
 };
-size_t gemm_scratch_ints(int M, int N, bool split);
 cudaError_t launch_gemm(const GemmParams& p, int sm_count, bool pdl, cudaStream_t st);
 
 // ---- install-time re-pack (device side) --------------------------------------

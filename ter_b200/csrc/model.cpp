@@ -42,6 +42,7 @@ struct TerbModel {
     // goes through the layers as a token batch (tensor-core GEMM), all rows sharing sequence 0's cache
     int rows_cap;
     int *tok_rows, *pos_rows;        // [rows_cap] token ids and positions of the tile
+    int32_t* xrs;                    // [rows_cap] row sums of the quantised activations (for the GEMM)
     cudaEvent_t ev_mid;
     float last_prefill_ms, last_prompt_ms;
 };
@@ -76,10 +77,11 @@ cudaError_t dalloc(T** p, size_t n) { return cudaMalloc((void**)p, n * sizeof(T)
 // GEMV for every sequence of the batch (rows of X against the same weights).  With `nq` the
 // quantiser runs inside the GEMV launch (fp32 rows in, no int8 round trip through memory).
 int mm(ter_b200_handle_t* h, const DevWeight* const* ws, int n, const int8_t* xq, int K, const float* xs,
-       float* const* outs, bool accumulate, int B, cudaStream_t st, const NormQuantParams* nq = nullptr) {
+       float* const* outs, bool accumulate, int B, cudaStream_t st, const NormQuantParams* nq = nullptr,
+       const int32_t* xrs = nullptr) {
     if (!nq && B >= h->gemm_min_m) {   // token batch: one tensor-core GEMM per matrix over all rows
         for (int i = 0; i < n; ++i) {
-            int rc = run_gemm(h, ws[i], xq, xs, B, outs[i], nullptr, st, accumulate);
+            int rc = run_gemm(h, ws[i], xq, xs, B, outs[i], nullptr, st, accumulate, xrs);
             if (rc) return rc;
         }
         return TER_B200_OK;
@@ -116,6 +118,7 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
     const ter_b200_model_cfg_t& c = m->c;
     const bool pre = prefill_rows > 0;
     const int B = pre ? prefill_rows : m->batch, H = c.H, F = c.F, Hq = c.Nh * c.Hd;
+    const bool gemm_rows = B >= h->gemm_min_m;   // token batch: projections on the tensor-core GEMM
     const int* posv = pre ? m->pos_rows : m->pos;
     const int* tokv = pre ? m->tok_rows : m->tokens;
     const bool pdl = h->gemv_cfg.pdl != 0;
@@ -186,8 +189,9 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
             float* outs[3] = {m->q + offa(Hq), m->k + offa(Hkv), m->v + offa(Hkv)};
             NormQuantParams nq{m->hidden, nullptr, vec[TER_B200_ATTN_NORM], m->xq, m->xs, nullptr, H, B, PRE_NONE, c.eps};
             const bool fz = can_fuse(h, ws, 3, B);
+            if (gemm_rows) nq.rowsum_out = m->xrs;
             if (!fz) CK(launch_norm_quant(nq, pdl, st));
-            int rc = mm(h, ws, 3, m->xq, H, m->xs, outs, false, B, st, fz ? &nq : nullptr);
+            int rc = mm(h, ws, 3, m->xq, H, m->xs, outs, false, B, st, fz ? &nq : nullptr, gemm_rows ? m->xrs : nullptr);
             if (rc) return rc;
             float* xb[3] = {m->q, m->k, m->v};
             const int xn[3] = {Hq, Hkv, Hkv};
@@ -216,8 +220,9 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
             NormQuantParams aq{m->att, nullptr, bitnet ? vec[TER_B200_ATTN_SUB_NORM] : nullptr, m->xq, m->xs, nullptr,
                                Hq, B, PRE_NONE, c.eps};
             const bool fz = can_fuse(h, ws, 1, B);
+            if (gemm_rows) aq.rowsum_out = m->xrs;
             if (!fz) CK(launch_norm_quant(aq, pdl, st));
-            int rc = mm(h, ws, 1, m->xq, Hq, m->xs, outs, true, B, st, fz ? &aq : nullptr);   // hidden += Wo(attn)
+            int rc = mm(h, ws, 1, m->xq, Hq, m->xs, outs, true, B, st, fz ? &aq : nullptr, gemm_rows ? m->xrs : nullptr);   // hidden += Wo(attn)
             if (rc) return rc;
             XCHG1(m->hidden, H, sa);
         }
@@ -231,6 +236,7 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
             const DevWeight* wd[1] = {&W[TER_B200_WDOWN]};
             const bool pair = fz && can_fuse(h, wd, 1, B) && (((ws[0]->Kpad >> 7) + 7) / 8) <= 4;
             const int act = bitnet ? PRE_RELU2_MUL : PRE_SILU_MUL;
+            if (gemm_rows) fq.rowsum_out = m->xrs;
             if (!fz) CK(launch_norm_quant(fq, pdl, st));
             if (pair) {
                 for (int b = 0; b < B; ++b) {
@@ -239,7 +245,7 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
                     if (rc) return rc;
                 }
             } else {
-                int rc = mm(h, ws, 2, m->xq, H, m->xs, outs, false, B, st, fz ? &fq : nullptr);
+                int rc = mm(h, ws, 2, m->xq, H, m->xs, outs, false, B, st, fz ? &fq : nullptr, gemm_rows ? m->xrs : nullptr);
                 if (rc) return rc;
             }
             if (pair) {
@@ -254,8 +260,9 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
             NormQuantParams gq{m->gate, pair ? nullptr : m->up, bitnet ? vec[TER_B200_FFN_SUB_NORM] : nullptr, m->xq,
                                m->xs, nullptr, F, B, pair ? PRE_NONE : act, c.eps};
             const bool fd = can_fuse(h, wd, 1, B);
+            if (gemm_rows) gq.rowsum_out = m->xrs;
             if (!fd) CK(launch_norm_quant(gq, pdl, st));
-            int rc = mm(h, wd, 1, m->xq, F, m->xs, outd, true, B, st, fd ? &gq : nullptr);    // hidden += Wdown(ffn)
+            int rc = mm(h, wd, 1, m->xq, F, m->xs, outd, true, B, st, fd ? &gq : nullptr, gemm_rows ? m->xrs : nullptr);    // hidden += Wdown(ffn)
             if (rc) return rc;
             XCHG1(m->hidden, H, sf);
         }
@@ -338,7 +345,7 @@ void ter_b200_model_free(ter_b200_handle_t* h) {
     if (m->embd && m->embd_owned) cudaFree(m->embd);
     void* bufs[] = {m->out_norm, m->hidden, m->q, m->k, m->v, m->att, m->gate, m->up, m->xnorm, m->logits,
                     m->attn_scratch, m->argmax_scratch, m->xs, m->xq, m->kcache, m->vcache, m->tokens, m->pos,
-                    m->greedy, m->forced, m->log, m->ctl, m->attn_counters, m->tok_rows, m->pos_rows};
+                    m->greedy, m->forced, m->log, m->ctl, m->attn_counters, m->tok_rows, m->pos_rows, m->xrs};
     for (void* b : bufs)
         if (b) cudaFree(b);
     if (m->ev0) cudaEventDestroy(m->ev0);
@@ -427,6 +434,7 @@ int ter_b200_model_create(ter_b200_handle_t* h, const ter_b200_model_cfg_t* cfg)
     A(dalloc(&m->xq, (size_t)R * wide));
     A(dalloc(&m->tok_rows, (size_t)R));
     A(dalloc(&m->pos_rows, (size_t)R));
+    A(dalloc(&m->xrs, (size_t)R));
     A(dalloc(&m->kcache, cache_elems(c)));
     A(dalloc(&m->vcache, cache_elems(c)));
     A(dalloc(&m->tokens, (size_t)B));

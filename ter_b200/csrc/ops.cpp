@@ -10,20 +10,31 @@ namespace terb {
 
 // Grows the handle's GEMM scratch (row sums + split-K partials) for M tokens x N columns.  Not for use
 // while a stream is capturing.
+// Row-sum scratch for M tokens and, when split-K may be used (M <= 256), a zeroed partial buffer of M*N ints.
 int ensure_gemm_scratch(ter_b200_handle_t* h, int M, int N) {
-    const size_t need = gemm_scratch_ints(M, N, h->gemm_split_k && M <= 256);
-    if (h->gemm_scratch_cap >= need) return TER_B200_OK;
+    const size_t need_part = (h->gemm_split_k && M <= 256) ? (size_t)M * (size_t)N : 0;
+    if (h->gemm_scratch_cap >= (size_t)M && h->gemm_part_cap >= need_part) return TER_B200_OK;
     TERB_CUDA(h, cudaDeviceSynchronize());
-    if (h->gemm_scratch) cudaFree(h->gemm_scratch);
-    h->gemm_scratch = nullptr;
-    h->gemm_scratch_cap = 0;
-    TERB_CUDA(h, cudaMalloc((void**)&h->gemm_scratch, need * sizeof(int)));
-    h->gemm_scratch_cap = need;
+    if (h->gemm_scratch_cap < (size_t)M) {
+        if (h->gemm_scratch) cudaFree(h->gemm_scratch);
+        h->gemm_scratch = nullptr;
+        h->gemm_scratch_cap = 0;
+        TERB_CUDA(h, cudaMalloc((void**)&h->gemm_scratch, (size_t)M * sizeof(int)));
+        h->gemm_scratch_cap = (size_t)M;
+    }
+    if (h->gemm_part_cap < need_part) {
+        if (h->gemm_part) cudaFree(h->gemm_part);
+        h->gemm_part = nullptr;
+        h->gemm_part_cap = 0;
+        TERB_CUDA(h, cudaMalloc((void**)&h->gemm_part, need_part * sizeof(int)));
+        TERB_CUDA(h, cudaMemset(h->gemm_part, 0, need_part * sizeof(int)));
+        h->gemm_part_cap = need_part;
+    }
     return TER_B200_OK;
 }
 
 int run_gemm(ter_b200_handle_t* h, const DevWeight* w, const int8_t* X, const float* x_scales, int M, float* out,
-             int32_t* acc, cudaStream_t st, bool accumulate) {
+             int32_t* acc, cudaStream_t st, bool accumulate, const int32_t* x_rowsum) {
     if (((uintptr_t)X & 15u) != 0) return TER_B200_E_SHAPE;
     if (M < h->gemm_min_m) {
         // small batches: one GEMV launch per row (exact; the weights are re-read M times)
@@ -50,20 +61,20 @@ int run_gemm(ter_b200_handle_t* h, const DevWeight* w, const int8_t* X, const fl
     p.status = h->status_dev;
     p.dbg = h->gemm_dbg;
     p.accumulate = accumulate ? 1 : 0;
+    p.x_rowsum = x_rowsum;
     {
-        const bool want_split = h->gemm_split_k && M <= 256;
-        const size_t need = gemm_scratch_ints(M, w->N, want_split);
-        if (h->gemm_scratch_cap < need) {
+        const size_t need_part = (h->gemm_split_k && M <= 256) ? (size_t)M * (size_t)w->N : 0;
+        if (h->gemm_scratch_cap < (size_t)M || h->gemm_part_cap < need_part) {
             cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
             cudaStreamIsCapturing(st, &cs);
-            if (cs != cudaStreamCaptureStatusNone && h->gemm_scratch_cap < (size_t)M) return TER_B200_E_STATE;
+            if (cs != cudaStreamCaptureStatusNone && h->gemm_scratch_cap < (size_t)M && !x_rowsum) return TER_B200_E_STATE;
             if (cs == cudaStreamCaptureStatusNone) {
                 int rc = ensure_gemm_scratch(h, M, w->N);
                 if (rc) return rc;
             }
         }
         p.scratch = h->gemm_scratch;
-        p.split_ok = want_split && h->gemm_scratch_cap >= need;
+        p.part_buf = (need_part && h->gemm_part_cap >= need_part) ? h->gemm_part : nullptr;
     }
     TERB_CUDA(h, launch_gemm(p, h->sm_count, h->gemv_cfg.pdl != 0, st));
     h->launches += 2;

@@ -3,7 +3,8 @@
     python -m ter_b200.profile_cases gemv_stream      # 2048 x 513024 GEMV (263 MB of trits), 4 launches
     python -m ter_b200.profile_cases sweep            # Llama-1B fabric (113 matrices, 309 MB) as one sweep-plan launch, 8 launches
     python -m ter_b200.profile_cases gemm             # BitNet gate 2560 x 6912 GEMM at M = 16, 256, 1024
-    python -m ter_b200.profile_cases decode llama     # three decode steps at position ~300 (or: bitnet)
+    python -m ter_b200.profile_cases decode llama     # three decode steps at position ~300 (or: bitnet, position ~2100)
+    python -m ter_b200.profile_cases decode bitnet 64 # the same for a batch of 64 sequences
 
 Each holds at most a few GB on the device and finishes in seconds, so an `ncu` capture of it ends by itself.
 """
@@ -109,20 +110,23 @@ def gemm():
     print("gemm ok, status", tb.device_status())
 
 
-def decode(which="llama"):
+def decode(which="llama", batch="1"):
     import torch
     from . import TerB200, synth
+    batch = int(batch)
     base, smax, pos0 = (synth.LLAMA_1B_CFG, 512, 300) if which == "llama" else (synth.BITNET_2B_CFG, 2304, 2100)
     tb = TerB200(0)
-    build_random_model(tb, dict(base, Smax=smax), torch.device("cuda:0"))
-    tb.model_reset(1)
-    tok = 5
+    dev = torch.device("cuda:0")
+    cfg = dict(base, Smax=smax)
+    build_random_model(tb, cfg, dev, max_batch=batch)
+    tb.model_reset(batch)
+    tok = [5 + b for b in range(batch)]
     for i in range(3):
-        tok = int(tb.decode_step([tok], [pos0 + i])[0])
+        tok = [int(t) for t in tb.decode_step(tok, [pos0 + i] * batch)]
     torch.cuda.synchronize()
-    print("decode ok", which, tok, tb.device_status())
+    print("decode ok", which, "batch", batch, tok[0], tb.device_status())
 
 
 if __name__ == "__main__":
     case = sys.argv[1] if len(sys.argv) > 1 else "gemv_stream"
-    {"gemv_stream": gemv_stream, "sweep": sweep, "gemm": gemm, "decode": lambda: decode(*sys.argv[2:3])}[case]()
+    {"gemv_stream": gemv_stream, "sweep": sweep, "gemm": gemm, "decode": lambda: decode(*sys.argv[2:4])}[case]()
