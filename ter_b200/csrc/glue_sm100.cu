@@ -148,13 +148,13 @@ constexpr int kMaxGroup = 8;   // query heads per KV head
 // COMPACT: K and V take turns in ONE chunk buffer (V is fetched once the scores are done), which
 // halves the footprint so that two to five CTAs fit an SM: for large grids (token batches, prompt
 // tiles), where throughput counts; the two-buffer form keeps both copies in flight for a lone step.
-template <int HD, bool COMPACT>
+template <int HD, int G, bool COMPACT>
 struct AttnSmem {
     static constexpr int kKOff = 0;
     static constexpr int kVOff = COMPACT ? 0 : kAttnChunk * HD * 2;
     static constexpr int kQOff = (COMPACT ? 1 : 2) * kAttnChunk * HD * 2;
-    static constexpr int kScOff = kQOff + kMaxGroup * HD * 4;
-    static constexpr int kRedOff = kScOff + kMaxGroup * kAttnChunk * 4;
+    static constexpr int kScOff = kQOff + G * HD * 4;
+    static constexpr int kRedOff = kScOff + G * kAttnChunk * 4;
     static constexpr int kBarOff = kRedOff + 64;
     static constexpr int kBytes = kBarOff + 16;
 };
@@ -164,9 +164,9 @@ struct AttnSmem {
 // whose chunk contains the new position, rotates k, rounds k and v to bf16, appends them to the
 // cache and uses them.  Otherwise q is taken as already rotated and the cache as already appended.
 template <int HD, int G, bool COMPACT>
-__global__ void __launch_bounds__(kT) attn_partial_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(kT, COMPACT ? 3 : 1) attn_partial_kernel(const AttnParams p) {
     extern __shared__ __align__(128) uint8_t asmem[];
-    using L = AttnSmem<HD, COMPACT>;
+    using L = AttnSmem<HD, G, COMPACT>;
     uint16_t* Ks = reinterpret_cast<uint16_t*>(asmem + L::kKOff);
     uint16_t* Vs = reinterpret_cast<uint16_t*>(asmem + L::kVOff);
     float* qs = reinterpret_cast<float*>(asmem + L::kQOff);
@@ -456,12 +456,12 @@ cudaError_t launch_attn_variant(const AttnParams& p, bool pdl, cudaStream_t st, 
     static bool attr_set[64] = {};
     if (!attr_set[dev]) {
         cudaError_t e = cudaFuncSetAttribute(attn_partial_kernel<HD, G, COMPACT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             AttnSmem<HD, COMPACT>::kBytes);
+                                             AttnSmem<HD, G, COMPACT>::kBytes);
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
     const dim3 grid((unsigned)p.max_chunks, (unsigned)p.Nkv, (unsigned)p.B);
-    return launch_pdl(attn_partial_kernel<HD, G, COMPACT>, grid, dim3(kT), AttnSmem<HD, COMPACT>::kBytes, pdl, st, p);
+    return launch_pdl(attn_partial_kernel<HD, G, COMPACT>, grid, dim3(kT), AttnSmem<HD, G, COMPACT>::kBytes, pdl, st, p);
 }
 template <int HD, int G>
 cudaError_t launch_attn_partial(const AttnParams& p, bool pdl, cudaStream_t st, int dev) {
