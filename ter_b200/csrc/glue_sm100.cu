@@ -170,7 +170,10 @@ __global__ void __launch_bounds__(kT, COMPACT ? 3 : 1) attn_partial_kernel(const
     uint16_t* Ks = reinterpret_cast<uint16_t*>(asmem + L::kKOff);
     uint16_t* Vs = reinterpret_cast<uint16_t*>(asmem + L::kVOff);
     float* qs = reinterpret_cast<float*>(asmem + L::kQOff);
-    float (*sc)[kAttnChunk] = reinterpret_cast<float (*)[kAttnChunk]>(asmem + L::kScOff);
+    // scores, then probabilities: [head][position]; the throughput variant keeps [position][head] so that
+    // one vector load gives a position's probabilities for all heads of the group
+    float* scf = reinterpret_cast<float*>(asmem + L::kScOff);
+    auto SC = [&](int hh, int t) -> float& { return COMPACT ? scf[t * G + hh] : scf[hh * kAttnChunk + t]; };
     float* red = reinterpret_cast<float*>(asmem + L::kRedOff);
     uint64_t* bars = reinterpret_cast<uint64_t*>(asmem + L::kBarOff);
     __shared__ float redg[kMaxGroup * 8];
@@ -309,7 +312,7 @@ __global__ void __launch_bounds__(kT, COMPACT ? 3 : 1) attn_partial_kernel(const
             acc = acc + __shfl_xor_sync(0xffffffffu, acc, 4);
             acc = acc + __shfl_xor_sync(0xffffffffu, acc, 2);
             acc = acc + __shfl_xor_sync(0xffffffffu, acc, 1);
-            if (j == 0) sc[hh][t] = valid ? acc * inv_sqrt : -CUDART_INF_F;
+            if (j == 0) SC(hh, t) = valid ? acc * inv_sqrt : -CUDART_INF_F;
         }
     }
     __syncthreads();
@@ -337,7 +340,7 @@ __global__ void __launch_bounds__(kT, COMPACT ? 3 : 1) attn_partial_kernel(const
     for (int hh = 0; hh < kMaxGroup; ++hh) {
         sv[hh] = -CUDART_INF_F;
         if (hh < G) {
-            sv[hh] = sc[hh][tid];
+            sv[hh] = SC(hh, tid);
             const float w = warp_max(sv[hh]);
             if (lane == 0) redg[hh * 8 + warp] = w;
         }
@@ -358,7 +361,7 @@ __global__ void __launch_bounds__(kT, COMPACT ? 3 : 1) attn_partial_kernel(const
     for (int hh = 0; hh < kMaxGroup; ++hh) {
         if (hh < G) {
             const float pt = tid < cnt ? exp_fixed(sv[hh] - mv[hh]) : 0.0f;
-            sc[hh][tid] = pt;
+            SC(hh, tid) = pt;
             const float w = warp_sum_butterfly(pt);
             if (lane == 0) redg[hh * 8 + warp] = w;
         }
@@ -376,14 +379,52 @@ __global__ void __launch_bounds__(kT, COMPACT ? 3 : 1) attn_partial_kernel(const
     }
     if (n_copy > 0) mbar_wait_bounded(&bars[1], 0, p.status);
 
-    for (int idx = tid; idx < G * HD; idx += kT) {
-        const int hh = idx / HD, d = idx % HD;
-        const float* pr = sc[hh];
-        const uint16_t* vp = Vs + d;
-        float acc = 0.0f;
+    // o[hh][d] = sum_t p[t][hh] * V[t][d], ascending t
+    if constexpr (COMPACT) {
+        // throughput form: one thread per dim d keeps the G heads' accumulators; per position one vector
+        // load of the G probabilities and one load of V[t][d] feed G multiply-adds
+        if (tid < HD) {
+            const int d = tid;
+            float acc[G];
+#pragma unroll
+            for (int hh = 0; hh < G; ++hh) acc[hh] = 0.0f;
+            const uint16_t* vp = Vs + d;
+#pragma unroll 4
+            for (int t = 0; t < cnt; ++t) {
+                const float v = bf16_bits_to_f32(vp[t * HD]);
+                float pr[G];
+                if constexpr (G == 4) {
+                    const float4 q4 = *reinterpret_cast<const float4*>(scf + t * 4);
+                    pr[0] = q4.x; pr[1] = q4.y; pr[2] = q4.z; pr[3] = q4.w;
+                } else if constexpr (G == 8) {
+                    const float4 q4 = *reinterpret_cast<const float4*>(scf + t * 8);
+                    const float4 q5 = *reinterpret_cast<const float4*>(scf + t * 8 + 4);
+                    pr[0] = q4.x; pr[1] = q4.y; pr[2] = q4.z; pr[3] = q4.w;
+                    pr[4] = q5.x; pr[5] = q5.y; pr[6] = q5.z; pr[7] = q5.w;
+                } else if constexpr (G == 2) {
+                    const float2 q2 = *reinterpret_cast<const float2*>(scf + t * 2);
+                    pr[0] = q2.x; pr[1] = q2.y;
+                } else {
+#pragma unroll
+                    for (int hh = 0; hh < G; ++hh) pr[hh] = scf[t * G + hh];
+                }
+#pragma unroll
+                for (int hh = 0; hh < G; ++hh) acc[hh] = fmaf(pr[hh], v, acc[hh]);
+            }
+#pragma unroll
+            for (int hh = 0; hh < G; ++hh) rec0[hh * rec_stride + 2 + d] = acc[hh];
+        }
+    } else {
+        // latency form: one thread per (head, dim)
+        for (int idx = tid; idx < G * HD; idx += kT) {
+            const int hh = idx / HD, d = idx % HD;
+            const float* pr = scf + hh * kAttnChunk;
+            const uint16_t* vp = Vs + d;
+            float acc = 0.0f;
 #pragma unroll 8
-        for (int t = 0; t < cnt; ++t) acc = fmaf(pr[t], bf16_bits_to_f32(vp[t * HD]), acc);
-        rec0[hh * rec_stride + 2 + d] = acc;
+            for (int t = 0; t < cnt; ++t) acc = fmaf(pr[t], bf16_bits_to_f32(vp[t * HD]), acc);
+            rec0[hh * rec_stride + 2 + d] = acc;
+        }
     }
 
     // Merge of the chunks by the last CTA of this (sequence, KV head) to finish, when the caller gave
