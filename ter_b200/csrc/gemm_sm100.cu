@@ -113,7 +113,15 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_trit_kernel(const __grid_co
     int* tok_sum = reinterpret_cast<int*>(tok_scale + 256);         // [256] sum_k X[m][k]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int tile = blockIdx.x;                       // 128-column tile
+    // 128-column tile of which matrix of the group
+    int mi = 0;
+    while (mi + 1 < p.n_w && (int)blockIdx.x >= p.tile_begin[mi + 1]) ++mi;
+    const int tile = (int)blockIdx.x - p.tile_begin[mi];
+    const uint8_t* Wm = p.Wg[mi];
+    const int Nm = p.Ng[mi], strips_m = p.stripsg[mi];
+    float* outm = p.outg[mi];
+    const float wsm = p.wsg[mi];
+    int32_t* partm = p.part ? p.part + p.part_off[mi] : nullptr;
     const int ksplit = blockIdx.y;                     // K range
     const int m0 = blockIdx.z * p.tokens;              // first token of this token tile
     const int steps_total = p.Kpad / kKStep;
@@ -154,12 +162,12 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_trit_kernel(const __grid_co
         const int seg = tid >> 3, part = tid & 7;          // 32 segments x 8 x 16 bytes
         const int strip_l = seg >> 2, bc = seg & 3;
         const int strip = tile * 8 + strip_l;
-        const bool strip_ok = strip < p.n_strips;
-        const uint8_t* sbase = p.W + (size_t)strip * 4u * (size_t)p.Kpad;
+        const bool strip_ok = strip < strips_m;
+        const uint8_t* sbase = Wm + (size_t)strip * 4u * (size_t)p.Kpad;
         // per-token epilogue constants
         if (tid < p.tokens) {
             const int m = m0 + tid;
-            tok_scale[tid] = (m < p.M && p.x_scales) ? p.x_scales[m] * p.w_scale : 0.0f;
+            tok_scale[tid] = (m < p.M && p.x_scales) ? p.x_scales[m] * wsm : 0.0f;
             tok_sum[tid] = (m < p.M) ? p.x_rowsum[m] : 0;
         }
         bool ok = true;
@@ -273,20 +281,20 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_trit_kernel(const __grid_co
                       "=r"(d[24]), "=r"(d[25]), "=r"(d[26]), "=r"(d[27]), "=r"(d[28]), "=r"(d[29]), "=r"(d[30]), "=r"(d[31])
                     : "r"(taddr));
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (n < p.N) {
+                if (n < Nm) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         const int m = m0 + c0 + j;
                         if (c0 + j < p.tokens && m < p.M) {
-                            const size_t o = (size_t)m * p.N + n;
+                            const size_t o = (size_t)m * Nm + n;
                             if (p.ksplits > 1) {
-                                atomicAdd(&p.part[o], (int)d[j]);
+                                atomicAdd(&partm[o], (int)d[j]);
                             } else {
                                 const int v = ((int)d[j] >> shift) - tok_sum[c0 + j];
                                 if (p.acc_out) p.acc_out[o] = v;
-                                if (p.out) {
+                                if (outm) {
                                     const float f = (float)v * tok_scale[c0 + j];
-                                    p.out[o] = p.accumulate ? p.out[o] + f : f;
+                                    outm[o] = p.accumulate ? outm[o] + f : f;
                                 }
                             }
                         }
@@ -310,7 +318,8 @@ __global__ void __launch_bounds__(256) gemm_prep_kernel(const GemmParams p) {
     pdl_launch_dependents();
     pdl_wait();
     if (p.part) {   // split-K partials start at zero
-        const size_t total = (size_t)p.M * p.N;
+        size_t total = 0;
+        for (int w = 0; w < p.n_w; ++w) total += (size_t)p.M * p.Ng[w];
         for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (size_t)gridDim.x * 256) p.part[i] = 0;
     }
     if (!p.x_rowsum_w) return;
@@ -335,14 +344,20 @@ __global__ void __launch_bounds__(256) gemm_prep_kernel(const GemmParams p) {
 __global__ void __launch_bounds__(256) gemm_finalize_kernel(const GemmParams p) {
     pdl_launch_dependents();
     pdl_wait();
-    const size_t total = (size_t)p.M * p.N;
-    for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (size_t)gridDim.x * 256) {
-        const int m = (int)(i / p.N), n = (int)(i % p.N);
-        const int v = (p.part[i] >> (2 * (n & 3))) - p.x_rowsum[m];
-        if (p.acc_out) p.acc_out[i] = v;
-        if (p.out) {
-            const float f = (float)v * (p.x_scales[m] * p.w_scale);
-            p.out[i] = p.accumulate ? p.out[i] + f : f;
+    for (int w = 0; w < p.n_w; ++w) {
+        const int N = p.Ng[w];
+        const int32_t* part = p.part + p.part_off[w];
+        float* out = p.outg[w];
+        const float ws = p.wsg[w];
+        const size_t total = (size_t)p.M * N;
+        for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (size_t)gridDim.x * 256) {
+            const int m = (int)(i / N), n = (int)(i % N);
+            const int v = (part[i] >> (2 * (n & 3))) - p.x_rowsum[m];
+            if (p.acc_out) p.acc_out[i] = v;
+            if (out) {
+                const float f = (float)v * (p.x_scales[m] * ws);
+                out[i] = p.accumulate ? out[i] + f : f;
+            }
         }
     }
 }
@@ -376,7 +391,20 @@ cudaError_t launch_gemm(const GemmParams& p_in, int sm_count, bool pdl, cudaStre
     while (cols < tokens) cols *= 2;
     p.tmem_cols = cols;
     const int m_tiles = (p.M + tokens - 1) / tokens;
-    const int n_tiles = (p.n_strips + 7) / 8;
+    if (p.n_w == 0) {   // the single matrix given by the scalar fields
+        p.n_w = 1;
+        p.Wg[0] = p.W; p.outg[0] = p.out; p.wsg[0] = p.w_scale; p.Ng[0] = p.N; p.stripsg[0] = p.n_strips;
+    }
+    if (p.n_w < 1 || p.n_w > kGemmMaxGroup || (p.n_w > 1 && p.acc_out)) return cudaErrorInvalidValue;
+    int n_tiles = 0;
+    size_t part_ints = 0;
+    for (int w = 0; w < p.n_w; ++w) {
+        p.tile_begin[w] = n_tiles;
+        n_tiles += (p.stripsg[w] + 7) / 8;
+        p.part_off[w] = part_ints;
+        part_ints += (size_t)p.M * (size_t)p.Ng[w];
+    }
+    p.tile_begin[p.n_w] = n_tiles;
     const int steps = p.Kpad / kKStep;
     // split K so that the grid covers the SMs (the weights are the traffic; every CTA streams its share)
     int ksplits = 1;
@@ -427,7 +455,7 @@ cudaError_t launch_gemm(const GemmParams& p_in, int sm_count, bool pdl, cudaStre
     }
     if (p.part || p.x_rowsum_w) {
         cudaLaunchConfig_t lr = {};
-        size_t g = p.part ? ((size_t)p.M * p.N + 1023) / 1024 : (size_t)(p.M + 7) / 8;
+        size_t g = p.part ? (part_ints + 1023) / 1024 : (size_t)(p.M + 7) / 8;
         if (p.x_rowsum_w && g < (size_t)(p.M + 7) / 8) g = (size_t)(p.M + 7) / 8;
         if (g > (size_t)sm_count * 8) g = (size_t)sm_count * 8;
         lr.gridDim = dim3((unsigned)g);
@@ -448,7 +476,7 @@ cudaError_t launch_gemm(const GemmParams& p_in, int sm_count, bool pdl, cudaStre
     e = cudaLaunchKernelEx(&lc, gemm_trit_kernel, p);
     if (e != cudaSuccess || ksplits == 1) return e;
     cudaLaunchConfig_t lf = {};
-    size_t g = ((size_t)p.M * p.N + 255) / 256;
+    size_t g = (part_ints + 255) / 256;
     lf.gridDim = dim3((unsigned)(g > (size_t)sm_count * 8 ? (size_t)sm_count * 8 : g));
     lf.blockDim = dim3(256);
     lf.stream = st;

@@ -141,6 +141,9 @@ int ensure_gemm_scratch(ter_b200_handle_t* h, int M, int N);
 // x_rowsum: sum_k X[m][k] per token when the caller has it (the quantiser kernel can produce it), else null
 int run_gemm(ter_b200_handle_t* h, const DevWeight* w, const int8_t* X, const float* x_scales, int M, float* out,
              int32_t* acc, cudaStream_t st, bool accumulate = false, const int32_t* x_rowsum = nullptr);
+int run_gemm_group(ter_b200_handle_t* h, const DevWeight* const* ws, int n, const int8_t* X, const float* x_scales,
+                   int M, float* const* outs, int32_t* acc, cudaStream_t st, bool accumulate = false,
+                   const int32_t* x_rowsum = nullptr);
 // One launch over up to kGemvMaxGroup weights sharing x (abi.cpp).
 int run_gemv(ter_b200_handle_t* h, const DevWeight* const* ws, int n, const int8_t* x_dev, const float* x_scale_dev,
              float x_scale_imm, float* const* outs, int32_t* const* accs, bool accumulate, cudaStream_t st,

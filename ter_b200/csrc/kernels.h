@@ -104,6 +104,8 @@ struct GemvLaunchCfg {
 cudaError_t launch_gemv(const GemvParams& p, const GemvLaunchCfg& cfg, cudaStream_t st);
 
 // ---- batched GEMM (tcgen05) ---------------------------------------------------
+constexpr int kGemmMaxGroup = 3;
+
 struct GemmParams {
     // TMA descriptor of X as a 2-D byte tensor {K, M}, box {128 k, token tile}, 128-byte swizzle: one copy
     // lands a whole activation stage in the layout the tensor core reads.  Set by the launcher.
@@ -123,6 +125,16 @@ struct GemmParams {
     int M, N, K, Kpad, n_strips;
     int tokens, tmem_cols, ksplits, stages;   // set by the launcher
     int dbg;                  // unused
+    // Group of up to kGemmMaxGroup weight matrices with the same K multiplied by the same X in ONE launch
+    // (q/k/v, gate/up).  n_w == 0: the single matrix described by W / out / w_scale / N / n_strips; the
+    // launcher then fills entry 0 from them.  tile_begin: first 128-column tile of each matrix in the grid's
+    // tile numbering; part_off: offset (ints) of each matrix's split-K partials in part_buf.
+    int n_w;
+    const uint8_t* Wg[kGemmMaxGroup];
+    float* outg[kGemmMaxGroup];
+    float wsg[kGemmMaxGroup];
+    int Ng[kGemmMaxGroup], stripsg[kGemmMaxGroup], tile_begin[kGemmMaxGroup + 1];
+    size_t part_off[kGemmMaxGroup];
     int* status;
 };
 cudaError_t launch_gemm(const GemmParams& p, int sm_count, bool pdl, cudaStream_t st);

@@ -79,13 +79,8 @@ cudaError_t dalloc(T** p, size_t n) { return cudaMalloc((void**)p, n * sizeof(T)
 int mm(ter_b200_handle_t* h, const DevWeight* const* ws, int n, const int8_t* xq, int K, const float* xs,
        float* const* outs, bool accumulate, int B, cudaStream_t st, const NormQuantParams* nq = nullptr,
        const int32_t* xrs = nullptr) {
-    if (!nq && B >= h->gemm_min_m) {   // token batch: one tensor-core GEMM per matrix over all rows
-        for (int i = 0; i < n; ++i) {
-            int rc = run_gemm(h, ws[i], xq, xs, B, outs[i], nullptr, st, accumulate, xrs);
-            if (rc) return rc;
-        }
-        return TER_B200_OK;
-    }
+    if (!nq && B >= h->gemm_min_m)     // token batch: one tensor-core GEMM over all rows and all the matrices
+        return run_gemm_group(h, ws, n, xq, xs, B, outs, nullptr, st, accumulate, xrs);
     for (int b = 0; b < B; ++b) {
         float* o[kGemvMaxGroup];
         for (int i = 0; i < n; ++i) o[i] = outs[i] + (size_t)b * ws[i]->N;

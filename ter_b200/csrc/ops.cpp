@@ -33,43 +33,59 @@ int ensure_gemm_scratch(ter_b200_handle_t* h, int M, int N) {
     return TER_B200_OK;
 }
 
-int run_gemm(ter_b200_handle_t* h, const DevWeight* w, const int8_t* X, const float* x_scales, int M, float* out,
-             int32_t* acc, cudaStream_t st, bool accumulate, const int32_t* x_rowsum) {
+// Up to kGemmMaxGroup weights with the same K against the same X in one tensor-core launch (M >= gemm_min_m),
+// else one GEMV launch per row and matrix.
+int run_gemm_group(ter_b200_handle_t* h, const DevWeight* const* ws, int n, const int8_t* X, const float* x_scales,
+                   int M, float* const* outs, int32_t* acc, cudaStream_t st, bool accumulate, const int32_t* x_rowsum) {
+    if (n < 1 || n > kGemmMaxGroup || (n > 1 && acc)) return TER_B200_E_SHAPE;
     if (((uintptr_t)X & 15u) != 0) return TER_B200_E_SHAPE;
+    for (int i = 1; i < n; ++i)
+        if (ws[i]->K != ws[0]->K) return TER_B200_E_SHAPE;
     if (M < h->gemm_min_m) {
         // small batches: one GEMV launch per row (exact; the weights are re-read M times)
-        for (int m = 0; m < M; ++m) {
-            const DevWeight* ws[1] = {w};
-            float* o[1] = {out ? out + (size_t)m * w->N : nullptr};
-            int32_t* a[1] = {acc ? acc + (size_t)m * w->N : nullptr};
-            int rc = run_gemv(h, ws, 1, X + (size_t)m * w->K, x_scales ? x_scales + m : nullptr, 1.0f, out ? o : nullptr,
-                              acc ? a : nullptr, accumulate, st);
-            if (rc) return rc;
+        for (int i = 0; i < n; ++i) {
+            const DevWeight* w = ws[i];
+            float* out = outs ? outs[i] : nullptr;
+            for (int m = 0; m < M; ++m) {
+                const DevWeight* w1[1] = {w};
+                float* o[1] = {out ? out + (size_t)m * w->N : nullptr};
+                int32_t* a[1] = {acc ? acc + (size_t)m * w->N : nullptr};
+                int rc = run_gemv(h, w1, 1, X + (size_t)m * w->K, x_scales ? x_scales + m : nullptr, 1.0f,
+                                  out ? o : nullptr, acc ? a : nullptr, accumulate, st);
+                if (rc) return rc;
+            }
         }
         return TER_B200_OK;
     }
-    if (!x_scales && out) return TER_B200_E_NULL;
+    if (!x_scales && outs && outs[0]) return TER_B200_E_NULL;
     GemmParams p;
     memset(&p, 0, sizeof p);
-    p.W = w->data;
     p.X = X;
     p.x_scales = x_scales;
-    p.out = out;
     p.acc_out = acc;
-    p.w_scale = w->scale;
-    p.M = M; p.N = w->N; p.K = w->K; p.Kpad = w->Kpad; p.n_strips = w->tiles();
+    p.M = M; p.K = ws[0]->K; p.Kpad = ws[0]->Kpad;
+    p.n_w = n;
+    size_t n_sum = 0;
+    for (int i = 0; i < n; ++i) {
+        p.Wg[i] = ws[i]->data;
+        p.outg[i] = outs ? outs[i] : nullptr;
+        p.wsg[i] = ws[i]->scale;
+        p.Ng[i] = ws[i]->N;
+        p.stripsg[i] = ws[i]->tiles();
+        n_sum += (size_t)ws[i]->N;
+    }
+    p.W = p.Wg[0]; p.out = p.outg[0]; p.w_scale = p.wsg[0]; p.N = p.Ng[0]; p.n_strips = p.stripsg[0];
     p.status = h->status_dev;
-    p.dbg = h->gemm_dbg;
     p.accumulate = accumulate ? 1 : 0;
     p.x_rowsum = x_rowsum;
     {
-        const size_t need_part = (h->gemm_split_k && M <= 256) ? (size_t)M * (size_t)w->N : 0;
+        const size_t need_part = (h->gemm_split_k && M <= 256) ? (size_t)M * n_sum : 0;
         if (h->gemm_scratch_cap < (size_t)M || h->gemm_part_cap < need_part) {
             cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
             cudaStreamIsCapturing(st, &cs);
             if (cs != cudaStreamCaptureStatusNone && h->gemm_scratch_cap < (size_t)M && !x_rowsum) return TER_B200_E_STATE;
             if (cs == cudaStreamCaptureStatusNone) {
-                int rc = ensure_gemm_scratch(h, M, w->N);
+                int rc = ensure_gemm_scratch(h, M, (int)n_sum);
                 if (rc) return rc;
             }
         }
@@ -78,8 +94,15 @@ int run_gemm(ter_b200_handle_t* h, const DevWeight* w, const int8_t* X, const fl
     }
     TERB_CUDA(h, launch_gemm(p, h->sm_count, h->gemv_cfg.pdl != 0, st));
     h->launches += 2;
-    count_gemv(h, w->K, w->N, M);
+    for (int i = 0; i < n; ++i) count_gemv(h, ws[i]->K, ws[i]->N, M);
     return TER_B200_OK;
+}
+
+int run_gemm(ter_b200_handle_t* h, const DevWeight* w, const int8_t* X, const float* x_scales, int M, float* out,
+             int32_t* acc, cudaStream_t st, bool accumulate, const int32_t* x_rowsum) {
+    const DevWeight* ws[1] = {w};
+    float* outs[1] = {out};
+    return run_gemm_group(h, ws, 1, X, x_scales, M, out ? outs : nullptr, acc, st, accumulate, x_rowsum);
 }
 
 }  // namespace terb
