@@ -500,7 +500,7 @@ def main():
     if sampler:
         clocks = sampler.stop()
 
-    # ---- decode tokens/s (BASELINE configs[3]: Llama-3.2-1B architecture, batch 1, prompt 128 + 256 greedy)
+    # ---- decode tokens/s (Llama-3.2-1B architecture, batch 1, prompt 128 + 256 greedy tokens)
     decode = None
     decode_bitnet = None
     if not args.no_decode:
@@ -526,7 +526,7 @@ def main():
             return d
         decode = tp_fix(decode_bench(tb, dev, 0))  # the same model on every rank; the library keeps its slice
         if not args.no_bitnet:
-            # BASELINE configs[4]: BitNet-2B architecture, context 2048 + 128 greedy tokens; batch 1 (tensor
+            # BitNet-2B architecture, context 2048 + 128 greedy tokens; batch 1 (tensor
             # parallel at N > 1) and, on one GPU, batch 64 (token batch through the tensor-core GEMM)
             decode_bitnet = [tp_fix(decode_bench(tb, dev, 0, "bitnet", n_prompt=2048, n_gen=128, smax=2176))]
             if world == 1 and not args.no_batch64:
