@@ -529,9 +529,28 @@ def main():
             # BitNet-2B architecture, context 2048 + 128 greedy tokens; batch 1 (tensor
             # parallel at N > 1) and, on one GPU, batch 64 (token batch through the tensor-core GEMM)
             decode_bitnet = [tp_fix(decode_bench(tb, dev, 0, "bitnet", n_prompt=2048, n_gen=128, smax=2176))]
-            if world == 1 and not args.no_batch64:
-                decode_bitnet.append(decode_bench(tb, dev, 0, "bitnet", n_prompt=2048, n_gen=128, batch=64, smax=2176,
-                                                  warm=False))
+            if not args.no_batch64 and 64 % world == 0:
+                # 64 sequences: on one GPU a token batch through the tensor-core GEMM; on N GPUs every rank
+                # owns 64/N whole sequences and their KV cache with a full copy of the weights (no collective:
+                # sequences are independent), through a second handle that has no communicator
+                per_rank = 64 // world
+                tb2 = tb if world == 1 else TerB200(local)
+                if per_rank < 16:
+                    tb2.set_option("gemm_min_m", 2)      # small token batches still go through the GEMM
+                d = decode_bench(tb2, dev, rank, "bitnet", n_prompt=2048, n_gen=128, batch=per_rank, smax=2176, warm=False)
+                if world > 1:
+                    t = torch.tensor([d["ms_per_step"], d["prompt_ms"]], device=dev)
+                    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                    d["ms_per_step"], d["prompt_ms"] = float(t[0].item()), float(t[1].item())
+                    d["batch"] = 64
+                    d["ms_per_token"] = d["ms_per_step"] / 64
+                    d["tokens_per_s"] = 64e3 / d["ms_per_step"]
+                    d["prompt_tokens_per_s"] = 64 * 2048 / d["prompt_ms"] * 1e3
+                    d["parallelism"] = f"{world} ranks x {per_rank} sequences, weights replicated, no collective"
+                    d["workload"] = d["workload"].replace(f"batch {per_rank}", f"batch 64 ({per_rank} per GPU)")
+                    d.pop("e2e_tokens_per_s", None)
+                    tb2.close()
+                decode_bitnet.append(d)
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
