@@ -175,7 +175,9 @@ int ter_b200_gemv_host(ter_b200_handle_t* h, const char* slot, const int8_t* x_h
  * (int8[K_i]), x_scales[i], out_hosts[i] (float[N_i]).  SYNCHRONOUS: the results are in out_hosts when
  * it returns.  Vectors given with the same pointer, scale and K travel once; all inputs go up in one
  * copy; the GEMVs run as one launch (more only past 512 matrices, 16 distinct vectors or 64 KB of x);
- * outputs that lie back to back in host memory, in call order, come down in one copy. */
+ * outputs that lie back to back in host memory, in call order, form a run: a run in pinned host memory
+ * is written by the kernel itself while it streams the weights (option "host_batch_direct", default
+ * 1), any other run comes down in one copy. */
 int ter_b200_gemv_host_batch(ter_b200_handle_t* h, int n, const char* const* slots, const int8_t* const* x_hosts,
                              const float* x_scales, float* const* out_hosts, void* stream);
 int ter_b200_sync(ter_b200_handle_t* h, void* stream);
@@ -357,7 +359,7 @@ int ter_b200_device_status(ter_b200_handle_t* h);
 /* Last CUDA error code seen by the handle (cudaError_t as int), 0 if none. */
 int ter_b200_last_cuda_error(const ter_b200_handle_t* h);
 /* Tuning knobs (integers): "gemv_ctas_per_sm", "gemv_stages", "gemv_split_max_strips", "pdl",
- * "fuse_quant", "gemm_min_m", "gemm_split_k", "attn_inline_merge", "prefill", "tp_p2p" (1, default: tensor-
+ * "fuse_quant", "gemm_min_m", "gemm_split_k", "attn_inline_merge", "prefill", "host_batch_direct", "tp_p2p" (1, default: tensor-
  * parallel output slices travel by peer stores over NVLink inside one small kernel per exchange;
  * 0: NCCL all-gathers) and "tp_shard" (which blocks of a layer are column-sharded over the ranks:
  * bit 0 the attention block q/k/v/o, bit 1 the FFN block gate/up/down; the lm_head always is.

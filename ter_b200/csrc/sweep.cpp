@@ -269,6 +269,32 @@ int ter_b200_gemv_host_batch(ter_b200_handle_t* h, int n, const char* const* slo
     }
     if (rc) { cleanup(); return rc; }
 
+    // Outputs that lie back to back in host memory form a run.  A run in PINNED host memory that the
+    // device can address is written by the kernel itself (its 2 MB of results leave over PCIe while the
+    // weights are still streaming), the others are staged on the device and copied afterwards.
+    float** direct = (float**)calloc((size_t)n, sizeof(float*));   // device-visible address of out_hosts[i], or null
+    if (!direct) { cleanup(); return TER_B200_E_ALLOC; }
+    if (h->host_batch_direct) {
+        for (int i = 0; i < n;) {
+            size_t len = (size_t)sl[i]->w.N;
+            int j = i + 1;
+            while (j < n && sl[j - 1]->w.N == sl[j - 1]->w.Npad && out_hosts[j] == out_hosts[i] + len) {
+                len += (size_t)sl[j]->w.N;
+                ++j;
+            }
+            cudaPointerAttributes a0, a1;
+            if (cudaPointerGetAttributes(&a0, out_hosts[i]) == cudaSuccess && a0.type == cudaMemoryTypeHost &&
+                a0.devicePointer &&
+                cudaPointerGetAttributes(&a1, out_hosts[i] + len - 1) == cudaSuccess && a1.type == cudaMemoryTypeHost &&
+                a1.devicePointer == (void*)((float*)a0.devicePointer + len - 1)) {
+                for (int k = i; k < j; ++k) direct[k] = (float*)a0.devicePointer + (out_hosts[k] - out_hosts[i]);
+            } else {
+                (void)cudaGetLastError();
+            }
+            i = j;
+        }
+    }
+
     // Pass 3: fill the pinned image of the staging buffer and the launch parameters.
     size_t oo = 0;
     for (int c = 0; c < n_chunks; ++c) {
@@ -280,7 +306,7 @@ int ter_b200_gemv_host_batch(ter_b200_handle_t* h, int n, const char* const* slo
         for (int i = ch.i0; i < ch.i1; ++i) {
             TerbSlot* s = sl[i];
             const int before = b->p.n_x;
-            const int u = b->add(s->w, x_hosts[i], scale_key(i), h->hout_dev + oo);
+            const int u = b->add(s->w, x_hosts[i], scale_key(i), direct[i] ? direct[i] : h->hout_dev + oo);
             if (u == before) {   // a new vector: copy it into the image
                 memcpy(h->hpin + x_off + b->p.uoff[u], x_hosts[i], (size_t)s->w.K);
                 sc_host[u] = x_scales[i];
@@ -313,10 +339,13 @@ int ter_b200_gemv_host_batch(ter_b200_handle_t* h, int n, const char* const* slo
             oo += (size_t)sl[j]->w.Npad;
             ++j;
         }
-        e = cudaMemcpyAsync(dst, h->hout_dev + src_off, len * sizeof(float), cudaMemcpyDeviceToHost, st);
-        if (e != cudaSuccess) rc = cuda_fail(h, e);
+        if (!direct[i]) {
+            e = cudaMemcpyAsync(dst, h->hout_dev + src_off, len * sizeof(float), cudaMemcpyDeviceToHost, st);
+            if (e != cudaSuccess) rc = cuda_fail(h, e);
+        }
         i = j;
     }
+    free(direct);
     cleanup();
     if (rc) return rc;
     TERB_CUDA(h, cudaStreamSynchronize(st));   // the pinned image is reused by the next call

@@ -262,10 +262,22 @@ def test_host_batch_entry_point(tb):
         scales.append(float(xs))
         wants.append(oracle.gemv_epilogue(exact_acc(x, t).astype(np.int32), xs, ws))
     plan = tb.gemv_host_batch_plan([s[0] for s in specs], xs_h, scales, outs_h)
-    tb.gemv_host_batch(plan)
-    tb.sync()
-    for o, w in zip(outs_h, wants):
-        assert np.array_equal(o.numpy().view(np.uint32), w.view(np.uint32))
+    try:
+        for direct in (1, 0):     # results written by the kernel into the pinned buffers / staged and copied
+            tb.set_option("host_batch_direct", direct)
+            for o in outs_h:
+                o.fill_(float("nan"))
+            tb.gemv_host_batch(plan)
+            for o, w in zip(outs_h, wants):
+                assert np.array_equal(o.numpy().view(np.uint32), w.view(np.uint32)), direct
+        # pageable outputs always take the staged path
+        pag = [np.full(N, np.nan, np.float32) for _, _, N in specs]
+        tb.set_option("host_batch_direct", 1)
+        tb.gemv_host_batch(tb.gemv_host_batch_plan([s[0] for s in specs], xs_h, scales, pag))
+        for o, w in zip(pag, wants):
+            assert np.array_equal(o.view(np.uint32), w.view(np.uint32))
+    finally:
+        tb.set_option("host_batch_direct", 1)
 
 
 def test_host_batch_shared_vectors_contiguous_outputs_and_chunking(tb):
