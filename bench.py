@@ -306,7 +306,7 @@ def decode_bench(tb, dev, rank, which="llama", n_prompt=128, n_gen=256, batch=1,
             "tokens_per_s": batch * gen_steps / gen_ms * 1e3, "ms_per_step": gen_ms / gen_steps,
             "ms_per_token": gen_ms / gen_steps / batch, "steps": gen_steps, "batch": batch,
             "prompt_ms": prompt_ms, "prompt_tokens_per_s": batch * n_prompt / prompt_ms * 1e3,
-            "prompt_mode": "token batches of up to 256 positions through the tensor-core GEMM" if batched_prompt
+            "prompt_mode": "token batches of up to 1024 positions through the tensor-core GEMM" if batched_prompt
                            else "one position per step (the reference's method)",
             "e2e_tokens_per_s": batch * n_gen / wall, "first_tokens": [int(t) for t in out[0][:4]],
             "roofline_frac_hbm": (step_bytes / (gen_ms / gen_steps * 1e-3) / 1e9) / peak,

@@ -313,7 +313,8 @@ int ter_b200_generate(ter_b200_handle_t* h, const int32_t* prompts, int batch, i
 /* Milliseconds the device spent in the latest ter_b200_generate call (CUDA events), and the part of
  * it spent on the prompt when the prompt was run as token batches (0 otherwise).  With option
  * "prefill" 1 (default) a single sequence's prompt of 2 or more tokens goes through the layers in
- * tiles of up to 256 positions on the tensor-core GEMM with causal attention over the shared cache;
+ * passes of up to 1024 positions (option "prefill_tile") on the tensor-core GEMM with causal attention
+ * over the shared cache;
  * cache, position and tokens come out exactly as from feeding it one position at a time, which is
  * what the reference does (cuda/ter_cuda_forward_packed.cu:729-747) and what option 0 does. */
 float ter_b200_last_generate_ms(const ter_b200_handle_t* h);
@@ -359,7 +360,7 @@ int ter_b200_device_status(ter_b200_handle_t* h);
 /* Last CUDA error code seen by the handle (cudaError_t as int), 0 if none. */
 int ter_b200_last_cuda_error(const ter_b200_handle_t* h);
 /* Tuning knobs (integers): "gemv_ctas_per_sm", "gemv_stages", "gemv_split_max_strips", "pdl",
- * "fuse_quant", "gemm_min_m", "gemm_split_k", "attn_inline_merge", "prefill", "host_batch_direct", "tp_p2p" (1, default: tensor-
+ * "fuse_quant", "gemm_min_m", "gemm_split_k", "attn_inline_merge", "prefill", "prefill_tile", "host_batch_direct", "tp_p2p" (1, default: tensor-
  * parallel output slices travel by peer stores over NVLink inside one small kernel per exchange;
  * 0: NCCL all-gathers) and "tp_shard" (which blocks of a layer are column-sharded over the ranks:
  * bit 0 the attention block q/k/v/o, bit 1 the FFN block gate/up/down; the lm_head always is.

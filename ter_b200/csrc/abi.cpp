@@ -199,6 +199,7 @@ ter_b200_handle_t* ter_b200_create(int device) {
     h->tp_p2p = 1;
     h->tp_shard = 0;
     h->prefill = 1;
+    h->prefill_tile = 1024;
     h->host_batch_direct = 1;
     h->gemm_split_k = 1;
     int sms = 0;
@@ -500,6 +501,9 @@ int ter_b200_set_option(ter_b200_handle_t* h, const char* key, int value) {
         h->attn_inline_merge = value ? 1 : 0;
     } else if (strcmp(key, "host_batch_direct") == 0) {
         h->host_batch_direct = value ? 1 : 0;
+    } else if (strcmp(key, "prefill_tile") == 0) {
+        if (value < 1 || value > 1024) return TER_B200_E_SHAPE;
+        h->prefill_tile = value;
     } else if (strcmp(key, "prefill") == 0) {
         h->prefill = value ? 1 : 0;     // buffers are sized by the next ter_b200_model_create
     } else if (strcmp(key, "tp_shard") == 0) {

@@ -73,6 +73,7 @@ struct ter_b200_handle_t {
     int gemm_split_k;           // 0 = never split K
     int gemm_dbg;
     int host_batch_direct;      // 1: ter_b200_gemv_host_batch lets the kernel write results into pinned host buffers
+    int prefill_tile;           // prompt positions per pass (at most 1024)
     int prefill;                // 1: ter_b200_generate runs the prompt of a single sequence as token batches
     int tp_shard;               // bit 0: attention block column-sharded, bit 1: FFN block; the lm_head always is
     int tp_p2p;                 // 1: tensor-parallel exchanges over peer memory (exchange_sm100.cu); 0: NCCL all-gathers

@@ -47,7 +47,7 @@ struct TerbModel {
     float last_prefill_ms, last_prompt_ms;
 };
 
-constexpr int kPrefillTile = 256;    // prompt positions per pass = the token tile of the GEMM
+constexpr int kPrefillTile = 1024;   // prompt positions per pass (four 256-token tiles of the GEMM)
 
 namespace {
 
@@ -681,7 +681,7 @@ int ter_b200_generate(ter_b200_handle_t* h, const int32_t* prompts, int batch, i
         if (rc) return rc;
     }
     // Prompt processing.  One sequence with a prompt of at least two tokens: the prompt goes through the
-    // layers in tiles of up to 256 positions as a token batch (tensor-core GEMM, causal attention per
+    // layers in passes of up to 1024 positions as a token batch (tensor-core GEMM, causal attention per
     // row over the shared cache), which leaves the cache, the position and the first generated token
     // exactly as feeding the prompt one position at a time does.  Under tensor parallelism only with
     // replicated layers (the default policy).  Otherwise: one graph replay per prompt position.
@@ -690,7 +690,7 @@ int ter_b200_generate(ter_b200_handle_t* h, const int32_t* prompts, int batch, i
     TERB_CUDA(h, cudaEventRecord(m->ev0, st));
     int replays = steps;
     if (use_prefill) {
-        const int T = m->rows_cap < kPrefillTile ? m->rows_cap : kPrefillTile;
+        const int T = m->rows_cap < h->prefill_tile ? m->rows_cap : h->prefill_tile;
         int widest = m->c.F > m->c.H ? m->c.F : m->c.H;
         if (m->c.Nh * m->c.Hd > widest) widest = m->c.Nh * m->c.Hd;
         rc = ensure_gemm_scratch(h, T, widest);

@@ -102,11 +102,12 @@ def test_reference_numpy_forward_tokens_on_gpu(tb, golden_dir):
 
 @pytest.mark.parametrize("cfg,seed", [(SMALL_LLAMA, 41), (SMALL_BITNET, 42), (SMALL_PACKED_HEAD, 43)])
 def test_prompt_as_token_batches_equals_one_position_at_a_time(tb, cfg, seed):
-    """Prompt processing through the tensor-core GEMM (tiles of up to 256 positions, causal attention over
-    the shared cache) leaves tokens and logits bit-identical to feeding the prompt position by position."""
+    """Prompt processing through the tensor-core GEMM (passes of `prefill_tile` positions, causal attention
+    over the shared cache) leaves tokens and logits bit-identical to feeding the prompt position by position."""
     rng = np.random.default_rng(seed)
     lengths = [2, 17, 40] if cfg["Smax"] < 300 else [2, 17, 255, 256, 290]
     try:
+        tb.set_option("prefill_tile", 64)     # several passes per prompt, ragged last pass
         for n_prompt in lengths:
             n_gen = min(6, cfg["Smax"] - n_prompt + 1)
             prompt = rng.integers(0, cfg["V"], size=n_prompt).astype(np.int32)
@@ -122,6 +123,7 @@ def test_prompt_as_token_batches_equals_one_position_at_a_time(tb, cfg, seed):
             assert tb.device_status() == 0
     finally:
         tb.set_option("prefill", 1)
+        tb.set_option("prefill_tile", 1024)
 
 
 def test_packed_model_files_load_and_reproduce_reference_tokens(tb, golden_dir, tmp_path):
