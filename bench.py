@@ -168,6 +168,36 @@ def per_shape_bench(tb, dev, peak, reps=20):
     return rows
 
 
+def reference_gpu_bench(tb, dev, n_gen=48):
+    """The UNMODIFIED reference CUDA decode programs (cuda/ter_cuda_forward_packed.cu and
+    cuda/ter_cuda_forward_bitnet.cu, built for sm_100a into oracle/_ref/ by oracle/Makefile) in their
+    random-weight bench mode on this GPU: packed-trit lm_head, context limit 64, 4 warm-up positions, then
+    n_gen graph-replayed decode steps; and this library on the same terms (same architecture, packed-trit
+    lm_head, Smax 64, generation steps at positions 4 .. 4 + n_gen)."""
+    import re
+    out = []
+    for which, exe in (("llama", "ref_forward_packed"), ("bitnet", "ref_forward_bitnet")):
+        row = {"arch": "llama-3.2-1b" if which == "llama" else "bitnet-b1.58-2b", "n_gen": n_gen}
+        path = os.path.join(ROOT, "oracle", "_ref", exe)
+        if os.path.exists(path):
+            try:
+                r = subprocess.run([path, str(n_gen)], capture_output=True, text=True, timeout=300)
+                m = re.search(r"tokens/s\s*:\s*([0-9.]+)", r.stdout)
+                row["reference_tokens_per_s"] = float(m.group(1)) if m else None
+                if not m:
+                    row["reference_error"] = (r.stdout[-200:] + r.stderr[-200:]).strip()
+            except Exception as e:  # noqa: BLE001
+                row["reference_tokens_per_s"], row["reference_error"] = None, str(e)
+        else:
+            row["reference_tokens_per_s"], row["reference_error"] = None, "oracle/_ref/" + exe + " not built"
+        d = decode_bench(tb, dev, 0, which, n_prompt=4, n_gen=n_gen, smax=64, lm_head_packed=True)
+        row["ours_tokens_per_s"] = d["tokens_per_s"]
+        if row.get("reference_tokens_per_s"):
+            row["ratio"] = d["tokens_per_s"] / row["reference_tokens_per_s"]
+        out.append(row)
+    return out
+
+
 def gemm_bench(tb, dev):
     """Batched ternary GEMM (tcgen05 kind::i8) on the BitNet-2B projection shapes at M = 16, 64, 256, 1024
     tokens: microseconds per call (CUDA events around a graph of 20 calls; includes the row-sum pre-kernel
@@ -253,7 +283,8 @@ def cpu_reference_run(steps: int, warmup: int, threads: int):
             "ms_per_step": dt / steps * 1e3}
 
 
-def decode_bench(tb, dev, rank, which="llama", n_prompt=128, n_gen=256, batch=1, smax=512, warm=True):
+def decode_bench(tb, dev, rank, which="llama", n_prompt=128, n_gen=256, batch=1, smax=512, warm=True,
+                 lm_head_packed=False):
     """Random-init ternarised decode of one of the two benchmark architectures (tied bf16 lm_head, bf16 KV
     cache): Llama-3.2-1B (16 layers, H 2048, 32/8 heads x 64, FFN 8192 SiLU) or BitNet-b1.58-2B (30 layers,
     H 2560, 20/5 heads x 128, FFN 6912 squared-ReLU with sub-norms), vocab 128256.  n_prompt random prompt
@@ -262,8 +293,11 @@ def decode_bench(tb, dev, rank, which="llama", n_prompt=128, n_gen=256, batch=1,
     import torch
     from ter_b200 import FMT_V11, synth
     base = synth.LLAMA_1B_CFG if which == "llama" else synth.BITNET_2B_CFG
-    cfg = dict(base, Smax=smax)
+    cfg = dict(base, Smax=smax, lm_head_packed=1 if lm_head_packed else 0)
     tb.model_create(cfg, max_batch=batch)
+    if lm_head_packed:   # the reference's bench mode: random packed-trit lm_head instead of the tied table
+        seed = synth.seed_for(rank, "dec", which, "lm_head")
+        tb.model_set_matrix(-1, 0, synth.packed_v11_cuda(cfg["H"], cfg["V"], seed, dev), FMT_V11, float(synth.weight_scale(seed)))
     g = torch.Generator(device=dev)
     g.manual_seed(synth.seed_for(rank, "embd") & 0x7FFFFFFF)
     emb = (torch.randn((cfg["V"], cfg["H"]), generator=g, device=dev) * 0.02).to(torch.bfloat16)
@@ -299,10 +333,11 @@ def decode_bench(tb, dev, rank, which="llama", n_prompt=128, n_gen=256, batch=1,
     shapes_bytes = sum(K * N // 4 for K, N in shapes.values()) * cfg["L"]
     # per generation step: packed layer weights + bf16 lm_head + the KV cache read at the mean context
     kv_bytes = batch * (n_prompt + n_gen / 2) * cfg["L"] * 2 * cfg["Nkv"] * cfg["Hd"] * 2
-    step_bytes = shapes_bytes + 2 * cfg["V"] * cfg["H"] + kv_bytes
+    step_bytes = shapes_bytes + (cfg["V"] * cfg["H"] // 4 if lm_head_packed else 2 * cfg["V"] * cfg["H"]) + kv_bytes
     peak, _ = peaks()
     name = "llama-3.2-1b" if which == "llama" else "bitnet-b1.58-2b"
-    return {"workload": f"{name} architecture decode, batch {batch}, prompt {n_prompt} + {n_gen} greedy tokens, random-init",
+    return {"workload": f"{name} architecture decode, batch {batch}, prompt {n_prompt} + {n_gen} greedy tokens, random-init"
+                        + (", packed-trit lm_head" if lm_head_packed else ""),
             "tokens_per_s": batch * gen_steps / gen_ms * 1e3, "ms_per_step": gen_ms / gen_steps,
             "ms_per_token": gen_ms / gen_steps / batch, "steps": gen_steps, "batch": batch,
             "prompt_ms": prompt_ms, "prompt_tokens_per_s": batch * n_prompt / prompt_ms * 1e3,
@@ -344,6 +379,7 @@ def main():
     ap.add_argument("--no-per-shape", action="store_true")
     ap.add_argument("--no-gemm", action="store_true")
     ap.add_argument("--no-bitnet", action="store_true", help="skip the BitNet-2B decode runs")
+    ap.add_argument("--no-reference-gpu", action="store_true", help="skip the reference's CUDA programs on this GPU")
     ap.add_argument("--no-batch64", action="store_true", help="skip the batch-64 BitNet decode run (about 30 s)")
     ap.add_argument("--layers", type=int, default=16, help="layers of the fabric (profiling captures use fewer)")
     args = ap.parse_args()
@@ -552,6 +588,10 @@ def main():
                     tb2.close()
                 decode_bitnet.append(d)
 
+    reference_gpu = None
+    if rank == 0 and world == 1 and not args.no_decode and not args.no_reference_gpu:
+        reference_gpu = reference_gpu_bench(tb, dev)
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         try:
@@ -597,6 +637,7 @@ def main():
                     "d2h_bytes_per_step": sum(4 * N for _, _, N, _, _ in mats) * world},
             "decode": decode,
             "decode_bitnet": decode_bitnet,
+            "reference_gpu": reference_gpu,
             "gpu_launches": launches,
             "clocks": clocks,
         }
