@@ -198,6 +198,25 @@ def reference_gpu_bench(tb, dev, n_gen=48):
     return out
 
 
+def reference_gpu_gemv():
+    """The reference's own packed-trit GEMV benchmark (cuda/ter_cuda_forward_packed_v12.cu, unmodified, built
+    for sm_100a into oracle/_ref/): kernels v11 and v12 on the five Llama-1B shapes, median of 200 launches on
+    one weight buffer per shape (its method: the small shapes stay in L2), GB/s on packed bytes K*N/4."""
+    path = os.path.join(ROOT, "oracle", "_ref", "ref_gemv_bench")
+    if not os.path.exists(path):
+        return {"error": "oracle/_ref/ref_gemv_bench not built"}
+    try:
+        r = subprocess.run([path], capture_output=True, text=True, timeout=300)
+    except Exception as e:  # noqa: BLE001
+        return {"error": str(e)}
+    rows = []
+    for line in r.stdout.splitlines():
+        f = line.strip().split(",")
+        if len(f) == 5 and f[0] in ("v11", "v12"):
+            rows.append({"kernel": f[0], "shape": f[1], "ms": float(f[2]), "gbs": float(f[3])})
+    return {"rows": rows} if rows else {"error": (r.stdout[-200:] + r.stderr[-200:]).strip()}
+
+
 def gemm_bench(tb, dev):
     """Batched ternary GEMM (tcgen05 kind::i8) on the BitNet-2B projection shapes at M = 16, 64, 256, 1024
     tokens: microseconds per call (CUDA events around a graph of 20 calls; includes the row-sum pre-kernel
@@ -590,7 +609,7 @@ def main():
 
     reference_gpu = None
     if rank == 0 and world == 1 and not args.no_decode and not args.no_reference_gpu:
-        reference_gpu = reference_gpu_bench(tb, dev)
+        reference_gpu = {"decode": reference_gpu_bench(tb, dev), "gemv": reference_gpu_gemv()}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
