@@ -102,10 +102,17 @@ int ter_b200_weight_info(const ter_b200_handle_t* h, const char* name, int* K, i
  * (src/tx/forward.cpp:376-380):
  *   "tk_matmul_b_9t"  args = { (int64)(const char*)weight_slot_name, x_dev, x_scale_dev,
  *                              out_dev, M, stream }            M = 1 -> GEMV, M > 1 -> GEMM
- *   "tk_rmsnorm"      args = { x_dev, gamma_dev, n, eps_bits, q_dev, scale_dev, stream }
- *   "tk_silu"         args = { gate_dev, up_dev, n, q_dev, scale_dev, stream }
- *   "tk_rope"         args = { v_dev, n_heads, head_dim, pos, neox, stream }   (table of the model)
- *   "tk_softmax"      args = { q_dev, kcache_dev, vcache_dev, out_dev, seq_len, stream } (model dims)
+ *   "tk_rmsnorm"      args = { x_dev, gamma_dev, n, rows, eps (float bits), q_dev, scale_dev }
+ *                              = ter_b200_rmsnorm_quant on the handle's stream
+ *   "tk_silu"         args = { gate_dev, up_dev, n, rows, q_dev, scale_dev [, stream] }
+ *                              = ter_b200_act_quant with the SiLU gate
+ *   "tk_rope"         args = { q_dev, k_dev, pos_dev, dims, Smax, theta (double bits), neox }
+ *                              = ter_b200_rope_kv without the cache append (rotation in place)
+ *   "tk_softmax"      args = { q_dev, kcache_dev, vcache_dev, pos_dev, dims, Smax, out_dev }
+ *                              = ter_b200_attention_noalloc (on this path the softmax lives inside
+ *                                the attention kernel; there is no stand-alone softmax)
+ *   dims = B | Nh << 16 | Nkv << 32 | Hd << 48.  Unknown names return TER_B200_E_UNKNOWN, more than
+ *   7 arguments TER_B200_E_NARGS, too few TER_B200_E_SHAPE.
  */
 int ter_b200_call(ter_b200_handle_t* h, const char* name, const int64_t* args, size_t n_args);
 
@@ -215,6 +222,7 @@ int ter_b200_act_quant(ter_b200_handle_t* h, int act, const float* gate_dev, con
  * (cuda/ter_cuda_forward_packed.cu:64-90).  neox = 0: pairs (2k,2k+1); neox = 1: pairs (k,k+Hd/2)
  * (cuda/ter_cuda_forward_bitnet.cu:185-201).  Angles pos*theta^(-2k/Hd) come from a table evaluated
  * in double on the host (src/tx/forward.cpp:78-88). */
+/* v_dev, kcache_dev and vcache_dev may all be NULL: rotation only, nothing appended. */
 int ter_b200_rope_kv(ter_b200_handle_t* h, float* q_dev, float* k_dev, const float* v_dev, const int* pos_dev,
                      int B, int Nh, int Nkv, int Hd, int Smax, double theta, int neox, uint16_t* kcache_dev,
                      uint16_t* vcache_dev, void* stream);

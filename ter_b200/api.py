@@ -16,6 +16,7 @@ _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "libter_b200.so")
 
 FMT_V11, FMT_ROWMAJOR, FMT_I32 = 0, 1, 2
+ACT_SILU, ACT_RELU2 = 1, 2
 E_NULL, E_UNKNOWN, E_ALLOC, E_NARGS, E_SHAPE, E_FULL, E_NAME, E_CUDA, E_NCCL, E_STATE, E_TIMEOUT, E_VALUE, E_IO = \
     -1, -2, -3, -4, -5, -6, -7, -8, -9, -10, -11, -12, -13
 

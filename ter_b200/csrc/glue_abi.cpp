@@ -87,7 +87,9 @@ int ter_b200_act_quant(ter_b200_handle_t* h, int act, const float* gate_dev, con
 int ter_b200_rope_kv(ter_b200_handle_t* h, float* q_dev, float* k_dev, const float* v_dev, const int* pos_dev,
                      int B, int Nh, int Nkv, int Hd, int Smax, double theta, int neox, uint16_t* kcache_dev,
                      uint16_t* vcache_dev, void* stream) {
-    if (!h || !q_dev || !k_dev || !v_dev || !pos_dev || !kcache_dev || !vcache_dev) return TER_B200_E_NULL;
+    if (!h || !q_dev || !k_dev || !pos_dev) return TER_B200_E_NULL;
+    // all three of v / kcache / vcache, or none of them (rotation only, nothing appended)
+    if ((v_dev || kcache_dev || vcache_dev) && !(v_dev && kcache_dev && vcache_dev)) return TER_B200_E_NULL;
     if (B < 1 || Nh < 1 || Nkv < 1 || Hd < 2 || (Hd & 1) || Smax < 1) return TER_B200_E_SHAPE;
     TERB_CUDA(h, cudaSetDevice(h->device));
     const float* table = nullptr;

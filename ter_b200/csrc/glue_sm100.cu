@@ -113,12 +113,13 @@ __global__ void __launch_bounds__(kT) rope_kv_kernel(const RopeKvParams p) {
         const float o0 = a - bb, o1 = d + e;
         base[i0] = o0;
         base[i1] = o1;
-        if (is_k) {
+        if (is_k && p.kcache) {
             const size_t co = (((size_t)bs * p.Nkv + (head - p.Nh)) * p.Smax + pos) * p.Hd;
             p.kcache[co + i0] = f32_to_bf16_bits(o0);
             p.kcache[co + i1] = f32_to_bf16_bits(o1);
         }
     }
+    if (!p.vcache) return;
     for (int idx = threadIdx.x; idx < p.Nkv * p.Hd; idx += kT) {
         const int g = idx / p.Hd, d = idx % p.Hd;
         const size_t co = (((size_t)bs * p.Nkv + g) * p.Smax + pos) * p.Hd;

@@ -143,6 +143,37 @@ int ter_b200_call(ter_b200_handle_t* h, const char* name, const int64_t* args, s
         if (M == 1) return ter_b200_gemv(h, slot, x, xs, out, stream);
         return ter_b200_gemm(h, slot, x, xs, M, out, stream);
     }
+    // The other four operator names the reference's forward looks up (src/tx/forward.cpp:376-380), mapped
+    // onto the typed entry points; several small integers share one argument where seven would not do.
+    auto f32 = [](int64_t a) { uint32_t b = (uint32_t)a; float f; memcpy(&f, &b, 4); return f; };
+    auto f64 = [](int64_t a) { double d; memcpy(&d, &a, 8); return d; };
+    auto ptr = [](int64_t a) { return (void*)(intptr_t)a; };
+    if (strcmp(name, "tk_rmsnorm") == 0) {   // x, gamma, n, rows, eps (float bits), q, scale
+        if (!args || n_args < 7) return TER_B200_E_SHAPE;
+        return ter_b200_rmsnorm_quant(h, (const float*)ptr(args[0]), (const float*)ptr(args[1]), (int)args[2], (int)args[3],
+                                      f32(args[4]), (int8_t*)ptr(args[5]), (float*)ptr(args[6]), nullptr, nullptr);
+    }
+    if (strcmp(name, "tk_silu") == 0) {      // gate, up, n, rows, q, scale[, stream]
+        if (!args || n_args < 6) return TER_B200_E_SHAPE;
+        return ter_b200_act_quant(h, TER_B200_ACT_SILU, (const float*)ptr(args[0]), (const float*)ptr(args[1]), nullptr,
+                                  (int)args[2], (int)args[3], 0.0f, (int8_t*)ptr(args[4]), (float*)ptr(args[5]),
+                                  n_args > 6 ? ptr(args[6]) : nullptr);
+    }
+    if (strcmp(name, "tk_rope") == 0) {      // q, k, pos, dims = B | Nh<<16 | Nkv<<32 | Hd<<48, Smax, theta (double bits), neox
+        if (!args || n_args < 7) return TER_B200_E_SHAPE;
+        const uint64_t d = (uint64_t)args[3];
+        return ter_b200_rope_kv(h, (float*)ptr(args[0]), (float*)ptr(args[1]), nullptr, (const int*)ptr(args[2]),
+                                (int)(d & 0xffff), (int)((d >> 16) & 0xffff), (int)((d >> 32) & 0xffff), (int)(d >> 48),
+                                (int)args[4], f64(args[5]), (int)args[6], nullptr, nullptr, nullptr);
+    }
+    if (strcmp(name, "tk_softmax") == 0) {   // the softmax of the path lives inside attention: q, kcache, vcache, pos, dims, Smax, out
+        if (!args || n_args < 7) return TER_B200_E_SHAPE;
+        const uint64_t d = (uint64_t)args[4];
+        return ter_b200_attention_noalloc(h, (const float*)ptr(args[0]), (const uint16_t*)ptr(args[1]),
+                                          (const uint16_t*)ptr(args[2]), (const int*)ptr(args[3]), (int)(d & 0xffff),
+                                          (int)((d >> 16) & 0xffff), (int)((d >> 32) & 0xffff), (int)(d >> 48),
+                                          (int)args[5], (float*)ptr(args[6]), nullptr);
+    }
     return TER_B200_E_UNKNOWN;
 }
 

@@ -178,3 +178,70 @@ def test_fused_quantiser_gemv_matches_two_step(tb):
     want = oracle.gemv_epilogue(oracle.gemv_acc_fast(oq, t), os_, synth.weight_scale(640))
     got = tb.norm_gemv_group(names[:1], xd, gd, 1e-5)[0].cpu().numpy()
     assert np.array_equal(bits(got), bits(want))
+
+
+def test_named_operator_calls_equal_typed_entry_points(tb):
+    """The reference's five operator slot names (src/tx/forward.cpp:376-380) through the K4-style call verb."""
+    import struct
+    from ter_b200 import api
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev)
+    g.manual_seed(5)
+    stream = torch.cuda.current_stream()
+    n, rows = 512, 3
+    x = torch.randn((rows, n), device=dev, generator=g)
+    gamma = torch.rand(n, device=dev, generator=g) + 0.5
+    eps = 1e-5
+    q_t, s_t, _ = tb.rmsnorm_quant(x, gamma, eps)
+    tb.sync()
+    q_c = torch.empty_like(q_t)
+    s_c = torch.empty_like(s_t)
+    eps_bits = struct.unpack("<I", struct.pack("<f", eps))[0]
+    assert tb.call("tk_rmsnorm", [x.data_ptr(), gamma.data_ptr(), n, rows, eps_bits, q_c.data_ptr(), s_c.data_ptr()]) == 0
+    tb.sync()
+    torch.cuda.synchronize()
+    assert torch.equal(q_c, q_t) and torch.equal(s_c, s_t)
+
+    gate = torch.randn((rows, n), device=dev, generator=g)
+    up = torch.randn((rows, n), device=dev, generator=g)
+    q_t, s_t = tb.act_quant(api.ACT_SILU, gate, up, None, 0.0)
+    tb.sync()
+    q_c = torch.empty_like(q_t)
+    s_c = torch.empty_like(s_t)
+    assert tb.call("tk_silu", [gate.data_ptr(), up.data_ptr(), n, rows, q_c.data_ptr(), s_c.data_ptr()]) == 0
+    tb.sync()
+    torch.cuda.synchronize()
+    assert torch.equal(q_c, q_t) and torch.equal(s_c, s_t)
+
+    B, Nh, Nkv, Hd, Smax, theta = 2, 4, 2, 64, 300, 500000.0
+    pos = torch.tensor([7, 270], dtype=torch.int32, device=dev)
+    qv = torch.randn((B, Nh * Hd), device=dev, generator=g)
+    kv = torch.randn((B, Nkv * Hd), device=dev, generator=g)
+    vv = torch.randn((B, Nkv * Hd), device=dev, generator=g)
+    kc = torch.zeros((B, Nkv, Smax, Hd), dtype=torch.int16, device=dev)
+    vc = torch.zeros_like(kc)
+    q1, k1 = qv.clone(), kv.clone()
+    tb.rope_kv(q1, k1, vv, pos, Nh, Nkv, Hd, Smax, theta, 0, kc, vc)
+    tb.sync()
+    q2, k2 = qv.clone(), kv.clone()
+    dims = B | (Nh << 16) | (Nkv << 32) | (Hd << 48)
+    theta_bits = struct.unpack("<q", struct.pack("<d", theta))[0]
+    assert tb.call("tk_rope", [q2.data_ptr(), k2.data_ptr(), pos.data_ptr(), dims, Smax, theta_bits, 0]) == 0
+    tb.sync()
+    torch.cuda.synchronize()
+    assert torch.equal(q1, q2) and torch.equal(k1, k2)
+
+    kc.copy_(torch.randn(kc.shape, device=dev, generator=g).to(torch.bfloat16).view(torch.int16))
+    vc.copy_(torch.randn(vc.shape, device=dev, generator=g).to(torch.bfloat16).view(torch.int16))
+    want = tb.attention(q1, kc, vc, pos, Nh, Nkv, Hd, Smax)
+    tb.sync()
+    out = torch.empty_like(want)
+    assert tb.call("tk_softmax", [q1.data_ptr(), kc.data_ptr(), vc.data_ptr(), pos.data_ptr(), dims, Smax, out.data_ptr()]) == 0
+    tb.sync()
+    torch.cuda.synchronize()
+    assert torch.equal(out.view(torch.int32), want.view(torch.int32)) and not torch.isnan(out).any()
+
+    assert tb.call("tk_rmsnorm", [1, 2, 3]) == api.E_SHAPE
+    assert tb.call("tk_nothing", [0]) == api.E_UNKNOWN
+    assert tb.call("tk_rope", [0] * 8) == api.E_NARGS
+    assert tb.device_status() == 0
