@@ -511,8 +511,6 @@ int ter_b200_set_option(ter_b200_handle_t* h, const char* key, int value) {
         h->tp_shard = value;            // read by the next ter_b200_model_create
     } else if (strcmp(key, "tp_p2p") == 0) {
         h->tp_p2p = value ? 1 : 0;      // read by the next ter_b200_model_create
-    } else if (strcmp(key, "gemm_dbg") == 0) {
-        h->gemm_dbg = value;
     } else if (strcmp(key, "gemm_split_k") == 0) {
         h->gemm_split_k = value ? 1 : 0;
     } else if (strcmp(key, "fuse_quant") == 0) {

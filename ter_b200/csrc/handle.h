@@ -71,7 +71,6 @@ struct ter_b200_handle_t {
     size_t gemm_part_cap;       // ints
     int gemm_min_m;             // batches below this go row by row through the GEMV kernel
     int gemm_split_k;           // 0 = never split K
-    int gemm_dbg;
     int host_batch_direct;      // 1: ter_b200_gemv_host_batch lets the kernel write results into pinned host buffers
     int prefill_tile;           // prompt positions per pass (at most 1024)
     int prefill;                // 1: ter_b200_generate runs the prompt of a single sequence as token batches

@@ -124,7 +124,6 @@ struct GemmParams {
     float w_scale;
     int M, N, K, Kpad, n_strips;
     int tokens, tmem_cols, ksplits, stages;   // set by the launcher
-    int dbg;                  // unused
     // Group of up to kGemmMaxGroup weight matrices with the same K multiplied by the same X in ONE launch
     // (q/k/v, gate/up).  n_w == 0: the single matrix described by W / out / w_scale / N / n_strips; the
     // launcher then fills entry 0 from them.  tile_begin: first 128-column tile of each matrix in the grid's
