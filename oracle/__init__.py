@@ -28,9 +28,10 @@ ATTN_NORM, FFN_NORM, ATTN_SUB_NORM, FFN_SUB_NORM = range(4)
 MAT_NAMES = ["q", "k", "v", "o", "gate", "up", "down"]
 
 
-def build(ref: str = "/root/reference") -> None:
-    """Compile the C restatement, and the reference driver when the reference
-    checkout is present."""
+def build(ref: str | None = None) -> None:
+    """Compile the C restatement, and the reference driver and programs when a reference
+    checkout is given (argument, or TER_REFERENCE in the environment)."""
+    ref = ref if ref is not None else os.environ.get("TER_REFERENCE", "")
     subprocess.run(["make", "-s", "-C", _HERE, "all", f"REF={ref}"], check=True)
 
 

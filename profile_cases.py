@@ -1,24 +1,27 @@
 """Small, self-contained workloads for profiling one kernel at a time:
 
-    python -m ter_b200.profile_cases gemv_stream      # 2048 x 513024 GEMV (263 MB of trits), 4 launches
-    python -m ter_b200.profile_cases sweep            # Llama-1B fabric (113 matrices, 309 MB) as one sweep-plan launch, 8 launches
-    python -m ter_b200.profile_cases gemm             # BitNet gate 2560 x 6912 GEMM at M = 16, 256, 1024
-    python -m ter_b200.profile_cases decode llama     # three decode steps at position ~300 (or: bitnet, position ~2100)
-    python -m ter_b200.profile_cases decode bitnet 64 # the same for a batch of 64 sequences
+    python profile_cases.py gemv_stream      # 2048 x 513024 GEMV (263 MB of trits), 4 launches
+    python profile_cases.py sweep            # Llama-1B fabric (113 matrices, 309 MB) as one sweep-plan launch, 8 launches
+    python profile_cases.py gemm             # BitNet gate 2560 x 6912 GEMM at M = 16, 256, 1024
+    python profile_cases.py decode llama     # three decode steps at position ~300 (or: bitnet, position ~2100)
+    python profile_cases.py decode bitnet 64 # the same for a batch of 64 sequences
 
 Each holds at most a few GB on the device and finishes in seconds, so an `ncu` capture of it ends by itself.
 """
 from __future__ import annotations
 
+import os
 import sys
 
 import numpy as np
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 
 def build_random_model(tb, cfg, dev, max_batch=1, seed=1):
     """Random-init ternarised model generated on the device (weights never visit the host)."""
     import torch
-    from . import FMT_V11, synth
+    from ter_b200 import FMT_V11, synth
     tb.model_create(cfg, max_batch=max_batch)
     g = torch.Generator(device=dev)
     g.manual_seed(seed)
@@ -37,7 +40,7 @@ def build_random_model(tb, cfg, dev, max_batch=1, seed=1):
 
 def gemv_stream():
     import torch
-    from . import FMT_V11, TerB200, synth
+    from ter_b200 import FMT_V11, TerB200, synth
     tb = TerB200(0)
     dev = torch.device("cuda:0")
     K, N = 2048, 128256 * 4
@@ -60,7 +63,7 @@ def gemv_stream():
 
 def sweep():
     import torch
-    from . import FMT_V11, TerB200, synth
+    from ter_b200 import FMT_V11, TerB200, synth
     tb = TerB200(0)
     dev = torch.device("cuda:0")
     names, xs, ss, outs, nbytes = [], [], [], [], 0
@@ -95,7 +98,7 @@ def sweep():
 
 def gemm():
     import torch
-    from . import FMT_V11, TerB200, synth
+    from ter_b200 import FMT_V11, TerB200, synth
     tb = TerB200(0)
     dev = torch.device("cuda:0")
     K, N = synth.BITNET_2B_SHAPES["gate"]
@@ -112,7 +115,7 @@ def gemm():
 
 def decode(which="llama", batch="1"):
     import torch
-    from . import TerB200, synth
+    from ter_b200 import TerB200, synth
     batch = int(batch)
     base, smax, pos0 = (synth.LLAMA_1B_CFG, 512, 300) if which == "llama" else (synth.BITNET_2B_CFG, 2304, 2100)
     tb = TerB200(0)

@@ -234,6 +234,7 @@ void ter_b200_destroy(ter_b200_handle_t* h) {
     if (h->hscale_dev) cudaFree(h->hscale_dev);
     if (h->gemm_scratch) cudaFree(h->gemm_scratch);
     if (h->gemm_part) cudaFree(h->gemm_part);
+    for (int i = 0; i < h->n_retired; ++i) cudaFree(h->retired[i]);
     if (h->hx_dev) cudaFree(h->hx_dev);
     if (h->hout_dev) cudaFree(h->hout_dev);
     if (h->hpin) cudaFreeHost(h->hpin);

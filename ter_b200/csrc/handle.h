@@ -69,6 +69,11 @@ struct ter_b200_handle_t {
     size_t gemm_scratch_cap;    // ints
     int32_t* gemm_part;         // split-K partials
     size_t gemm_part_cap;       // ints
+    // Scratch buffers that were outgrown.  Captured graphs (the model's decode step, user graphs) keep
+    // the addresses they were recorded with, so an outgrown buffer stays allocated until the handle goes.
+    void* retired[64];
+    int n_retired;
+    size_t gemm_scratch_cap_prev, gemm_part_cap_prev;   // sizes of the latest allocations (growth is geometric)
     int gemm_min_m;             // batches below this go row by row through the GEMV kernel
     int gemm_split_k;           // 0 = never split K
     int host_batch_direct;      // 1: ter_b200_gemv_host_batch lets the kernel write results into pinned host buffers

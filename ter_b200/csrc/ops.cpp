@@ -15,20 +15,30 @@ int ensure_gemm_scratch(ter_b200_handle_t* h, int M, int N) {
     const size_t need_part = (h->gemm_split_k && M <= 256) ? (size_t)M * (size_t)N : 0;
     if (h->gemm_scratch_cap >= (size_t)M && h->gemm_part_cap >= need_part) return TER_B200_OK;
     TERB_CUDA(h, cudaDeviceSynchronize());
+    // An outgrown buffer is parked, not freed: a captured graph may still launch kernels on it.
+    auto retire = [&](void* p) -> bool {
+        if (!p) return true;
+        if (h->n_retired >= (int)(sizeof h->retired / sizeof h->retired[0])) return false;
+        h->retired[h->n_retired++] = p;
+        return true;
+    };
     if (h->gemm_scratch_cap < (size_t)M) {
-        if (h->gemm_scratch) cudaFree(h->gemm_scratch);
+        if (!retire(h->gemm_scratch)) return TER_B200_E_ALLOC;
         h->gemm_scratch = nullptr;
         h->gemm_scratch_cap = 0;
-        TERB_CUDA(h, cudaMalloc((void**)&h->gemm_scratch, (size_t)M * sizeof(int)));
-        h->gemm_scratch_cap = (size_t)M;
+        // grow at least geometrically, so the parked list stays short
+        const size_t cap = (size_t)M > 2 * h->gemm_scratch_cap_prev ? (size_t)M : 2 * h->gemm_scratch_cap_prev;
+        TERB_CUDA(h, cudaMalloc((void**)&h->gemm_scratch, cap * sizeof(int)));
+        h->gemm_scratch_cap = h->gemm_scratch_cap_prev = cap;
     }
     if (h->gemm_part_cap < need_part) {
-        if (h->gemm_part) cudaFree(h->gemm_part);
+        if (!retire(h->gemm_part)) return TER_B200_E_ALLOC;
         h->gemm_part = nullptr;
         h->gemm_part_cap = 0;
-        TERB_CUDA(h, cudaMalloc((void**)&h->gemm_part, need_part * sizeof(int)));
-        TERB_CUDA(h, cudaMemset(h->gemm_part, 0, need_part * sizeof(int)));
-        h->gemm_part_cap = need_part;
+        const size_t cap = need_part > 2 * h->gemm_part_cap_prev ? need_part : 2 * h->gemm_part_cap_prev;
+        TERB_CUDA(h, cudaMalloc((void**)&h->gemm_part, cap * sizeof(int)));
+        TERB_CUDA(h, cudaMemset(h->gemm_part, 0, cap * sizeof(int)));
+        h->gemm_part_cap = h->gemm_part_cap_prev = cap;
     }
     return TER_B200_OK;
 }

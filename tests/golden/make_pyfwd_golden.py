@@ -9,7 +9,7 @@ The files are written here in the reference's on-disk format
 (tools/convert_llama_to_packed.py:13-43, tools/convert_bitnet_to_packed.py:4-31) from
 ter_b200.synth.model_weights(cfg, seed), so the tests can rebuild the same model without the
 reference.  Run from the repository root in a container that has the reference checkout:
-    python tests/golden/make_pyfwd_golden.py
+    TER_REFERENCE=<reference checkout> python tests/golden/make_pyfwd_golden.py
 """
 import ast
 import os
@@ -24,9 +24,9 @@ sys.path.insert(0, ROOT)
 from ter_b200 import modelfile, synth  # noqa: E402
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = os.environ.get("TER_REFERENCE", "/root/reference")
+REF = os.environ.get("TER_REFERENCE", "")   # path of the reference checkout
 
-TINY = dict(H=128, F=256, L=2, V=128256, Nh=2, Nkv=1, Hd=64, Smax=32, eps=1e-5, rope_theta=500000.0)
+TINY = dict(H=256, F=256, L=2, V=128256, Nh=4, Nkv=2, Hd=64, Smax=32, eps=1e-5, rope_theta=500000.0)
 CASES = {
     "llama": dict(TINY, arch=0, seed=101, script="tools/llama_pyfwd.py", bin="/tmp/llama_3_2_1b_packed.bin",
                   magic=0x4C4C5254),
@@ -40,6 +40,8 @@ def write_bin(case):
 
 
 def main():
+    if not REF:
+        sys.exit("set TER_REFERENCE to the reference checkout")
     out = {}
     for name, case in CASES.items():
         write_bin(case)

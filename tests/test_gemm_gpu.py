@@ -54,8 +54,6 @@ def test_small_shapes(tb, K, N, M):
 @pytest.mark.parametrize("M", [16, 64, 256, 1024])
 def test_bitnet_shapes(tb, name, M):
     K, N = synth.BITNET_2B_SHAPES[name]
-    if M == 1024 and name in ("gate",):
-        pytest.skip("covered by the other shapes at M=1024; keeps the suite short")
     check(tb, K, N, M, seed=synth.seed_for(K, N, M) & 0xFFFF)
 
 
@@ -82,3 +80,33 @@ def test_extreme_values(tb):
             X = np.full((M, K), xv, np.int8)
             acc = tb.gemm_acc("ex", dev(X)).cpu().numpy()
             assert np.all(acc == sign * xv * K)
+
+
+def test_captured_graph_survives_scratch_growth(tb):
+    """A captured GEMM keeps the scratch addresses it was recorded with.  A later eager call that needs a
+    larger scratch must not free them: the replay after it gives the same bits as before."""
+    from ter_b200 import TerB200
+    h = TerB200(0)            # a fresh handle: its scratch starts empty, so the second call has to grow it
+    try:
+        K, N = 512, 256
+        t, ws, X, xs = make(K, N, 24, 77)
+        h.install("sg", synth.pack_v11(t), FMT_V11, K, N, float(ws))
+        Xd, sd = dev(X), dev(xs)
+        out = torch.zeros((24, N), device="cuda")
+        base = h.gemm("sg", Xd, sd).clone()                        # split-K path (M <= 256): uses the partial buffer
+        gid = h.capture(lambda: h.gemm("sg", Xd, sd, out))
+        h.graph_launch(gid)
+        h.sync()
+        assert torch.equal(out, base)
+        t2, ws2, X2, xs2 = make(K, N, 200, 78)                     # 200 x 256 partials: outgrows the scratch
+        h.install("sg2", synth.pack_v11(t2), FMT_V11, K, N, float(ws2))
+        h.gemm("sg2", dev(X2), dev(xs2))
+        junk = [torch.full((1 << 20,), 7, dtype=torch.int32, device="cuda") for _ in range(4)]   # reuse freed memory, if any
+        out.zero_()
+        h.graph_launch(gid)
+        h.sync()
+        del junk
+        assert torch.equal(out, base)
+        assert h.device_status() == 0
+    finally:
+        h.close()

@@ -4,7 +4,8 @@
 (inside a stream capture, in a loop that handed all memory out at start-up, under a foreign
 allocator): its scratch is a fixed array in the library's device image.  The test calls it through
 the C ABI twice in a row on different inputs -- the array is shared and keeps the previous call's
-contents -- and requires the same bits as the regular entry point given a caller's scratch buffer.
+contents -- and requires the same bits as the regular entry point given a caller's scratch buffer,
+and as the CPU checker's chunked attention (so the comparison is not CUDA against itself only).
 It builds its own handle so that it passes alone in a fresh process as well as after the rest of
 the suite.  (The file name sorts last: a run that stops at the first failure has then already run
 every other test.)"""
@@ -39,6 +40,14 @@ def test_noalloc_attention_matches_regular_entry_point():
             got = h.attention_noalloc(q, kc, vc, pos, Nh, Nkv, Hd, Smax, out=out)
             torch.cuda.synchronize()
             assert torch.equal(got, want)                                  # same bits as the regular entry point
+            # ... and as the CPU checker, sequence by sequence
+            import oracle
+            qh, gh = q.cpu().numpy(), got.cpu().numpy()
+            kh = kc.view(torch.int16).cpu().numpy().view(np.uint16)
+            vh = vc.view(torch.int16).cpu().numpy().view(np.uint16)
+            for b, n in enumerate(lens):
+                ref = oracle.attention(qh[b], kh[b], vh[b], Nh, Nkv, Hd, Smax, n)
+                assert np.array_equal(gh[b].view(np.uint32), ref.view(np.uint32)), (b, n)
         # a problem whose records do not fit the fixed array is refused with a clear error
         B, Nh, Nkv, Hd, Smax = 64, 32, 8, 128, 2176
         assert h.L.ter_b200_attention_scratch_floats(B, Nh, Hd, Smax) > cap
