@@ -359,12 +359,38 @@ class Ref:
         L.ref_mm_row_repeat.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int]
         L.ref_quantize.restype = C.c_float
         L.ref_quantize.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p]
+        if hasattr(L, "ref_tx_create"):
+            L.ref_tx_create.restype = C.c_void_p
+            L.ref_tx_create.argtypes = [C.c_int] * 9 + [C.c_float, C.c_double, C.c_uint64]
+            L.ref_tx_destroy.argtypes = [C.c_void_p]
+            L.ref_tx_forward_tokens.restype = C.c_double
+            L.ref_tx_forward_tokens.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
         self.L = L
         self.ctx = L.ref_ctx_create()
 
     @staticmethod
     def available() -> bool:
         return os.path.exists(REF_SO)
+
+    def forward_token_seconds(self, cfg: dict, n_tokens: int = 3, first_pos: int = 27, seed: int = 1):
+        """Times the reference's CPU decode forward (ter::tx::forward_token, src/tx/transformer.cpp:116-223)
+        on a synthetic model of architecture `cfg` filled in place by the driver: returns (seconds per token,
+        greedy tokens).  Single-threaded, as the reference is."""
+        if not hasattr(self.L, "ref_tx_create"):
+            raise RuntimeError("libter_ref.so was built without the forward driver")
+        tx = self.L.ref_tx_create(int(cfg["arch"]), cfg["H"], cfg["F"], cfg["L"], cfg["V"], cfg["Nh"], cfg["Nkv"],
+                                  cfg["Hd"], max(cfg.get("Smax", 64), first_pos + n_tokens), C.c_float(cfg["eps"]),
+                                  C.c_double(cfg["rope_theta"]), seed)
+        if not tx:
+            raise MemoryError("reference model allocation failed")
+        try:
+            toks = np.zeros(n_tokens, np.int32)
+            secs = float(self.L.ref_tx_forward_tokens(tx, 1, first_pos, n_tokens, toks.ctypes.data))
+            if secs < 0:
+                raise RuntimeError(f"reference forward_token failed ({secs})")
+            return secs / n_tokens, toks
+        finally:
+            self.L.ref_tx_destroy(tx)
 
     def tensor(self, payload: np.ndarray, scale: float, rows: int, cols: int):
         p = np.ascontiguousarray(payload, dtype=np.int32)

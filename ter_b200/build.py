@@ -73,7 +73,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
     for src in sources():
         obj = os.path.join(OBJ_DIR, os.path.basename(src) + ".o")
         objs.append(obj)
-        cmd = [nvcc, "-c", src, "-o", obj] + ARCH + NVCC_FLAGS + extra_inc
+        # TER_B200_NVCC_EXTRA: extra compiler flags (diagnostic builds)
+        cmd = [nvcc, "-c", src, "-o", obj] + ARCH + NVCC_FLAGS + extra_inc + os.environ.get("TER_B200_NVCC_EXTRA", "").split()
         if verbose:
             cmd += ["-Xptxas", "-v"]
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))

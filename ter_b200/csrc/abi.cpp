@@ -196,6 +196,10 @@ ter_b200_handle_t* ter_b200_create(int device) {
     h->gemv_cfg = GemvLaunchCfg();
     h->gemm_min_m = 4;
     h->attn_inline_merge = 1;
+    h->decode_persistent = 1;
+    h->decode_fault_cta = -1;
+    h->decode_poll_ns = 0;
+    h->wait_ms = 2000;
     h->tp_p2p = 1;
     h->tp_shard = 0;
     h->prefill = 1;
@@ -498,6 +502,18 @@ int ter_b200_set_option(ter_b200_handle_t* h, const char* key, int value) {
     } else if (strcmp(key, "gemm_min_m") == 0) {
         if (value < 1) return TER_B200_E_SHAPE;
         h->gemm_min_m = value;
+    } else if (strcmp(key, "decode_persistent") == 0) {
+        h->decode_persistent = value ? 1 : 0;
+    } else if (strcmp(key, "decode_poll_ns") == 0) {
+        if (value < 0 || value > 100000) return TER_B200_E_SHAPE;
+        h->decode_poll_ns = value;
+        model_invalidate_graph(h);
+    } else if (strcmp(key, "decode_fault_cta") == 0) {
+        h->decode_fault_cta = value;
+        model_invalidate_graph(h);
+    } else if (strcmp(key, "wait_ms") == 0) {
+        if (value < 1) return TER_B200_E_SHAPE;
+        h->wait_ms = value;
     } else if (strcmp(key, "attn_inline_merge") == 0) {
         h->attn_inline_merge = value ? 1 : 0;
     } else if (strcmp(key, "host_batch_direct") == 0) {

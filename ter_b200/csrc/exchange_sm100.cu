@@ -16,6 +16,7 @@
 // kWaitNs; the context stays usable and the host reads TER_B200_E_TIMEOUT from the status word.
 #include "common.cuh"
 #include "glue.h"
+#include "tagged.cuh"
 
 namespace terb {
 
@@ -23,20 +24,6 @@ namespace {
 
 constexpr unsigned long long kWaitNs = 2000000000ull;   // 2 s
 constexpr int kXThreads = 256;
-
-__device__ __forceinline__ unsigned long long global_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-__device__ __forceinline__ uint4 ld_volatile16(const uint4* p) {
-    uint4 v;
-    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void st_volatile16(uint4* p, const uint4& v) {
-    asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-}
 
 __global__ void __launch_bounds__(kXThreads) peer_exchange_kernel(const __grid_constant__ ExchangeParams p) {
     const int tid = threadIdx.x;
@@ -70,12 +57,12 @@ __global__ void __launch_bounds__(kXThreads) peer_exchange_kernel(const __grid_c
             const uint4* src = reinterpret_cast<const uint4*>(my_base + p.recv_off) + (size_t)r * words_total + w;
             uint4 got = ld_volatile16(src);
             if (got.y != seq || got.w != seq) {
-                const unsigned long long t0 = global_ns();
+                const unsigned long long t0 = globaltimer_ns();
                 unsigned spins = 0;
                 while (!timed_out) {
                     got = ld_volatile16(src);
                     if (got.y == seq && got.w == seq) break;
-                    if ((++spins & 255u) == 0 && global_ns() - t0 > kWaitNs) {
+                    if ((++spins & 255u) == 0 && globaltimer_ns() - t0 > kWaitNs) {
                         atomicExch(p.status, 0x7e000000 | (p.point << 8) | r);   // which point, which peer
                         timed_out = true;
                     }

@@ -41,22 +41,6 @@ constexpr int kBarOff = 0;                          // u64[kWarps][kMaxStages] =
 constexpr int kXsumOff = kWarps * kMaxStages * 8;   // 512
 constexpr int kHdrBytes = 640;                      // multiple of 128
 
-// Accumulates one 32-bit word of weights (4 k x 4 columns) against 4 int8 activations.
-// t collects the UNMASKED product  S0 + 4*S1 + 16*S2 + 64*S3  (no AND needed); a1..a3 collect
-// 4*S1, 16*S2, 64*S3 from masked words; column 0 is recovered as t - a1 - a2 - a3.
-__device__ __forceinline__ void mac16(uint32_t w, int x, int& t, int& a1, int& a2, int& a3) {
-    t = dp4a_su(x, w, t);
-    a1 = dp4a_su(x, w & 0x0C0C0C0Cu, a1);
-    a2 = dp4a_su(x, w & 0x30303030u, a2);
-    a3 = dp4a_su(x, w & 0xC0C0C0C0u, a3);
-}
-__device__ __forceinline__ void mac64(const uint4& w, const int4& xv, int& t, int& a1, int& a2, int& a3) {
-    mac16(w.x, xv.x, t, a1, a2, a3);
-    mac16(w.y, xv.y, t, a1, a2, a3);
-    mac16(w.z, xv.z, t, a1, a2, a3);
-    mac16(w.w, xv.w, t, a1, a2, a3);
-}
-
 // Matrix and local strip of global strip number `strip` (by-value parameter arrays).
 __device__ __forceinline__ void locate(const GemvParams& p, int strip, int& m, int& ls) {
     m = 0;

@@ -88,6 +88,7 @@ struct SelectParams {
     int* log;            // [B][log_stride] or null
     const int* ctl;
     int B, forced_stride, log_stride;
+    unsigned* step_word;  // or null: the step number of the persistent decode kernel, advanced by this last kernel of the step
 };
 cudaError_t launch_select(const SelectParams& p, bool pdl, cudaStream_t st);
 

@@ -15,7 +15,7 @@
 // attention_k (cuda/ter_cuda_forward_packed.cu:64-90,118-157; NEOX variant
 // cuda/ter_cuda_forward_bitnet.cu:185-201), mm_fp16_lm_head_k and argmax_*_k
 // (cuda/ter_cuda_forward_packed.cu:165-259).
-#include "normq.cuh"
+#include "attn.cuh"
 
 namespace terb {
 
@@ -134,52 +134,19 @@ cudaError_t launch_rope_kv(const RopeKvParams& p, bool pdl, cudaStream_t st) {
 }
 
 // ============================================================ split-KV GQA attention
-// Chunked online softmax in a fixed order: the context is cut in chunks of 256 positions;
-// one CTA computes, for one (sequence, KV head, chunk) and every query head of the group,
-// the chunk maximum m, l = sum exp(s - m) (block order) and o[d] = sum_t exp(s_t - m) V[t][d]
-// (t ascending, fused multiply-adds).  A second kernel merges the chunks left to right.
-// Score of one position: 8 lanes each take 8 consecutive dims of every 64, fused
-// multiply-adds in ascending dim order, then an xor butterfly (4,2,1) over the 8 lanes.
+// One CTA per (chunk, KV head, row); the arithmetic lives in attn.cuh (shared with the persistent
+// decode kernel).  A second kernel merges the chunks left to right unless the caller gave arrival counters.
 namespace {
 
-constexpr int kMaxGroup = 8;   // query heads per KV head
-
-// Shared memory of attn_partial_kernel<HD>: K chunk, V chunk (bf16 [256][HD] each, filled by one
-// 1-D TMA bulk copy each), the group's query heads, the score / probability rows, barriers.
-// COMPACT: K and V take turns in ONE chunk buffer (V is fetched once the scores are done), which
-// halves the footprint so that two to five CTAs fit an SM: for large grids (token batches, prompt
-// tiles), where throughput counts; the two-buffer form keeps both copies in flight for a lone step.
-template <int HD, int G, bool COMPACT>
-struct AttnSmem {
-    static constexpr int kKOff = 0;
-    static constexpr int kVOff = COMPACT ? 0 : kAttnChunk * HD * 2;
-    static constexpr int kQOff = (COMPACT ? 1 : 2) * kAttnChunk * HD * 2;
-    static constexpr int kScOff = kQOff + G * HD * 4;
-    static constexpr int kRedOff = kScOff + G * kAttnChunk * 4;
-    static constexpr int kBarOff = kRedOff + 64;
-    static constexpr int kBytes = kBarOff + 16;
-};
-
-// When p.rope_table is set the kernel also does what rope_kv_kernel does, for its own data only:
-// it rotates the group's query heads on the fly (the q buffer is left untouched) and, in the CTA
-// whose chunk contains the new position, rotates k, rounds k and v to bf16, appends them to the
-// cache and uses them.  Otherwise q is taken as already rotated and the cache as already appended.
 template <int HD, int G, bool COMPACT>
 __global__ void __launch_bounds__(kT, COMPACT ? 3 : 1) attn_partial_kernel(const AttnParams p) {
     extern __shared__ __align__(128) uint8_t asmem[];
     using L = AttnSmem<HD, G, COMPACT>;
-    uint16_t* Ks = reinterpret_cast<uint16_t*>(asmem + L::kKOff);
-    uint16_t* Vs = reinterpret_cast<uint16_t*>(asmem + L::kVOff);
-    float* qs = reinterpret_cast<float*>(asmem + L::kQOff);
-    // scores, then probabilities: [head][position]; the throughput variant keeps [position][head] so that
-    // one vector load gives a position's probabilities for all heads of the group
-    float* scf = reinterpret_cast<float*>(asmem + L::kScOff);
-    auto SC = [&](int hh, int t) -> float& { return COMPACT ? scf[t * G + hh] : scf[hh * kAttnChunk + t]; };
-    float* red = reinterpret_cast<float*>(asmem + L::kRedOff);
     uint64_t* bars = reinterpret_cast<uint64_t*>(asmem + L::kBarOff);
     __shared__ float redg[kMaxGroup * 8];
+    __shared__ int is_last;
 
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x;
     if (tid == 0) {
         mbar_init(&bars[0], 1);
         mbar_init(&bars[1], 1);
@@ -209,258 +176,10 @@ __global__ void __launch_bounds__(kT, COMPACT ? 3 : 1) attn_partial_kernel(const
     pdl_launch_dependents();
     pdl_wait();
     __syncthreads();
-    const int pos = p.pos[b];
-    const int seq_len = pos + 1;
-    const int s0 = c * kAttnChunk;
-    if (s0 >= seq_len || seq_len > p.Smax || pos < 0) return;
-    const int cnt = min(kAttnChunk, seq_len - s0);
-    const bool fused = p.rope_table != nullptr;
-    const bool owner = fused && (pos >= s0) && (pos < s0 + kAttnChunk);   // this chunk holds the new row
-    const int n_copy = owner ? cnt - 1 : cnt;                             // rows already in the cache
-    const size_t head_off = ((size_t)bs * p.Nkv + g) * (size_t)p.Smax * HD;
-    const uint16_t* K = p.kcache + head_off;
-    const uint16_t* V = p.vcache + head_off;
-
-    if (tid == 0 && n_copy > 0) {
-        const uint32_t bytes = (uint32_t)n_copy * HD * 2u;
-        mbar_arrive_expect_tx(&bars[0], bytes);
-        bulk_g2s(Ks, K + (size_t)s0 * HD, bytes, &bars[0]);
-        if (!COMPACT) {
-            mbar_arrive_expect_tx(&bars[1], bytes);
-            bulk_g2s(Vs, V + (size_t)s0 * HD, bytes, &bars[1]);
-        }
-    }
-
-    // query heads of the group (rotated here when fused)
-    const float* q = p.q + ((size_t)b * p.Nh + (size_t)g * G) * HD;
-    if (fused) {
-        const float* row = p.rope_table + (size_t)pos * HD;
-        const int half = HD / 2;
-        for (int idx = tid; idx < G * half; idx += kT) {
-            const int hh = idx / half, kk = idx % half;
-            const int i0 = p.neox ? kk : 2 * kk, i1 = p.neox ? kk + half : 2 * kk + 1;
-            const float cs = row[2 * kk], sn = row[2 * kk + 1];
-            const float v0 = q[hh * HD + i0], v1 = q[hh * HD + i1];
-            const float a = v0 * cs, bb = v1 * sn;
-            const float d = v0 * sn, e = v1 * cs;
-            qs[hh * HD + i0] = a - bb;
-            qs[hh * HD + i1] = d + e;
-        }
-        if (owner) {
-            const float* kn = p.k_new + ((size_t)b * p.Nkv + g) * HD;
-            const float* vn = p.v_new + ((size_t)b * p.Nkv + g) * HD;
-            uint16_t* Kw = p.kcache_w + head_off + (size_t)pos * HD;
-            uint16_t* Vw = p.vcache_w + head_off + (size_t)pos * HD;
-            const int r = pos - s0;
-            for (int kk = tid; kk < half; kk += kT) {
-                const int i0 = p.neox ? kk : 2 * kk, i1 = p.neox ? kk + half : 2 * kk + 1;
-                const float cs = row[2 * kk], sn = row[2 * kk + 1];
-                const float v0 = kn[i0], v1 = kn[i1];
-                const float a = v0 * cs, bb = v1 * sn;
-                const float d = v0 * sn, e = v1 * cs;
-                const uint16_t k0 = f32_to_bf16_bits(a - bb), k1 = f32_to_bf16_bits(d + e);
-                Ks[r * HD + i0] = k0; Ks[r * HD + i1] = k1;
-                Kw[i0] = k0; Kw[i1] = k1;
-            }
-            for (int d = tid; d < HD; d += kT) {
-                const uint16_t vb = f32_to_bf16_bits(vn[d]);
-                if (!COMPACT) Vs[r * HD + d] = vb;     // COMPACT: the buffer still holds K; written after the scores
-                Vw[d] = vb;
-            }
-        }
-    } else {
-        for (int i = tid; i < G * HD; i += kT) qs[i] = q[i];
-    }
-    __syncthreads();
-    if (n_copy > 0) mbar_wait_bounded(&bars[0], 0, p.status);
-
-    const float inv_sqrt = 1.0f / sqrtf((float)HD);
-    const int sub = lane >> 3, j = lane & 7;
-#pragma unroll 2
-    for (int it = 0; it < 8; ++it) {
-        const int t = warp * 32 + it * 4 + sub;
-        const bool valid = t < cnt;
-        float kv[HD / 8];   // this lane's dims: 8 per 64-dim piece
-#pragma unroll
-        for (int pc = 0; pc < HD / 64; ++pc) {
-            uint4 raw = make_uint4(0, 0, 0, 0);
-            if (valid) raw = *reinterpret_cast<const uint4*>(Ks + t * HD + pc * 64 + 8 * j);
-            kv[pc * 8 + 0] = bf16_bits_to_f32(raw.x & 0xffffu);
-            kv[pc * 8 + 1] = bf16_bits_to_f32(raw.x >> 16);
-            kv[pc * 8 + 2] = bf16_bits_to_f32(raw.y & 0xffffu);
-            kv[pc * 8 + 3] = bf16_bits_to_f32(raw.y >> 16);
-            kv[pc * 8 + 4] = bf16_bits_to_f32(raw.z & 0xffffu);
-            kv[pc * 8 + 5] = bf16_bits_to_f32(raw.z >> 16);
-            kv[pc * 8 + 6] = bf16_bits_to_f32(raw.w & 0xffffu);
-            kv[pc * 8 + 7] = bf16_bits_to_f32(raw.w >> 16);
-        }
-#pragma unroll
-        for (int hh = 0; hh < G; ++hh) {
-            float acc = 0.0f;
-#pragma unroll
-            for (int pc = 0; pc < HD / 64; ++pc) {
-                const float4 qa = *reinterpret_cast<const float4*>(&qs[hh * HD + pc * 64 + 8 * j]);
-                const float4 qb = *reinterpret_cast<const float4*>(&qs[hh * HD + pc * 64 + 8 * j + 4]);
-                acc = fmaf(qa.x, kv[pc * 8 + 0], acc);
-                acc = fmaf(qa.y, kv[pc * 8 + 1], acc);
-                acc = fmaf(qa.z, kv[pc * 8 + 2], acc);
-                acc = fmaf(qa.w, kv[pc * 8 + 3], acc);
-                acc = fmaf(qb.x, kv[pc * 8 + 4], acc);
-                acc = fmaf(qb.y, kv[pc * 8 + 5], acc);
-                acc = fmaf(qb.z, kv[pc * 8 + 6], acc);
-                acc = fmaf(qb.w, kv[pc * 8 + 7], acc);
-            }
-            acc = acc + __shfl_xor_sync(0xffffffffu, acc, 4);
-            acc = acc + __shfl_xor_sync(0xffffffffu, acc, 2);
-            acc = acc + __shfl_xor_sync(0xffffffffu, acc, 1);
-            if (j == 0) SC(hh, t) = valid ? acc * inv_sqrt : -CUDART_INF_F;
-        }
-    }
-    __syncthreads();
-    if (COMPACT) {
-        // every score is computed: the chunk buffer now takes V (rows already in the cache by TMA, the
-        // new row, in the CTA that owns it, from the projection output)
-        if (tid == 0 && n_copy > 0) {
-            const uint32_t bytes = (uint32_t)n_copy * HD * 2u;
-            mbar_arrive_expect_tx(&bars[1], bytes);
-            bulk_g2s(Vs, V + (size_t)s0 * HD, bytes, &bars[1]);
-        }
-        if (owner) {
-            const float* vn = p.v_new + ((size_t)b * p.Nkv + g) * HD;
-            const int r = pos - s0;
-            for (int d = tid; d < HD; d += kT) Vs[r * HD + d] = f32_to_bf16_bits(vn[d]);
-        }
-    }
-
-    float* rec0 = p.scratch + (((size_t)b * p.Nh + (size_t)g * G) * p.max_chunks + c) * (HD + 2);
-    const size_t rec_stride = (size_t)p.max_chunks * (HD + 2);
-    // chunk maximum and sum of exponentials of every head of the group: same values, in the same
-    // order, as block_max / block_sum per head, with one barrier per reduction for all heads together
-    float sv[kMaxGroup], mv[kMaxGroup];
-#pragma unroll
-    for (int hh = 0; hh < kMaxGroup; ++hh) {
-        sv[hh] = -CUDART_INF_F;
-        if (hh < G) {
-            sv[hh] = SC(hh, tid);
-            const float w = warp_max(sv[hh]);
-            if (lane == 0) redg[hh * 8 + warp] = w;
-        }
-    }
-    __syncthreads();
-#pragma unroll
-    for (int hh = 0; hh < kMaxGroup; ++hh) {
-        mv[hh] = 0.0f;
-        if (hh < G) {
-            float t = redg[hh * 8];
-#pragma unroll
-            for (int w = 1; w < kT / 32; ++w) t = fmaxf(t, redg[hh * 8 + w]);
-            mv[hh] = t;
-        }
-    }
-    __syncthreads();
-#pragma unroll
-    for (int hh = 0; hh < kMaxGroup; ++hh) {
-        if (hh < G) {
-            const float pt = tid < cnt ? exp_fixed(sv[hh] - mv[hh]) : 0.0f;
-            SC(hh, tid) = pt;
-            const float w = warp_sum_butterfly(pt);
-            if (lane == 0) redg[hh * 8 + warp] = w;
-        }
-    }
-    __syncthreads();
-#pragma unroll
-    for (int hh = 0; hh < kMaxGroup; ++hh) {
-        if (tid == hh && hh < G) {
-            float t = redg[hh * 8];
-#pragma unroll
-            for (int w = 1; w < kT / 32; ++w) t = t + redg[hh * 8 + w];
-            rec0[hh * rec_stride + 0] = mv[hh];
-            rec0[hh * rec_stride + 1] = t;
-        }
-    }
-    if (n_copy > 0) mbar_wait_bounded(&bars[1], 0, p.status);
-
-    // o[hh][d] = sum_t p[t][hh] * V[t][d], ascending t
-    if constexpr (COMPACT) {
-        // throughput form: one thread per dim d keeps the G heads' accumulators; per position one vector
-        // load of the G probabilities and one load of V[t][d] feed G multiply-adds
-        if (tid < HD) {
-            const int d = tid;
-            float acc[G];
-#pragma unroll
-            for (int hh = 0; hh < G; ++hh) acc[hh] = 0.0f;
-            const uint16_t* vp = Vs + d;
-#pragma unroll 4
-            for (int t = 0; t < cnt; ++t) {
-                const float v = bf16_bits_to_f32(vp[t * HD]);
-                float pr[G];
-                if constexpr (G == 4) {
-                    const float4 q4 = *reinterpret_cast<const float4*>(scf + t * 4);
-                    pr[0] = q4.x; pr[1] = q4.y; pr[2] = q4.z; pr[3] = q4.w;
-                } else if constexpr (G == 8) {
-                    const float4 q4 = *reinterpret_cast<const float4*>(scf + t * 8);
-                    const float4 q5 = *reinterpret_cast<const float4*>(scf + t * 8 + 4);
-                    pr[0] = q4.x; pr[1] = q4.y; pr[2] = q4.z; pr[3] = q4.w;
-                    pr[4] = q5.x; pr[5] = q5.y; pr[6] = q5.z; pr[7] = q5.w;
-                } else if constexpr (G == 2) {
-                    const float2 q2 = *reinterpret_cast<const float2*>(scf + t * 2);
-                    pr[0] = q2.x; pr[1] = q2.y;
-                } else {
-#pragma unroll
-                    for (int hh = 0; hh < G; ++hh) pr[hh] = scf[t * G + hh];
-                }
-#pragma unroll
-                for (int hh = 0; hh < G; ++hh) acc[hh] = fmaf(pr[hh], v, acc[hh]);
-            }
-#pragma unroll
-            for (int hh = 0; hh < G; ++hh) rec0[hh * rec_stride + 2 + d] = acc[hh];
-        }
-    } else {
-        // latency form: one thread per (head, dim)
-        for (int idx = tid; idx < G * HD; idx += kT) {
-            const int hh = idx / HD, d = idx % HD;
-            const float* pr = scf + hh * kAttnChunk;
-            const uint16_t* vp = Vs + d;
-            float acc = 0.0f;
-#pragma unroll 8
-            for (int t = 0; t < cnt; ++t) acc = fmaf(pr[t], bf16_bits_to_f32(vp[t * HD]), acc);
-            rec0[hh * rec_stride + 2 + d] = acc;
-        }
-    }
-
-    // Merge of the chunks by the last CTA of this (sequence, KV head) to finish, when the caller gave
-    // arrival counters; the order of the merge is fixed (chunk 0, 1, 2, ...) whoever performs it.
-    if (p.counters) {
-        __shared__ int is_last;
-        const int nc = (seq_len + kAttnChunk - 1) / kAttnChunk;
-        __threadfence();
-        __syncthreads();
-        if (tid == 0) {
-            int* cnt_p = p.counters + (size_t)b * p.Nkv + g;
-            const int old = atomicAdd(cnt_p, 1);
-            is_last = (old == nc - 1);
-            if (is_last) *cnt_p = 0;          // ready for the next step
-        }
-        __syncthreads();
-        if (is_last) {
-            __threadfence();
-            for (int idx = tid; idx < G * HD; idx += kT) {
-                const int hh = idx / HD, d = idx % HD;
-                const float* rec = p.scratch + ((size_t)b * p.Nh + (size_t)g * G + hh) * rec_stride;
-                float M = __ldcg(rec), Lsum = __ldcg(rec + 1), O = __ldcg(rec + 2 + d);
-                for (int cc = 1; cc < nc; ++cc) {
-                    const float* r = rec + (size_t)cc * (HD + 2);
-                    const float mc = __ldcg(r), lc = __ldcg(r + 1), oc = __ldcg(r + 2 + d);
-                    const float Mn = fmaxf(M, mc);
-                    const float a = exp_fixed(M - Mn), bb = exp_fixed(mc - Mn);
-                    Lsum = fmaf(lc, bb, Lsum * a);
-                    O = fmaf(oc, bb, O * a);
-                    M = Mn;
-                }
-                p.out[((size_t)b * p.Nh + (size_t)g * G + hh) * HD + d] = O / Lsum;
-            }
-        }
-    }
+    const AttnItem it = attn_item<HD>(p, c, g, b, p.pos[b]);
+    if (!it.active) return;
+    if (tid == 0) attn_issue_kv<HD, G, COMPACT>(p, it, asmem);
+    attn_compute<HD, G, COMPACT, 0>(p, it, asmem, redg, &is_last, 0);
 }
 
 template <int HD>
@@ -741,6 +460,7 @@ __global__ void select_kernel(const SelectParams p) {
     pdl_launch_dependents();
     pdl_wait();
     const int b = threadIdx.x;
+    if (b == 0 && p.step_word) *p.step_word += 1u;
     if (b >= p.B) return;
     const int ps = p.pos[b];
     int nxt = p.greedy[b];

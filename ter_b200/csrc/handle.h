@@ -81,6 +81,10 @@ struct ter_b200_handle_t {
     int prefill;                // 1: ter_b200_generate runs the prompt of a single sequence as token batches
     int tp_shard;               // bit 0: attention block column-sharded, bit 1: FFN block; the lm_head always is
     int tp_p2p;                 // 1: tensor-parallel exchanges over peer memory (exchange_sm100.cu); 0: NCCL all-gathers
+    int decode_persistent;      // 1: a lone sequence on one GPU runs embedding + all layers of a step in one persistent kernel
+    int decode_poll_ns;         // persistent decode kernel: pause between polls of a value that has not arrived
+    int decode_fault_cta;       // test hook (-1: off): see DecodeParams::fault_cta
+    int wait_ms;                // limit of a device-side wait on another CTA or rank (milliseconds)
     int attn_inline_merge;      // 1: the last attention CTA of a KV head merges the chunks (no second kernel)
     cudaGraphExec_t graphs[16];
     uint64_t graph_launches[16];   // kernels recorded in each graph

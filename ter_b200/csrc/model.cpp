@@ -5,10 +5,14 @@
 #include <new>
 #include <stdlib.h>
 
+#include "decode.h"
 #include "glue.h"
 #include "handle.h"
 
 using namespace terb;
+#ifdef TERB_TRACE
+unsigned long long* g_terb_trace = nullptr;
+#endif
 
 struct TerbModel {
     ter_b200_model_cfg_t c;
@@ -45,6 +49,10 @@ struct TerbModel {
     int32_t* xrs;                    // [rows_cap] row sums of the quantised activations (for the GEMM)
     cudaEvent_t ev_mid;
     float last_prefill_ms, last_prompt_ms;
+    // persistent decode kernel (decode_sm100.cu): per-layer constants in device memory, its barrier word
+    DecodeLayerDev* dec_layers;
+    uint4* dec_state;        // tagged activation vectors + attention records (decode_state_layout), then 4 control words
+    bool dec_dirty;
 };
 
 constexpr int kPrefillTile = 1024;   // prompt positions per pass (four 256-token tiles of the GEMM)
@@ -174,8 +182,35 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
     };
 #define XCHG1(buf, n, sharded) do { float* b__[1] = {(buf)}; int n__[1] = {(n)}; int rc__ = exchange(b__, n__, 1, (sharded)); if (rc__) return rc__; } while (0)
 
+    // One sequence on one GPU: embedding and all layers in ONE cooperative launch (decode_sm100.cu).
+    const bool persist = !pre && B == 1 && G == 1 && h->decode_persistent && m->dec_layers && !m->dec_dirty &&
+                         decode_layers_supported(c.H, c.F, c.Nh, c.Nkv, c.Hd, c.L);
+    if (persist) {
+        DecodeParams dp;
+        memset(&dp, 0, sizeof dp);
+        const DecodeStateLayout sl = decode_state_layout(c.H, c.F, c.Nh, c.Nkv, c.Hd, c.Smax);
+        dp.layers = m->dec_layers; dp.embd = m->embd; dp.tokens = m->tokens; dp.pos = m->pos;
+        dp.hidden = m->hidden;
+        dp.hid_t = m->dec_state + sl.hid; dp.q_t = m->dec_state + sl.q; dp.k_t = m->dec_state + sl.k;
+        dp.v_t = m->dec_state + sl.v; dp.att_t = m->dec_state + sl.att; dp.gate_t = m->dec_state + sl.gate;
+        dp.rec_t = m->dec_state + sl.rec;
+        dp.ctl = reinterpret_cast<unsigned*>(m->dec_state + sl.total);
+        dp.rope = m->rope; dp.status = h->status_dev;
+        dp.L = c.L; dp.H = H; dp.F = F; dp.Nh = c.Nh; dp.Nkv = c.Nkv; dp.Hd = c.Hd; dp.Smax = c.Smax; dp.V = c.V;
+        dp.bitnet = bitnet ? 1 : 0; dp.eps = c.eps;
+        dp.wait_ns = (unsigned long long)h->wait_ms * 1000000ull;
+        dp.fault_cta = h->decode_fault_cta;
+        dp.poll_sleep_ns = h->decode_poll_ns;
+#ifdef TERB_TRACE
+        dp.trace = g_terb_trace;
+#endif
+        CK(launch_decode_layers(dp, h->sm_count, st));
+        for (int L = 0; L < c.L; ++L)
+            for (int w = 0; w < 7; ++w) count_gemv(h, m->mats[(size_t)L * 7 + w].K, m->mats[(size_t)L * 7 + w].N, 1);
+    } else {
     CK(launch_embed(m->embd, tokv, m->hidden, H, B, c.V, pdl, st));
-    for (int L = 0; L < c.L; ++L) {
+    }
+    for (int L = 0; L < c.L && !persist; ++L) {
         const DevWeight* W = m->mats + (size_t)L * 7;
         float** vec = m->vecs + (size_t)L * 4;
         // ---- attention block
@@ -287,7 +322,9 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
     h->launches += 1;
     if (pre) return TER_B200_OK;
     SelectParams sp{m->greedy, use_forced ? m->forced : nullptr, m->tokens, m->pos, use_forced ? m->log : nullptr,
-                    m->ctl, B, m->forced_cap, m->log_cap};
+                    m->ctl, B, m->forced_cap, m->log_cap,
+                    persist ? reinterpret_cast<unsigned*>(m->dec_state + decode_state_layout(c.H, c.F, c.Nh, c.Nkv, c.Hd, c.Smax).total)
+                            : nullptr};
     CK(launch_select(sp, pdl, st));
     return TER_B200_OK;
 }
@@ -306,8 +343,50 @@ bool model_complete(const TerbModel* m) {
     return true;
 }
 
+// Writes the per-layer constants of the persistent decode kernel to device memory (synchronous: not for
+// use while a stream is capturing) and clears its barrier word.
+int prepare_decode(ter_b200_handle_t* h, TerbModel* m) {
+#ifdef TERB_TRACE
+    if (!g_terb_trace) { cudaMalloc((void**)&g_terb_trace, 148 * 32 * 8); cudaMemset(g_terb_trace, 0, 148 * 32 * 8); }
+#endif
+    if (!m->dec_dirty && m->dec_layers) return TER_B200_OK;
+    const ter_b200_model_cfg_t& c = m->c;
+    if (!m->dec_layers) TERB_CUDA(h, dalloc(&m->dec_layers, (size_t)c.L));
+    const size_t state_words = decode_state_layout(c.H, c.F, c.Nh, c.Nkv, c.Hd, c.Smax).total + 1;
+    if (!m->dec_state) {
+        TERB_CUDA(h, dalloc(&m->dec_state, state_words));
+        TERB_CUDA(h, cudaMemset(m->dec_state, 0, state_words * sizeof(uint4)));
+    }
+    DecodeLayerDev* host = new (std::nothrow) DecodeLayerDev[(size_t)c.L];
+    if (!host) return TER_B200_E_ALLOC;
+    const size_t layer_cache = (size_t)c.max_batch * c.Nkv * (size_t)c.Smax * c.Hd;
+    for (int L = 0; L < c.L; ++L) {
+        memset(&host[L], 0, sizeof host[L]);
+        for (int w = 0; w < 7; ++w) {
+            host[L].W[w] = m->mats[(size_t)L * 7 + w].data;
+            host[L].ws[w] = m->mats[(size_t)L * 7 + w].scale;
+        }
+        for (int v = 0; v < 4; ++v) host[L].gamma[v] = m->vecs[(size_t)L * 4 + v];
+        host[L].kcache = m->kcache + L * layer_cache;
+        host[L].vcache = m->vcache + L * layer_cache;
+    }
+    TERB_CUDA(h, cudaDeviceSynchronize());
+    cudaError_t e = cudaMemcpy(m->dec_layers, host, (size_t)c.L * sizeof(DecodeLayerDev), cudaMemcpyHostToDevice);
+    delete[] host;
+    if (e != cudaSuccess) return cuda_fail(h, e);
+    m->dec_dirty = false;
+    return TER_B200_OK;
+}
+
 }  // namespace
 
+#ifdef TERB_TRACE
+extern "C" int ter_b200_debug_trace(unsigned long long* host) {
+    if (!g_terb_trace) return -1;
+    cudaDeviceSynchronize();
+    return (int)cudaMemcpy(host, g_terb_trace, 148 * 32 * 8, cudaMemcpyDeviceToHost);
+}
+#endif
 namespace terb {
 // A tuning knob changed: the captured decode step no longer matches the settings.
 void model_invalidate_graph(ter_b200_handle_t* h) {
@@ -340,7 +419,8 @@ void ter_b200_model_free(ter_b200_handle_t* h) {
     if (m->embd && m->embd_owned) cudaFree(m->embd);
     void* bufs[] = {m->out_norm, m->hidden, m->q, m->k, m->v, m->att, m->gate, m->up, m->xnorm, m->logits,
                     m->attn_scratch, m->argmax_scratch, m->xs, m->xq, m->kcache, m->vcache, m->tokens, m->pos,
-                    m->greedy, m->forced, m->log, m->ctl, m->attn_counters, m->tok_rows, m->pos_rows, m->xrs};
+                    m->greedy, m->forced, m->log, m->ctl, m->attn_counters, m->tok_rows, m->pos_rows, m->xrs,
+                    m->dec_layers, m->dec_state};
     for (void* b : bufs)
         if (b) cudaFree(b);
     if (m->ev0) cudaEventDestroy(m->ev0);
@@ -376,6 +456,7 @@ int ter_b200_model_create(ter_b200_handle_t* h, const ter_b200_model_cfg_t* cfg)
     if (!m) return TER_B200_E_ALLOC;
     m->c = c;
     m->batch = 1;
+    m->dec_dirty = true;
     m->shard_attn = (h->tp_shard & 1) != 0;
     m->shard_ffn = (h->tp_shard & 2) != 0;
     h->model = m;
@@ -498,6 +579,7 @@ static int set_matrix_common(ter_b200_handle_t* h, int layer, int which, const v
     if (rc) return rc;
     free_weight(dst);
     *dst = w;
+    m->dec_dirty = true;
     return TER_B200_OK;
 }
 
@@ -524,6 +606,7 @@ int ter_b200_model_set_vector(ter_b200_handle_t* h, int layer, int which, const 
         n = vec_len(m->c, which);
     }
     drop_graph(m);
+    m->dec_dirty = true;
     if (!*slot) TERB_CUDA(h, dalloc(slot, (size_t)n));
     TERB_CUDA(h, cudaMemcpy(*slot, v, (size_t)n * sizeof(float), cudaMemcpyHostToDevice));
     return TER_B200_OK;
@@ -579,6 +662,7 @@ int ter_b200_decode_step(ter_b200_handle_t* h, const int32_t* tokens_host, const
     TERB_CUDA(h, cudaSetDevice(h->device));
     cudaStream_t st = pick_stream(h, stream);
     const int B = m->batch;
+    { int rc0 = prepare_decode(h, m); if (rc0) return rc0; }
     if (pos_host)
         for (int b = 0; b < B; ++b)
             if (pos_host[b] < 0 || pos_host[b] >= m->c.Smax) return TER_B200_E_SHAPE;
@@ -627,6 +711,7 @@ int ter_b200_generate(ter_b200_handle_t* h, const int32_t* prompts, int batch, i
     const int steps = n_prompt + n_gen - 1;
     int rc = ter_b200_model_reset(h, batch);
     if (rc) return rc;
+    if ((rc = prepare_decode(h, m))) return rc;
     if (m->forced_cap < n_prompt || m->log_cap < steps) {
         drop_graph(m);
         if (m->forced) cudaFree(m->forced);
@@ -710,7 +795,7 @@ int ter_b200_generate(ter_b200_handle_t* h, const int32_t* prompts, int batch, i
         // bookkeeping of the last prompt position: log the first generated token, pos = n_prompt
         const int last = n_prompt - 1;
         TERB_CUDA(h, cudaMemcpyAsync(m->pos, &last, sizeof(int), cudaMemcpyHostToDevice, st));
-        SelectParams sp{m->greedy, m->forced, m->tokens, m->pos, m->log, m->ctl, 1, m->forced_cap, m->log_cap};
+        SelectParams sp{m->greedy, m->forced, m->tokens, m->pos, m->log, m->ctl, 1, m->forced_cap, m->log_cap, nullptr};
         cudaError_t ce = launch_select(sp, h->gemv_cfg.pdl != 0, st);
         if (ce != cudaSuccess) return cuda_fail(h, ce);
         h->launches += 1;
@@ -733,7 +818,11 @@ int ter_b200_generate(ter_b200_handle_t* h, const int32_t* prompts, int batch, i
                                 n_gen * sizeof(int), cudaMemcpyDeviceToHost));
     int dst = 0;
     TERB_CUDA(h, cudaMemcpy(&dst, h->status_dev, sizeof(int), cudaMemcpyDeviceToHost));
-    if (dst != 0) { cudaMemset(h->status_dev, 0, sizeof(int)); return TER_B200_E_TIMEOUT; }
+    if (dst != 0) {
+        cudaMemset(h->status_dev, 0, sizeof(int));
+        cudaMemset(m->attn_counters, 0, (size_t)m->rows_cap * m->c.Nkv * sizeof(int));
+        return TER_B200_E_TIMEOUT;
+    }
     return TER_B200_OK;
 }
 

@@ -8,6 +8,7 @@
 
 #include "common.cuh"
 #include "glue.h"
+#include "tagged.cuh"
 
 namespace terb {
 namespace {
@@ -209,21 +210,51 @@ __device__ __forceinline__ void norm_quant_prefetch_gamma(const NormQuantParams&
 // Same arithmetic, in the same order, as block_norm_quant, for rows of at most 8192 elements with
 // 16-byte aligned pointers: the row lives in registers, x / up / gamma are fetched with one batch of
 // independent 16-byte loads, and each reduction costs one barrier.  red16: 16 floats of shared memory.
-__device__ __forceinline__ float block_norm_quant_fast(const NormQuantParams& p, int row, float* red16,
-                                                       int8_t* q_out, float* normed_out) {
-    constexpr int R = kNqFastMax / (4 * kT);
+// ts (optional): the row comes from a flag-in-data vector instead of p.x (persistent decode kernel: the
+// values are polled until the producing CTAs have stored them); p.u must then be null.
+// R: float4 slots per thread compiled in (the row has at most 1024*R elements).
+template <int R>
+__device__ __forceinline__ float block_norm_quant_fast_r(const NormQuantParams& p, int row, float* red16,
+                                                         int8_t* q_out, float* normed_out, const TaggedSrc* ts) {
     const int tid = threadIdx.x, n = p.n;
     const size_t off = (size_t)row * (size_t)n;
     const float4* x4 = reinterpret_cast<const float4*>(p.x + off);
     const float4* u4 = p.u ? reinterpret_cast<const float4*>(p.u + off) : nullptr;
     const float4* g4 = reinterpret_cast<const float4*>(p.gamma);
     float4 v[R], g[R];
+    if (ts) {
+        // all of this thread's words are requested first and validated afterwards: one round trip when the
+        // producers are done, instead of one per word; only a word that is not there yet is polled
+        uint4 w[2 * R];
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-        const int idx = tid + kT * r;
-        const bool valid = 4 * idx < n;
-        v[r] = valid ? x4[idx] : make_float4(0.f, 0.f, 0.f, 0.f);
-        g[r] = (valid && g4) ? g4[idx] : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int r = 0; r < R; ++r) {
+            const int idx = tid + kT * r;
+            if (4 * idx < n) {
+                w[2 * r] = ld_volatile16(ts->words + 2 * idx);
+                w[2 * r + 1] = ld_volatile16(ts->words + 2 * idx + 1);
+            }
+            g[r] = (4 * idx < n && g4) ? g4[idx] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const int idx = tid + kT * r;
+            v[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (4 * idx < n) {
+                if (w[2 * r].y != ts->seq || w[2 * r].w != ts->seq) w[2 * r] = poll_tagged(ts->words + 2 * idx, ts->seq, ts->ctx);
+                if (w[2 * r + 1].y != ts->seq || w[2 * r + 1].w != ts->seq)
+                    w[2 * r + 1] = poll_tagged(ts->words + 2 * idx + 1, ts->seq, ts->ctx);
+                v[r] = make_float4(__uint_as_float(w[2 * r].x), __uint_as_float(w[2 * r].z), __uint_as_float(w[2 * r + 1].x),
+                                   __uint_as_float(w[2 * r + 1].z));
+            }
+        }
+    } else {
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const int idx = tid + kT * r;
+            const bool valid = 4 * idx < n;
+            v[r] = valid ? x4[idx] : make_float4(0.f, 0.f, 0.f, 0.f);
+            g[r] = (valid && g4) ? g4[idx] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
     }
     if (u4) {
 #pragma unroll
@@ -286,6 +317,14 @@ __device__ __forceinline__ float block_norm_quant_fast(const NormQuantParams& p,
             }
     }
     return stored;
+}
+
+// Dispatch on the row length, so that a short row does not pay for the slots of a long one.
+__device__ __forceinline__ float block_norm_quant_fast(const NormQuantParams& p, int row, float* red16,
+                                                       int8_t* q_out, float* normed_out,
+                                                       const TaggedSrc* ts = nullptr) {
+    if (p.n <= 3072) return block_norm_quant_fast_r<3>(p, row, red16, q_out, normed_out, ts);
+    return block_norm_quant_fast_r<kNqFastMax / (4 * kT)>(p, row, red16, q_out, normed_out, ts);
 }
 
 }  // namespace

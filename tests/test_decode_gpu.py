@@ -50,6 +50,54 @@ def test_step_by_step_logits_and_tokens(tb, cfg, seed, n_prompt, n_gen):
     assert tb.device_status() == 0
 
 
+@pytest.mark.parametrize("cfg,seed,n_prompt", [(SMALL_LLAMA, 51, 300), (SMALL_BITNET, 52, 280)])
+def test_persistent_kernel_and_launch_chain_agree(tb, cfg, seed, n_prompt):
+    """One sequence runs embedding + all layers of a step in ONE persistent kernel (option
+    "decode_persistent", default 1); the chain of per-stage launches must give the same bits, and the
+    persistent step must be the shorter launch sequence."""
+    modelutil.build_gpu(tb, cfg, seed)
+    prompt = np.random.default_rng(seed).integers(0, cfg["V"], size=n_prompt).astype(np.int32)
+    res = []
+    try:
+        for persistent in (1, 0):
+            tb.set_option("decode_persistent", persistent)
+            l0 = tb.launch_count()
+            out = tb.generate(prompt, 12)
+            res.append((out[0].copy(), tb.model_logits()[0].copy(), tb.launch_count() - l0))
+    finally:
+        tb.set_option("decode_persistent", 1)
+    assert res[0][0].tolist() == res[1][0].tolist()
+    assert np.array_equal(res[0][1].view(np.uint32), res[1][1].view(np.uint32))
+    assert res[0][2] < res[1][2]
+    assert tb.device_status() == 0
+
+
+def test_bounded_wait_runs_out_and_the_context_survives(tb):
+    """Inside the persistent kernel a CTA waits for values that other CTAs publish.  With the test hook
+    "decode_fault_cta" one CTA keeps its q/k/v columns of layer 0 to itself, so its consumers' waits run out
+    after "wait_ms": the kernel must return by itself, the call must report TER_B200_E_TIMEOUT, and the next
+    call on the same handle must work and give the right tokens.  Nothing faults or hangs."""
+    from ter_b200 import TerB200Error
+    cfg, seed = SMALL_LLAMA, 61
+    modelutil.build_gpu(tb, cfg, seed)
+    om = modelutil.build_oracle(cfg, seed)
+    prompt = np.random.default_rng(seed).integers(0, cfg["V"], size=5).astype(np.int32)
+    want, _ = modelutil.oracle_generate(om, prompt, 6)
+    assert tb.generate(prompt, 6)[0].tolist() == want.tolist()
+    try:
+        tb.set_option("wait_ms", 20)
+        tb.set_option("decode_fault_cta", 147)       # owns the last strip of v in this model
+        with pytest.raises(TerB200Error) as e:
+            tb.generate(prompt, 6)
+        assert e.value.code == api.E_TIMEOUT
+    finally:
+        tb.set_option("decode_fault_cta", -1)
+        tb.set_option("wait_ms", 2000)
+    assert tb.device_status() == 0                   # the status word was cleared by the failed call
+    assert tb.generate(prompt, 6)[0].tolist() == want.tolist()
+    assert tb.device_status() == 0
+
+
 def test_batch_sequences_are_independent(tb):
     cfg, seed = SMALL_LLAMA, 21
     modelutil.build_gpu(tb, cfg, seed, max_batch=3)
