@@ -158,6 +158,7 @@ def per_shape_bench(tb, dev, peak, reps=20):
         sweep_gbs = R * nbytes / (ms_sweep * 1e-3) / 1e9
         rows.append({"model": model, "proj": nm, "K": K, "N": N, "copies": R,
                      "sweep_gbs": round(sweep_gbs, 1), "sweep_frac": round(sweep_gbs / peak, 3),
+                     "sweep_frac_of_8tbs_nominal": round(sweep_gbs / 8000.0, 3),
                      "per_launch_gbs": round(R * nbytes / (ms_single * 1e-3) / 1e9, 1),
                      "per_launch_us": round(ms_single * 1e3 / R, 2)})
         tb.gemv_plan_destroy(plan)
@@ -218,26 +219,35 @@ def reference_gpu_gemv():
 
 
 def gemm_bench(tb, dev):
-    """Batched ternary GEMM (tcgen05 kind::i8) on the BitNet-2B projection shapes at M = 16, 64, 256, 1024
-    tokens: microseconds per call (CUDA events around a graph of 20 calls; includes the row-sum pre-kernel
-    and the split-K finalize kernel) and int8 TOPS = 2*M*K*N / time.  The 1-4 MB weight matrix stays in L2."""
+    """Batched ternary GEMM (tcgen05 kind::i8) on the BitNet-2B projection shapes at M = 16, 64, 256, 1024 tokens:
+    microseconds per call (CUDA events around graph replays; every launch of a call included) and int8 TOPS =
+    2*M*K*N / time.  At M <= 64 the call is bound by the weight bytes, so it is measured over R distinct copies of
+    the matrix (at least 256 MB in total, twice the L2) touched once each per pass, and the weight GB/s is
+    reported; at M >= 256 one matrix (1-4 MB, L2-resident: the tensor-pipe regime) is called 20 times."""
     import torch
     from ter_b200 import FMT_V11, synth
     rows = []
     cur = torch.cuda.current_stream()
     for nm in ("q", "k", "gate", "down"):
         K, N = synth.BITNET_2B_SHAPES[nm]
-        tb.install("gm", synth.packed_v11_cuda(K, N, synth.seed_for("gemm", K, N), dev), FMT_V11, K, N, 0.02)
+        nbytes = K * N // 4
+        R = max(2, min(256, -(-(256 << 20) // nbytes)))
+        w = synth.packed_v11_cuda(K, N, synth.seed_for("gemm", K, N), dev)
+        names = [f"gm{i}" for i in range(R)]
+        for n_ in names:
+            tb.install(n_, w, FMT_V11, K, N, 0.02)
+        del w
         for M in (16, 64, 256, 1024):
             g = torch.Generator(device=dev)
             g.manual_seed(M)
             X = torch.randint(-127, 128, (M, K), dtype=torch.int8, device=dev, generator=g)
             xs = torch.rand(M, device=dev, generator=g) * 0.05 + 0.001
             out = torch.empty((M, N), device=dev)
+            use = names if M <= 64 else names[:1] * 20
             for _ in range(3):
-                tb.gemm("gm", X, xs, out)
+                tb.gemm(use[0], X, xs, out)
             torch.cuda.synchronize()
-            gid = tb.capture(lambda: [tb.gemm("gm", X, xs, out) for _ in range(20)])
+            gid = tb.capture(lambda: [tb.gemm(n_, X, xs, out) for n_ in use])
             tb.graph_launch(gid, stream=cur)
             torch.cuda.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -246,34 +256,58 @@ def gemm_bench(tb, dev):
                 tb.graph_launch(gid, stream=cur)
             e1.record()
             torch.cuda.synchronize()
-            us = e0.elapsed_time(e1) / 60 * 1e3
+            us = e0.elapsed_time(e1) / (3 * len(use)) * 1e3
             tb.graph_destroy(gid)
-            rows.append({"proj": nm, "K": K, "N": N, "M": M, "us": round(us, 2), "tops": round(2 * M * K * N / us / 1e6, 1)})
-        tb.remove("gm")
+            row = {"proj": nm, "K": K, "N": N, "M": M, "us": round(us, 2), "tops": round(2 * M * K * N / us / 1e6, 1),
+                   "weights": f"{len(use)} distinct copies" if M <= 64 else "one matrix, L2-resident"}
+            if M <= 64:
+                row["weight_gbs"] = round(nbytes / us / 1e3, 1)
+            rows.append(row)
+        for n_ in names:
+            tb.remove(n_)
     return rows
 
 
 def cpu_reference_run(steps: int, warmup: int, threads: int):
-    """Times the reference's CPU GEMV (mm_row, src/tx/forward.cpp:299-352) on the host cores:
-    the unmodified reference when oracle/_ref was built, else the C restatement."""
+    """Times the reference's CPU GEMV (mm_row, src/tx/forward.cpp:299-352) on the host cores over the SAME
+    workload as the GPU arm: one step = one M=1 pass over all 113 matrices of the Llama-3.2-1B fabric (int32
+    payloads, as ter::TritTensor holds them).  The reference is single-threaded; the matrices of a pass are
+    dealt to `threads` threads (largest first, the lm_head cut into per-thread column blocks), every thread
+    calling the unmodified mm_row (oracle/_ref) or, where that was not built, the C restatement."""
     import threading
     import oracle
     from ter_b200 import synth
-    shapes = [synth.LLAMA_1B_SHAPES[n] for n in LAYER_MATS]          # one layer's seven projections
     kind = "reference" if oracle.Ref.available() else "port"
+    units = []                                   # (K, N) pieces of one pass
+    for _, K, N, _, nm in fabric_spec(16):
+        if nm == "lm_head":
+            step = -(-N // threads)
+            units += [(K, min(step, N - c0)) for c0 in range(0, N, step)]
+        else:
+            units.append((K, N))
+    units.sort(key=lambda kn: -kn[0] * kn[1])
+    load = [0] * threads
+    mine = [[] for _ in range(threads)]
+    for K, N in units:
+        t = load.index(min(load))
+        mine[t].append((K, N))
+        load[t] += K * N
     ctxs = []
+    rng = np.random.default_rng(7)
     for t in range(threads):
         ref = oracle.Ref() if kind == "reference" else None
         items = []
-        for (K, N) in shapes:
-            W = synth.trits(K, N, synth.seed_for("cpu", K, N)).astype(np.int32)
+        for (K, N) in mine[t]:
+            W = (rng.integers(0, 10, size=(K, N), dtype=np.int8))
+            W = ((W >= 7).astype(np.int32) - (W < 3).astype(np.int32))      # P(-1)=0.3, P(0)=0.4, P(+1)=0.3
             x, xs = synth.activation(K, 5)
             if ref:
                 items.append((ref.tensor(x.astype(np.int32), float(xs), 1, K), ref.tensor(W, 0.03, K, N), K, N))
             else:
                 items.append((x.astype(np.int32), W, K, N))
+            del W
         ctxs.append((ref, items))
-    bytes_step = sum(K * N // 4 for K, N in shapes) * threads
+    bytes_step = sum(K * N // 4 for K, N in units)
 
     def one_pass(ctx):
         ref, items = ctx
@@ -297,13 +331,59 @@ def cpu_reference_run(steps: int, warmup: int, threads: int):
         step()
     dt = time.perf_counter() - t0
     return {"value": bytes_step * steps / dt / 1e9, "unit": UNIT, "cores": threads, "kind": kind,
-            "sample": f"one Llama-1B layer's 7 projections per thread per step (int32 payload mm_row), "
-                      f"{threads} threads x {steps} steps, {dt:.1f} s; GB/s counted on packed bytes K*N/4",
+            "sample": f"the whole fabric pass (113 matrices, {bytes_step / 1e6:.1f} MB packed; int32 payload mm_row) dealt to "
+                      f"{threads} threads, {steps} steps, {dt:.1f} s; GB/s counted on packed bytes K*N/4",
             "ms_per_step": dt / steps * 1e3}
 
 
+def cpu_forward_baseline(n_tokens=3):
+    """The reference's CPU decode forward (ter::tx::forward_token, src/tx/transformer.cpp:116-223, unmodified, from
+    oracle/_ref) on a synthetic model of the Llama-3.2-1B architecture (BASELINE configs[3]): seconds per token on
+    ONE core (the reference is single-threaded), a few tokens at positions >= 27."""
+    import oracle
+    from ter_b200 import synth
+    if not oracle.Ref.available():
+        return {"error": "oracle/_ref/libter_ref.so not built"}
+    try:
+        ref = oracle.Ref()
+        t0 = time.perf_counter()
+        s_tok, toks = ref.forward_token_seconds(dict(synth.LLAMA_1B_CFG, Smax=64), n_tokens=n_tokens, first_pos=27)
+        return {"s_per_token": s_tok, "tokens_per_s": 1.0 / s_tok, "tokens": n_tokens, "cores": 1,
+                "host_cores": os.cpu_count(), "kind": "reference",
+                "workload": "llama-3.2-1b architecture (16 layers, H 2048, FFN 8192, vocab 128256), random ternary int32 "
+                            "payloads, 9-trit tied embedding, batch 1, positions 27.." + str(27 + n_tokens - 1),
+                "wall_s_with_model_fill": time.perf_counter() - t0}
+    except Exception as e:  # noqa: BLE001
+        return {"error": str(e)}
+
+
+def oracle_tokens(cfg, host_items, prompt, n_tokens):
+    """Greedy tokens of the CPU checker (oracle.Model, all host threads) for one sequence: the prompt is fed one
+    position at a time, then n_tokens are generated.  host_items: the model's tensors as numpy arrays."""
+    import oracle
+    om = oracle.Model(cfg)
+    for item in host_items:
+        if item[0] == "embd":
+            om.set_embd(item[1])
+        elif item[0] == "vector":
+            om.set_vector(item[1], item[2], item[3])
+        else:
+            om.set_matrix(item[1], item[2], item[3], float(item[4]))
+    st = om.new_state(1)
+    tok, toks = int(prompt[0]), []
+    for pos in range(len(prompt) + n_tokens - 1):
+        nxt, _, _ = om.forward(st, 0, tok, pos, want_logits=False)
+        if pos + 1 < len(prompt):
+            tok = int(prompt[pos + 1])
+        else:
+            tok = nxt
+            toks.append(int(nxt))
+    om.close()
+    return toks
+
+
 def decode_bench(tb, dev, rank, which="llama", n_prompt=128, n_gen=256, batch=1, smax=512, warm=True,
-                 lm_head_packed=False):
+                 lm_head_packed=False, check=None):
     """Random-init ternarised decode of one of the two benchmark architectures (tied bf16 lm_head, bf16 KV
     cache): Llama-3.2-1B (16 layers, H 2048, 32/8 heads x 64, FFN 8192 SiLU) or BitNet-b1.58-2B (30 layers,
     H 2560, 20/5 heads x 128, FFN 6912 squared-ReLU with sub-norms), vocab 128256.  n_prompt random prompt
@@ -314,6 +394,7 @@ def decode_bench(tb, dev, rank, which="llama", n_prompt=128, n_gen=256, batch=1,
     base = synth.LLAMA_1B_CFG if which == "llama" else synth.BITNET_2B_CFG
     cfg = dict(base, Smax=smax, lm_head_packed=1 if lm_head_packed else 0)
     tb.model_create(cfg, max_batch=batch)
+    host = [] if check else None          # the same tensors for the CPU checker (check = (prompt length, tokens))
     if lm_head_packed:   # the reference's bench mode: random packed-trit lm_head instead of the tied table
         seed = synth.seed_for(rank, "dec", which, "lm_head")
         tb.model_set_matrix(-1, 0, synth.packed_v11_cuda(cfg["H"], cfg["V"], seed, dev), FMT_V11, float(synth.weight_scale(seed)))
@@ -321,27 +402,41 @@ def decode_bench(tb, dev, rank, which="llama", n_prompt=128, n_gen=256, batch=1,
     g.manual_seed(synth.seed_for(rank, "embd") & 0x7FFFFFFF)
     emb = (torch.randn((cfg["V"], cfg["H"]), generator=g, device=dev) * 0.02).to(torch.bfloat16)
     tb.model_set_embd(emb.view(torch.int16))
+    if host is not None:
+        host.append(("embd", emb.view(torch.int16).cpu().numpy().view(np.uint16)))
     del emb
     rng = np.random.default_rng(synth.seed_for(rank, "vec"))
-    tb.model_set_vector(-1, 0, rng.normal(1.0, 0.02, cfg["H"]).astype(np.float32))
+    v = rng.normal(1.0, 0.02, cfg["H"]).astype(np.float32)
+    tb.model_set_vector(-1, 0, v)
+    if host is not None:
+        host.append(("vector", -1, 0, v))
     shapes = synth.model_shapes(cfg)
     for L in range(cfg["L"]):
         for wi, nm in enumerate(synth.MAT_ORDER):
             K, N = shapes[nm]
             seed = synth.seed_for(rank, "dec", which, L, nm)
-            tb.model_set_matrix(L, wi, synth.packed_v11_cuda(K, N, seed, dev), FMT_V11, float(synth.weight_scale(seed)))
+            w = synth.packed_v11_cuda(K, N, seed, dev)
+            tb.model_set_matrix(L, wi, w, FMT_V11, float(synth.weight_scale(seed)))
+            if host is not None:
+                host.append(("matrix", L, wi, w.cpu().numpy(), float(synth.weight_scale(seed))))
+            del w
         for vi in range(4 if cfg["arch"] == 1 else 2):
-            n = cfg["F"] if vi == 3 else cfg["H"]
-            tb.model_set_vector(L, vi, rng.normal(1.0, 0.02, n).astype(np.float32))
+            n = cfg["F"] if vi == 3 else (cfg["Nh"] * cfg["Hd"] if vi == 2 else cfg["H"])
+            v = rng.normal(1.0, 0.02, n).astype(np.float32)
+            tb.model_set_vector(L, vi, v)
+            if host is not None:
+                host.append(("vector", L, vi, v))
     prompt = np.random.default_rng(synth.seed_for(rank, "prompt", which)).integers(
         0, cfg["V"], size=(batch, n_prompt)).astype(np.int32)
     if batch == 1:
         prompt = prompt[0]
     if warm:
         tb.generate(prompt, n_gen)             # captures the graph, warms up
+    l0 = tb.launch_count()
     t0 = time.perf_counter()
     out = tb.generate(prompt, n_gen)           # host tokens in, host tokens out
     wall = time.perf_counter() - t0
+    launches = tb.launch_count() - l0
     ms = tb.last_generate_ms()
     prompt_ms = tb.last_prompt_ms()
     batched_prompt = tb.last_prefill_ms() > 0.0
@@ -355,7 +450,18 @@ def decode_bench(tb, dev, rank, which="llama", n_prompt=128, n_gen=256, batch=1,
     step_bytes = shapes_bytes + (cfg["V"] * cfg["H"] // 4 if lm_head_packed else 2 * cfg["V"] * cfg["H"]) + kv_bytes
     peak, _ = peaks()
     name = "llama-3.2-1b" if which == "llama" else "bitnet-b1.58-2b"
-    return {"workload": f"{name} architecture decode, batch {batch}, prompt {n_prompt} + {n_gen} greedy tokens, random-init"
+    parity = None
+    if check:
+        # outside every timed region: greedy tokens against the CPU checker on the same weights (rank 0 computes)
+        cp, cn = check
+        t0 = time.perf_counter()
+        pr = prompt if batch == 1 else prompt[0]
+        got = [int(t) for t in (out[0][:cn] if cp == n_prompt else tb.generate(pr[:cp], cn)[0])]
+        want = oracle_tokens(cfg, host, pr[:cp], cn) if rank == 0 else None
+        parity = {"prompt": cp, "tokens": cn, "got": got, "want": want, "seconds": round(time.perf_counter() - t0, 1),
+                  "checker": "oracle.Model (CPU restatement, all host threads), prompt fed one position at a time",
+                  "ok": (got == want) if want is not None else None}
+    res = {"workload": f"{name} architecture decode, batch {batch}, prompt {n_prompt} + {n_gen} greedy tokens, random-init"
                         + (", packed-trit lm_head" if lm_head_packed else ""),
             "tokens_per_s": batch * gen_steps / gen_ms * 1e3, "ms_per_step": gen_ms / gen_steps,
             "ms_per_token": gen_ms / gen_steps / batch, "steps": gen_steps, "batch": batch,
@@ -368,6 +474,18 @@ def decode_bench(tb, dev, rank, which="llama", n_prompt=128, n_gen=256, batch=1,
             "note": "tokens_per_s = generated tokens per second of device time (CUDA events) over the generation steps, "
                     "at contexts n_prompt .. n_prompt + n_gen; e2e = generated tokens / wall clock of the whole generate() "
                     "call (prompt included)" + ("" if warm else "; single call, includes the graph's first replays")}
+    if parity is not None:
+        res["parity"] = parity
+    res["launches_in_call"] = int(launches)
+    return res
+
+
+def workload_config(layers=16):
+    """The `config` of both arms (this library and --impl reference): the same workload, named the same way."""
+    nbytes = packed_bytes(fabric_spec(layers))
+    return {"workload": f"llama-3.2-1b GEMV fabric sweep: {layers} layers x 7 projections + packed lm_head, M=1, "
+                        f"{nbytes / 1e6:.1f} MB packed trits per GPU per step",
+            "l2": "inputs larger than L2 (309 MB vs 126 MB), same order every step"}
 
 
 def run_reference_arm(args):
@@ -375,12 +493,11 @@ def run_reference_arm(args):
     if rank != 0:
         return
     threads = os.cpu_count() or 1
-    steps = max(1, min(args.steps, 40))
-    r = cpu_reference_run(steps, max(1, min(args.warmup, 2)), threads)
+    r = cpu_reference_run(args.steps, args.warmup, threads)
     line = {"impl": "reference", "metric": METRIC, "value": r["value"], "unit": UNIT, "n_gpus": args.gpus,
-            "steps": steps, "warmup": max(1, min(args.warmup, 2)), "ms_per_step": r["ms_per_step"],
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int32 x int32 -> int64",
-            "data": "synthetic", "config": {"workload": "llama-3.2-1b GEMV fabric sweep (bounded CPU sample)"},
+            "data": "synthetic", "config": workload_config(),
             "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
             "e2e": {"value": r["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
@@ -400,9 +517,11 @@ def main():
     ap.add_argument("--no-bitnet", action="store_true", help="skip the BitNet-2B decode runs")
     ap.add_argument("--no-reference-gpu", action="store_true", help="skip the reference's CUDA programs on this GPU")
     ap.add_argument("--no-batch64", action="store_true", help="skip the batch-64 BitNet decode run (about 30 s)")
+    ap.add_argument("--no-parity", action="store_true", help="skip the decode token checks against the CPU checker")
+    ap.add_argument("--cold-batch64", action="store_true", help="time the batch-64 run without a warm-up call")
     ap.add_argument("--layers", type=int, default=16, help="layers of the fabric (profiling captures use fewer)")
     args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    args.warmup = max(args.warmup, 3)
 
     if args.impl == "reference":
         run_reference_arm(args)
@@ -567,7 +686,24 @@ def main():
             tb.set_option("tp_p2p", int(os.environ.get("TER_TP_P2P", "1")))   # 0: NCCL all-gathers, for comparison
             if "TER_TP_SHARD" in os.environ:                                  # else the library's default policy
                 tb.set_option("tp_shard", int(os.environ["TER_TP_SHARD"]))
+        failures = []
+
         def tp_fix(d):
+            # parity first: every rank must hold rank 0's tokens, and rank 0's must be the CPU checker's
+            if d.get("parity") is not None:
+                par = d["parity"]
+                if world > 1:
+                    mine = torch.tensor(par["got"], dtype=torch.int64, device=dev)
+                    ref = mine.clone()
+                    dist.broadcast(ref, 0)
+                    same = torch.tensor([1 if torch.equal(mine, ref) else 0], device=dev)
+                    dist.all_reduce(same, op=dist.ReduceOp.MIN)
+                    par["all_ranks_equal"] = bool(int(same.item()))
+                    flag = torch.tensor([1 if (par["ok"] in (True, None)) else 0], device=dev)
+                    dist.broadcast(flag, 0)
+                    par["ok"] = bool(int(flag.item())) and par["all_ranks_equal"]
+                if not par["ok"]:
+                    failures.append(d["workload"])
             if world > 1:
                 t = torch.tensor([d["ms_per_step"]], device=dev)
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -579,20 +715,24 @@ def main():
                 d["sharded_blocks"] = os.environ.get("TER_TP_SHARD", "library default")
                 d["exchange"] = "peer-memory kernel" if os.environ.get("TER_TP_P2P", "1") != "0" else "nccl all-gather"
             return d
-        decode = tp_fix(decode_bench(tb, dev, 0))  # the same model on every rank; the library keeps its slice
+        # the same model on every rank; the library keeps its slice.  Checked: the first 16 greedy tokens of the
+        # full-depth run against the CPU checker (whole 128-token prompt)
+        decode = tp_fix(decode_bench(tb, dev, 0, check=None if args.no_parity else (128, 16)))
         if not args.no_bitnet:
             # BitNet-2B architecture, context 2048 + 128 greedy tokens; batch 1 (tensor
             # parallel at N > 1) and, on one GPU, batch 64 (token batch through the tensor-core GEMM)
-            decode_bitnet = [tp_fix(decode_bench(tb, dev, 0, "bitnet", n_prompt=2048, n_gen=128, smax=2176))]
+            # checked against the CPU checker at a SHORTENED prompt (48 positions + 8 tokens, all 30 layers): the
+            # checker needs about half a second per position, the 2048-position prompt would take a quarter hour
+            decode_bitnet = [tp_fix(decode_bench(tb, dev, 0, "bitnet", n_prompt=2048, n_gen=128, smax=2176,
+                                                 check=None if args.no_parity else (48, 8)))]
             if not args.no_batch64 and 64 % world == 0:
                 # 64 sequences: on one GPU a token batch through the tensor-core GEMM; on N GPUs every rank
                 # owns 64/N whole sequences and their KV cache with a full copy of the weights (no collective:
                 # sequences are independent), through a second handle that has no communicator
                 per_rank = 64 // world
                 tb2 = tb if world == 1 else TerB200(local)
-                if per_rank < 16:
-                    tb2.set_option("gemm_min_m", 2)      # small token batches still go through the GEMM
-                d = decode_bench(tb2, dev, rank, "bitnet", n_prompt=2048, n_gen=128, batch=per_rank, smax=2176, warm=False)
+                d = decode_bench(tb2, dev, rank, "bitnet", n_prompt=2048, n_gen=128, batch=per_rank, smax=2176,
+                                 warm=not args.cold_batch64)
                 if world > 1:
                     t = torch.tensor([d["ms_per_step"], d["prompt_ms"]], device=dev)
                     dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -614,8 +754,9 @@ def main():
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         try:
-            r = cpu_reference_run(steps=12, warmup=1, threads=os.cpu_count() or 1)
+            r = cpu_reference_run(steps=6, warmup=1, threads=os.cpu_count() or 1)
             cpu = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")}
+            cpu["forward_token"] = cpu_forward_baseline()
         except Exception as e:  # noqa: BLE001
             cpu = {"value": None, "unit": UNIT, "cores": 0, "kind": "port", "sample": f"failed: {e}"}
 
@@ -624,12 +765,10 @@ def main():
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "int8 x trit -> int32", "data": "synthetic",
-            "config": {"workload": f"llama-3.2-1b GEMV fabric sweep: {args.layers} layers x 7 projections + packed "
-                                   f"lm_head, M=1, {step_bytes / 1e6:.1f} MB packed trits per GPU per step",
-                       "l2": "inputs larger than L2 (309 MB vs 126 MB), same order every step",
-                       "launches_per_step": launches // args.steps,
-                       "timed": "one sweep-plan launch per step (ter_b200_gemv_plan_launch): the 113 independent GEMVs are "
-                                "rows of a device descriptor table and one persistent grid streams all of them"},
+            "config": workload_config(args.layers),
+            "timed": {"launches_per_step": launches // args.steps,
+                      "how": "one sweep-plan launch per step (ter_b200_gemv_plan_launch): the 113 independent GEMVs are "
+                             "rows of a device descriptor table and one persistent grid streams all of them"},
             "per_matrix_launches": {"value": total_bytes * args.steps / (ms_par * 1e-3) / 1e9, "unit": UNIT,
                                     "ms_per_step": ms_par / args.steps, "launches_per_step": launches_par // args.steps,
                                     "note": "same pass as 65 launches (q+k+v and gate+up grouped) replayed from a CUDA "
@@ -654,6 +793,14 @@ def main():
                     "note": "ter_b200_gemv_host_batch: pinned host x in, one launch, fp32 outputs back to one pinned "
                             "host buffer; synchronous call",
                     "d2h_bytes_per_step": sum(4 * N for _, _, N, _, _ in mats) * world},
+            "decode_scaling": None if decode is None else {
+                "n_gpus": world,
+                "llama_1b_batch1_tokens_per_s": decode["tokens_per_s"],
+                "bitnet_2b_batch1_tokens_per_s": decode_bitnet[0]["tokens_per_s"] if decode_bitnet else None,
+                "bitnet_2b_batch64_tokens_per_s": decode_bitnet[1]["tokens_per_s"] if decode_bitnet and len(decode_bitnet) > 1 else None,
+                "tokens_checked": None if args.no_parity else "first tokens equal on every rank and equal to the CPU checker's",
+                "note": "strong scaling of one model over the GPUs of this run (batch 1: tensor parallel; batch 64: whole "
+                        "sequences per GPU); compare the same keys across the N = 1, 2, 4, 8 runs"},
             "decode": decode,
             "decode_bitnet": decode_bitnet,
             "reference_gpu": reference_gpu,
@@ -664,6 +811,9 @@ def main():
     tb.close()
     if world > 1:
         dist.destroy_process_group()
+    if not args.no_decode and failures:
+        sys.stderr.write("decode tokens differ from the CPU checker: " + "; ".join(failures) + "\n")
+        sys.exit(3)
 
 
 if __name__ == "__main__":

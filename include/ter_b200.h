@@ -127,6 +127,23 @@ typedef struct {
 } ter_b200_op_counts_t;
 void ter_b200_op_counts(const ter_b200_handle_t* h, ter_b200_op_counts_t* out);
 void ter_b200_reset_counters(ter_b200_handle_t* h);
+/* The report of dump_op_stats (include/ter/tx/op_stats.hpp:86-127) for this handle's counters, written into
+ * `buf` (at most buf_len bytes, always terminated): total kernel ops, TVMAC and lane-MACs (TVMAC*27), the
+ * analytical fp16 MACs of `n_forwards` forwards of the architecture (Q+K+V+O+gate+up+down per layer + lm_head)
+ * and their ratio.  Counters this path never bumps print as 0.  Returns the length the full report needs. */
+int ter_b200_dump_op_stats(const ter_b200_handle_t* h, const char* label, int hidden_size, int intermediate_size,
+                           int n_heads, int n_kv_heads, int head_dim, int n_layers, int vocab_size, int n_forwards,
+                           char* buf, size_t buf_len);
+/* Which kernel serves a product of M activation rows with a K x N weight on this handle: the ONE dispatch rule
+ * of the library (the reference's pick_kernel(K, N), cuda/ter_cuda_hybrid_dispatch_v13.cu:120-126, extended by
+ * the row count).  Returns one of TER_B200_KERNEL_*; ter_b200_kernel_name gives its name. */
+#define TER_B200_KERNEL_GEMV_SPLIT   0   /* M = 1, few strips: register-prefetch split-K GEMV (decode projections) */
+#define TER_B200_KERNEL_GEMV_STREAM  1   /* M = 1, many strips: persistent TMA-ring GEMV (lm_head, sweeps) */
+#define TER_B200_KERNEL_GEMV_ROWS    2   /* 2 <= M <= 16: multi-row GEMV, the weights stream once */
+#define TER_B200_KERNEL_GEMM_TCGEN05 3   /* M >= "gemm_min_m": tcgen05 kind::i8 GEMM, TMEM accumulators */
+#define TER_B200_KERNEL_GEMV_PER_ROW 4   /* otherwise: one GEMV launch per row */
+int ter_b200_pick_kernel(const ter_b200_handle_t* h, int M, int K, int N);
+const char* ter_b200_kernel_name(int kernel);
 
 /* ---- packed-trit GEMV, M = 1 ------------------------------------------------
  * Replaces mm_packed_dispatch / mm_packed_v4 (cuda/ter_cuda_forward_packed.cu:346-397,
@@ -302,6 +319,12 @@ int ter_b200_model_set_embd_dev(ter_b200_handle_t* h, const uint16_t* table_dev)
 int ter_b200_model_load_file(ter_b200_handle_t* h, const char* path, int smax, int max_batch,
                              ter_b200_model_cfg_t* cfg_out);
 int ter_b200_model_file_info(const char* path, ter_b200_model_cfg_t* cfg_out);
+/* microsoft/BitNet GGUF "i2_s" tensor (N output rows x K inputs, 128-element blocks of 32 bytes, the scale in
+ * the 32 bytes after the codes) -> TER_B200_FMT_V11 bytes [N/4][K] and the per-tensor scale: the conversion of
+ * tools/convert_bitnet_to_packed.py:85-152 (read_i2s_scale, i2s_to_col_packed; decode as in
+ * vendor/ntransformer/core/dequant.cpp:114-145).  i2s_bytes: bytes available at `i2s` (codes + trailer).
+ * Host memory only: needs no handle and no GPU.  scale_out may be NULL. */
+int ter_b200_convert_i2s(const void* i2s, size_t i2s_bytes, int N, int K, uint8_t* v11_out, float* scale_out);
 int ter_b200_model_reset(ter_b200_handle_t* h, int batch);
 /* One decode step for every sequence: forward_token (cuda/ter_cuda_forward_packed.cu:671-678).
  * tokens_host / pos_host ([batch], may be NULL: continue from the device-resident state, i.e. the
@@ -365,6 +388,11 @@ int ter_b200_graph_destroy(ter_b200_handle_t* h, int graph_id);
  * Kernels never spin without a bound; a wait that ran out records a code that this call
  * returns (TER_B200_E_TIMEOUT) after synchronising the handle's streams. */
 int ter_b200_device_status(ter_b200_handle_t* h);
+/* Self-test of the bounded waits (no counterpart in the reference): runs the tensor-parallel exchange kernel
+ * on this one GPU against a stand-in peer that never sends.  The wait runs out after option "wait_ms", the
+ * kernel returns, and the next ter_b200_device_status reports TER_B200_E_TIMEOUT once.  Returns 0 when the
+ * kernel came back by itself. */
+int ter_b200_selftest_exchange_timeout(ter_b200_handle_t* h);
 /* Last CUDA error code seen by the handle (cudaError_t as int), 0 if none. */
 int ter_b200_last_cuda_error(const ter_b200_handle_t* h);
 /* Tuning knobs (integers): "gemv_ctas_per_sm", "gemv_stages", "gemv_split_max_strips", "pdl",

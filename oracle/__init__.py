@@ -256,6 +256,21 @@ def attention(q, kc, vc, n_heads, n_kv, head_dim, smax, seq_len, twopass=False):
     return out
 
 
+def i2s_decode(raw, n_elems: int):
+    """Restatement of the microsoft/BitNet i2_s decode (vendor/ntransformer/core/dequant.cpp:114-145,
+    tools/convert_bitnet_to_packed.py:95-143): blocks of 128 elements in 32 bytes, byte p holds block positions
+    p, p+32, p+64, p+96 with position p in the HIGH two bits; codes 0 -> -1, 1 -> 0, 2 -> +1, 3 -> 0; the fp32
+    after the codes is the scale.  Returns (trits int8 [n_elems], scale)."""
+    raw = np.ascontiguousarray(raw, dtype=np.uint8)
+    blocks = raw[:n_elems // 4].reshape(-1, 32)
+    lut = np.array([-1, 0, 1, 0], dtype=np.int8)
+    out = np.empty((blocks.shape[0], 4, 32), dtype=np.int8)
+    for g in range(4):
+        out[:, g, :] = lut[(blocks >> (6 - 2 * g)) & 3]
+    scale = float(raw[n_elems // 4:n_elems // 4 + 4].view(np.float32)[0])
+    return out.reshape(-1), scale
+
+
 def lm_head_bf16(embd, x):
     embd = np.ascontiguousarray(embd, dtype=np.uint16)
     x = np.ascontiguousarray(x, dtype=np.float32)
@@ -371,6 +386,15 @@ class Ref:
     @staticmethod
     def available() -> bool:
         return os.path.exists(REF_SO)
+
+    def dequant_i2s(self, raw: np.ndarray, n_elems: int) -> np.ndarray:
+        """nt::dequant_i2_s of the reference (vendor/ntransformer/core/dequant.cpp:114-145): raw = code bytes +
+        32-byte trailer; returns n_elems floats (scale * {-1, 0, +1})."""
+        raw = np.ascontiguousarray(raw, dtype=np.uint8)
+        out = np.empty(n_elems, dtype=np.float32)
+        self.L.ref_dequant_i2s.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p]
+        self.L.ref_dequant_i2s(raw.ctypes.data, n_elems, out.ctypes.data)
+        return out
 
     def forward_token_seconds(self, cfg: dict, n_tokens: int = 3, first_pos: int = 27, seed: int = 1):
         """Times the reference's CPU decode forward (ter::tx::forward_token, src/tx/transformer.cpp:116-223)

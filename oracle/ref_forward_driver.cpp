@@ -12,12 +12,15 @@
 // simulator's bytecode kernels (src/tx/forward.cpp:469-470), which need kernel blobs and tables from disk;
 // the timed tokens therefore sit at positions >= 27 (the cache below is zero: same arithmetic, same cost).
 //
-// Exports: ref_tx_create / ref_tx_destroy / ref_tx_forward_tokens.
+// Exports: ref_tx_create / ref_tx_destroy / ref_tx_forward_tokens, and ref_dequant_i2s = nt::dequant_i2_s
+// (vendor/ntransformer/core/dequant.cpp:114-145), the reference's decode of microsoft/BitNet "i2_s" tensors.
 #include <ter/kernels.hpp>
 #include <ter/numfmt.hpp>
 #include <ter/sim.hpp>
 #include <ter/tx/forward.hpp>
 #include <ter/tx/transformer.hpp>
+
+#include <core/dequant.hpp>
 
 #include <chrono>
 #include <cstdint>
@@ -131,5 +134,8 @@ double ref_tx_forward_tokens(void* c, int first_token, int first_pos, int n_toke
     }
     return total;
 }
+
+// src: n_elems/4 code bytes followed by the 32-byte trailer whose first fp32 is the scale.
+void ref_dequant_i2s(const void* src, size_t n_elems, float* out) { nt::dequant_i2_s(src, n_elems, out); }
 
 }  // extern "C"

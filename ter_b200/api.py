@@ -100,6 +100,10 @@ SIGNATURES = {
     "ter_b200_model_set_embd_dev": (_I, [_VP, _VP]),
     "ter_b200_model_load_file": (_I, [_VP, _CP, _I, _I, C.POINTER(ModelCfg)]),
     "ter_b200_model_file_info": (_I, [_CP, C.POINTER(ModelCfg)]),
+    "ter_b200_convert_i2s": (_I, [_VP, _SZ, _I, _I, _VP, _VP]),
+    "ter_b200_dump_op_stats": (_I, [_VP, _CP, _I, _I, _I, _I, _I, _I, _I, _I, _VP, _SZ]),
+    "ter_b200_pick_kernel": (_I, [_VP, _I, _I, _I]),
+    "ter_b200_kernel_name": (_CP, [_I]),
     "ter_b200_model_reset": (_I, [_VP, _I]),
     "ter_b200_decode_step": (_I, [_VP, _VP, _VP, _VP, _VP]),
     "ter_b200_model_logits": (_I, [_VP, _VP]),
@@ -118,6 +122,7 @@ SIGNATURES = {
     "ter_b200_graph_launch": (_I, [_VP, _I, _VP]),
     "ter_b200_graph_destroy": (_I, [_VP, _I]),
     "ter_b200_device_status": (_I, [_VP]),
+    "ter_b200_selftest_exchange_timeout": (_I, [_VP]),
     "ter_b200_last_cuda_error": (_I, [_VP]),
     "ter_b200_set_option": (_I, [_VP, _CP, _I]),
     "ter_b200_launch_count": (_U64, [_VP]),
@@ -166,6 +171,18 @@ def _stream_ptr(stream=None):
     if stream is None:
         stream = torch.cuda.current_stream()
     return C.c_void_p(stream.cuda_stream or _CUDA_STREAM_LEGACY)
+
+
+def convert_i2s(raw, N: int, K: int):
+    """microsoft/BitNet i2_s tensor bytes (codes + 32-byte trailer) -> (v11 bytes [N/4][K], scale).  Host only."""
+    import numpy as np
+    raw = np.ascontiguousarray(raw, dtype=np.uint8)
+    out = np.empty((N // 4, K), dtype=np.uint8)
+    scale = C.c_float(0.0)
+    rc = load().ter_b200_convert_i2s(raw.ctypes.data, raw.size, N, K, out.ctypes.data, C.byref(scale))
+    if rc != 0:
+        raise TerB200Error(rc, "convert_i2s")
+    return out, float(scale.value)
 
 
 class TerB200:
@@ -584,6 +601,22 @@ class TerB200:
 
     def device_status(self) -> int:
         return self.L.ter_b200_device_status(self.h)
+
+    def pick_kernel(self, M: int, K: int, N: int) -> str:
+        """Name of the kernel the library's dispatch rule picks for M rows against a K x N weight."""
+        k = self.L.ter_b200_pick_kernel(self.h, M, K, N)
+        if k < 0:
+            raise TerB200Error(k, "pick_kernel")
+        return self.L.ter_b200_kernel_name(k).decode()
+
+    def op_stats_report(self, label: str, cfg: dict, n_forwards: int) -> str:
+        buf = C.create_string_buffer(4096)
+        self.L.ter_b200_dump_op_stats(self.h, label.encode(), cfg["H"], cfg["F"], cfg["Nh"], cfg["Nkv"], cfg["Hd"],
+                                      cfg["L"], cfg["V"], n_forwards, buf, len(buf))
+        return buf.value.decode()
+
+    def selftest_exchange_timeout(self):
+        self._ck(self.L.ter_b200_selftest_exchange_timeout(self.h), "selftest_exchange_timeout")
 
     def set_option(self, key: str, value: int):
         self._ck(self.L.ter_b200_set_option(self.h, key.encode(), int(value)), f"set_option {key}")

@@ -15,6 +15,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 ROOT = os.path.dirname(PKG)
 LIB = os.path.join(PKG, "libter_b200.so")
+CLI = os.path.join(PKG, "ter_b200_generate")      # command-line front end (csrc/cli/generate_main.cpp)
 OBJ_DIR = os.path.join(PKG, "build")
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
@@ -56,7 +57,10 @@ def needs_build() -> bool:
     if not os.path.exists(LIB):
         return True
     t = os.path.getmtime(LIB)
+    if not os.path.exists(CLI):
+        return True
     deps = sources() + glob.glob(os.path.join(CSRC, "*.h")) + glob.glob(os.path.join(CSRC, "*.cuh")) + \
+        glob.glob(os.path.join(CSRC, "cli", "*.cpp")) + \
         [os.path.join(ROOT, "include", "ter_b200.h"), os.path.abspath(__file__)]
     return any(os.path.getmtime(d) > t for d in deps)
 
@@ -91,6 +95,10 @@ def build(force: bool = False, verbose: bool = False) -> str:
     # NCCL is resolved at run time from the process (torch loads it) or the system library.
     link = [nvcc, "-shared", "-o", LIB] + objs + ARCH + ["-Xcompiler", "-fPIC", "-lcudart_static", "-ldl", "-lpthread"]
     subprocess.run(link, check=True)
+    # the command-line front end: plain C++ over the C ABI, finds the library next to itself
+    subprocess.run([os.environ.get("CXX", "g++"), "-O2", "-std=c++17", "-I", os.path.join(ROOT, "include"),
+                    os.path.join(CSRC, "cli", "generate_main.cpp"), "-o", CLI, "-L", PKG, "-lter_b200",
+                    "-Wl,-rpath,$ORIGIN"], check=True)
     return LIB
 
 

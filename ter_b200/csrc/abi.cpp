@@ -154,6 +154,8 @@ int run_gemv(ter_b200_handle_t* h, const DevWeight* const* ws, int n, const int8
     p.act_out = act_out;
     GemvLaunchCfg cfg = h->gemv_cfg;
     cfg.sm_count = h->sm_count;
+    // the dispatch rule decides; the launcher is told which of its two M = 1 kernels to use
+    cfg.split_max_strips = pick_kernel(h, 1, p.K, tiles) == TER_B200_KERNEL_GEMV_SPLIT ? tiles : 0;
     TERB_CUDA(h, launch_gemv(p, cfg, st));
     h->launches += 1;
     for (int i = 0; i < n; ++i) count_gemv(h, ws[i]->K, ws[i]->N, 1);
@@ -194,7 +196,7 @@ ter_b200_handle_t* ter_b200_create(int device) {
     if (!h) return nullptr;
     h->device = device;
     h->gemv_cfg = GemvLaunchCfg();
-    h->gemm_min_m = 4;
+    h->gemm_min_m = 17;     // up to 16 token rows take the multi-row GEMV
     h->attn_inline_merge = 1;
     h->decode_persistent = 1;
     h->decode_fault_cta = -1;
@@ -487,6 +489,53 @@ int ter_b200_device_status(ter_b200_handle_t* h) {
 }
 
 int ter_b200_last_cuda_error(const ter_b200_handle_t* h) { return h ? h->last_cuda : 0; }
+
+int ter_b200_pick_kernel(const ter_b200_handle_t* h, int M, int K, int N) {
+    if (!h) return TER_B200_E_NULL;
+    if (M < 1 || K < 1 || N < 1) return TER_B200_E_SHAPE;
+    return pick_kernel(h, M, K, (N + 15) / 16);
+}
+const char* ter_b200_kernel_name(int kernel) {
+    switch (kernel) {
+        case TER_B200_KERNEL_GEMV_SPLIT: return "gemv_trit_split_kernel";
+        case TER_B200_KERNEL_GEMV_STREAM: return "gemv_trit_kernel";
+        case TER_B200_KERNEL_GEMV_ROWS: return "gemv_trit_rows_kernel";
+        case TER_B200_KERNEL_GEMM_TCGEN05: return "gemm_trit_kernel";
+        case TER_B200_KERNEL_GEMV_PER_ROW: return "gemv per row";
+        default: return "?";
+    }
+}
+
+int ter_b200_dump_op_stats(const ter_b200_handle_t* h, const char* label, int hidden_size, int intermediate_size,
+                           int n_heads, int n_kv_heads, int head_dim, int n_layers, int vocab_size, int n_forwards,
+                           char* buf, size_t buf_len) {
+    if (!h || !buf || buf_len == 0) return TER_B200_E_NULL;
+    // analytical_fp16_macs_per_forward (include/ter/tx/op_stats.hpp:66-84)
+    const uint64_t H = (uint64_t)hidden_size, F = (uint64_t)intermediate_size;
+    const uint64_t HQ = (uint64_t)n_heads * (uint64_t)head_dim, HKV = (uint64_t)n_kv_heads * (uint64_t)head_dim;
+    const uint64_t per_fwd = (H * HQ + 2 * H * HKV + HQ * H + 2 * H * F + F * H) * (uint64_t)n_layers + H * (uint64_t)vocab_size;
+    const uint64_t total = per_fwd * (uint64_t)(n_forwards < 0 ? 0 : n_forwards);
+    const uint64_t lane_macs = h->counts.tvmac * 27ull;
+    const double ratio = total == 0 ? 0.0 : (double)lane_macs / (double)total;
+    const int n = snprintf(buf, buf_len,
+        "\n=== op-stats: %s (n_forwards=%d) ===\n"
+        "  total kernel ops : %llu\n"
+        "  TVMAC            : %llu  (lane-MACs: %llu = TVMAC*27)\n"
+        "  TVADD/TVSUB/TVMUL: %llu / %llu / %llu\n"
+        "  TVSUM/TVBCAST    : 0 / 0\n"
+        "  TVLOAD/TVSTORE   : 0 / 0\n"
+        "  TLOAD/TSTORE     : 0 / 0\n"
+        "  TADD/TSUB/TCMP   : 0 / 0 / 0\n"
+        "  TJUMP/TCALL/Tbr  : 0 / 0 / 0\n"
+        "  -- analytical baseline --\n"
+        "  fp16 MACs/forward: %llu  (Q+K+V+O+gate+up+down per layer, +lm_head)\n"
+        "  fp16 MACs total  : %llu  (per-fwd x n_forwards)\n"
+        "  lane-MAC : fp16  : %.3f x  (>1 means ternary substrate does more MACs)\n",
+        label ? label : "", n_forwards, (unsigned long long)h->counts.total_ops, (unsigned long long)h->counts.tvmac,
+        (unsigned long long)lane_macs, (unsigned long long)h->counts.tvadd, (unsigned long long)h->counts.tvsub,
+        (unsigned long long)h->counts.tvmul, (unsigned long long)per_fwd, (unsigned long long)total, ratio);
+    return n;
+}
 
 int ter_b200_set_option(ter_b200_handle_t* h, const char* key, int value) {
     if (!h || !key) return TER_B200_E_NULL;

@@ -7,13 +7,17 @@
 // {v0, seq, v1, seq} and stores it straight into every peer's receive area; a receiver polls each
 // word until both halves carry the expected number and copies the floats into its full-size buffer.
 // Each 8-byte half validates itself, so no fence, no separate flag and no second round trip is
-// needed: one NVLink crossing per exchange.  Sequence numbers only grow (one per execution of an
+// needed: one NVLink crossing per exchange.  A point owns TWO receive blocks, used in turn by sequence
+// parity: a rank that has everything it needs may run ahead and start execution n+1 of the point while a
+// peer still reads the words of execution n, so n+1 must not land on them.  It cannot reach n+2 (the
+// block of n again) before that peer has sent its own n+1 slice, which the peer does only after it has
+// finished reading n.  Sequence numbers only grow (one per execution of an
 // exchange point, kept per CTA in device memory), every point has its own receive block, nothing
 // is ever reset, and a replayed CUDA graph needs no new arguments.  The reference has no multi-GPU
 // code; this stands where ncclAllGather calls would.
 //
 // Bounded wait: a peer that never arrives makes the kernel record a status code and return after
-// kWaitNs; the context stays usable and the host reads TER_B200_E_TIMEOUT from the status word.
+// the limit it is given (handle option "wait_ms"); the context stays usable and the host reads TER_B200_E_TIMEOUT from the status word.
 #include "common.cuh"
 #include "glue.h"
 #include "tagged.cuh"
@@ -22,7 +26,6 @@ namespace terb {
 
 namespace {
 
-constexpr unsigned long long kWaitNs = 2000000000ull;   // 2 s
 constexpr int kXThreads = 256;
 
 __global__ void __launch_bounds__(kXThreads) peer_exchange_kernel(const __grid_constant__ ExchangeParams p) {
@@ -34,6 +37,8 @@ __global__ void __launch_bounds__(kXThreads) peer_exchange_kernel(const __grid_c
 
     const int words_total = p.words_total;           // 16-byte words per rank for this point
     uint8_t* my_base = p.base[p.rank];
+    // this execution's receive block (two per point, by sequence parity)
+    const size_t recv_off = p.recv_off + (size_t)(seq & 1u) * (size_t)words_total * 16u * (size_t)p.size;
     bool timed_out = false;
     for (int w = blockIdx.x * kXThreads + tid; w < words_total; w += gridDim.x * kXThreads) {
         // which segment, which pair of floats
@@ -45,7 +50,7 @@ __global__ void __launch_bounds__(kXThreads) peer_exchange_kernel(const __grid_c
         const uint4 word = make_uint4(__float_as_uint(v.x), seq, __float_as_uint(v.y), seq);
         for (int r = 0; r < p.size; ++r)
             if (r != p.rank)
-                st_volatile16(reinterpret_cast<uint4*>(p.base[r] + p.recv_off) + (size_t)p.rank * words_total + w, word);
+                st_volatile16(reinterpret_cast<uint4*>(p.base[r] + recv_off) + (size_t)p.rank * words_total + w, word);
     }
     for (int w = blockIdx.x * kXThreads + tid; w < words_total; w += gridDim.x * kXThreads) {
         int s = 0, idx = w;
@@ -54,7 +59,7 @@ __global__ void __launch_bounds__(kXThreads) peer_exchange_kernel(const __grid_c
         float* full = reinterpret_cast<float*>(my_base + p.seg_buf_off[s]);
         for (int r = 0; r < p.size; ++r) {
             if (r == p.rank) continue;
-            const uint4* src = reinterpret_cast<const uint4*>(my_base + p.recv_off) + (size_t)r * words_total + w;
+            const uint4* src = reinterpret_cast<const uint4*>(my_base + recv_off) + (size_t)r * words_total + w;
             uint4 got = ld_volatile16(src);
             if (got.y != seq || got.w != seq) {
                 const unsigned long long t0 = globaltimer_ns();
@@ -62,7 +67,7 @@ __global__ void __launch_bounds__(kXThreads) peer_exchange_kernel(const __grid_c
                 while (!timed_out) {
                     got = ld_volatile16(src);
                     if (got.y == seq && got.w == seq) break;
-                    if ((++spins & 255u) == 0 && globaltimer_ns() - t0 > kWaitNs) {
+                    if ((++spins & 255u) == 0 && globaltimer_ns() - t0 > p.wait_ns) {
                         atomicExch(p.status, 0x7e000000 | (p.point << 8) | r);   // which point, which peer
                         timed_out = true;
                     }

@@ -414,6 +414,112 @@ __global__ void __launch_bounds__(kThreads) gemv_trit_split_kernel(const __grid_
     }
 }
 
+// ---------------------------------------------------------------------------------
+// Small token batches (2 <= M <= 16 rows of X against the same weights), one launch for up to
+// kGemvMaxGroup matrices: the weights stream ONCE (16-byte read-only loads into registers, one CTA per
+// strip, the 8 warps split K as in the latency path) and every unpacked word feeds the multiply-adds of
+// all rows.  Below the token count where the tensor-core GEMM pays, this replaces one GEMV launch per
+// row (the reference's batched decode does the same per-row work, cuda/ter_cuda_addonly_batched.cu:32-123).
+// Rows are processed RB at a time (accumulators in registers); a second pass re-reads the strip from L2.
+// ---------------------------------------------------------------------------------
+template <int RB>
+__global__ void __launch_bounds__(kThreads, 2) gemv_trit_rows_kernel(const __grid_constant__ GemvParams p) {
+    __shared__ int red[kWarps][RB][17];      // 16 columns + the row's sum of x
+    const int tid = threadIdx.x;
+    const int lane = tid & 31, warp = tid >> 5;
+    const int c = lane >> 3, sgm = lane & 7;
+    const int n_chunks = p.Kpad >> 7;
+    const int nb = (p.Kpad + kGemvKC - 1) / kGemvKC;
+    const int last_kc = p.Kpad - (nb - 1) * kGemvKC;
+    int m, ls;
+    locate(p, (int)blockIdx.x, m, ls);
+    const uint8_t* sbase = p.W[m] + (size_t)ls * 4u * (size_t)p.Kpad;
+    auto waddr = [&](int j) -> const uint8_t* {
+        const int q = j >> 3;
+        const int kc = (q == nb - 1) ? last_kc : kGemvKC;
+        return sbase + (size_t)q * kStageBytes + c * kc + (j & 7) * 128 + sgm * 16;
+    };
+    constexpr int CB = 4;                    // chunks per warp held in registers at once
+    const int n_batches = (n_chunks + CB * kWarps - 1) / (CB * kWarps);
+    uint4 w[CB];
+#pragma unroll
+    for (int i = 0; i < CB; ++i) {
+        const int j = warp + kWarps * i;
+        w[i] = j < n_chunks ? ldg_stream(waddr(j)) : make_uint4(0, 0, 0, 0);
+    }
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int r0 = 0; r0 < p.rows; r0 += RB) {
+        int acc[RB][4];
+        int xl[RB];
+#pragma unroll
+        for (int rr = 0; rr < RB; ++rr) { acc[rr][0] = acc[rr][1] = acc[rr][2] = acc[rr][3] = 0; xl[rr] = 0; }
+        for (int b = 0; b < n_batches; ++b) {
+            if (b > 0 || r0 > 0) {
+#pragma unroll
+                for (int i = 0; i < CB; ++i) {
+                    const int j = warp + kWarps * (i + b * CB);
+                    w[i] = j < n_chunks ? ldg_stream(waddr(j)) : make_uint4(0, 0, 0, 0);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < CB; ++i) {
+                const int j = warp + kWarps * (i + b * CB);
+                const int k0 = j * 128 + sgm * 16;
+                const bool in = j < n_chunks && k0 < p.K;
+#pragma unroll
+                for (int rr = 0; rr < RB; ++rr) {
+                    int4 xv = make_int4(0, 0, 0, 0);
+                    if (in && r0 + rr < p.rows) xv = *reinterpret_cast<const int4*>(p.x + (size_t)(r0 + rr) * p.K + k0);
+                    mac64(w[i], xv, acc[rr][0], acc[rr][1], acc[rr][2], acc[rr][3]);
+                    xl[rr] = __dp4a(xv.x, 0x01010101, xl[rr]);
+                    xl[rr] = __dp4a(xv.y, 0x01010101, xl[rr]);
+                    xl[rr] = __dp4a(xv.z, 0x01010101, xl[rr]);
+                    xl[rr] = __dp4a(xv.w, 0x01010101, xl[rr]);
+                }
+            }
+        }
+#pragma unroll
+        for (int o = 1; o < 8; o <<= 1) {
+#pragma unroll
+            for (int rr = 0; rr < RB; ++rr) {
+                acc[rr][0] += __shfl_xor_sync(0xffffffffu, acc[rr][0], o);
+                acc[rr][1] += __shfl_xor_sync(0xffffffffu, acc[rr][1], o);
+                acc[rr][2] += __shfl_xor_sync(0xffffffffu, acc[rr][2], o);
+                acc[rr][3] += __shfl_xor_sync(0xffffffffu, acc[rr][3], o);
+                xl[rr] += __shfl_xor_sync(0xffffffffu, xl[rr], o);
+            }
+        }
+        if (sgm == 0) {
+#pragma unroll
+            for (int rr = 0; rr < RB; ++rr) {
+                int* r = &red[warp][rr][c * 4];
+                r[0] = acc[rr][0] - acc[rr][1] - acc[rr][2] - acc[rr][3];
+                r[1] = acc[rr][1]; r[2] = acc[rr][2]; r[3] = acc[rr][3];
+                if (c == 0) red[warp][rr][16] = xl[rr];
+            }
+        }
+        __syncthreads();
+        if (tid < RB * 16) {
+            const int rr = tid >> 4, lc = tid & 15;
+            const int row = r0 + rr, col = ls * 16 + lc;
+            if (row < p.rows && col < p.N[m]) {
+                int sum = 0, xsum = 0;
+#pragma unroll
+                for (int wi = 0; wi < kWarps; ++wi) { sum += red[wi][rr][lc]; xsum += red[wi][rr][16]; }
+                const int v = (sum >> (2 * (lc & 3))) - xsum;
+                const size_t o = (size_t)row * (size_t)p.N[m] + col;
+                if (p.acc_out[m]) p.acc_out[m][o] = v;
+                if (p.out[m]) {
+                    const float f = (float)v * (p.x_scale[row] * p.w_scale[m]);
+                    p.out[m][o] = p.accumulate ? p.out[m][o] + f : f;
+                }
+            }
+        }
+        __syncthreads();
+    }
+}
+
 }  // namespace
 
 static size_t gemv_smem_bytes(int tab_bytes, int x_bytes, int stages) {
@@ -431,6 +537,22 @@ cudaError_t launch_gemv(const GemvParams& p_in, const GemvLaunchCfg& cfg, cudaSt
         e = cudaFuncSetAttribute(gemv_trit_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
+    }
+    if (p_in.rows >= 2) {   // a small token batch: all rows in one launch, one CTA per strip
+        if (p_in.multi || p_in.fuse.x || p_in.act_pair || p_in.table || !p_in.x || (p_in.K & 15) ||
+            (p_in.out[0] && !p_in.x_scale) || p_in.n_mats < 1 || p_in.n_mats > kGemvMaxGroup || p_in.rows > kGemvMaxRows)
+            return cudaErrorInvalidValue;
+        cudaLaunchConfig_t lc = {};
+        lc.gridDim = dim3((unsigned)p_in.n_tiles);
+        lc.blockDim = dim3(kThreads);
+        lc.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        lc.attrs = attr;
+        lc.numAttrs = cfg.pdl ? 1 : 0;
+        return p_in.rows <= 4 ? cudaLaunchKernelEx(&lc, gemv_trit_rows_kernel<4>, p_in)
+                              : cudaLaunchKernelEx(&lc, gemv_trit_rows_kernel<8>, p_in);
     }
     GemvParams p = p_in;
     if (!p.multi) {   // one shared activation vector, in the form the streaming kernel reads

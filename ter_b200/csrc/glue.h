@@ -95,8 +95,9 @@ cudaError_t launch_select(const SelectParams& p, bool pdl, cudaStream_t st);
 // Tensor-parallel exchange of output slices over peer memory (exchange_sm100.cu).  base[r] = rank r's
 // arena as mapped in THIS process (base[rank] = the local one).  A segment is one exchanged buffer:
 // seg_buf_off = byte offset of the FULL buffer in the arena, seg_floats = floats per rank slice (rank
-// r's slice starts at float r*seg_floats).  recv_off: byte offset of this point's receive block,
-// uint4[size][words_total]; seq: this point's int[kMaxExchangeCtas] sequence words (local).
+// r's slice starts at float r*seg_floats).  recv_off: byte offset of this point's TWO receive blocks,
+// uint4[2][size][words_total] (used in turn by sequence parity); seq: this point's int[kMaxExchangeCtas]
+// sequence words (local).  wait_ns: limit of a wait for a peer's word.
 constexpr int kMaxRanks = 8;
 constexpr int kMaxExchangeSegs = 3;
 constexpr int kMaxExchangePoints = 512;
@@ -111,6 +112,7 @@ struct ExchangeParams {
     int* seq;
     int* status;
     int point;
+    unsigned long long wait_ns;
 };
 cudaError_t launch_peer_exchange(const ExchangeParams& p, bool pdl, cudaStream_t st);
 

@@ -146,4 +146,49 @@ int ter_b200_argmax(ter_b200_handle_t* h, const float* logits_dev, int V, int B,
     return TER_B200_OK;
 }
 
+
+// Self-test of the bounded wait of the tensor-parallel exchange on ONE GPU: the exchange kernel runs as
+// rank 0 of 2 against a second local buffer that stands for a peer which never sends.  Its wait runs out
+// after "wait_ms", the kernel returns by itself and the status word reads as TER_B200_E_TIMEOUT through
+// ter_b200_device_status.  Nothing faults and nothing hangs; the handle stays usable.
+int ter_b200_selftest_exchange_timeout(ter_b200_handle_t* h) {
+    if (!h) return TER_B200_E_NULL;
+    TERB_CUDA(h, cudaSetDevice(h->device));
+    const int n_floats = 256;                       // per-rank slice
+    const size_t buf_bytes = 2 * n_floats * sizeof(float);
+    const size_t recv_bytes = 2u * (n_floats / 2) * 16u * 2u;
+    const size_t total = buf_bytes + recv_bytes + kMaxExchangeCtas * sizeof(int);
+    uint8_t* arena[2] = {nullptr, nullptr};
+    for (int i = 0; i < 2; ++i) {
+        cudaError_t e = cudaMalloc((void**)&arena[i], total);
+        if (e == cudaSuccess) e = cudaMemset(arena[i], 0, total);
+        if (e != cudaSuccess) {
+            for (int k = 0; k < 2; ++k) if (arena[k]) cudaFree(arena[k]);
+            return cuda_fail(h, e);
+        }
+    }
+    ExchangeParams xp;
+    memset(&xp, 0, sizeof xp);
+    xp.base[0] = arena[0];
+    xp.base[1] = arena[1];                          // the "peer": receives this rank's words, sends nothing
+    xp.seg_buf_off[0] = 0;
+    xp.seg_floats[0] = n_floats;
+    xp.n_seg = 1;
+    xp.words_total = n_floats / 2;
+    xp.rank = 0;
+    xp.size = 2;
+    xp.recv_off = buf_bytes;
+    xp.seq = reinterpret_cast<int*>(arena[0] + buf_bytes + recv_bytes);
+    xp.status = h->status_dev;
+    xp.point = 0;
+    xp.wait_ns = (unsigned long long)h->wait_ms * 1000000ull;
+    cudaError_t e = launch_peer_exchange(xp, false, h->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(h->stream);
+    h->launches += 1;
+    cudaFree(arena[0]);
+    cudaFree(arena[1]);
+    if (e != cudaSuccess) return cuda_fail(h, e);
+    return TER_B200_OK;
+}
+
 }  // extern "C"

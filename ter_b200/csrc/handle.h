@@ -127,6 +127,17 @@ inline const TerbSlot* find_slot(const ter_b200_handle_t* h, const char* name) {
     return find_slot(const_cast<ter_b200_handle_t*>(h), name);
 }
 
+// The one dispatch rule: which kernel multiplies M activation rows by a K x N weight (n_strips = total strips
+// of the launch group).  Everything that launches a GEMV or GEMM asks here.
+inline int pick_kernel(const ter_b200_handle_t* h, int M, int K, int n_strips) {
+    if (M <= 1)
+        return (h->gemv_cfg.split_max_strips > 0 && n_strips <= h->gemv_cfg.split_max_strips) ? TER_B200_KERNEL_GEMV_SPLIT
+                                                                                              : TER_B200_KERNEL_GEMV_STREAM;
+    if (M >= h->gemm_min_m) return TER_B200_KERNEL_GEMM_TCGEN05;
+    if (M <= kGemvMaxRows && (K & 15) == 0) return TER_B200_KERNEL_GEMV_ROWS;
+    return TER_B200_KERNEL_GEMV_PER_ROW;
+}
+
 inline void count_gemv(ter_b200_handle_t* h, int K, int N, int rows) {
     const uint64_t n = (uint64_t)((K + 26) / 27) * (uint64_t)N * (uint64_t)rows;
     h->counts.tvmac += n;

@@ -38,6 +38,7 @@ __host__ __device__ inline size_t weight_offset(int jb, int k, int Kpad) {
 }
 
 constexpr int kGemvMaxGroup = 8;
+constexpr int kGemvMaxRows = 16;       // token rows one multi-row GEMV launch takes
 constexpr int kGemvMaxK = 32768;
 constexpr int kGemvMaxX = 16;          // distinct activation vectors one streaming launch can stage
 constexpr int kGemvMaxTable = 512;     // matrices in one table-mode launch
@@ -79,6 +80,9 @@ struct GemvParams {
     int K, Kpad;
     int n_mats, n_tiles, stages;
     int accumulate;         // out[j] = out[j] + value (residual add fused in the epilogue)
+    // Multi-row form (rows >= 2, at most kGemvMaxRows): x is [rows][K] int8, x_scale [rows], out[m] / acc_out[m]
+    // are [rows][N[m]]; K a multiple of 16.  No fused prologue, no paired epilogue, no table.
+    int rows;
     // Fused prologue (latency path only): when fuse.x is set, every CTA derives the int8 activation
     // vector and its scale itself from fp32 inputs (pre-op -> RMSNorm -> absmax int8, row fuse_row)
     // instead of reading x / x_scale.

@@ -149,4 +149,39 @@ int ter_b200_model_load_file(ter_b200_handle_t* h, const char* path, int smax, i
     return TER_B200_OK;
 }
 
+
+// microsoft/BitNet "i2_s" tensor -> the v11 packed-trit bytes this library (and the reference's CUDA
+// forward) takes.  What the reference's converter does in NumPy (tools/convert_bitnet_to_packed.py:85-152:
+// read_i2s_scale, i2s_to_col_packed) and its CPU loader in C++ (vendor/ntransformer/core/dequant.cpp:114-145):
+//   * the tensor is N rows (output features) of K inputs, flat row-major, in blocks of 128 elements;
+//     a block is 32 bytes; byte p holds the codes of block positions p, p+32, p+64, p+96, position p
+//     (group 0) in the HIGH two bits; codes 0 -> -1, 1 -> 0, 2 -> +1, 3 -> 0;
+//   * 32 bytes follow the codes, the first four an fp32: the per-tensor scale.
+// Output: bytes [N/4][K]; byte (n/4)*K + k holds output column n at bits 2*(n%4), codes 0 -> 0, +1 -> 1,
+// -1 -> 2 (cuda/ter_cuda_forward_packed.cu:354-372).  Host memory only; needs no handle and no GPU.
+int ter_b200_convert_i2s(const void* i2s, size_t i2s_bytes, int N, int K, uint8_t* v11_out, float* scale_out) {
+    if (!i2s || !v11_out) return TER_B200_E_NULL;
+    if (N < 4 || K < 1 || (N & 3) != 0) return TER_B200_E_SHAPE;
+    const size_t total = (size_t)N * (size_t)K;
+    if (total % 128 != 0) return TER_B200_E_SHAPE;
+    if (i2s_bytes < total / 4 + (scale_out ? 4 : 0)) return TER_B200_E_IO;
+    const uint8_t* src = static_cast<const uint8_t*>(i2s);
+    if (scale_out) memcpy(scale_out, src + total / 4, sizeof(float));
+    static const uint8_t kCode[4] = {2, 0, 1, 0};            // i2_s code -> v11 code (-1 -> 2, 0 -> 0, +1 -> 1)
+    memset(v11_out, 0, total / 4);
+    for (size_t blk = 0; blk < total / 128; ++blk) {
+        const uint8_t* bb = src + blk * 32;
+        for (int g = 0; g < 4; ++g) {
+            const int shift = 6 - 2 * g;
+            for (int p = 0; p < 32; ++p) {
+                const size_t e = blk * 128 + (size_t)g * 32 + (size_t)p;   // flat element: row n, input k
+                const size_t n = e / (size_t)K, k = e % (size_t)K;
+                const uint8_t code = kCode[(bb[p] >> shift) & 3];
+                v11_out[(n >> 2) * (size_t)K + k] |= (uint8_t)(code << (2 * (n & 3)));
+            }
+        }
+    }
+    return TER_B200_OK;
+}
+
 }  // extern "C"

@@ -34,6 +34,7 @@ struct TerbModel {
     int graph_batch;
     bool graph_forced;
     uint64_t graph_launches;
+    uint64_t graph_tvmac;        // op-counter increment of one replay of the captured step
     cudaEvent_t ev0, ev1;
     float last_ms;
     // tensor parallelism over peer memory: the exchanged buffers (hidden, q, k, v, gate, up, logits) and
@@ -87,8 +88,9 @@ cudaError_t dalloc(T** p, size_t n) { return cudaMalloc((void**)p, n * sizeof(T)
 int mm(ter_b200_handle_t* h, const DevWeight* const* ws, int n, const int8_t* xq, int K, const float* xs,
        float* const* outs, bool accumulate, int B, cudaStream_t st, const NormQuantParams* nq = nullptr,
        const int32_t* xrs = nullptr) {
-    if (!nq && B >= h->gemm_min_m)     // token batch: one tensor-core GEMM over all rows and all the matrices
-        return run_gemm_group(h, ws, n, xq, xs, B, outs, nullptr, st, accumulate, xrs);
+    if (!nq && B >= 2)     // token batch: one launch over all rows and all the matrices (multi-row GEMV for a few
+                           // rows, the tensor-core GEMM from gemm_min_m rows on)
+        return run_gemm_group(h, ws, n, xq, xs, B, outs, nullptr, st, accumulate, B >= h->gemm_min_m ? xrs : nullptr);
     for (int b = 0; b < B; ++b) {
         float* o[kGemvMaxGroup];
         for (int i = 0; i < n; ++i) o[i] = outs[i] + (size_t)b * ws[i]->N;
@@ -100,7 +102,7 @@ int mm(ter_b200_handle_t* h, const DevWeight* const* ws, int n, const int8_t* xq
 }
 
 bool can_fuse(const ter_b200_handle_t* h, const DevWeight* const* ws, int n, int B) {
-    if (B >= h->gemm_min_m) return false;   // batches go through the GEMM, which takes quantised rows
+    if (B >= 2) return false;   // batches go through the multi-row GEMV / the GEMM, which take quantised rows
     int tiles = 0;
     for (int i = 0; i < n; ++i) tiles += ws[i]->tiles();
     return h->gemv_cfg.fuse_quant && h->gemv_cfg.split_max_strips > 0 && tiles <= h->gemv_cfg.split_max_strips;
@@ -166,14 +168,15 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
         xp.n_seg = nb;
         xp.rank = R;
         xp.size = G;
-        // this point's receive block: one 16-byte word per pair of floats and per source rank
-        const size_t block = (size_t)xp.words_total * 16u * (size_t)G;
+        // this point's two receive blocks (used in turn): one 16-byte word per pair of floats and per source rank
+        const size_t block = 2u * (size_t)xp.words_total * 16u * (size_t)G;
         if (recv_cursor + block > m->xrecv_bytes) return TER_B200_E_SHAPE;
         xp.recv_off = m->xrecv_off + recv_cursor;
         recv_cursor += block;
         xp.seq = m->xseq + (size_t)point * kMaxExchangeCtas;
         xp.status = h->status_dev;
         xp.point = point;
+        xp.wait_ns = (unsigned long long)h->wait_ms * 1000000ull;
         ++point;
         cudaError_t e = launch_peer_exchange(xp, pdl, st);
         if (e != cudaSuccess) return cuda_fail(h, e);
@@ -183,7 +186,8 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
 #define XCHG1(buf, n, sharded) do { float* b__[1] = {(buf)}; int n__[1] = {(n)}; int rc__ = exchange(b__, n__, 1, (sharded)); if (rc__) return rc__; } while (0)
 
     // One sequence on one GPU: embedding and all layers in ONE cooperative launch (decode_sm100.cu).
-    const bool persist = !pre && B == 1 && G == 1 && h->decode_persistent && m->dec_layers && !m->dec_dirty &&
+    // (under tensor parallelism when the layers are replicated: every rank runs them whole)
+    const bool persist = !pre && B == 1 && (G == 1 || (!sa && !sf)) && h->decode_persistent && m->dec_layers && !m->dec_dirty &&
                          decode_layers_supported(c.H, c.F, c.Nh, c.Nkv, c.Hd, c.L);
     if (persist) {
         DecodeParams dp;
@@ -483,7 +487,7 @@ int ter_b200_model_create(ter_b200_handle_t* h, const ter_b200_model_cfg_t* cfg)
             for (int i = 0; i < 7; ++i) { offs[i] = total; total += (xn[i] * sizeof(float) + 255) & ~(size_t)255; }
             // receive blocks: 16 bytes per pair of floats of every exchanged vector of a step (see forward())
             const size_t recv_off = total;
-            const size_t recv_bytes = ((size_t)c.L * ((size_t)Hq + 2 * Hkv + 2 * (size_t)c.H + 2 * (size_t)c.F) + c.V) * 8u;
+            const size_t recv_bytes = ((size_t)c.L * ((size_t)Hq + 2 * Hkv + 2 * (size_t)c.H + 2 * (size_t)c.F) + c.V) * 16u;
             total += (recv_bytes + 255) & ~(size_t)255;
             const size_t seq_off = total;
             total += (size_t)kMaxExchangePoints * kMaxExchangeCtas * sizeof(int);
@@ -747,6 +751,7 @@ int ter_b200_generate(ter_b200_handle_t* h, const int32_t* prompts, int batch, i
     if (!m->graph || m->graph_batch != batch || !m->graph_forced) {
         drop_graph(m);
         const uint64_t mark = h->launches;
+        const ter_b200_op_counts_t cmark = h->counts;
         TERB_CUDA(h, cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
         rc = forward(h, m, true, st);
         cudaGraph_t g = nullptr;
@@ -758,6 +763,8 @@ int ter_b200_generate(ter_b200_handle_t* h, const int32_t* prompts, int batch, i
         if (ce != cudaSuccess) { m->graph = nullptr; return cuda_fail(h, ce); }
         m->graph_launches = h->launches - mark;
         h->launches = mark;
+        m->graph_tvmac = h->counts.tvmac - cmark.tvmac;      // recording is not executing: counted per replay below
+        h->counts = cmark;
         m->graph_batch = batch;
         m->graph_forced = true;
     }
@@ -807,6 +814,8 @@ int ter_b200_generate(ter_b200_handle_t* h, const int32_t* prompts, int batch, i
         if (!use_prefill && i == n_prompt - 1) TERB_CUDA(h, cudaEventRecord(m->ev_mid, st));
         TERB_CUDA(h, cudaGraphLaunch(m->graph, st));
         h->launches += m->graph_launches;
+        h->counts.tvmac += m->graph_tvmac;
+        h->counts.total_ops += m->graph_tvmac;
     }
     TERB_CUDA(h, cudaEventRecord(m->ev1, st));
     TERB_CUDA(h, cudaStreamSynchronize(st));

@@ -51,8 +51,43 @@ int run_gemm_group(ter_b200_handle_t* h, const DevWeight* const* ws, int n, cons
     if (((uintptr_t)X & 15u) != 0) return TER_B200_E_SHAPE;
     for (int i = 1; i < n; ++i)
         if (ws[i]->K != ws[0]->K) return TER_B200_E_SHAPE;
-    if (M < h->gemm_min_m) {
-        // small batches: one GEMV launch per row (exact; the weights are re-read M times)
+    int group_strips = 0;
+    for (int i = 0; i < n; ++i) group_strips += ws[i]->tiles();
+    const int kernel = pick_kernel(h, M, ws[0]->K, group_strips);
+    if (kernel != TER_B200_KERNEL_GEMM_TCGEN05) {
+        if (kernel == TER_B200_KERNEL_GEMV_ROWS && n <= kGemvMaxGroup) {
+            // a small token batch: ONE launch, the weights stream once for all rows (gemv_trit_rows_kernel)
+            if (!x_scales && outs && outs[0]) return TER_B200_E_NULL;
+            GemvParams gp;
+            memset(&gp, 0, sizeof gp);
+            gp.K = ws[0]->K;
+            gp.Kpad = ws[0]->Kpad;
+            int tiles = 0;
+            for (int i = 0; i < n; ++i) {
+                gp.W[i] = ws[i]->data;
+                gp.out[i] = outs ? outs[i] : nullptr;
+                gp.acc_out[i] = (acc && i == 0) ? acc : nullptr;
+                gp.w_scale[i] = ws[i]->scale;
+                gp.N[i] = ws[i]->N;
+                gp.tile_begin[i] = tiles;
+                tiles += ws[i]->tiles();
+            }
+            for (int i = n; i <= kGemvMaxGroup; ++i) gp.tile_begin[i] = tiles;
+            gp.x = X;
+            gp.x_scale = x_scales;
+            gp.n_mats = n;
+            gp.n_tiles = tiles;
+            gp.rows = M;
+            gp.status = h->status_dev;
+            gp.accumulate = accumulate ? 1 : 0;
+            GemvLaunchCfg cfg = h->gemv_cfg;
+            cfg.sm_count = h->sm_count;
+            TERB_CUDA(h, launch_gemv(gp, cfg, st));
+            h->launches += 1;
+            for (int i = 0; i < n; ++i) count_gemv(h, ws[i]->K, ws[i]->N, M);
+            return TER_B200_OK;
+        }
+        // otherwise one GEMV launch per row (exact; the weights are re-read M times)
         for (int i = 0; i < n; ++i) {
             const DevWeight* w = ws[i];
             float* out = outs ? outs[i] : nullptr;

@@ -93,6 +93,16 @@ def main():
         rec[f"{name}_head"] = out[:16].copy()
         rec[f"{name}_x_sha256"] = np.frombuffer(hashlib.sha256(x.tobytes() + t.tobytes()).digest(), dtype=np.uint8)
     np.savez_compressed(os.path.join(HERE, "mm_row_recipes.npz"), **rec)
+
+    # microsoft/BitNet i2_s blocks decoded by the reference's own nt::dequant_i2_s
+    # (vendor/ntransformer/core/dequant.cpp:114-145): 8 x 384 elements = 24 blocks, every byte value present
+    irng = np.random.default_rng(20261125)
+    N, K = 8, 384
+    raw = np.concatenate([irng.integers(0, 256, size=N * K // 4, dtype=np.uint8), np.zeros(32, np.uint8)])
+    raw[N * K // 4:N * K // 4 + 4] = np.array([0.0371], np.float32).view(np.uint8)
+    raw[:256] = np.arange(256, dtype=np.uint8)
+    np.savez(os.path.join(HERE, "i2s_blocks.npz"), raw=raw, N=np.array([N]), K=np.array([K]),
+             dequant=ref.dequant_i2s(raw, N * K))
     print("wrote", sorted(os.listdir(HERE)))
 
 

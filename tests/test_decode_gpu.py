@@ -216,6 +216,45 @@ def test_full_size_shapes_few_layers(tb, base, L):
     assert np.array_equal(lg.view(np.uint32), want_logits[-1].view(np.uint32))
 
 
+def test_command_line_front_end_prints_the_reference_tokens(golden_dir, tmp_path):
+    """ter_b200_generate (the counterpart of the reference programs' main(): n_gen, model file) on a packed-model
+    file: greedy tokens from BOS equal to the ones the reference's NumPy forward printed, with the device
+    sampler and with the host argmax sampler; the op-count report comes in the reference's format."""
+    import re
+    import subprocess
+    import make_pyfwd_golden as mk
+    from ter_b200 import build, modelfile
+    g = np.load(os.path.join(golden_dir, "pyfwd_tokens.npz"))
+    for name in ("llama", "bitnet"):
+        case = mk.CASES[name]
+        path = str(tmp_path / f"{name}.bin")
+        modelfile.write_packed_model(path, case, synth.model_weights(case, case["seed"]))
+        want = g[f"{name}_tokens"].tolist()
+        for extra in ([], ["--host-sampler"], ["--op-stats"]):
+            r = subprocess.run([build.CLI, str(len(want)), path] + extra, capture_output=True, text=True, timeout=600)
+            assert r.returncode == 0, r.stdout[-500:] + r.stderr[-500:]
+            line = r.stdout.split("Greedy tokens")[1].splitlines()[1]
+            assert [int(t) for t in line.split()] == want, (name, extra)
+            if extra == ["--op-stats"]:
+                assert "=== op-stats:" in r.stderr and "TVMAC" in r.stderr
+                tv = int(re.search(r"TVMAC\s*:\s*(\d+)", r.stderr).group(1))
+                assert tv > 0
+
+
+def test_dispatch_rule_names_the_kernel(tb):
+    """ter_b200_pick_kernel is the one rule every launch goes through."""
+    assert tb.pick_kernel(1, 2048, 512) == "gemv_trit_split_kernel"
+    assert tb.pick_kernel(1, 2048, 128256) == "gemv_trit_kernel"
+    assert tb.pick_kernel(8, 2560, 6912) == "gemv_trit_rows_kernel"
+    assert tb.pick_kernel(16, 2560, 6912) == "gemv_trit_rows_kernel"
+    assert tb.pick_kernel(64, 2560, 6912) == "gemm_trit_kernel"
+    try:
+        tb.set_option("gemm_min_m", 4)
+        assert tb.pick_kernel(8, 2560, 6912) == "gemm_trit_kernel"
+    finally:
+        tb.set_option("gemm_min_m", 17)
+
+
 def test_model_state_errors(tb):
     from ter_b200 import TerB200, TerB200Error, api
     h = TerB200(0)

@@ -245,3 +245,20 @@ def test_named_operator_calls_equal_typed_entry_points(tb):
     assert tb.call("tk_nothing", [0]) == api.E_UNKNOWN
     assert tb.call("tk_rope", [0] * 8) == api.E_NARGS
     assert tb.device_status() == 0
+
+
+def test_exchange_wait_runs_out_without_a_peer(tb):
+    """The tensor-parallel exchange polls for words that a peer stores.  On one GPU, against a stand-in
+    peer that never sends, the wait must run out after "wait_ms": the kernel returns by itself, the status
+    word reports the timeout once, and the handle keeps working."""
+    from ter_b200 import api
+    try:
+        tb.set_option("wait_ms", 10)
+        tb.selftest_exchange_timeout()
+    finally:
+        tb.set_option("wait_ms", 2000)
+    assert tb.device_status() == api.E_TIMEOUT      # reported once ...
+    assert tb.device_status() == 0                   # ... and cleared
+    x = np.linspace(-1.0, 1.0, 256, dtype=np.float32).reshape(1, 256)
+    tb.rmsnorm_quant(dev(x), None, 1e-5)              # a following normal call works
+    assert tb.device_status() == 0

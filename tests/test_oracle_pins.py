@@ -185,3 +185,32 @@ def test_rope_conventions():
     assert np.allclose(a[:, 1::2], vv[:, 0::2] * s + vv[:, 1::2] * c, atol=1e-6)
     assert np.allclose(b[:, :32], vv[:, :32] * c - vv[:, 32:] * s, atol=1e-6)
     assert np.allclose(b[:, 32:], vv[:, :32] * s + vv[:, 32:] * c, atol=1e-6)
+
+
+def test_i2s_decode_and_converter_against_the_reference_decoder(golden_dir):
+    """microsoft/BitNet i2_s tensors: the checker's decode and the library's host-side converter
+    (ter_b200_convert_i2s, no GPU needed) against values decoded by the reference's own nt::dequant_i2_s
+    (committed fixture; live when oracle/_ref is present), and the reference test's own known-answer block
+    (tests/test_nt_dequant.cpp:37-60: all code bytes 0x1B, scale 2)."""
+    from ter_b200 import api, synth
+    g = np.load(os.path.join(golden_dir, "i2s_blocks.npz"))
+    raw, N, K = g["raw"], int(g["N"][0]), int(g["K"][0])
+    trits, scale = oracle.i2s_decode(raw, N * K)
+    assert np.array_equal(trits.astype(np.float32) * np.float32(scale), g["dequant"])
+    if oracle.Ref.available():
+        assert np.array_equal(oracle.Ref().dequant_i2s(raw, N * K), g["dequant"])
+    v11, sc = api.convert_i2s(raw, N, K)
+    assert sc == np.float32(0.0371)
+    # the tensor is N output rows x K inputs; the library's matrices are [K][N]
+    want = synth.pack_v11(np.ascontiguousarray(trits.reshape(N, K).T))
+    assert np.array_equal(v11, want)
+    # the reference test's block: positions 0..31 -> -1, 32..63 -> 0, 64..95 -> +1, 96..127 -> 0
+    blk = np.concatenate([np.full(32, 0x1B, np.uint8), np.array([2.0], np.float32).view(np.uint8), np.zeros(28, np.uint8)])
+    t1, s1 = oracle.i2s_decode(blk, 128)
+    assert s1 == 2.0 and np.all(t1[:32] == -1) and np.all(t1[32:64] == 0) and np.all(t1[64:96] == 1) and np.all(t1[96:] == 0)
+    v1, _ = api.convert_i2s(blk, 4, 32)
+    assert np.array_equal(v1, synth.pack_v11(np.ascontiguousarray(t1.reshape(4, 32).T)))
+    # errors are return codes
+    with pytest.raises(api.TerB200Error) as e:
+        api.convert_i2s(raw[:100], N, K)
+    assert e.value.code == api.E_IO
