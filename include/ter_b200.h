@@ -272,6 +272,13 @@ int ter_b200_attention_noalloc(ter_b200_handle_t* h, const float* q_dev, const u
  * (cuda/ter_cuda_forward_packed.cu:165-206) with a bf16 table and fp32 activations. */
 int ter_b200_lm_head_bf16(ter_b200_handle_t* h, const uint16_t* table_dev, const float* x_dev, float* logits_dev,
                           int V, int H, int B, void* stream);
+/* The same product for token batches (B >= 16 is where it pays) on the tensor cores: tcgen05 kind::f16 with the
+ * fp32 activations split into two bf16 parts and fp32 accumulators in tensor memory.  Equal to
+ * ter_b200_lm_head_bf16 up to rounding (about 1e-6 relative; the summation order differs), not bit for bit.
+ * H a multiple of 64; scratch_dev: ter_b200_lm_head_tc_scratch_bytes(B, H) bytes, 16-byte aligned. */
+int ter_b200_lm_head_bf16_tc(ter_b200_handle_t* h, const uint16_t* table_dev, const float* x_dev, float* logits_dev,
+                             int V, int H, int B, void* scratch_dev, size_t scratch_bytes, void* stream);
+size_t ter_b200_lm_head_tc_scratch_bytes(int B, int H);
 /* out[b] = lowest index among the maxima of logits[b][0..V): argmax_local_k + argmax_final_k
  * (cuda/ter_cuda_forward_packed.cu:209-241).  scratch_dev: B*256 floats. */
 int ter_b200_argmax(ter_b200_handle_t* h, const float* logits_dev, int V, int B, float* scratch_dev, int* out_dev,

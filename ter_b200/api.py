@@ -91,6 +91,8 @@ SIGNATURES = {
     "ter_b200_attention_noalloc_max_floats": (_SZ, []),
     "ter_b200_attention_noalloc": (_I, [_VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _VP, _VP]),
     "ter_b200_lm_head_bf16": (_I, [_VP, _VP, _VP, _VP, _I, _I, _I, _VP]),
+    "ter_b200_lm_head_bf16_tc": (_I, [_VP, _VP, _VP, _VP, _I, _I, _I, _VP, _SZ, _VP]),
+    "ter_b200_lm_head_tc_scratch_bytes": (_SZ, [_I, _I]),
     "ter_b200_argmax": (_I, [_VP, _VP, _I, _I, _VP, _VP, _VP]),
     "ter_b200_model_create": (_I, [_VP, C.POINTER(ModelCfg)]),
     "ter_b200_model_set_matrix": (_I, [_VP, _I, _I, _VP, _I, _F]),
@@ -444,6 +446,20 @@ class TerB200:
         logits = torch.empty((B, V), dtype=torch.float32, device=x.device)
         self._ck(self.L.ter_b200_lm_head_bf16(self.h, C.c_void_p(table.data_ptr()), C.c_void_p(x2.data_ptr()),
                                             C.c_void_p(logits.data_ptr()), V, H, B, _stream_ptr(stream)), "lm_head")
+        return logits
+
+    def lm_head_bf16_tc(self, table, x, stream=None):
+        """The bf16 lm_head of a token batch on the tensor cores (rounding-level differences from lm_head_bf16)."""
+        import torch
+        x2 = x.reshape(-1, x.shape[-1])
+        B, H = x2.shape
+        V = table.shape[0]
+        logits = torch.empty((B, V), dtype=torch.float32, device=x.device)
+        nbytes = int(self.L.ter_b200_lm_head_tc_scratch_bytes(B, H))
+        scratch = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+        self._ck(self.L.ter_b200_lm_head_bf16_tc(self.h, C.c_void_p(table.data_ptr()), C.c_void_p(x2.data_ptr()),
+                                               C.c_void_p(logits.data_ptr()), V, H, B, C.c_void_p(scratch.data_ptr()),
+                                               nbytes, _stream_ptr(stream)), "lm_head_tc")
         return logits
 
     def argmax(self, logits, stream=None):

@@ -199,6 +199,7 @@ ter_b200_handle_t* ter_b200_create(int device) {
     h->gemm_min_m = 17;     // up to 16 token rows take the multi-row GEMV
     h->attn_inline_merge = 1;
     h->decode_persistent = 1;
+    h->lm_head_tc_min = 16;
     h->decode_fault_cta = -1;
     h->decode_poll_ns = 0;
     h->wait_ms = 2000;
@@ -483,6 +484,8 @@ int ter_b200_device_status(ter_b200_handle_t* h) {
     TERB_CUDA(h, cudaMemcpy(&st, h->status_dev, sizeof(int), cudaMemcpyDeviceToHost));
     if (st != 0) {
         cudaMemset(h->status_dev, 0, sizeof(int));
+        // a kernel that gave up may have left split-K partials behind: they must read zero between calls
+        if (h->gemm_part) cudaMemset(h->gemm_part, 0, h->gemm_part_cap * sizeof(int));
         return TER_B200_E_TIMEOUT;
     }
     return TER_B200_OK;
@@ -551,6 +554,10 @@ int ter_b200_set_option(ter_b200_handle_t* h, const char* key, int value) {
     } else if (strcmp(key, "gemm_min_m") == 0) {
         if (value < 1) return TER_B200_E_SHAPE;
         h->gemm_min_m = value;
+    } else if (strcmp(key, "lm_head_tc_min") == 0) {
+        if (value < 0) return TER_B200_E_SHAPE;
+        h->lm_head_tc_min = value == 0 ? 0x7fffffff : value;
+        model_invalidate_graph(h);
     } else if (strcmp(key, "decode_persistent") == 0) {
         h->decode_persistent = value ? 1 : 0;
     } else if (strcmp(key, "decode_poll_ns") == 0) {

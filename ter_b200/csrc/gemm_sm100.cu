@@ -22,11 +22,15 @@
 //     stage back to the producers through an mbarrier.
 //   * epilogue (warps 0-7): tcgen05.ld the accumulators (TMEM lane = output column), scale, store
 //     out[m][n] coalesced over n.  With split-K the int32 partials are added into a scratch array
-//     with red.global.add.s32 (integer adds are exact and order-free) and a second kernel scales.
+//     with red.global.add.s32 (integer adds are exact and order-free) and a second, wide kernel scales the
+//     sums, stores the outputs and clears the partials again, so the scratch is zero between calls and needs
+//     no kernel to prepare it.  (Letting the last CTA of a tile to arrive do that work was measured slower:
+//     one CTA then reads a whole tile's partials back, 14 against 10 microseconds at 64 tokens.)
 // Every wait is bounded; on expiry a status code is recorded and all roles run to the end, so
 // tensor memory is always freed.
 #include "common.cuh"
 #include "kernels.h"
+#include "umma.cuh"
 
 namespace terb {
 
@@ -38,8 +42,10 @@ constexpr int kTileN = 128;                  // output columns per CTA = MMA M
 constexpr int kKStep = 128;                  // k per pipeline stage = one 128-byte swizzle row
 constexpr int kAStageBytes = kTileN * kKStep;   // 16 KB
 constexpr int kRawStageBytes = 4096;            // the packed trits of one step (128 columns x 128 k, 2 bits each)
-constexpr int kRawRing = 6;                     // thread-private ring of packed-trit steps
-constexpr int kRawAhead = 4;                    // cp.async copies in flight per producer thread (< kRawRing)
+// The packed trits travel through a thread-private ring of RING steps (template parameter of the kernel), RING - 2 of
+// them in flight as cp.async copies.  A step is 4 KB per CTA; with the weights coming from HBM (about a microsecond
+// away) a CTA needs tens of KB in flight to keep its share of the bandwidth: small token tiles, which leave the room,
+// take the deep ring; large ones, which are bound by the tensor pipe and need the room for operand stages, a short one.
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
@@ -48,35 +54,6 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-// Bounded wait that also gives up as soon as another role has flagged an abort.
-__device__ __forceinline__ bool mbar_wait_abortable(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                                    int* status) {
-    for (uint32_t i = 0; i < (1u << 21); ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 255u) == 255u && *abort_flag) return false;
-    }
-    *abort_flag = 1;
-    if (status) atomicExch(status, DEV_TIMEOUT_MBAR);
-    return false;
-}
-
-// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128 bytes, 8-row groups
-// 1024 bytes apart.
-__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);          // start address
-    d |= (uint64_t)1 << 16;                                // leading byte offset (unused for this layout)
-    d |= (uint64_t)(1024 >> 4) << 32;                      // stride byte offset between 8-row groups
-    d |= (uint64_t)1 << 46;                                // descriptor version (sm_100)
-    d |= (uint64_t)2 << 61;                                // 128-byte swizzle
-    return d;
-}
 // Instruction descriptor, kind::i8: D = s32, A = u8, B = s8, both K-major, M = 128, N = n_tokens.
 __device__ __forceinline__ uint32_t umma_idesc_i8(int n_tokens) {
     uint32_t d = 0;
@@ -89,21 +66,23 @@ __device__ __forceinline__ uint32_t umma_idesc_i8(int n_tokens) {
 }
 
 struct GemmSmemLayout {
-    int stages, tokens;   // tokens = padded token tile (multiple of 16)
+    int stages, tokens, ring;   // tokens = padded token tile (multiple of 16); ring = packed-trit steps buffered
     __host__ __device__ int b_stage_bytes() const { return tokens * kKStep; }
     __host__ __device__ int a_off(int s) const { return s * kAStageBytes; }
     __host__ __device__ int b_off(int s) const { return stages * kAStageBytes + s * b_stage_bytes(); }
     __host__ __device__ int raw_off(int s) const { return stages * (kAStageBytes + b_stage_bytes()) + s * kRawStageBytes; }
-    __host__ __device__ int tail_off() const { return stages * (kAStageBytes + b_stage_bytes()) + kRawRing * kRawStageBytes; }
+    __host__ __device__ int tail_off() const { return stages * (kAStageBytes + b_stage_bytes()) + ring * kRawStageBytes; }
     // tail: full[8], empty[8], done (u64 each) | tmem base, abort (16 B) | scale[256] (float) | rowsum[256] (int)
     __host__ __device__ int bytes() const { return tail_off() + 17 * 8 + 16 + 2 * 256 * 4 + 1024; }
 };
 
+template <int kRawRing>
 __global__ void __launch_bounds__(kGemmThreads) gemm_trit_kernel(const __grid_constant__ GemmParams p) {
+    constexpr int kRawAhead = kRawRing - 2;
     extern __shared__ uint8_t gsm_raw[];
     // 1024-byte alignment: the swizzle pattern is a function of the shared-memory address bits
     uint8_t* gsm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(gsm_raw) + 1023) & ~(uintptr_t)1023);
-    GemmSmemLayout L{p.stages, p.tokens};
+    GemmSmemLayout L{p.stages, p.tokens, kRawRing};
     uint64_t* full = reinterpret_cast<uint64_t*>(gsm + L.tail_off());
     uint64_t* empty = full + 8;
     uint64_t* done = full + 16;
@@ -317,11 +296,6 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_trit_kernel(const __grid_co
 __global__ void __launch_bounds__(256) gemm_prep_kernel(const GemmParams p) {
     pdl_launch_dependents();
     pdl_wait();
-    if (p.part) {   // split-K partials start at zero
-        size_t total = 0;
-        for (int w = 0; w < p.n_w; ++w) total += (size_t)p.M * p.Ng[w];
-        for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (size_t)gridDim.x * 256) p.part[i] = 0;
-    }
     if (!p.x_rowsum_w) return;
     const int lane = threadIdx.x & 31;
     for (int m = blockIdx.x * 8 + (threadIdx.x >> 5); m < p.M; m += gridDim.x * 8) {
@@ -340,19 +314,21 @@ __global__ void __launch_bounds__(256) gemm_prep_kernel(const GemmParams p) {
     }
 }
 
-// Split-K second pass: out[m][n] = float((part[m][n] >> 2*(n%4)) - rowsum[m]) * (x_scales[m] * w_scale).
+// Split-K second pass: out[m][n] = float((part[m][n] >> 2*(n%4)) - rowsum[m]) * (x_scales[m] * w_scale); the partials
+// are cleared on the way, ready for the next call.
 __global__ void __launch_bounds__(256) gemm_finalize_kernel(const GemmParams p) {
     pdl_launch_dependents();
     pdl_wait();
     for (int w = 0; w < p.n_w; ++w) {
         const int N = p.Ng[w];
-        const int32_t* part = p.part + p.part_off[w];
+        int32_t* part = p.part + p.part_off[w];
         float* out = p.outg[w];
         const float ws = p.wsg[w];
         const size_t total = (size_t)p.M * N;
         for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (size_t)gridDim.x * 256) {
             const int m = (int)(i / N), n = (int)(i % N);
             const int v = (part[i] >> (2 * (n & 3))) - p.x_rowsum[m];
+            part[i] = 0;
             if (p.acc_out) p.acc_out[i] = v;
             if (out) {
                 const float f = (float)v * (p.x_scales[m] * ws);
@@ -363,22 +339,6 @@ __global__ void __launch_bounds__(256) gemm_finalize_kernel(const GemmParams p) 
 }
 
 }  // namespace
-
-// cuTensorMapEncodeTiled, resolved through the runtime so that the library links against nothing but cudart.
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-static EncodeTiledFn encode_tiled() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* ptr = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)ptr;
-    }
-    return fn;
-}
 
 cudaError_t launch_gemm(const GemmParams& p_in, int sm_count, bool pdl, cudaStream_t st) {
     GemmParams p = p_in;
@@ -414,7 +374,8 @@ cudaError_t launch_gemm(const GemmParams& p_in, int sm_count, bool pdl, cudaStre
         if (ksplits < 1) ksplits = 1;
     }
     p.ksplits = ksplits;
-    GemmSmemLayout L{8, tokens};                                // as many stages as fit, at most 8
+    const int ring = tokens <= 64 ? 24 : (tokens <= 128 ? 16 : 8);
+    GemmSmemLayout L{8, tokens, ring};                          // as many stages as fit, at most 8
     while (L.stages > 2 && L.bytes() > 220 * 1024) --L.stages;
     if (L.bytes() > 220 * 1024) return cudaErrorInvalidValue;
     p.stages = L.stages;
@@ -437,7 +398,9 @@ cudaError_t launch_gemm(const GemmParams& p_in, int sm_count, bool pdl, cudaStre
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
     if (!attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_trit_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(gemm_trit_kernel<24>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_trit_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_trit_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
@@ -453,10 +416,9 @@ cudaError_t launch_gemm(const GemmParams& p_in, int sm_count, bool pdl, cudaStre
         p.x_rowsum_w = p.scratch;
         p.x_rowsum = p.scratch;
     }
-    if (p.part || p.x_rowsum_w) {
+    if (p.x_rowsum_w) {
         cudaLaunchConfig_t lr = {};
-        size_t g = p.part ? (part_ints + 1023) / 1024 : (size_t)(p.M + 7) / 8;
-        if (p.x_rowsum_w && g < (size_t)(p.M + 7) / 8) g = (size_t)(p.M + 7) / 8;
+        size_t g = (size_t)(p.M + 7) / 8;
         if (g > (size_t)sm_count * 8) g = (size_t)sm_count * 8;
         lr.gridDim = dim3((unsigned)g);
         lr.blockDim = dim3(256);
@@ -473,7 +435,8 @@ cudaError_t launch_gemm(const GemmParams& p_in, int sm_count, bool pdl, cudaStre
     lc.stream = st;
     lc.attrs = attr;
     lc.numAttrs = pdl ? 1 : 0;   // after a memset node keep plain stream order
-    e = cudaLaunchKernelEx(&lc, gemm_trit_kernel, p);
+    e = ring == 24 ? cudaLaunchKernelEx(&lc, gemm_trit_kernel<24>, p)
+                   : (ring == 16 ? cudaLaunchKernelEx(&lc, gemm_trit_kernel<16>, p) : cudaLaunchKernelEx(&lc, gemm_trit_kernel<8>, p));
     if (e != cudaSuccess || ksplits == 1) return e;
     cudaLaunchConfig_t lf = {};
     size_t g = (part_ints + 255) / 256;

@@ -424,6 +424,7 @@ __global__ void __launch_bounds__(kThreads) gemv_trit_split_kernel(const __grid_
 // ---------------------------------------------------------------------------------
 template <int RB>
 __global__ void __launch_bounds__(kThreads, 2) gemv_trit_rows_kernel(const __grid_constant__ GemvParams p) {
+    extern __shared__ __align__(16) uint8_t xrows[];   // [RB][Kpad] int8: the rows of this pass, zero-padded
     __shared__ int red[kWarps][RB][17];      // 16 columns + the row's sum of x
     const int tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
@@ -450,6 +451,17 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_trit_rows_kernel(const __gri
     pdl_launch_dependents();
     pdl_wait();
     for (int r0 = 0; r0 < p.rows; r0 += RB) {
+        // stage the rows of this pass in shared memory with one batch of coalesced 16-byte loads
+        {
+            const int per_row = p.Kpad >> 4;
+            for (int i = tid; i < RB * per_row; i += kThreads) {
+                const int rr = i / per_row, k0 = (i - rr * per_row) << 4;
+                int4 v = make_int4(0, 0, 0, 0);
+                if (r0 + rr < p.rows && k0 < p.K) v = *reinterpret_cast<const int4*>(p.x + (size_t)(r0 + rr) * p.K + k0);
+                *reinterpret_cast<int4*>(xrows + (size_t)rr * p.Kpad + k0) = v;
+            }
+        }
+        __syncthreads();
         int acc[RB][4];
         int xl[RB];
 #pragma unroll
@@ -466,11 +478,11 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_trit_rows_kernel(const __gri
             for (int i = 0; i < CB; ++i) {
                 const int j = warp + kWarps * (i + b * CB);
                 const int k0 = j * 128 + sgm * 16;
-                const bool in = j < n_chunks && k0 < p.K;
+                const bool in = j < n_chunks;
 #pragma unroll
                 for (int rr = 0; rr < RB; ++rr) {
                     int4 xv = make_int4(0, 0, 0, 0);
-                    if (in && r0 + rr < p.rows) xv = *reinterpret_cast<const int4*>(p.x + (size_t)(r0 + rr) * p.K + k0);
+                    if (in) xv = *reinterpret_cast<const int4*>(xrows + (size_t)rr * p.Kpad + k0);
                     mac64(w[i], xv, acc[rr][0], acc[rr][1], acc[rr][2], acc[rr][3]);
                     xl[rr] = __dp4a(xv.x, 0x01010101, xl[rr]);
                     xl[rr] = __dp4a(xv.y, 0x01010101, xl[rr]);
@@ -543,16 +555,27 @@ cudaError_t launch_gemv(const GemvParams& p_in, const GemvLaunchCfg& cfg, cudaSt
             (p_in.out[0] && !p_in.x_scale) || p_in.n_mats < 1 || p_in.n_mats > kGemvMaxGroup || p_in.rows > kGemvMaxRows)
             return cudaErrorInvalidValue;
         cudaLaunchConfig_t lc = {};
+        const int rb = p_in.rows <= 4 ? 4 : 8;
+        const size_t xsm = (size_t)rb * (size_t)p_in.Kpad;
+        if (xsm > 200 * 1024) return cudaErrorInvalidValue;
+        static bool rows_attr[64][2] = {};
+        if (xsm > 40 * 1024 && !rows_attr[dev][rb == 8]) {
+            cudaError_t e = rb == 8 ? cudaFuncSetAttribute(gemv_trit_rows_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)
+                                    : cudaFuncSetAttribute(gemv_trit_rows_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            if (e != cudaSuccess) return e;
+            rows_attr[dev][rb == 8] = true;
+        }
         lc.gridDim = dim3((unsigned)p_in.n_tiles);
         lc.blockDim = dim3(kThreads);
+        lc.dynamicSmemBytes = xsm;
         lc.stream = st;
         cudaLaunchAttribute attr[1];
         attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         lc.attrs = attr;
         lc.numAttrs = cfg.pdl ? 1 : 0;
-        return p_in.rows <= 4 ? cudaLaunchKernelEx(&lc, gemv_trit_rows_kernel<4>, p_in)
-                              : cudaLaunchKernelEx(&lc, gemv_trit_rows_kernel<8>, p_in);
+        return rb == 4 ? cudaLaunchKernelEx(&lc, gemv_trit_rows_kernel<4>, p_in)
+                       : cudaLaunchKernelEx(&lc, gemv_trit_rows_kernel<8>, p_in);
     }
     GemvParams p = p_in;
     if (!p.multi) {   // one shared activation vector, in the form the streaming kernel reads

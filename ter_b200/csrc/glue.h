@@ -68,6 +68,12 @@ size_t attention_scratch_floats(int B, int Nh, int Hd, int Smax);
 // logits[b][v] = sum_h bf16(table[v][h]) * x[b][h], fp32 accumulate.
 cudaError_t launch_lm_head_bf16(const uint16_t* table, const float* x, float* logits, int V, int H, int B,
                                 int sm_count, bool pdl, cudaStream_t st);
+// The same product on the tensor cores (tcgen05 kind::f16) for B >= 16 rows: x is split into two bf16 parts, the
+// accumulators are fp32; equal to the exact kernel up to rounding (about 1e-6 relative), not bit for bit.
+// scratch: lm_head_tc_scratch_bytes(B, H) bytes of device memory, 16-byte aligned; H a multiple of 64.
+size_t lm_head_tc_scratch_bytes(int B, int H);
+cudaError_t launch_lm_head_tc(const uint16_t* table, const float* x, float* logits, int V, int H, int B, void* scratch,
+                              int* status, bool pdl, cudaStream_t st);
 // out[b] = lowest index among the maxima of logits[b][0..V).  scratch: [B][kArgmaxParts][2] floats.
 constexpr int kArgmaxParts = 128;
 cudaError_t launch_argmax(const float* logits, int V, int B, float* scratch, int* out, bool pdl, cudaStream_t st);

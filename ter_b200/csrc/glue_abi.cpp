@@ -147,6 +147,18 @@ int ter_b200_argmax(ter_b200_handle_t* h, const float* logits_dev, int V, int B,
 }
 
 
+int ter_b200_lm_head_bf16_tc(ter_b200_handle_t* h, const uint16_t* table_dev, const float* x_dev, float* logits_dev,
+                             int V, int H, int B, void* scratch_dev, size_t scratch_bytes, void* stream) {
+    if (!h || !table_dev || !x_dev || !logits_dev || !scratch_dev) return TER_B200_E_NULL;
+    if (V < 1 || B < 1 || H < 64 || H % 64 != 0 || scratch_bytes < lm_head_tc_scratch_bytes(B, H)) return TER_B200_E_SHAPE;
+    TERB_CUDA(h, cudaSetDevice(h->device));
+    TERB_CUDA(h, launch_lm_head_tc(table_dev, x_dev, logits_dev, V, H, B, scratch_dev, h->status_dev,
+                                   h->gemv_cfg.pdl != 0, pick_stream(h, stream)));
+    h->launches += 2;
+    return TER_B200_OK;
+}
+size_t ter_b200_lm_head_tc_scratch_bytes(int B, int H) { return lm_head_tc_scratch_bytes(B, H); }
+
 // Self-test of the bounded wait of the tensor-parallel exchange on ONE GPU: the exchange kernel runs as
 // rank 0 of 2 against a second local buffer that stands for a peer which never sends.  Its wait runs out
 // after "wait_ms", the kernel returns by itself and the status word reads as TER_B200_E_TIMEOUT through

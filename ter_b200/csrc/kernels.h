@@ -121,7 +121,7 @@ struct GemmParams {
     int32_t* acc_out;         // [M][N] or null (raw int32 dot products)
     const int32_t* x_rowsum;  // [M] sum_k X[m][k], or null: computed into the scratch by a pre-kernel
     int32_t* scratch;         // M ints: row sums computed by the pre-kernel when x_rowsum is null
-    int32_t* part_buf;        // M*N ints or null: split-K partials (zeroed by the pre-kernel)
+    int32_t* part_buf;        // M*N ints or null: split-K partials, ZERO between calls (the finalize kernel clears them)
     int accumulate;           // out[m][n] = out[m][n] + value (residual add)
     int32_t* part;            // set by the launcher
     int32_t* x_rowsum_w;      // set by the launcher

@@ -51,6 +51,7 @@ struct TerbModel {
     cudaEvent_t ev_mid;
     float last_prefill_ms, last_prompt_ms;
     // persistent decode kernel (decode_sm100.cu): per-layer constants in device memory, its barrier word
+    uint16_t* xsplit;        // bf16 hi / lo parts of the normalised rows (tensor-core lm_head, batches of 16 or more)
     DecodeLayerDev* dec_layers;
     uint4* dec_state;        // tagged activation vectors + attention records (decode_state_layout), then 4 control words
     bool dec_dirty;
@@ -119,7 +120,8 @@ bool can_fuse(const ter_b200_handle_t* h, const DevWeight* const* ws, int n, int
 // prefill_rows > 0: the rows are `prefill_rows` consecutive positions of ONE prompt (tokens m->tok_rows,
 // positions m->pos_rows, all in sequence 0's cache): rotary + append for all rows first, then causal
 // attention per row; only the last row goes through the lm_head, and the step bookkeeping is left out.
-int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st, int prefill_rows = 0) {
+// pre_seq: the sequence whose prompt the rows belong to (its cache, its logits row, its greedy token).
+int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st, int prefill_rows = 0, int pre_seq = 0) {
     const ter_b200_model_cfg_t& c = m->c;
     const bool pre = prefill_rows > 0;
     const int B = pre ? prefill_rows : m->batch, H = c.H, F = c.F, Hq = c.Nh * c.Hd;
@@ -235,11 +237,11 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
         uint16_t* kc = m->kcache + L * layer_cache;
         uint16_t* vc = m->vcache + L * layer_cache;
         if (pre) {
-            RopeKvParams rp{m->q, m->k, m->v, m->rope, posv, kc, vc, B, c.Nh, c.Nkv, c.Hd, c.Smax, bitnet ? 1 : 0, 1};
+            RopeKvParams rp{m->q, m->k, m->v, m->rope, posv, kc, vc, B, c.Nh, c.Nkv, c.Hd, c.Smax, bitnet ? 1 : 0, pre_seq + 1};
             CK(launch_rope_kv(rp, pdl, st));
             AttnParams ap{m->q, kc, vc, posv, m->attn_scratch, m->att, B, c.Nh, c.Nkv, c.Hd, c.Smax,
                           (c.Smax + kAttnChunk - 1) / kAttnChunk, nullptr, nullptr, nullptr, nullptr, nullptr, 0,
-                          h->status_dev, h->attn_inline_merge ? m->attn_counters : nullptr, 1};
+                          h->status_dev, h->attn_inline_merge ? m->attn_counters : nullptr, pre_seq + 1};
             CK(launch_attention(ap, pdl, st));
         } else {
             AttnParams ap{m->q, kc, vc, m->pos, m->attn_scratch, m->att, B, c.Nh, c.Nkv, c.Hd, c.Smax,
@@ -304,25 +306,34 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
     // lm_head: every sequence of a decode step; of a prompt tile only its last position
     const int Bh = pre ? 1 : B;
     const float* hid = pre ? m->hidden + (size_t)(B - 1) * H : m->hidden;
+    float* logits = m->logits + (pre ? (size_t)pre_seq * c.V : 0);      // a prompt's last row fills its sequence's row
     if (c.lm_head_packed) {
         // bench-mode packed lm_head: cuda/ter_cuda_forward_packed.cu:541-545
         NormQuantParams oq{hid, nullptr, m->out_norm, m->xq, m->xs, nullptr, H, Bh, PRE_NONE, c.eps};
         CK(launch_norm_quant(oq, pdl, st));
         const DevWeight* ws[1] = {&m->lm_head};
-        float* outs[1] = {m->logits + off(c.V)};
+        float* outs[1] = {logits + off(c.V)};
         int rc = mm(h, ws, 1, m->xq, H, m->xs, outs, false, Bh, st);
         if (rc) return rc;
-        XCHG1(m->logits, c.V, true);
+        XCHG1(logits, c.V, true);
     } else {
         NormQuantParams on{hid, nullptr, m->out_norm, nullptr, nullptr, m->xnorm, H, Bh, PRE_NONE, c.eps};
         CK(launch_norm_quant(on, pdl, st));
-        CK(launch_lm_head_bf16(m->embd + off(c.V) * H, m->xnorm, m->logits + off(c.V), c.V / G, H, Bh, h->sm_count, pdl, st));
-        XCHG1(m->logits, c.V, true);
+        if (m->xsplit && Bh >= h->lm_head_tc_min && H % 64 == 0) {
+            // a token batch: the table goes through the tensor cores once for all rows (rounding-level differences
+            // from the exact kernel; option "lm_head_tc_min" moves or disables the switch)
+            CK(launch_lm_head_tc(m->embd + off(c.V) * H, m->xnorm, logits + off(c.V), c.V / G, H, Bh, m->xsplit,
+                                 h->status_dev, pdl, st));
+            h->launches += 1;
+        } else {
+            CK(launch_lm_head_bf16(m->embd + off(c.V) * H, m->xnorm, logits + off(c.V), c.V / G, H, Bh, h->sm_count, pdl, st));
+        }
+        XCHG1(logits, c.V, true);
         const uint64_t n = (uint64_t)((H + 26) / 27) * (uint64_t)c.V * (uint64_t)Bh;
         h->counts.tvmac += n;
         h->counts.total_ops += n;
     }
-    CK(launch_argmax(m->logits, c.V, Bh, m->argmax_scratch, m->greedy, pdl, st));
+    CK(launch_argmax(logits, c.V, Bh, m->argmax_scratch, m->greedy + (pre ? pre_seq : 0), pdl, st));
     h->launches += 1;
     if (pre) return TER_B200_OK;
     SelectParams sp{m->greedy, use_forced ? m->forced : nullptr, m->tokens, m->pos, use_forced ? m->log : nullptr,
@@ -424,7 +435,7 @@ void ter_b200_model_free(ter_b200_handle_t* h) {
     void* bufs[] = {m->out_norm, m->hidden, m->q, m->k, m->v, m->att, m->gate, m->up, m->xnorm, m->logits,
                     m->attn_scratch, m->argmax_scratch, m->xs, m->xq, m->kcache, m->vcache, m->tokens, m->pos,
                     m->greedy, m->forced, m->log, m->ctl, m->attn_counters, m->tok_rows, m->pos_rows, m->xrs,
-                    m->dec_layers, m->dec_state};
+                    m->dec_layers, m->dec_state, m->xsplit};
     for (void* b : bufs)
         if (b) cudaFree(b);
     if (m->ev0) cudaEventDestroy(m->ev0);
@@ -508,6 +519,7 @@ int ter_b200_model_create(ter_b200_handle_t* h, const ter_b200_model_cfg_t* cfg)
     }
     A(dalloc(&m->att, (size_t)R * Hq));
     A(dalloc(&m->xnorm, (size_t)B * c.H));
+    if (B >= 16 && !c.lm_head_packed) A(dalloc(&m->xsplit, (size_t)2 * B * c.H));
     A(dalloc(&m->attn_scratch, attention_scratch_floats(R, c.Nh, c.Hd, c.Smax)));
     A(dalloc(&m->argmax_scratch, (size_t)B * kArgmaxParts * 2));
     A(dalloc(&m->xs, (size_t)R));
@@ -772,12 +784,12 @@ int ter_b200_generate(ter_b200_handle_t* h, const int32_t* prompts, int batch, i
         rc = comm_barrier(h, st);
         if (rc) return rc;
     }
-    // Prompt processing.  One sequence with a prompt of at least two tokens: the prompt goes through the
-    // layers in passes of up to 1024 positions as a token batch (tensor-core GEMM, causal attention per
-    // row over the shared cache), which leaves the cache, the position and the first generated token
-    // exactly as feeding the prompt one position at a time does.  Under tensor parallelism only with
+    // Prompt processing.  Prompts of at least two tokens go through the layers in passes of up to 1024
+    // positions as a token batch (tensor-core GEMM, causal attention per row over the sequence's cache),
+    // one sequence after the other, which leaves the caches, the positions and the first generated tokens
+    // exactly as feeding the prompts one position at a time does.  Under tensor parallelism only with
     // replicated layers (the default policy).  Otherwise: one graph replay per prompt position.
-    const bool use_prefill = h->prefill && batch == 1 && n_prompt >= 2 && m->rows_cap >= 2 &&
+    const bool use_prefill = h->prefill && n_prompt >= 2 && m->rows_cap >= 2 &&
                              (comm_size(h) == 1 || (!m->shard_attn && !m->shard_ffn));
     TERB_CUDA(h, cudaEventRecord(m->ev0, st));
     int replays = steps;
@@ -789,20 +801,25 @@ int ter_b200_generate(ter_b200_handle_t* h, const int32_t* prompts, int batch, i
         if (rc) return rc;
         int* iota = (int*)malloc(sizeof(int) * (size_t)T);
         if (!iota) return TER_B200_E_ALLOC;
-        for (int p0 = 0; p0 < n_prompt && !rc; p0 += T) {
-            const int rows = n_prompt - p0 < T ? n_prompt - p0 : T;
-            for (int r = 0; r < rows; ++r) iota[r] = p0 + r;
-            cudaError_t ce = cudaMemcpyAsync(m->tok_rows, prompts + p0, rows * sizeof(int), cudaMemcpyHostToDevice, st);
-            if (ce == cudaSuccess) ce = cudaMemcpyAsync(m->pos_rows, iota, rows * sizeof(int), cudaMemcpyHostToDevice, st);
-            if (ce != cudaSuccess) { rc = cuda_fail(h, ce); break; }
-            rc = forward(h, m, false, st, rows);
-        }
+        for (int b = 0; b < batch && !rc; ++b)
+            for (int p0 = 0; p0 < n_prompt && !rc; p0 += T) {
+                const int rows = n_prompt - p0 < T ? n_prompt - p0 : T;
+                for (int r = 0; r < rows; ++r) iota[r] = p0 + r;
+                cudaError_t ce = cudaMemcpyAsync(m->tok_rows, prompts + (size_t)b * n_prompt + p0, rows * sizeof(int),
+                                                 cudaMemcpyHostToDevice, st);
+                if (ce == cudaSuccess) ce = cudaMemcpyAsync(m->pos_rows, iota, rows * sizeof(int), cudaMemcpyHostToDevice, st);
+                if (ce != cudaSuccess) { rc = cuda_fail(h, ce); break; }
+                rc = forward(h, m, false, st, rows, b);
+            }
+        if (rc) { free(iota); return rc; }
+        // bookkeeping of the last prompt position of every sequence: log the first generated token, pos = n_prompt
+        for (int b = 0; b < batch; ++b) iota[b % T] = n_prompt - 1;
+        cudaError_t cp = cudaSuccess;
+        for (int b0 = 0; b0 < batch && cp == cudaSuccess; b0 += T)
+            cp = cudaMemcpyAsync(m->pos + b0, iota, (size_t)(batch - b0 < T ? batch - b0 : T) * sizeof(int), cudaMemcpyHostToDevice, st);
         free(iota);
-        if (rc) return rc;
-        // bookkeeping of the last prompt position: log the first generated token, pos = n_prompt
-        const int last = n_prompt - 1;
-        TERB_CUDA(h, cudaMemcpyAsync(m->pos, &last, sizeof(int), cudaMemcpyHostToDevice, st));
-        SelectParams sp{m->greedy, m->forced, m->tokens, m->pos, m->log, m->ctl, 1, m->forced_cap, m->log_cap, nullptr};
+        if (cp != cudaSuccess) return cuda_fail(h, cp);
+        SelectParams sp{m->greedy, m->forced, m->tokens, m->pos, m->log, m->ctl, batch, m->forced_cap, m->log_cap, nullptr};
         cudaError_t ce = launch_select(sp, h->gemv_cfg.pdl != 0, st);
         if (ce != cudaSuccess) return cuda_fail(h, ce);
         h->launches += 1;

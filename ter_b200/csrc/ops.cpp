@@ -36,6 +36,7 @@ int ensure_gemm_scratch(ter_b200_handle_t* h, int M, int N) {
         h->gemm_part = nullptr;
         h->gemm_part_cap = 0;
         const size_t cap = need_part > 2 * h->gemm_part_cap_prev ? need_part : 2 * h->gemm_part_cap_prev;
+        // the partials stay zero between calls (whoever reads them clears them)
         TERB_CUDA(h, cudaMalloc((void**)&h->gemm_part, cap * sizeof(int)));
         TERB_CUDA(h, cudaMemset(h->gemm_part, 0, cap * sizeof(int)));
         h->gemm_part_cap = h->gemm_part_cap_prev = cap;

@@ -135,6 +135,31 @@ def test_token_batch_through_tensor_core_gemm(tb, cfg, seed):
     assert tb.device_status() == 0
 
 
+def test_batch_of_sixteen_prompts_as_token_batches_and_tensor_core_lm_head(tb):
+    """Sixteen sequences: the prompts run one sequence after the other as token batches, the decode steps take
+    the multi-row GEMV, and the lm_head runs on the tensor cores (rounding-level differences in the logits).
+    Every sequence must reproduce its own single-sequence tokens; logits within 1e-4 of the largest."""
+    cfg, seed, B = dict(SMALL_BITNET, H=512, V=3000), 71, 16
+    modelutil.build_gpu(tb, cfg, seed, max_batch=B)
+    om = modelutil.build_oracle(cfg, seed)
+    prompts = np.random.default_rng(seed).integers(0, cfg["V"], size=(B, 21)).astype(np.int32)
+    out = tb.generate(prompts, 5)
+    lg = tb.model_logits()
+    try:
+        tb.set_option("lm_head_tc_min", 0)          # the exact CUDA-core lm_head for every batch size
+        out_exact = tb.generate(prompts, 5)
+        lg_exact = tb.model_logits()
+    finally:
+        tb.set_option("lm_head_tc_min", 16)
+    for b in range(B):
+        want, wl = modelutil.oracle_generate(om, prompts[b], 5, want_logits=True)
+        assert out_exact[b].tolist() == want.tolist(), b
+        assert np.array_equal(lg_exact[b].view(np.uint32), wl[-1].view(np.uint32)), b
+        assert out[b].tolist() == want.tolist(), b
+        assert np.max(np.abs(lg[b] - wl[-1])) <= 1e-4 * np.max(np.abs(wl[-1])), b
+    assert tb.device_status() == 0
+
+
 def test_reference_numpy_forward_tokens_on_gpu(tb, golden_dir):
     """Greedy tokens printed by the reference's own tools/llama_pyfwd.py / bitnet_pyfwd.py."""
     import make_pyfwd_golden as mk

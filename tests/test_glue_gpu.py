@@ -247,6 +247,30 @@ def test_named_operator_calls_equal_typed_entry_points(tb):
     assert tb.device_status() == 0
 
 
+@pytest.mark.parametrize("V,H,B", [(4099, 2048, 16), (128256, 2560, 64), (3000, 256, 37), (1000, 2560, 300)])
+def test_lm_head_on_tensor_cores(tb, V, H, B):
+    """Token batches run the bf16 lm_head on tcgen05 (x split into two bf16 parts, fp32 accumulators).  The
+    summation order is the tensor core's, not the checker's, so the comparison is a tolerance: 1e-4 of the
+    largest logit of the row per element (measured: about 1e-6), and the greedy token must be the checker's
+    unless its two best logits are closer than that tolerance."""
+    rng = np.random.default_rng(V + B)
+    table = oracle.f32_to_bf16((rng.standard_normal((V, H)) * 0.02).astype(np.float32))
+    x = rng.standard_normal((B, H)).astype(np.float32)
+    td = dev(table.view(np.int16))
+    got = tb.lm_head_bf16_tc(td, dev(x)).cpu().numpy()
+    exact = tb.lm_head_bf16(td, dev(x)).cpu().numpy()          # bit-equal to the checker (test_lm_head_and_argmax)
+    for b in range(0, B, max(1, B // 4)):
+        want = oracle.lm_head_bf16(table, x[b])
+        assert np.array_equal(exact[b].view(np.uint32), want.view(np.uint32))
+    tol = 1e-4 * np.max(np.abs(exact), axis=1, keepdims=True)
+    assert np.all(np.abs(got - exact) <= tol), float(np.max(np.abs(got - exact) / tol))
+    for b in range(B):
+        i, j = int(np.argmax(got[b])), int(np.argmax(exact[b]))
+        if i != j:
+            assert abs(exact[b][i] - exact[b][j]) <= tol[b, 0], (b, i, j)
+    assert tb.device_status() == 0
+
+
 def test_exchange_wait_runs_out_without_a_peer(tb):
     """The tensor-parallel exchange polls for words that a peer stores.  On one GPU, against a stand-in
     peer that never sends, the wait must run out after "wait_ms": the kernel returns by itself, the status
