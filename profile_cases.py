@@ -5,6 +5,9 @@
     python profile_cases.py gemm             # BitNet gate 2560 x 6912 GEMM at M = 16, 256, 1024
     python profile_cases.py decode llama     # three decode steps at position ~300 (or: bitnet, position ~2100)
     python profile_cases.py decode bitnet 64 # the same for a batch of 64 sequences
+    python profile_cases.py glue             # the glue kernels alone: RMSNorm + int8 quantiser (64 rows x 2560), batched
+                                             # attention (24 sequences x 5 KV heads x 2048 positions, 126 MB of K/V),
+                                             # bf16 lm_head for 1 row (CUDA cores) and 64 rows (tensor cores), 657 MB table
 
 Each holds at most a few GB on the device and finishes in seconds, so an `ncu` capture of it ends by itself.
 """
@@ -130,6 +133,39 @@ def decode(which="llama", batch="1"):
     print("decode ok", which, "batch", batch, tok[0], tb.device_status())
 
 
+def glue():
+    import torch
+    from ter_b200 import TerB200
+    tb = TerB200(0)
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device=dev)
+    g.manual_seed(3)
+    # RMSNorm + absmax int8 quantiser, 64 rows of the BitNet hidden size
+    x = torch.randn((64, 2560), generator=g, device=dev)
+    gamma = torch.ones(2560, device=dev)
+    for _ in range(3):
+        tb.rmsnorm_quant(x, gamma, 1e-5)
+    # batched attention: 24 sequences, 20 query / 5 KV heads of 128, context 2048 (the batch-64 decode kernel)
+    B, Nh, Nkv, Hd, Smax = 24, 20, 5, 128, 2048
+    q = torch.randn((B, Nh * Hd), generator=g, device=dev)
+    kc = torch.randn((B, Nkv, Smax, Hd), generator=g, device=dev).to(torch.bfloat16)
+    vc = torch.randn((B, Nkv, Smax, Hd), generator=g, device=dev).to(torch.bfloat16)
+    pos = torch.full((B,), Smax - 1, dtype=torch.int32, device=dev)
+    for _ in range(3):
+        tb.attention(q, kc, vc, pos, Nh, Nkv, Hd, Smax)
+    del kc, vc
+    # bf16 lm_head: one row on the CUDA cores, 64 rows on the tensor cores
+    table = (torch.randn((128256, 2560), generator=g, device=dev) * 0.02).to(torch.bfloat16).view(torch.int16)
+    x1 = torch.randn((1, 2560), generator=g, device=dev)
+    x64 = torch.randn((64, 2560), generator=g, device=dev)
+    for _ in range(3):
+        tb.lm_head_bf16(table, x1)
+    for _ in range(3):
+        tb.lm_head_bf16_tc(table, x64)
+    torch.cuda.synchronize()
+    print("glue ok, status", tb.device_status())
+
+
 if __name__ == "__main__":
     case = sys.argv[1] if len(sys.argv) > 1 else "gemv_stream"
-    {"gemv_stream": gemv_stream, "sweep": sweep, "gemm": gemm, "decode": lambda: decode(*sys.argv[2:4])}[case]()
+    {"gemv_stream": gemv_stream, "sweep": sweep, "gemm": gemm, "decode": lambda: decode(*sys.argv[2:4]), "glue": glue}[case]()

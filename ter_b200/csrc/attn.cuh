@@ -198,7 +198,7 @@ __device__ __forceinline__ void attn_compute(const AttnParams& p, const AttnItem
     ATR(2);
 
     const float inv_sqrt = 1.0f / sqrtf((float)HD);
-    if constexpr (MODE == 2 && G * HD / 8 <= 64) {
+    if constexpr (G * HD / 8 <= 64) {
         // The form below with this lane's slices of the query heads held in registers (the lane always
         // multiplies the same 8 dims of every 64): one 16-byte load per position and piece instead of one
         // per position, piece and head.  Same operations in the same order.
