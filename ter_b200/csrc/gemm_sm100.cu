@@ -43,9 +43,7 @@ constexpr int kKStep = 128;                  // k per pipeline stage = one 128-b
 constexpr int kAStageBytes = kTileN * kKStep;   // 16 KB
 constexpr int kRawStageBytes = 4096;            // the packed trits of one step (128 columns x 128 k, 2 bits each)
 // The packed trits travel through a thread-private ring of RING steps (template parameter of the kernel), RING - 2 of
-// them in flight as cp.async copies.  A step is 4 KB per CTA; with the weights coming from HBM (about a microsecond
-// away) a CTA needs tens of KB in flight to keep its share of the bandwidth: small token tiles, which leave the room,
-// take the deep ring; large ones, which are bound by the tensor pipe and need the room for operand stages, a short one.
+// them in flight as cp.async copies (a step is 4 KB per CTA).
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
@@ -315,26 +313,30 @@ __global__ void __launch_bounds__(256) gemm_prep_kernel(const GemmParams p) {
 }
 
 // Split-K second pass: out[m][n] = float((part[m][n] >> 2*(n%4)) - rowsum[m]) * (x_scales[m] * w_scale); the partials
-// are cleared on the way, ready for the next call.
+// are cleared on the way, ready for the next call.  Grid: (column groups of 1024, token rows, matrices); a thread
+// takes four adjacent columns (N is a multiple of 16), so there is no index arithmetic beyond a multiply-add.
 __global__ void __launch_bounds__(256) gemm_finalize_kernel(const GemmParams p) {
     pdl_launch_dependents();
     pdl_wait();
-    for (int w = 0; w < p.n_w; ++w) {
-        const int N = p.Ng[w];
-        int32_t* part = p.part + p.part_off[w];
-        float* out = p.outg[w];
-        const float ws = p.wsg[w];
-        const size_t total = (size_t)p.M * N;
-        for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (size_t)gridDim.x * 256) {
-            const int m = (int)(i / N), n = (int)(i % N);
-            const int v = (part[i] >> (2 * (n & 3))) - p.x_rowsum[m];
-            part[i] = 0;
-            if (p.acc_out) p.acc_out[i] = v;
-            if (out) {
-                const float f = (float)v * (p.x_scales[m] * ws);
-                out[i] = p.accumulate ? out[i] + f : f;
-            }
+    const int w = blockIdx.z, m = blockIdx.y;
+    const int N = p.Ng[w];
+    const int n = (blockIdx.x * 256 + threadIdx.x) * 4;
+    if (n >= N) return;
+    const size_t i = (size_t)m * N + n;
+    int32_t* part = p.part + p.part_off[w] + i;
+    const int4 raw = *reinterpret_cast<const int4*>(part);
+    *reinterpret_cast<int4*>(part) = make_int4(0, 0, 0, 0);
+    const int rs = p.x_rowsum[m];
+    const int v0 = raw.x - rs, v1 = (raw.y >> 2) - rs, v2 = (raw.z >> 4) - rs, v3 = (raw.w >> 6) - rs;   // n % 4 == 0
+    if (p.acc_out) *reinterpret_cast<int4*>(p.acc_out + i) = make_int4(v0, v1, v2, v3);
+    if (float* out = p.outg[w]) {
+        const float sc = p.x_scales[m] * p.wsg[w];
+        float4 f = make_float4((float)v0 * sc, (float)v1 * sc, (float)v2 * sc, (float)v3 * sc);
+        if (p.accumulate) {
+            const float4 o = *reinterpret_cast<const float4*>(out + i);
+            f.x = o.x + f.x; f.y = o.y + f.y; f.z = o.z + f.z; f.w = o.w + f.w;
         }
+        *reinterpret_cast<float4*>(out + i) = f;
     }
 }
 
@@ -373,8 +375,11 @@ cudaError_t launch_gemm(const GemmParams& p_in, int sm_count, bool pdl, cudaStre
         if (ksplits > steps / 4) ksplits = steps / 4;
         if (ksplits < 1) ksplits = 1;
     }
+    for (int w = 0; w < p.n_w; ++w)     // the second pass moves four columns at a time
+        if ((p.Ng[w] & 3) || (reinterpret_cast<uintptr_t>(p.outg[w]) & 15u)) ksplits = 1;
+    if (reinterpret_cast<uintptr_t>(p.acc_out) & 15u) ksplits = 1;
     p.ksplits = ksplits;
-    const int ring = tokens <= 64 ? 24 : (tokens <= 128 ? 16 : 8);
+    const int ring = 8;     // a 24-step ring for small token tiles measured no faster: the producers' work per step paces the loop
     GemmSmemLayout L{8, tokens, ring};                          // as many stages as fit, at most 8
     while (L.stages > 2 && L.bytes() > 220 * 1024) --L.stages;
     if (L.bytes() > 220 * 1024) return cudaErrorInvalidValue;
@@ -398,9 +403,7 @@ cudaError_t launch_gemm(const GemmParams& p_in, int sm_count, bool pdl, cudaStre
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
     if (!attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_trit_kernel<24>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_trit_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_trit_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(gemm_trit_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
@@ -435,12 +438,12 @@ cudaError_t launch_gemm(const GemmParams& p_in, int sm_count, bool pdl, cudaStre
     lc.stream = st;
     lc.attrs = attr;
     lc.numAttrs = pdl ? 1 : 0;   // after a memset node keep plain stream order
-    e = ring == 24 ? cudaLaunchKernelEx(&lc, gemm_trit_kernel<24>, p)
-                   : (ring == 16 ? cudaLaunchKernelEx(&lc, gemm_trit_kernel<16>, p) : cudaLaunchKernelEx(&lc, gemm_trit_kernel<8>, p));
+    e = cudaLaunchKernelEx(&lc, gemm_trit_kernel<8>, p);
     if (e != cudaSuccess || ksplits == 1) return e;
     cudaLaunchConfig_t lf = {};
-    size_t g = (part_ints + 255) / 256;
-    lf.gridDim = dim3((unsigned)(g > (size_t)sm_count * 8 ? (size_t)sm_count * 8 : g));
+    int max_n = 0;
+    for (int w = 0; w < p.n_w; ++w) max_n = p.Ng[w] > max_n ? p.Ng[w] : max_n;
+    lf.gridDim = dim3((unsigned)((max_n + 1023) / 1024), (unsigned)p.M, (unsigned)p.n_w);
     lf.blockDim = dim3(256);
     lf.stream = st;
     lf.attrs = attr;
