@@ -382,6 +382,9 @@ def oracle_tokens(cfg, host_items, prompt, n_tokens):
     return toks
 
 
+HOST_BARRIER = None     # set when the job has several ranks: a barrier that waits on the host (gloo)
+
+
 def decode_bench(tb, dev, rank, which="llama", n_prompt=128, n_gen=256, batch=1, smax=512, warm=True,
                  lm_head_packed=False, check=None):
     """Random-init ternarised decode of one of the two benchmark architectures (tied bf16 lm_head, bf16 KV
@@ -394,7 +397,9 @@ def decode_bench(tb, dev, rank, which="llama", n_prompt=128, n_gen=256, batch=1,
     base = synth.LLAMA_1B_CFG if which == "llama" else synth.BITNET_2B_CFG
     cfg = dict(base, Smax=smax, lm_head_packed=1 if lm_head_packed else 0)
     tb.model_create(cfg, max_batch=batch)
-    host = [] if check else None          # the same tensors for the CPU checker (check = (prompt length, tokens))
+    # the CPU checker runs in ONE process of the job (the others would only fight it for the host cores)
+    checker = check is not None and int(os.environ.get("RANK", "0")) == 0
+    host = [] if checker else None        # the same tensors for the CPU checker (check = (prompt length, tokens))
     if lm_head_packed:   # the reference's bench mode: random packed-trit lm_head instead of the tied table
         seed = synth.seed_for(rank, "dec", which, "lm_head")
         tb.model_set_matrix(-1, 0, synth.packed_v11_cuda(cfg["H"], cfg["V"], seed, dev), FMT_V11, float(synth.weight_scale(seed)))
@@ -457,7 +462,9 @@ def decode_bench(tb, dev, rank, which="llama", n_prompt=128, n_gen=256, batch=1,
         t0 = time.perf_counter()
         pr = prompt if batch == 1 else prompt[0]
         got = [int(t) for t in (out[0][:cn] if cp == n_prompt else tb.generate(pr[:cp], cn)[0])]
-        want = oracle_tokens(cfg, host, pr[:cp], cn) if rank == 0 else None
+        want = oracle_tokens(cfg, host, pr[:cp], cn) if checker else None
+        if HOST_BARRIER is not None:
+            HOST_BARRIER()                  # the other ranks sleep in a socket wait, not in a spinning collective
         parity = {"prompt": cp, "tokens": cn, "got": got, "want": want, "seconds": round(time.perf_counter() - t0, 1),
                   "checker": "oracle.Model (CPU restatement, all host threads), prompt fed one position at a time",
                   "ok": (got == want) if want is not None else None}
@@ -537,6 +544,9 @@ def main():
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+        global HOST_BARRIER
+        host_group = dist.new_group(backend="gloo")
+        HOST_BARRIER = lambda: dist.barrier(group=host_group)
     torch.cuda.set_device(local)
     dev = torch.device(f"cuda:{local}")
 

@@ -403,7 +403,13 @@ int ter_b200_selftest_exchange_timeout(ter_b200_handle_t* h);
 /* Last CUDA error code seen by the handle (cudaError_t as int), 0 if none. */
 int ter_b200_last_cuda_error(const ter_b200_handle_t* h);
 /* Tuning knobs (integers): "gemv_ctas_per_sm", "gemv_stages", "gemv_split_max_strips", "pdl",
- * "fuse_quant", "gemm_min_m", "gemm_split_k", "attn_inline_merge", "prefill", "prefill_tile", "host_batch_direct", "tp_p2p" (1, default: tensor-
+ * "fuse_quant", "gemm_min_m" (rows from which the tcgen05 GEMM runs, default 17; 2..16 rows take the multi-row GEMV),
+ * "gemm_split_k", "attn_inline_merge", "prefill", "prefill_tile", "host_batch_direct",
+ * "decode_persistent" (1, default: one sequence runs the embedding and all layers of a step in one persistent kernel),
+ * "decode_poll_ns" (pause between polls inside that kernel, default 0), "decode_fault_cta" (test hook, -1 = off: that
+ * CTA keeps its q/k/v columns of layer 0 to itself so that its consumers' waits run out), "wait_ms" (limit of a
+ * device-side wait on another CTA or GPU, default 2000), "lm_head_tc_min" (batch size from which the bf16 lm_head runs
+ * on the tensor cores, default 16, 0 = never), "tp_p2p" (1, default: tensor-
  * parallel output slices travel by peer stores over NVLink inside one small kernel per exchange;
  * 0: NCCL all-gathers) and "tp_shard" (which blocks of a layer are column-sharded over the ranks:
  * bit 0 the attention block q/k/v/o, bit 1 the FFN block gate/up/down; the lm_head always is.

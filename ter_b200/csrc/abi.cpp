@@ -200,6 +200,7 @@ ter_b200_handle_t* ter_b200_create(int device) {
     h->attn_inline_merge = 1;
     h->decode_persistent = 1;
     h->lm_head_tc_min = 16;
+    h->attn_mma_min = 8;
     h->decode_fault_cta = -1;
     h->decode_poll_ns = 0;
     h->wait_ms = 2000;
@@ -557,6 +558,10 @@ int ter_b200_set_option(ter_b200_handle_t* h, const char* key, int value) {
     } else if (strcmp(key, "lm_head_tc_min") == 0) {
         if (value < 0) return TER_B200_E_SHAPE;
         h->lm_head_tc_min = value == 0 ? 0x7fffffff : value;
+        model_invalidate_graph(h);
+    } else if (strcmp(key, "attn_mma_min") == 0) {
+        if (value < 0) return TER_B200_E_SHAPE;
+        h->attn_mma_min = value == 0 ? 0x7fffffff : value;
         model_invalidate_graph(h);
     } else if (strcmp(key, "decode_persistent") == 0) {
         h->decode_persistent = value ? 1 : 0;

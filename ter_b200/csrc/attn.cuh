@@ -77,6 +77,43 @@ __device__ __forceinline__ void attn_issue_kv(const AttnParams& p, const AttnIte
     }
 }
 
+// Merge of the chunks by the last CTA of this (row, KV head) to finish, when the caller gave arrival
+// counters; the order of the merge is fixed (chunk 0, 1, 2, ...) whoever performs it.  All threads call it.
+template <int HD, int G>
+__device__ __forceinline__ void attn_merge_last(const AttnParams& p, const AttnItem& it, int* is_last) {
+    if (!p.counters) return;
+    const int tid = threadIdx.x, b = it.b, g = it.g;
+    const size_t rec_stride = (size_t)p.max_chunks * (HD + 2);
+    const int nc = (it.seq_len + kAttnChunk - 1) / kAttnChunk;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        int* cnt_p = p.counters + (size_t)b * p.Nkv + g;
+        const int old = atomicAdd(cnt_p, 1);
+        *is_last = (old == nc - 1);
+        if (*is_last) *cnt_p = 0;          // ready for the next step
+    }
+    __syncthreads();
+    if (*is_last) {
+        __threadfence();
+        for (int idx = tid; idx < G * HD; idx += kT) {
+            const int hh = idx / HD, d = idx % HD;
+            const float* rec = p.scratch + ((size_t)b * p.Nh + (size_t)g * G + hh) * rec_stride;
+            float M = __ldcg(rec), Lsum = __ldcg(rec + 1), O = __ldcg(rec + 2 + d);
+            for (int cc = 1; cc < nc; ++cc) {
+                const float* r = rec + (size_t)cc * (HD + 2);
+                const float mc = __ldcg(r), lc = __ldcg(r + 1), oc = __ldcg(r + 2 + d);
+                const float Mn = fmaxf(M, mc);
+                const float a = exp_fixed(M - Mn), bb = exp_fixed(mc - Mn);
+                Lsum = fmaf(lc, bb, Lsum * a);
+                O = fmaf(oc, bb, O * a);
+                M = Mn;
+            }
+            p.out[((size_t)b * p.Nh + (size_t)g * G + hh) * HD + d] = O / Lsum;
+        }
+    }
+}
+
 // Flag-in-data inputs and outputs of an item inside the persistent decode kernel (MODE 2 of attn_compute):
 // q / k / v of the new position arrive as tagged vectors written by other CTAs; partial records and the
 // attention output leave as tagged words; the rotary row and the chunk's (m, l) live in shared memory.
@@ -525,38 +562,7 @@ __device__ __forceinline__ void attn_compute(const AttnParams& p, const AttnItem
         }
     }
 
-    // Merge of the chunks by the last CTA of this (sequence, KV head) to finish, when the caller gave
-    // arrival counters; the order of the merge is fixed (chunk 0, 1, 2, ...) whoever performs it.
-    if (MODE != 2 && p.counters) {
-        const int nc = (it.seq_len + kAttnChunk - 1) / kAttnChunk;
-        __threadfence();
-        __syncthreads();
-        if (tid == 0) {
-            int* cnt_p = p.counters + (size_t)b * p.Nkv + g;
-            const int old = atomicAdd(cnt_p, 1);
-            *is_last = (old == nc - 1);
-            if (*is_last) *cnt_p = 0;          // ready for the next step
-        }
-        __syncthreads();
-        if (*is_last) {
-            __threadfence();
-            for (int idx = tid; idx < G * HD; idx += kT) {
-                const int hh = idx / HD, d = idx % HD;
-                const float* rec = p.scratch + ((size_t)b * p.Nh + (size_t)g * G + hh) * rec_stride;
-                float M = __ldcg(rec), Lsum = __ldcg(rec + 1), O = __ldcg(rec + 2 + d);
-                for (int cc = 1; cc < nc; ++cc) {
-                    const float* r = rec + (size_t)cc * (HD + 2);
-                    const float mc = __ldcg(r), lc = __ldcg(r + 1), oc = __ldcg(r + 2 + d);
-                    const float Mn = fmaxf(M, mc);
-                    const float a = exp_fixed(M - Mn), bb = exp_fixed(mc - Mn);
-                    Lsum = fmaf(lc, bb, Lsum * a);
-                    O = fmaf(oc, bb, O * a);
-                    M = Mn;
-                }
-                p.out[((size_t)b * p.Nh + (size_t)g * G + hh) * HD + d] = O / Lsum;
-            }
-        }
-    }
+    if constexpr (MODE != 2) attn_merge_last<HD, G>(p, it, is_last);
 }
 
 }  // namespace

@@ -61,6 +61,8 @@ struct AttnParams {
                              // the chunks itself (no second kernel); null = merge in attn_combine_kernel
     int shared_seq;          // 0: row b reads the cache of sequence b; s > 0: every row reads sequence s - 1
                              // (the rows are positions of one prompt, each with its own pos[b])
+    int mma;                 // 1: the two contractions on the tensor cores (attn_mma.cuh): equal to the fixed-order
+                             // kernel up to the rounding of fp32 sums, not bit for bit; for token batches
 };
 cudaError_t launch_attention(const AttnParams& p, bool pdl, cudaStream_t st);
 size_t attention_scratch_floats(int B, int Nh, int Hd, int Smax);

@@ -117,6 +117,7 @@ int ter_b200_attention(ter_b200_handle_t* h, const float* q_dev, const uint16_t*
     AttnParams p{q_dev, kcache_dev, vcache_dev, pos_dev, scratch_dev, out_dev, B, Nh, Nkv, Hd, Smax,
                  (Smax + kAttnChunk - 1) / kAttnChunk, nullptr, nullptr, nullptr, nullptr, nullptr, 0,
                  h->status_dev};
+    p.mma = B >= h->attn_mma_min;
     TERB_CUDA(h, launch_attention(p, h->gemv_cfg.pdl != 0, pick_stream(h, stream)));
     h->launches += 2;
     return TER_B200_OK;

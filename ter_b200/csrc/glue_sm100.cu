@@ -15,7 +15,7 @@
 // attention_k (cuda/ter_cuda_forward_packed.cu:64-90,118-157; NEOX variant
 // cuda/ter_cuda_forward_bitnet.cu:185-201), mm_fp16_lm_head_k and argmax_*_k
 // (cuda/ter_cuda_forward_packed.cu:165-259).
-#include "attn.cuh"
+#include "attn_mma.cuh"
 
 namespace terb {
 
@@ -182,6 +182,27 @@ __global__ void __launch_bounds__(kT, COMPACT ? 2 : 1) attn_partial_kernel(const
     attn_compute<HD, G, COMPACT, 0>(p, it, asmem, redg, &is_last, 0);
 }
 
+// The tensor-core form (attn_mma.cuh), two CTAs per SM.
+template <int HD, int G>
+__global__ void __launch_bounds__(kT, 2) attn_mma_kernel(const AttnParams p) {
+    extern __shared__ __align__(128) uint8_t asmem[];
+    using L = AttnMmaSmem<HD, G>;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(asmem + L::kBarOff);
+    __shared__ float redg[kMaxGroup * 8];
+    __shared__ int is_last;
+    if (threadIdx.x == 0) {
+        mbar_init(&bars[0], 1);
+        mbar_init(&bars[1], 1);
+        mbar_fence_init();
+    }
+    pdl_launch_dependents();
+    pdl_wait();
+    __syncthreads();
+    const AttnItem it = attn_item<HD>(p, blockIdx.x, blockIdx.y, blockIdx.z, p.pos[blockIdx.z]);
+    if (!it.active) return;
+    attn_compute_mma<HD, G>(p, it, asmem, redg, &is_last);
+}
+
 template <int HD>
 __global__ void __launch_bounds__(HD) attn_combine_kernel(const AttnParams p) {
     pdl_launch_dependents();
@@ -225,7 +246,20 @@ cudaError_t launch_attn_variant(const AttnParams& p, bool pdl, cudaStream_t st, 
     return launch_pdl(attn_partial_kernel<HD, G, COMPACT>, grid, dim3(kT), AttnSmem<HD, G, COMPACT>::kBytes, pdl, st, p);
 }
 template <int HD, int G>
+cudaError_t launch_attn_mma(const AttnParams& p, bool pdl, cudaStream_t st, int dev) {
+    static bool attr_set[64] = {};
+    if (!attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(attn_mma_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             AttnMmaSmem<HD, G>::kBytes);
+        if (e != cudaSuccess) return e;
+        attr_set[dev] = true;
+    }
+    const dim3 grid((unsigned)p.max_chunks, (unsigned)p.Nkv, (unsigned)p.B);
+    return launch_pdl(attn_mma_kernel<HD, G>, grid, dim3(kT), AttnMmaSmem<HD, G>::kBytes, pdl, st, p);
+}
+template <int HD, int G>
 cudaError_t launch_attn_partial(const AttnParams& p, bool pdl, cudaStream_t st, int dev) {
+    if (p.mma) return launch_attn_mma<HD, G>(p, pdl, st, dev);
     // many CTAs (token batches, prompt tiles): the one-buffer form, several CTAs per SM
     const bool compact = (long)p.max_chunks * p.Nkv * p.B >= 512;
     return compact ? launch_attn_variant<HD, G, true>(p, pdl, st, dev) : launch_attn_variant<HD, G, false>(p, pdl, st, dev);

@@ -242,11 +242,13 @@ int forward(ter_b200_handle_t* h, TerbModel* m, bool use_forced, cudaStream_t st
             AttnParams ap{m->q, kc, vc, posv, m->attn_scratch, m->att, B, c.Nh, c.Nkv, c.Hd, c.Smax,
                           (c.Smax + kAttnChunk - 1) / kAttnChunk, nullptr, nullptr, nullptr, nullptr, nullptr, 0,
                           h->status_dev, h->attn_inline_merge ? m->attn_counters : nullptr, pre_seq + 1};
+            ap.mma = B >= h->attn_mma_min;
             CK(launch_attention(ap, pdl, st));
         } else {
             AttnParams ap{m->q, kc, vc, m->pos, m->attn_scratch, m->att, B, c.Nh, c.Nkv, c.Hd, c.Smax,
                           (c.Smax + kAttnChunk - 1) / kAttnChunk, m->rope, m->k, m->v, kc, vc, bitnet ? 1 : 0,
                           h->status_dev, h->attn_inline_merge ? m->attn_counters : nullptr, 0};
+            ap.mma = B >= h->attn_mma_min;
             CK(launch_attention(ap, pdl, st));
         }
         if (!h->attn_inline_merge) h->launches += 1;

@@ -121,6 +121,43 @@ def test_attention(tb, Nh, Nkv, Hd, Smax, lens):
         assert np.array_equal(bits(out[b]), bits(want)), (b, n)        # the chunked form, bit for bit
 
 
+@pytest.mark.parametrize("Nh,Nkv,Hd,Smax,lens", [
+    (32, 8, 64, 512, [1, 2, 15, 16, 17, 255, 256, 257, 400, 512]),
+    (20, 5, 128, 2176, [1, 300, 2048, 2176, 33, 1000, 513, 2047]),
+    (4, 1, 64, 700, [77, 700, 1, 256]),
+    (8, 1, 128, 300, [64, 300]),
+    (8, 4, 128, 600, [600, 31, 272]),
+    (3, 3, 64, 300, [300, 8, 129]),
+])
+def test_attention_on_tensor_cores(tb, Nh, Nkv, Hd, Smax, lens):
+    """Token batches sum the two contractions of attention on the tensor cores (bf16 mma, q and the
+    probabilities split into three bf16 parts, so every product is exact).  Only the order of the fp32 sums
+    differs from the checker's, hence a tolerance: 2e-6 of the largest output of the head per element."""
+    rng = np.random.default_rng(Smax + Hd)
+    B = len(lens)
+    q = rng.standard_normal((B, Nh * Hd)).astype(np.float32)
+    kc, vc = make_cache(rng, B, Nkv, Smax, Hd)
+    pos = np.array([n - 1 for n in lens], np.int32)
+    args = (dev(q), dev(kc.view(np.int16)), dev(vc.view(np.int16)), dev(pos), Nh, Nkv, Hd, Smax)
+    tb.set_option("attn_mma_min", 1)
+    try:
+        got = tb.attention(*args).cpu().numpy()
+    finally:
+        tb.set_option("attn_mma_min", 0)
+    try:
+        exact = tb.attention(*args).cpu().numpy()
+    finally:
+        tb.set_option("attn_mma_min", 8)
+    for b, n in enumerate(lens):
+        want = oracle.attention(q[b], kc[b], vc[b], Nh, Nkv, Hd, Smax, n)
+        assert np.array_equal(bits(exact[b]), bits(want)), (b, n)
+    g3, e3 = got.reshape(B, Nh, Hd), exact.reshape(B, Nh, Hd)
+    tol = 2e-6 * np.max(np.abs(e3), axis=2, keepdims=True)
+    assert not np.isnan(got).any()
+    assert np.all(np.abs(g3 - e3) <= tol), float(np.max(np.abs(g3 - e3) / tol))
+    assert tb.device_status() == 0
+
+
 @pytest.mark.parametrize("V,H,B", [(1000, 256, 1), (4099, 2048, 2), (128256, 2048, 1), (3000, 2560, 3)])
 def test_lm_head_and_argmax(tb, V, H, B):
     rng = np.random.default_rng(V)
