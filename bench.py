@@ -525,6 +525,8 @@ def main():
     ap.add_argument("--no-reference-gpu", action="store_true", help="skip the reference's CUDA programs on this GPU")
     ap.add_argument("--no-batch64", action="store_true", help="skip the batch-64 BitNet decode run (about 30 s)")
     ap.add_argument("--no-parity", action="store_true", help="skip the decode token checks against the CPU checker")
+    ap.add_argument("--no-mma-attention", action="store_true",
+                    help="skip the extra batch-64 run with the opt-in tensor-core attention (about 20 s)")
     ap.add_argument("--cold-batch64", action="store_true", help="time the batch-64 run without a warm-up call")
     ap.add_argument("--layers", type=int, default=16, help="layers of the fabric (profiling captures use fewer)")
     args = ap.parse_args()
@@ -756,6 +758,20 @@ def main():
                     d.pop("e2e_tokens_per_s", None)
                     tb2.close()
                 decode_bitnet.append(d)
+                if world == 1 and not args.no_mma_attention:
+                    # the same batch with option "attn_mma_min" = 8: attention of token batches sums its two
+                    # contractions on the tensor cores.  Opt-in, because the result is no longer bit-equal to the
+                    # CPU checker: sums differ in the last places, the int8 quantisers downstream turn some of
+                    # that into different roundings, and greedy tokens drift apart after some steps.
+                    tb.set_option("attn_mma_min", 8)
+                    try:
+                        m = decode_bench(tb, dev, rank, "bitnet", n_prompt=2048, n_gen=128, batch=64, smax=2176)
+                    finally:
+                        tb.set_option("attn_mma_min", 0)
+                    m["workload"] += ", opt-in tensor-core attention"
+                    m["option"] = "attn_mma_min=8 (default: off)"
+                    m["first_tokens_equal_to_default_path"] = m["first_tokens"] == d["first_tokens"]
+                    decode_bitnet.append(m)
 
     reference_gpu = None
     if rank == 0 and world == 1 and not args.no_decode and not args.no_reference_gpu:

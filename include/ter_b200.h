@@ -409,7 +409,10 @@ int ter_b200_last_cuda_error(const ter_b200_handle_t* h);
  * "decode_poll_ns" (pause between polls inside that kernel, default 0), "decode_fault_cta" (test hook, -1 = off: that
  * CTA keeps its q/k/v columns of layer 0 to itself so that its consumers' waits run out), "wait_ms" (limit of a
  * device-side wait on another CTA or GPU, default 2000), "lm_head_tc_min" (batch size from which the bf16 lm_head runs
- * on the tensor cores, default 16, 0 = never), "tp_p2p" (1, default: tensor-
+ * on the tensor cores, default 16, 0 = never), "attn_mma_min" (rows, i.e. sequences of a batch or positions of a
+ * prompt tile, from which attention sums its two contractions on the tensor cores; default 0 = never, because the
+ * result then differs from the fixed-order kernel in the last places and, after the int8 quantisers of the following
+ * layers, in some greedy tokens of a long generation; about 1.4x on a 64-sequence step at context 2048), "tp_p2p" (1, default: tensor-
  * parallel output slices travel by peer stores over NVLink inside one small kernel per exchange;
  * 0: NCCL all-gathers) and "tp_shard" (which blocks of a layer are column-sharded over the ranks:
  * bit 0 the attention block q/k/v/o, bit 1 the FFN block gate/up/down; the lm_head always is.

@@ -8,6 +8,8 @@
     python profile_cases.py glue             # the glue kernels alone: RMSNorm + int8 quantiser (64 rows x 2560), batched
                                              # attention (24 sequences x 5 KV heads x 2048 positions, 126 MB of K/V),
                                              # bf16 lm_head for 1 row (CUDA cores) and 64 rows (tensor cores), 657 MB table
+    python profile_cases.py attn 64          # attention of 64 sequences at context 2048 (335 MB of K/V): tensor-core and
+                                             # fixed-order kernels, 4 launches each, CUDA-event times printed
 
 Each holds at most a few GB on the device and finishes in seconds, so an `ncu` capture of it ends by itself.
 """
@@ -166,6 +168,36 @@ def glue():
     print("glue ok, status", tb.device_status())
 
 
+def attn(batch="64"):
+    """Attention of a token batch alone: `batch` sequences, 20 query / 5 KV heads of 128, context 2048, on the
+    tensor cores and in the fixed-order form; CUDA-event times of both are printed."""
+    import torch
+    from ter_b200 import TerB200
+    tb = TerB200(0)
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device=dev)
+    g.manual_seed(5)
+    B, Nh, Nkv, Hd, Smax = int(batch), 20, 5, 128, 2048
+    q = torch.randn((B, Nh * Hd), generator=g, device=dev)
+    kc = torch.randn((B, Nkv, Smax, Hd), generator=g, device=dev).to(torch.bfloat16)
+    vc = torch.randn((B, Nkv, Smax, Hd), generator=g, device=dev).to(torch.bfloat16)
+    pos = torch.full((B,), Smax - 1, dtype=torch.int32, device=dev)
+    for mode, name in ((1, "tensor cores"), (0, "fixed order")):
+        tb.set_option("attn_mma_min", mode)
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        for i in range(4):
+            if i == 1:
+                ev[0].record()
+            tb.attention(q, kc, vc, pos, Nh, Nkv, Hd, Smax)
+        ev[1].record()
+        torch.cuda.synchronize()
+        us = ev[0].elapsed_time(ev[1]) / 3 * 1e3
+        tb.set_option("attn_mma_min", 0)
+        print(f"attention {name}: {us:.1f} us per call, {2 * kc.numel() * 2 / us / 1e6:.2f} TB/s of K/V")
+    print("attn ok, status", tb.device_status())
+
+
 if __name__ == "__main__":
     case = sys.argv[1] if len(sys.argv) > 1 else "gemv_stream"
-    {"gemv_stream": gemv_stream, "sweep": sweep, "gemm": gemm, "decode": lambda: decode(*sys.argv[2:4]), "glue": glue}[case]()
+    {"gemv_stream": gemv_stream, "sweep": sweep, "gemm": gemm, "decode": lambda: decode(*sys.argv[2:4]), "glue": glue,
+     "attn": lambda: attn(*sys.argv[2:3])}[case]()

@@ -200,7 +200,7 @@ ter_b200_handle_t* ter_b200_create(int device) {
     h->attn_inline_merge = 1;
     h->decode_persistent = 1;
     h->lm_head_tc_min = 16;
-    h->attn_mma_min = 8;
+    h->attn_mma_min = 0x7fffffff;     // off: the fixed-order kernel keeps the forward equal to the CPU checker bit for bit
     h->decode_fault_cta = -1;
     h->decode_poll_ns = 0;
     h->wait_ms = 2000;

@@ -182,11 +182,18 @@ __global__ void __launch_bounds__(kT, COMPACT ? 2 : 1) attn_partial_kernel(const
     attn_compute<HD, G, COMPACT, 0>(p, it, asmem, redg, &is_last, 0);
 }
 
-// The tensor-core form (attn_mma.cuh), two CTAs per SM.
+// The tensor-core form (attn_mma.cuh), two or three CTAs per SM.
+struct AttnMmaArgs {
+    AttnParams a;
+    alignas(64) CUtensorMap kmap;     // over the rows of a.kcache / a.vcache: [rows][HD] bf16, boxes of 64 x 256
+    alignas(64) CUtensorMap vmap;
+};
 template <int HD, int G>
-__global__ void __launch_bounds__(kT, 2) attn_mma_kernel(const AttnParams p) {
-    extern __shared__ __align__(128) uint8_t asmem[];
+__global__ void __launch_bounds__(kT, AttnMmaSmem<HD, G>::kCtasPerSm) attn_mma_kernel(const __grid_constant__ AttnMmaArgs P) {
+    extern __shared__ uint8_t asmem_raw[];
+    uint8_t* asmem = asmem_raw + ((1024u - (smem_u32(asmem_raw) & 1023u)) & 1023u);   // the swizzle pattern wants it
     using L = AttnMmaSmem<HD, G>;
+    const AttnParams& p = P.a;
     uint64_t* bars = reinterpret_cast<uint64_t*>(asmem + L::kBarOff);
     __shared__ float redg[kMaxGroup * 8];
     __shared__ int is_last;
@@ -200,7 +207,7 @@ __global__ void __launch_bounds__(kT, 2) attn_mma_kernel(const AttnParams p) {
     __syncthreads();
     const AttnItem it = attn_item<HD>(p, blockIdx.x, blockIdx.y, blockIdx.z, p.pos[blockIdx.z]);
     if (!it.active) return;
-    attn_compute_mma<HD, G>(p, it, asmem, redg, &is_last);
+    attn_compute_mma<HD, G>(p, &P.kmap, &P.vmap, it, asmem, redg, &is_last);
 }
 
 template <int HD>
@@ -245,8 +252,32 @@ cudaError_t launch_attn_variant(const AttnParams& p, bool pdl, cudaStream_t st, 
     const dim3 grid((unsigned)p.max_chunks, (unsigned)p.Nkv, (unsigned)p.B);
     return launch_pdl(attn_partial_kernel<HD, G, COMPACT>, grid, dim3(kT), AttnSmem<HD, G, COMPACT>::kBytes, pdl, st, p);
 }
+// False when the cache cannot be described by a tensor map (base not 16-byte aligned): the caller then takes
+// the fixed-order kernel.
+template <int HD>
+bool attn_mma_maps(const AttnParams& p, AttnMmaArgs& args) {
+    EncodeTiledFn enc = encode_tiled();
+    if (!enc) return false;
+    const long seqs = p.shared_seq ? p.shared_seq : p.B;
+    const cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)(seqs * p.Nkv) * (cuuint64_t)p.Smax};
+    const cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)kAttnChunk};
+    const cuuint32_t estr[2] = {1, 1};
+    for (int i = 0; i < 2; ++i) {
+        void* base = const_cast<uint16_t*>(i == 0 ? p.kcache : p.vcache);
+        if (enc(i == 0 ? &args.kmap : &args.vmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return false;
+    }
+    return true;
+}
 template <int HD, int G>
-cudaError_t launch_attn_mma(const AttnParams& p, bool pdl, cudaStream_t st, int dev) {
+cudaError_t launch_attn_mma(const AttnParams& p, bool pdl, cudaStream_t st, int dev, bool& taken) {
+    AttnMmaArgs args;
+    args.a = p;
+    taken = attn_mma_maps<HD>(p, args);
+    if (!taken) return cudaSuccess;
     static bool attr_set[64] = {};
     if (!attr_set[dev]) {
         cudaError_t e = cudaFuncSetAttribute(attn_mma_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -255,11 +286,15 @@ cudaError_t launch_attn_mma(const AttnParams& p, bool pdl, cudaStream_t st, int 
         attr_set[dev] = true;
     }
     const dim3 grid((unsigned)p.max_chunks, (unsigned)p.Nkv, (unsigned)p.B);
-    return launch_pdl(attn_mma_kernel<HD, G>, grid, dim3(kT), AttnMmaSmem<HD, G>::kBytes, pdl, st, p);
+    return launch_pdl(attn_mma_kernel<HD, G>, grid, dim3(kT), AttnMmaSmem<HD, G>::kBytes, pdl, st, args);
 }
 template <int HD, int G>
 cudaError_t launch_attn_partial(const AttnParams& p, bool pdl, cudaStream_t st, int dev) {
-    if (p.mma) return launch_attn_mma<HD, G>(p, pdl, st, dev);
+    if (p.mma) {
+        bool taken = false;
+        const cudaError_t e = launch_attn_mma<HD, G>(p, pdl, st, dev, taken);
+        if (taken || e != cudaSuccess) return e;
+    }
     // many CTAs (token batches, prompt tiles): the one-buffer form, several CTAs per SM
     const bool compact = (long)p.max_chunks * p.Nkv * p.B >= 512;
     return compact ? launch_attn_variant<HD, G, true>(p, pdl, st, dev) : launch_attn_variant<HD, G, false>(p, pdl, st, dev);

@@ -82,7 +82,7 @@ struct ter_b200_handle_t {
     int tp_shard;               // bit 0: attention block column-sharded, bit 1: FFN block; the lm_head always is
     int tp_p2p;                 // 1: tensor-parallel exchanges over peer memory (exchange_sm100.cu); 0: NCCL all-gathers
     int attn_mma_min;           // attention over at least this many rows (sequences of a batch, positions of a prompt tile)
-                                // sums its two contractions on the tensor cores (0: never)
+                                // sums its two contractions on the tensor cores (default: never)
     int lm_head_tc_min;         // batches of at least this many sequences run the bf16 lm_head on the tensor cores (0: never)
     int decode_persistent;      // 1: a lone sequence on one GPU runs embedding + all layers of a step in one persistent kernel
     int decode_poll_ns;         // persistent decode kernel: pause between polls of a value that has not arrived

@@ -160,6 +160,38 @@ def test_batch_of_sixteen_prompts_as_token_batches_and_tensor_core_lm_head(tb):
     assert tb.device_status() == 0
 
 
+@pytest.mark.parametrize("cfg,seed", [(SMALL_LLAMA, 81), (SMALL_BITNET, 82)])
+def test_opt_in_tensor_core_attention_stays_close(tb, cfg, seed):
+    """Option "attn_mma_min" (off by default) sums the two contractions of attention on the tensor cores for
+    token batches and prompt tiles.  Its output differs from the checker's in the last places, and the int8
+    quantisers after it turn some of those differences into different roundings, so this path is NOT held to
+    token equality: the logits at the end of a 40-position prompt must stay within 5 % of the largest logit, nothing may
+    be NaN, and with the option off again the forward is the checker's bit for bit."""
+    B = 8
+    modelutil.build_gpu(tb, cfg, seed, max_batch=B)
+    om = modelutil.build_oracle(cfg, seed)
+    prompts = np.random.default_rng(seed).integers(0, cfg["V"], size=(B, 40)).astype(np.int32)
+    tb.set_option("lm_head_tc_min", 0)
+    try:
+        tb.set_option("attn_mma_min", 2)
+        tb.generate(prompts, 1)
+        lg_mma = tb.model_logits().copy()
+        tb.set_option("attn_mma_min", 0)
+        out = tb.generate(prompts, 1)
+        lg = tb.model_logits().copy()
+    finally:
+        tb.set_option("attn_mma_min", 0)
+        tb.set_option("lm_head_tc_min", 16)
+    assert not np.isnan(lg_mma).any()
+    for b in range(B):
+        want, wl = modelutil.oracle_generate(om, prompts[b], 1, want_logits=True)
+        assert out[b].tolist() == want.tolist(), b
+        assert np.array_equal(lg[b].view(np.uint32), wl[-1].view(np.uint32)), b
+    # both runs fed the same 40 prompt tokens: the logits of the last prompt position
+    assert np.max(np.abs(lg_mma - lg)) <= 5e-2 * np.max(np.abs(lg)), float(np.max(np.abs(lg_mma - lg)) / np.max(np.abs(lg)))
+    assert tb.device_status() == 0
+
+
 def test_reference_numpy_forward_tokens_on_gpu(tb, golden_dir):
     """Greedy tokens printed by the reference's own tools/llama_pyfwd.py / bitnet_pyfwd.py."""
     import make_pyfwd_golden as mk
