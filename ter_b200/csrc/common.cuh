@@ -42,12 +42,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait.  On expiry records DEV_TIMEOUT_MBAR in *status and returns false;
 // the caller carries on (its results are then meaningless, and the host sees the code).
+// Once any wait of the launch has expired (the status word is set), later waits give up after a short
+// budget instead of spinning the full limit each: a kernel with one lost copy returns promptly.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, int* status) {
-    for (uint32_t i = 0; i < kMbarSpinLimit; ++i)
+    bool expired_elsewhere = false;
+    for (uint32_t i = 0; i < kMbarSpinLimit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 0x3fffu) == 0x3fffu && status && *reinterpret_cast<volatile int*>(status) != DEV_OK) {
+            expired_elsewhere = true;
+            break;
+        }
+    }
     if (status) atomicExch(status, DEV_TIMEOUT_MBAR);
     // Second bounded chance for copies still in flight before the CTA moves on.
-    for (uint32_t i = 0; i < kMbarSpinLimit; ++i)
+    const uint32_t second = expired_elsewhere ? (1u << 14) : kMbarSpinLimit;
+    for (uint32_t i = 0; i < second; ++i)
         if (mbar_try_wait(bar, parity)) return false;
     return false;
 }

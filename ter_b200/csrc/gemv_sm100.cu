@@ -425,33 +425,39 @@ __global__ void __launch_bounds__(kThreads) gemv_trit_split_kernel(const __grid_
 template <int RB>
 __global__ void __launch_bounds__(kThreads, 2) gemv_trit_rows_kernel(const __grid_constant__ GemvParams p) {
     extern __shared__ __align__(16) uint8_t xrows[];   // [RB][Kpad] int8: the rows of this pass, zero-padded
-    __shared__ int red[kWarps][RB][17];      // 16 columns + the row's sum of x
+    __shared__ int red[kWarps][RB][16];
+    __shared__ int xsum_s[RB];                // sum of each staged row
     const int tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
     const int c = lane >> 3, sgm = lane & 7;
     const int n_chunks = p.Kpad >> 7;
     const int nb = (p.Kpad + kGemvKC - 1) / kGemvKC;
     const int last_kc = p.Kpad - (nb - 1) * kGemvKC;
-    int m, ls;
-    locate(p, (int)blockIdx.x, m, ls);
-    const uint8_t* sbase = p.W[m] + (size_t)ls * 4u * (size_t)p.Kpad;
-    auto waddr = [&](int j) -> const uint8_t* {
-        const int q = j >> 3;
-        const int kc = (q == nb - 1) ? last_kc : kGemvKC;
-        return sbase + (size_t)q * kStageBytes + c * kc + (j & 7) * 128 + sgm * 16;
-    };
     constexpr int CB = 4;                    // chunks per warp held in registers at once
     const int n_batches = (n_chunks + CB * kWarps - 1) / (CB * kWarps);
-    uint4 w[CB];
+    // chunk j of strip `strip` for this lane (chunk j -> warp j % kWarps)
+    auto load_batch = [&](int strip, int bt, uint4 (&w)[CB]) {
+        int m, ls;
+        locate(p, strip, m, ls);
+        const uint8_t* sbase = p.W[m] + (size_t)ls * 4u * (size_t)p.Kpad;
 #pragma unroll
-    for (int i = 0; i < CB; ++i) {
-        const int j = warp + kWarps * i;
-        w[i] = j < n_chunks ? ldg_stream(waddr(j)) : make_uint4(0, 0, 0, 0);
-    }
+        for (int i = 0; i < CB; ++i) {
+            const int j = warp + kWarps * (i + bt * CB);
+            if (j < n_chunks) {
+                const int q = j >> 3;
+                const int kc = (q == nb - 1) ? last_kc : kGemvKC;
+                w[i] = ldg_stream(sbase + (size_t)q * kStageBytes + c * kc + (j & 7) * 128 + sgm * 16);
+            }
+        }
+    };
+    uint4 w[CB];
+    int strip = (int)blockIdx.x;
+    load_batch(strip, 0, w);                 // weights are immutable: fetched before the producer of x is waited for
+    bool preloaded = true;                   // w holds batch 0 of the strip about to be processed
     pdl_launch_dependents();
     pdl_wait();
     for (int r0 = 0; r0 < p.rows; r0 += RB) {
-        // stage the rows of this pass in shared memory with one batch of coalesced 16-byte loads
+        // stage the rows of this pass in shared memory with one batch of coalesced 16-byte loads, then sum each
         {
             const int per_row = p.Kpad >> 4;
             for (int i = tid; i < RB * per_row; i += kThreads) {
@@ -460,75 +466,109 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_trit_rows_kernel(const __gri
                 if (r0 + rr < p.rows && k0 < p.K) v = *reinterpret_cast<const int4*>(p.x + (size_t)(r0 + rr) * p.K + k0);
                 *reinterpret_cast<int4*>(xrows + (size_t)rr * p.Kpad + k0) = v;
             }
-        }
-        __syncthreads();
-        int acc[RB][4];
-        int xl[RB];
+            __syncthreads();
+            if (warp < RB) {
+                int local = 0;
+                for (int i = lane; i < per_row; i += 32) {
+                    const int4 v = *reinterpret_cast<const int4*>(xrows + (size_t)warp * p.Kpad + (i << 4));
+                    local = __dp4a(v.x, 0x01010101, local);
+                    local = __dp4a(v.y, 0x01010101, local);
+                    local = __dp4a(v.z, 0x01010101, local);
+                    local = __dp4a(v.w, 0x01010101, local);
+                }
 #pragma unroll
-        for (int rr = 0; rr < RB; ++rr) { acc[rr][0] = acc[rr][1] = acc[rr][2] = acc[rr][3] = 0; xl[rr] = 0; }
-        for (int b = 0; b < n_batches; ++b) {
-            if (b > 0 || r0 > 0) {
+                for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
+                if (lane == 0) xsum_s[warp] = local;
+            }
+        }
+        // this CTA's strips: blockIdx, blockIdx + grid, ...
+        for (strip = (int)blockIdx.x; strip < p.n_tiles; strip += (int)gridDim.x) {
+            int m, ls;
+            locate(p, strip, m, ls);
+            int acc[RB][4];
+#pragma unroll
+            for (int rr = 0; rr < RB; ++rr) acc[rr][0] = acc[rr][1] = acc[rr][2] = acc[rr][3] = 0;
+            for (int bt = 0; bt < n_batches; ++bt) {
+                if (bt > 0 || !preloaded) load_batch(strip, bt, w);
+                preloaded = false;
 #pragma unroll
                 for (int i = 0; i < CB; ++i) {
-                    const int j = warp + kWarps * (i + b * CB);
-                    w[i] = j < n_chunks ? ldg_stream(waddr(j)) : make_uint4(0, 0, 0, 0);
+                    const int j = warp + kWarps * (i + bt * CB);
+                    if (j < n_chunks) {                     // uniform over the warp
+                        const int k0 = j * 128 + sgm * 16;
+#pragma unroll
+                        for (int rr = 0; rr < RB; ++rr)
+                            mac64(w[i], *reinterpret_cast<const int4*>(xrows + (size_t)rr * p.Kpad + k0), acc[rr][0],
+                                  acc[rr][1], acc[rr][2], acc[rr][3]);
+                    }
                 }
             }
+            // the 8 segment lanes of a byte-column: halve the values a lane carries at every step of the butterfly
+            // (lanes whose bit is set keep the upper half), so 4 + 2 + 1 row-quads cross lanes instead of 3 x 8
+            int v[RB * 4];
 #pragma unroll
-            for (int i = 0; i < CB; ++i) {
-                const int j = warp + kWarps * (i + b * CB);
-                const int k0 = j * 128 + sgm * 16;
-                const bool in = j < n_chunks;
+            for (int rr = 0; rr < RB; ++rr)
 #pragma unroll
-                for (int rr = 0; rr < RB; ++rr) {
-                    int4 xv = make_int4(0, 0, 0, 0);
-                    if (in) xv = *reinterpret_cast<const int4*>(xrows + (size_t)rr * p.Kpad + k0);
-                    mac64(w[i], xv, acc[rr][0], acc[rr][1], acc[rr][2], acc[rr][3]);
-                    xl[rr] = __dp4a(xv.x, 0x01010101, xl[rr]);
-                    xl[rr] = __dp4a(xv.y, 0x01010101, xl[rr]);
-                    xl[rr] = __dp4a(xv.z, 0x01010101, xl[rr]);
-                    xl[rr] = __dp4a(xv.w, 0x01010101, xl[rr]);
+                for (int e = 0; e < 4; ++e) v[rr * 4 + e] = acc[rr][e];
+            int n = RB * 4;
+#pragma unroll
+            for (int o = 4; o >= 1; o >>= 1) {
+                const bool up = (sgm & o) != 0;
+                n >>= 1;
+#pragma unroll
+                for (int i = 0; i < RB * 2; ++i) {
+                    if (i < n) {
+                        const int send = up ? v[i] : v[i + n];
+                        const int keep = up ? v[i + n] : v[i];
+                        v[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+                    }
                 }
             }
-        }
+            // lane sgm now holds values [sgm' * n, sgm' * n + n) of the RB*4, n = RB/2, with sgm' the bit-reversal
+            // implied by the three steps: the index of value i is  ((sgm&4) ? RB*2 : 0) + ((sgm&2) ? RB : 0) + ((sgm&1) ? RB/2 : 0) + i
+            {
+                const int base = ((sgm & 4) ? RB * 2 : 0) + ((sgm & 2) ? RB : 0) + ((sgm & 1) ? RB / 2 : 0);
 #pragma unroll
-        for (int o = 1; o < 8; o <<= 1) {
-#pragma unroll
-            for (int rr = 0; rr < RB; ++rr) {
-                acc[rr][0] += __shfl_xor_sync(0xffffffffu, acc[rr][0], o);
-                acc[rr][1] += __shfl_xor_sync(0xffffffffu, acc[rr][1], o);
-                acc[rr][2] += __shfl_xor_sync(0xffffffffu, acc[rr][2], o);
-                acc[rr][3] += __shfl_xor_sync(0xffffffffu, acc[rr][3], o);
-                xl[rr] += __shfl_xor_sync(0xffffffffu, xl[rr], o);
-            }
-        }
-        if (sgm == 0) {
-#pragma unroll
-            for (int rr = 0; rr < RB; ++rr) {
-                int* r = &red[warp][rr][c * 4];
-                r[0] = acc[rr][0] - acc[rr][1] - acc[rr][2] - acc[rr][3];
-                r[1] = acc[rr][1]; r[2] = acc[rr][2]; r[3] = acc[rr][3];
-                if (c == 0) red[warp][rr][16] = xl[rr];
-            }
-        }
-        __syncthreads();
-        if (tid < RB * 16) {
-            const int rr = tid >> 4, lc = tid & 15;
-            const int row = r0 + rr, col = ls * 16 + lc;
-            if (row < p.rows && col < p.N[m]) {
-                int sum = 0, xsum = 0;
-#pragma unroll
-                for (int wi = 0; wi < kWarps; ++wi) { sum += red[wi][rr][lc]; xsum += red[wi][rr][16]; }
-                const int v = (sum >> (2 * (lc & 3))) - xsum;
-                const size_t o = (size_t)row * (size_t)p.N[m] + col;
-                if (p.acc_out[m]) p.acc_out[m][o] = v;
-                if (p.out[m]) {
-                    const float f = (float)v * (p.x_scale[row] * p.w_scale[m]);
-                    p.out[m][o] = p.accumulate ? p.out[m][o] + f : f;
+                for (int i = 0; i < RB / 2; ++i) {
+                    const int idx = base + i, rr = idx >> 2, e = idx & 3;
+                    red[warp][rr][c * 4 + e] = v[i];
                 }
             }
+            __syncthreads();
+            // the next strip's first weights travel while this one is reduced and stored
+            const int next = strip + (int)gridDim.x;
+            if (next < p.n_tiles) { load_batch(next, 0, w); preloaded = true; }
+            else if (r0 + RB < p.rows) { load_batch((int)blockIdx.x, 0, w); preloaded = true; }
+            if (tid < RB * 16) {
+                const int rr = tid >> 4, lc = tid & 15;
+                const int row = r0 + rr, col = ls * 16 + lc;
+                if (row < p.rows && col < p.N[m]) {
+                    int sum = 0;
+#pragma unroll
+                    for (int wi = 0; wi < kWarps; ++wi) sum += red[wi][rr][lc];
+                    // fields 1..3 of a byte-column carry 4^i times their sum; field 0 is what is left of the
+                    // unmasked product after the other three are taken off
+                    const int f = lc & 3;
+                    int val;
+                    if (f == 0) {
+                        int s1 = 0, s2 = 0, s3 = 0;
+#pragma unroll
+                        for (int wi = 0; wi < kWarps; ++wi) { s1 += red[wi][rr][lc + 1]; s2 += red[wi][rr][lc + 2]; s3 += red[wi][rr][lc + 3]; }
+                        val = sum - s1 - s2 - s3;
+                    } else {
+                        val = sum >> (2 * f);
+                    }
+                    const int vv = val - xsum_s[rr];
+                    const size_t o = (size_t)row * (size_t)p.N[m] + col;
+                    if (p.acc_out[m]) p.acc_out[m][o] = vv;
+                    if (p.out[m]) {
+                        const float fl = (float)vv * (p.x_scale[row] * p.w_scale[m]);
+                        p.out[m][o] = p.accumulate ? p.out[m][o] + fl : fl;
+                    }
+                }
+            }
+            __syncthreads();
         }
-        __syncthreads();
     }
 }
 
@@ -550,7 +590,7 @@ cudaError_t launch_gemv(const GemvParams& p_in, const GemvLaunchCfg& cfg, cudaSt
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
-    if (p_in.rows >= 2) {   // a small token batch: all rows in one launch, one CTA per strip
+    if (p_in.rows >= 2) {   // a small token batch: all rows in one launch
         if (p_in.multi || p_in.fuse.x || p_in.act_pair || p_in.table || !p_in.x || (p_in.K & 15) ||
             (p_in.out[0] && !p_in.x_scale) || p_in.n_mats < 1 || p_in.n_mats > kGemvMaxGroup || p_in.rows > kGemvMaxRows)
             return cudaErrorInvalidValue;
@@ -565,7 +605,9 @@ cudaError_t launch_gemv(const GemvParams& p_in, const GemvLaunchCfg& cfg, cudaSt
             if (e != cudaSuccess) return e;
             rows_attr[dev][rb == 8] = true;
         }
-        lc.gridDim = dim3((unsigned)p_in.n_tiles);
+        // two CTAs per SM, every CTA resident; a CTA takes strips blockIdx, blockIdx + grid, ... and stages x once
+        const int wave = 2 * (cfg.sm_count > 0 ? cfg.sm_count : 148);
+        lc.gridDim = dim3((unsigned)(p_in.n_tiles < wave ? p_in.n_tiles : wave));
         lc.blockDim = dim3(kThreads);
         lc.dynamicSmemBytes = xsm;
         lc.stream = st;

@@ -295,8 +295,9 @@ cudaError_t launch_attn_partial(const AttnParams& p, bool pdl, cudaStream_t st, 
         const cudaError_t e = launch_attn_mma<HD, G>(p, pdl, st, dev, taken);
         if (taken || e != cudaSuccess) return e;
     }
-    // many CTAs (token batches, prompt tiles): the one-buffer form, several CTAs per SM
-    const bool compact = (long)p.max_chunks * p.Nkv * p.B >= 512;
+    // more CTAs than SMs (token batches, prompt tiles): the one-buffer form, three CTAs per SM, so that grids of
+    // up to 444 items still run as one wave
+    const bool compact = (long)p.max_chunks * p.Nkv * p.B > 148;
     return compact ? launch_attn_variant<HD, G, true>(p, pdl, st, dev) : launch_attn_variant<HD, G, false>(p, pdl, st, dev);
 }
 template <int HD>

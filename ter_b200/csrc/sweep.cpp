@@ -17,6 +17,8 @@
 
 #include "handle.h"
 
+#include <cuda.h>
+
 namespace terb {
 int ensure_host_staging(ter_b200_handle_t* h, size_t x_bytes, size_t out_floats);   // abi.cpp
 }
@@ -215,6 +217,26 @@ int ter_b200_gemv_plan_destroy(ter_b200_handle_t* h, int plan_id) {
     return TER_B200_OK;
 }
 
+
+// True when [dev_ptr, dev_ptr + bytes) lies inside a single allocation (or host registration) known to the driver.
+static bool run_in_one_allocation(void* dev_ptr, size_t bytes) {
+    typedef CUresult (*RangeFn)(CUdeviceptr*, size_t*, CUdeviceptr);
+    static RangeFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (RangeFn)ptr;
+    }
+    if (!fn) return false;
+    CUdeviceptr base = 0;
+    size_t size = 0;
+    if (fn(&base, &size, (CUdeviceptr)(uintptr_t)dev_ptr) != CUDA_SUCCESS) return false;
+    const uintptr_t p0 = (uintptr_t)dev_ptr;
+    return p0 >= (uintptr_t)base && p0 + bytes <= (uintptr_t)base + size;
+}
+
 int ter_b200_gemv_host_batch(ter_b200_handle_t* h, int n, const char* const* slots, const int8_t* const* x_hosts,
                              const float* x_scales, float* const* out_hosts, void* stream) {
     if (!h || !slots || !x_hosts || !x_scales || !out_hosts) return TER_B200_E_NULL;
@@ -282,11 +304,11 @@ int ter_b200_gemv_host_batch(ter_b200_handle_t* h, int n, const char* const* slo
                 len += (size_t)sl[j]->w.N;
                 ++j;
             }
-            cudaPointerAttributes a0, a1;
+            // The whole run must lie inside ONE pinned allocation or registration: with unified addressing the two
+            // ends alone prove nothing (pageable memory may lie between two pinned regions).
+            cudaPointerAttributes a0;
             if (cudaPointerGetAttributes(&a0, out_hosts[i]) == cudaSuccess && a0.type == cudaMemoryTypeHost &&
-                a0.devicePointer &&
-                cudaPointerGetAttributes(&a1, out_hosts[i] + len - 1) == cudaSuccess && a1.type == cudaMemoryTypeHost &&
-                a1.devicePointer == (void*)((float*)a0.devicePointer + len - 1)) {
+                a0.devicePointer && run_in_one_allocation(a0.devicePointer, len * sizeof(float))) {
                 for (int k = i; k < j; ++k) direct[k] = (float*)a0.devicePointer + (out_hosts[k] - out_hosts[i]);
             } else {
                 (void)cudaGetLastError();
