@@ -403,7 +403,7 @@ int ter_b200_selftest_exchange_timeout(ter_b200_handle_t* h);
 /* Last CUDA error code seen by the handle (cudaError_t as int), 0 if none. */
 int ter_b200_last_cuda_error(const ter_b200_handle_t* h);
 /* Tuning knobs (integers): "gemv_ctas_per_sm", "gemv_stages", "gemv_split_max_strips", "pdl",
- * "fuse_quant", "gemm_min_m" (rows from which the tcgen05 GEMM runs, default 17; 2..16 rows take the multi-row GEMV),
+ * "fuse_quant", "gemm_min_m" (rows from which the tcgen05 GEMM runs, default 9; 2..8 rows take the multi-row GEMV),
  * "gemm_split_k", "attn_inline_merge", "prefill", "prefill_tile", "host_batch_direct",
  * "decode_persistent" (1, default: one sequence runs the embedding and all layers of a step in one persistent kernel),
  * "decode_poll_ns" (pause between polls inside that kernel, default 0), "decode_fault_cta" (test hook, -1 = off: that

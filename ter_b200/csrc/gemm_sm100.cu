@@ -45,6 +45,32 @@ constexpr int kRawStageBytes = 4096;            // the packed trits of one step 
 // The packed trits travel through a thread-private ring of RING steps (template parameter of the kernel), RING - 2 of
 // them in flight as cp.async copies (a step is 4 KB per CTA).
 
+#ifdef TERB_TRACE
+// diagnostic build only: timestamps of the phases of each CTA of the last launch
+__device__ unsigned long long g_gemm_trace[512][8];
+__device__ __forceinline__ void gtr(int k) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+    if (cta < 512) g_gemm_trace[cta][k] = t;
+}
+#define GTR(k) gtr(k)
+// per-step timestamps of CTA 0: [step][0] MMA warp saw the stage full, [1] producer warp 0 has its packed bytes,
+// [2] ... has the free stage, [3] ... has arrived, [4] loader issued the copy
+__device__ unsigned long long g_gemm_steps[64][8];
+__device__ __forceinline__ void gts(int step, int k) {
+    if (blockIdx.x + blockIdx.y + blockIdx.z == 0 && step < 64) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        g_gemm_steps[step][k] = t;
+    }
+}
+#define GTS(s, k) gts(s, k)
+#else
+#define GTR(k) do {} while (0)
+#define GTS(s, k) do {} while (0)
+#endif
+
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
 }
@@ -65,31 +91,42 @@ __device__ __forceinline__ uint32_t umma_idesc_i8(int n_tokens) {
 
 struct GemmSmemLayout {
     int stages, tokens, ring;   // tokens = padded token tile (multiple of 16); ring = packed-trit steps buffered
+    int tiles;                  // 128-column tiles per CTA (1 or 2)
+    __host__ __device__ int a_stage_bytes() const { return tiles * kAStageBytes; }
+    __host__ __device__ int raw_stage_bytes() const { return tiles * kRawStageBytes; }
     __host__ __device__ int b_stage_bytes() const { return tokens * kKStep; }
-    __host__ __device__ int a_off(int s) const { return s * kAStageBytes; }
-    __host__ __device__ int b_off(int s) const { return stages * kAStageBytes + s * b_stage_bytes(); }
-    __host__ __device__ int raw_off(int s) const { return stages * (kAStageBytes + b_stage_bytes()) + s * kRawStageBytes; }
-    __host__ __device__ int tail_off() const { return stages * (kAStageBytes + b_stage_bytes()) + ring * kRawStageBytes; }
-    // tail: full[8], empty[8], done (u64 each) | tmem base, abort (16 B) | scale[256] (float) | rowsum[256] (int)
-    __host__ __device__ int bytes() const { return tail_off() + 17 * 8 + 16 + 2 * 256 * 4 + 1024; }
+    __host__ __device__ int a_off(int s) const { return s * a_stage_bytes(); }
+    __host__ __device__ int b_off(int s) const { return stages * a_stage_bytes() + s * b_stage_bytes(); }
+    __host__ __device__ int raw_off(int s) const { return stages * (a_stage_bytes() + b_stage_bytes()) + s * raw_stage_bytes(); }
+    __host__ __device__ int tail_off() const { return stages * (a_stage_bytes() + b_stage_bytes()) + ring * raw_stage_bytes(); }
+    // tail: full[8], empty[8], done, pad (u64 each) | tmem base, abort (16 B) | scale[256] (float) | rowsum[256] (int)
+    __host__ __device__ int bytes() const { return tail_off() + 18 * 8 + 16 + 2 * 256 * 4 + 1024; }
 };
 
-template <int kRawRing>
+// TILES: 128-column tiles per CTA.  With two, both tiles are multiplied by the same activation stage (two
+// accumulators in tensor memory), which halves the activation bytes a CTA pulls from L2 per multiply-add: for
+// batches whose one-tile grid would not fit the SMs in one wave.
+// PG: producer groups.  The eight producer warps form PG groups and group g expands steps g, g + PG, ...: what
+// paces a producer is the chain wait -> expand -> proxy fence -> arrive of one step, so several steps are expanded
+// side by side (a thread then owns PG times as many bytes of its steps).
+template <int kRawRing, int TILES, int PG>
 __global__ void __launch_bounds__(kGemmThreads) gemm_trit_kernel(const __grid_constant__ GemmParams p) {
-    constexpr int kRawAhead = kRawRing - 2;
+    constexpr int kRawAhead = (kRawRing - 2) / PG;      // own steps in flight per thread
+    constexpr int kGroupThreads = 32 * kProducerWarps / PG;
     extern __shared__ uint8_t gsm_raw[];
     // 1024-byte alignment: the swizzle pattern is a function of the shared-memory address bits
     uint8_t* gsm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(gsm_raw) + 1023) & ~(uintptr_t)1023);
-    GemmSmemLayout L{p.stages, p.tokens, kRawRing};
+    GemmSmemLayout L{p.stages, p.tokens, kRawRing, TILES};
     uint64_t* full = reinterpret_cast<uint64_t*>(gsm + L.tail_off());
     uint64_t* empty = full + 8;
     uint64_t* done = full + 16;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 2);   // keeps the arrays behind it 16-byte aligned
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     float* tok_scale = reinterpret_cast<float*>(tmem_slot + 4);     // [256] x_scales[m] * w_scale
     int* tok_sum = reinterpret_cast<int*>(tok_scale + 256);         // [256] sum_k X[m][k]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) GTR(0);
     // 128-column tile of which matrix of the group
     int mi = 0;
     while (mi + 1 < p.n_w && (int)blockIdx.x >= p.tile_begin[mi + 1]) ++mi;
@@ -108,7 +145,7 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_trit_kernel(const __grid_co
     const int S = p.stages;
 
     if (tid == 0) {
-        for (int i = 0; i < S; ++i) { mbar_init(&full[i], kProducerWarps + 1 /* the producer warps + the loader */); mbar_init(&empty[i], 1); }
+        for (int i = 0; i < S; ++i) { mbar_init(&full[i], kProducerWarps / PG + 1 /* the warps of one producer group + the loader */); mbar_init(&empty[i], 1); }
         mbar_init(done, 1);
         *abort_flag = 0;
         mbar_fence_init();
@@ -123,24 +160,23 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_trit_kernel(const __grid_co
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (tid == 0) GTR(1);
 
     pdl_launch_dependents();
     pdl_wait();
+    if (tid == 0) GTR(2);
 
     if (warp < kProducerWarps) {
         // ------------------------------------------------------------------ producers (256 threads)
-        // Every thread owns 16 packed bytes of every step (segment = (strip, byte-column) of 128 bytes,
-        // part = 16 of them): it copies them with cp.async into its private slot of a ring (kRawAhead steps
-        // in flight, no barrier needed: the same thread reads them back), then expands them into 4 rows of
-        // the A stage.  All producer warps take part in every step, so each sees every phase of the stage
-        // barriers in order (a parity wait must never skip a phase).
+        // A thread owns 16-byte pieces of the packed bytes of its group's steps (segment = (strip, byte-column) of
+        // 128 bytes, part = 16 of them): it copies them with cp.async into its private slots of a ring (kRawAhead
+        // of its steps in flight, no barrier needed: the same thread reads them back), then expands each piece
+        // into 4 rows of the A stage.  A group waits on the stage barriers of its own steps only; a barrier cannot
+        // run two phases ahead of such a wait, because the later phase needs this group's step to be multiplied.
         const int nb = (p.Kpad + kGemvKC - 1) / kGemvKC;
         const int last_kc = p.Kpad - (nb - 1) * kGemvKC;
-        const int seg = tid >> 3, part = tid & 7;          // 32 segments x 8 x 16 bytes
-        const int strip_l = seg >> 2, bc = seg & 3;
-        const int strip = tile * 8 + strip_l;
-        const bool strip_ok = strip < strips_m;
-        const uint8_t* sbase = Wm + (size_t)strip * 4u * (size_t)p.Kpad;
+        // a 128-column tile of a step is 32 segments x 8 parts of 16 bytes; a thread of a group owns PG of those pairs
+        const int grp = tid / kGroupThreads, gtid = tid % kGroupThreads;
         // per-token epilogue constants
         if (tid < p.tokens) {
             const int m = m0 + tid;
@@ -148,41 +184,56 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_trit_kernel(const __grid_co
             tok_sum[tid] = (m < p.M) ? p.x_rowsum[m] : 0;
         }
         bool ok = true;
-        auto issue = [&](int j) {
+        auto issue = [&](int j) {      // the packed bytes this thread owns of step j
             const int ks = step_begin + j;
-            uint8_t* raw = gsm + L.raw_off(j % kRawRing) + seg * 128 + part * 16;
-            if (strip_ok) {
-                const int q = ks >> 3;
-                const int kc = (q == nb - 1) ? last_kc : kGemvKC;
-                cp_async16(raw, sbase + (size_t)q * (4 * kGemvKC) + (size_t)bc * kc + (ks & 7) * 128 + part * 16);
-            } else {
-                *reinterpret_cast<uint4*>(raw) = make_uint4(0x55555555u, 0x55555555u, 0x55555555u, 0x55555555u);
-            }
+            const int q = ks >> 3;
+            const int kc = (q == nb - 1) ? last_kc : kGemvKC;
+#pragma unroll
+            for (int t = 0; t < TILES; ++t)
+#pragma unroll
+                for (int i = 0; i < PG; ++i) {
+                    const int pr = gtid + i * kGroupThreads, seg = pr >> 3, part = pr & 7;
+                    const int strip = (tile * TILES + t) * 8 + (seg >> 2), bc = seg & 3;
+                    uint8_t* raw = gsm + L.raw_off(j % kRawRing) + t * kRawStageBytes + seg * 128 + part * 16;
+                    if (strip < strips_m) {
+                        cp_async16(raw, Wm + (size_t)strip * 4u * (size_t)p.Kpad + (size_t)q * (4 * kGemvKC) + (size_t)bc * kc +
+                                            (ks & 7) * 128 + part * 16);
+                    } else {
+                        *reinterpret_cast<uint4*>(raw) = make_uint4(0x55555555u, 0x55555555u, 0x55555555u, 0x55555555u);
+                    }
+                }
             cp_async_commit();
         };
         for (int j = 0; j < kRawAhead; ++j)
-            if (j < n_steps) issue(j); else cp_async_commit();
-        for (int it = 0; it < n_steps; ++it) {
+            if (grp + j * PG < n_steps) issue(grp + j * PG); else cp_async_commit();
+        for (int it = grp; it < n_steps; it += PG) {
             const int s = it % S;
-            if (it + kRawAhead < n_steps) issue(it + kRawAhead); else cp_async_commit();
+            if (it + kRawAhead * PG < n_steps) issue(it + kRawAhead * PG); else cp_async_commit();
             cp_async_wait<kRawAhead>();      // this thread's packed bytes of step `it` have landed
+            if (gtid == 0) GTS(it, 1);
             // the A stage is free once the MMAs of step it - S have completed
             if (it >= S) ok = ok && mbar_wait_abortable(&empty[s], ((uint32_t)(it / S) & 1u) ^ 1u, abort_flag, p.status);
             if (!ok) break;
-            {
-                uint8_t* A = gsm + L.a_off(s);
-                const uint4 w = *reinterpret_cast<const uint4*>(gsm + L.raw_off(it % kRawRing) + seg * 128 + part * 16);
+            if (gtid == 0) GTS(it, 2);
 #pragma unroll
-                for (int f = 0; f < 4; ++f) {
-                    const uint32_t mk = 0x03030303u << (2 * f);
-                    const int r = strip_l * 16 + bc * 4 + f;                     // A row = local output column
-                    *reinterpret_cast<uint4*>(A + (r >> 3) * 1024 + (r & 7) * 128 + ((part ^ (r & 7)) * 16)) =
-                        make_uint4(w.x & mk, w.y & mk, w.z & mk, w.w & mk);
+            for (int t = 0; t < TILES; ++t)
+#pragma unroll
+                for (int i = 0; i < PG; ++i) {
+                    const int pr = gtid + i * kGroupThreads, seg = pr >> 3, part = pr & 7;
+                    uint8_t* A = gsm + L.a_off(s) + t * kAStageBytes;
+                    const uint4 w = *reinterpret_cast<const uint4*>(gsm + L.raw_off(it % kRawRing) + t * kRawStageBytes + seg * 128 + part * 16);
+#pragma unroll
+                    for (int f = 0; f < 4; ++f) {
+                        const uint32_t mk = 0x03030303u << (2 * f);
+                        const int r = (seg >> 2) * 16 + (seg & 3) * 4 + f;           // A row = local output column
+                        *reinterpret_cast<uint4*>(A + (r >> 3) * 1024 + (r & 7) * 128 + ((part ^ (r & 7)) * 16)) =
+                            make_uint4(w.x & mk, w.y & mk, w.z & mk, w.w & mk);
+                    }
                 }
-            }
             fence_async_smem();          // make the generic-proxy writes visible to the tensor core
             __syncwarp();
             if (lane == 0) mbar_arrive(&full[s]);
+            if (gtid == 0) GTS(it, 3);
         }
         cp_async_wait<0>();
     } else if (warp == kProducerWarps + 1) {
@@ -195,6 +246,7 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_trit_kernel(const __grid_co
                 if (j >= S) ok = mbar_wait_abortable(&empty[s], ((uint32_t)(j / S) & 1u) ^ 1u, abort_flag, p.status);
                 if (!ok) break;
                 mbar_arrive_expect_tx(&full[s], bytes);
+                GTS(j, 4);
                 asm volatile(
                     "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                     ::"r"(smem_u32(gsm + L.b_off(s))), "l"(reinterpret_cast<uint64_t>(&p.xmap)),
@@ -211,18 +263,23 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_trit_kernel(const __grid_co
             const uint32_t ph = (uint32_t)(it / S) & 1u;
             ok = mbar_wait_abortable(&full[s], ph, abort_flag, p.status);
             if (!ok) break;
+            if (it == 0) GTR(3);
+            GTS(it, 0);
             tc_fence_after();
-            const uint64_t adesc = umma_desc_sw128(smem_u32(gsm + L.a_off(s)));
             const uint64_t bdesc = umma_desc_sw128(smem_u32(gsm + L.b_off(s)));
 #pragma unroll
-            for (int kk = 0; kk < kKStep / 32; ++kk) {
-                const uint32_t accum = (it > 0 || kk > 0) ? 1u : 0u;
-                asm volatile(
-                    "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                    "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-                    ::"r"(tmem_base), "l"(adesc + (uint64_t)(kk * 2)), "l"(bdesc + (uint64_t)(kk * 2)), "r"(idesc),
-                      "r"(accum)
-                    : "memory");
+            for (int t = 0; t < TILES; ++t) {
+                const uint64_t adesc = umma_desc_sw128(smem_u32(gsm + L.a_off(s) + t * kAStageBytes));
+#pragma unroll
+                for (int kk = 0; kk < kKStep / 32; ++kk) {
+                    const uint32_t accum = (it > 0 || kk > 0) ? 1u : 0u;
+                    asm volatile(
+                        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+                        ::"r"(tmem_base + (uint32_t)(t * p.tokens)), "l"(adesc + (uint64_t)(kk * 2)),
+                          "l"(bdesc + (uint64_t)(kk * 2)), "r"(idesc), "r"(accum)
+                        : "memory");
+                }
             }
             // release the stage when the MMAs that read it have completed
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
@@ -231,6 +288,7 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_trit_kernel(const __grid_co
         }
         asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(done))
                      : "memory");
+        GTR(4);
     }
     __syncwarp();
 
@@ -238,40 +296,60 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_trit_kernel(const __grid_co
         // ------------------------------------------------------------------ epilogue (8 warps)
         asm volatile("bar.sync 1, 256;" ::: "memory");     // tok_scale / tok_sum visible to all producer warps
         const bool ok = n_steps > 0 && mbar_wait_abortable(done, 0, abort_flag, p.status);
+        if (tid == 0) GTR(5);
         tc_fence_after();
         const int quarter = warp & 3;                      // the TMEM lanes this warp may read
         const int nl = quarter * 32 + lane;                // TMEM lane = local output column
-        const int n = tile * kTileN + nl;
         const int shift = 2 * (nl & 3);
         // warps 0-3 take the even 32-token groups, warps 4-7 the odd ones
         if (ok) {
-            for (int c0 = (warp >> 2) * 32; c0 < p.tokens; c0 += 64) {
-                uint32_t d[32];
-                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
-                asm volatile(
-                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                    "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-                    "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-                    : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]), "=r"(d[4]), "=r"(d[5]), "=r"(d[6]), "=r"(d[7]),
-                      "=r"(d[8]), "=r"(d[9]), "=r"(d[10]), "=r"(d[11]), "=r"(d[12]), "=r"(d[13]), "=r"(d[14]), "=r"(d[15]),
-                      "=r"(d[16]), "=r"(d[17]), "=r"(d[18]), "=r"(d[19]), "=r"(d[20]), "=r"(d[21]), "=r"(d[22]), "=r"(d[23]),
-                      "=r"(d[24]), "=r"(d[25]), "=r"(d[26]), "=r"(d[27]), "=r"(d[28]), "=r"(d[29]), "=r"(d[30]), "=r"(d[31])
-                    : "r"(taddr));
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (n < Nm) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int m = m0 + c0 + j;
-                        if (c0 + j < p.tokens && m < p.M) {
-                            const size_t o = (size_t)m * Nm + n;
-                            if (p.ksplits > 1) {
-                                atomicAdd(&partm[o], (int)d[j]);
-                            } else {
-                                const int v = ((int)d[j] >> shift) - tok_sum[c0 + j];
-                                if (p.acc_out) p.acc_out[o] = v;
-                                if (outm) {
-                                    const float f = (float)v * tok_scale[c0 + j];
-                                    outm[o] = p.accumulate ? outm[o] + f : f;
+            for (int t = 0; t < TILES; ++t) {
+                const int n = (tile * TILES + t) * kTileN + nl;
+                for (int c0 = (warp >> 2) * 32; c0 < p.tokens; c0 += 64) {
+                    uint32_t d[32];
+                    const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(t * p.tokens + c0);
+                    asm volatile(
+                        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+                        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]), "=r"(d[4]), "=r"(d[5]), "=r"(d[6]), "=r"(d[7]),
+                          "=r"(d[8]), "=r"(d[9]), "=r"(d[10]), "=r"(d[11]), "=r"(d[12]), "=r"(d[13]), "=r"(d[14]), "=r"(d[15]),
+                          "=r"(d[16]), "=r"(d[17]), "=r"(d[18]), "=r"(d[19]), "=r"(d[20]), "=r"(d[21]), "=r"(d[22]), "=r"(d[23]),
+                          "=r"(d[24]), "=r"(d[25]), "=r"(d[26]), "=r"(d[27]), "=r"(d[28]), "=r"(d[29]), "=r"(d[30]), "=r"(d[31])
+                        : "r"(taddr));
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (n < Nm) {
+                        // tokens of this group that exist; the common case (a full group, plain fp32 output) runs
+                        // without a test per element: the epilogue is instruction-bound (8 warps, 128 values a thread)
+                        const int rows = min(32, min(p.tokens - c0, p.M - (m0 + c0)));
+                        if (p.ksplits > 1) {
+                            int32_t* po = partm + (size_t)(m0 + c0) * Nm + n;
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (j < rows) atomicAdd(po + (size_t)j * Nm, (int)d[j]);
+                        } else if (rows == 32 && !p.acc_out && outm && !p.accumulate) {
+                            float* po = outm + (size_t)(m0 + c0) * Nm + n;
+#pragma unroll
+                            for (int j4 = 0; j4 < 8; ++j4) {
+                                const int4 ts = *reinterpret_cast<const int4*>(&tok_sum[c0 + 4 * j4]);
+                                const float4 sc = *reinterpret_cast<const float4*>(&tok_scale[c0 + 4 * j4]);
+                                po[(size_t)(4 * j4 + 0) * Nm] = (float)(((int)d[4 * j4 + 0] >> shift) - ts.x) * sc.x;
+                                po[(size_t)(4 * j4 + 1) * Nm] = (float)(((int)d[4 * j4 + 1] >> shift) - ts.y) * sc.y;
+                                po[(size_t)(4 * j4 + 2) * Nm] = (float)(((int)d[4 * j4 + 2] >> shift) - ts.z) * sc.z;
+                                po[(size_t)(4 * j4 + 3) * Nm] = (float)(((int)d[4 * j4 + 3] >> shift) - ts.w) * sc.w;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                if (j < rows) {
+                                    const size_t o = (size_t)(m0 + c0 + j) * Nm + n;
+                                    const int v = ((int)d[j] >> shift) - tok_sum[c0 + j];
+                                    if (p.acc_out) p.acc_out[o] = v;
+                                    if (outm) {
+                                        const float f = (float)v * tok_scale[c0 + j];
+                                        outm[o] = p.accumulate ? outm[o] + f : f;
+                                    }
                                 }
                             }
                         }
@@ -280,8 +358,10 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_trit_kernel(const __grid_co
             }
         }
     }
+    if (tid == 0) GTR(6);
     tc_fence_before();
     __syncthreads();
+    if (tid == 0) GTR(7);
     if (warp == kProducerWarps) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)p.tmem_cols)
@@ -342,6 +422,11 @@ __global__ void __launch_bounds__(256) gemm_finalize_kernel(const GemmParams p) 
 
 }  // namespace
 
+#ifndef TERB_GEMM_PG
+#define TERB_GEMM_PG 1     // 2 and 4 measured the same: the MMA-issuing thread paces the loop, not the producers
+#endif
+constexpr int kPG = TERB_GEMM_PG;
+
 cudaError_t launch_gemm(const GemmParams& p_in, int sm_count, bool pdl, cudaStream_t st) {
     GemmParams p = p_in;
     if (p.M < 1 || p.K % 16 != 0 || p.Kpad % kKStep != 0) return cudaErrorInvalidValue;
@@ -349,38 +434,54 @@ cudaError_t launch_gemm(const GemmParams& p_in, int sm_count, bool pdl, cudaStre
     int tokens = (p.M + 15) / 16 * 16;
     if (tokens > 256) tokens = 256;
     p.tokens = tokens;
-    int cols = 32;
-    while (cols < tokens) cols *= 2;
-    p.tmem_cols = cols;
     const int m_tiles = (p.M + tokens - 1) / tokens;
     if (p.n_w == 0) {   // the single matrix given by the scalar fields
         p.n_w = 1;
         p.Wg[0] = p.W; p.outg[0] = p.out; p.wsg[0] = p.w_scale; p.Ng[0] = p.N; p.stripsg[0] = p.n_strips;
     }
     if (p.n_w < 1 || p.n_w > kGemmMaxGroup || (p.n_w > 1 && p.acc_out)) return cudaErrorInvalidValue;
+    // Two 128-column tiles per CTA when the one-tile grid would need more than one wave of the SMs (several token
+    // tiles): the CTA then reads each activation stage once for 256 columns.
+    int tiles = 1;
+    {
+        int t1 = 0;
+        for (int w = 0; w < p.n_w; ++w) t1 += (p.stripsg[w] + 7) / 8;
+        if (m_tiles >= 2 && (long)t1 * m_tiles > sm_count && tokens == 256) tiles = 2;
+    }
+    int cols = 32;
+    while (cols < tiles * tokens) cols *= 2;
+    p.tmem_cols = cols;
     int n_tiles = 0;
     size_t part_ints = 0;
     for (int w = 0; w < p.n_w; ++w) {
         p.tile_begin[w] = n_tiles;
-        n_tiles += (p.stripsg[w] + 7) / 8;
+        n_tiles += (p.stripsg[w] + 8 * tiles - 1) / (8 * tiles);
         p.part_off[w] = part_ints;
         part_ints += (size_t)p.M * (size_t)p.Ng[w];
     }
     p.tile_begin[p.n_w] = n_tiles;
     const int steps = p.Kpad / kKStep;
-    // split K so that the grid covers the SMs (the weights are the traffic; every CTA streams its share)
+    // Split K so that the grid covers the SMs, when that pays: a CTA's main loop costs about 0.48 us per 128-k step
+    // whatever the token tile (the MMA-issuing thread paces it), and splitting saves (1 - 1/ksplits) of it; against
+    // that stand the integer atomics of the partial sums and the second kernel, about 1.5 us + 1 us per 100 k
+    // outputs (measured on the BitNet-2B shapes, 17 to 256 rows).
     int ksplits = 1;
-    if (p.part_buf && p.M <= 256) {   // weight-bandwidth-bound regime only; larger batches have enough work per tile
-        ksplits = sm_count / (n_tiles * m_tiles);
-        if (ksplits > steps / 4) ksplits = steps / 4;
-        if (ksplits < 1) ksplits = 1;
+    if (p.part_buf && p.M <= 256) {
+        int ks = sm_count / (n_tiles * m_tiles);
+        if (ks > steps / 4) ks = steps / 4;
+        if (ks > 1) {
+            size_t outputs = 0;
+            for (int w = 0; w < p.n_w; ++w) outputs += (size_t)p.M * (size_t)p.Ng[w];
+            const double gain = 0.48 * steps * (1.0 - 1.0 / ks), cost = 1.5 + (double)outputs / 1.0e5;
+            if (gain > cost) ksplits = ks;
+        }
     }
     for (int w = 0; w < p.n_w; ++w)     // the second pass moves four columns at a time
         if ((p.Ng[w] & 3) || (reinterpret_cast<uintptr_t>(p.outg[w]) & 15u)) ksplits = 1;
     if (reinterpret_cast<uintptr_t>(p.acc_out) & 15u) ksplits = 1;
     p.ksplits = ksplits;
     const int ring = 8;     // a 24-step ring for small token tiles measured no faster: the producers' work per step paces the loop
-    GemmSmemLayout L{8, tokens, ring};                          // as many stages as fit, at most 8
+    GemmSmemLayout L{8, tokens, ring, tiles};                   // as many stages as fit, at most 8
     while (L.stages > 2 && L.bytes() > 220 * 1024) --L.stages;
     if (L.bytes() > 220 * 1024) return cudaErrorInvalidValue;
     p.stages = L.stages;
@@ -403,7 +504,9 @@ cudaError_t launch_gemm(const GemmParams& p_in, int sm_count, bool pdl, cudaStre
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
     if (!attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_trit_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(gemm_trit_kernel<8, 1, kPG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        if (e != cudaSuccess) return e;
+        e = cudaFuncSetAttribute(gemm_trit_kernel<8, 2, kPG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
@@ -438,7 +541,7 @@ cudaError_t launch_gemm(const GemmParams& p_in, int sm_count, bool pdl, cudaStre
     lc.stream = st;
     lc.attrs = attr;
     lc.numAttrs = pdl ? 1 : 0;   // after a memset node keep plain stream order
-    e = cudaLaunchKernelEx(&lc, gemm_trit_kernel<8>, p);
+    e = tiles == 2 ? cudaLaunchKernelEx(&lc, gemm_trit_kernel<8, 2, kPG>, p) : cudaLaunchKernelEx(&lc, gemm_trit_kernel<8, 1, kPG>, p);
     if (e != cudaSuccess || ksplits == 1) return e;
     cudaLaunchConfig_t lf = {};
     int max_n = 0;
@@ -450,5 +553,16 @@ cudaError_t launch_gemm(const GemmParams& p_in, int sm_count, bool pdl, cudaStre
     lf.numAttrs = pdl ? 1 : 0;
     return cudaLaunchKernelEx(&lf, gemm_finalize_kernel, p);
 }
+
+#ifdef TERB_TRACE
+extern "C" int ter_b200_debug_gemm_steps(unsigned long long* host) {
+    cudaDeviceSynchronize();
+    return (int)cudaMemcpyFromSymbol(host, g_gemm_steps, sizeof(unsigned long long) * 64 * 8);
+}
+extern "C" int ter_b200_debug_gemm_trace(unsigned long long* host) {
+    cudaDeviceSynchronize();
+    return (int)cudaMemcpyFromSymbol(host, g_gemm_trace, sizeof(unsigned long long) * 512 * 8);
+}
+#endif
 
 }  // namespace terb

@@ -74,7 +74,7 @@ struct ter_b200_handle_t {
     void* retired[64];
     int n_retired;
     size_t gemm_scratch_cap_prev, gemm_part_cap_prev;   // sizes of the latest allocations (growth is geometric)
-    int gemm_min_m;             // batches below this go row by row through the GEMV kernel
+    int gemm_min_m;             // batches below this take the multi-row GEMV (or, past its limits, one GEMV per row)
     int gemm_split_k;           // 0 = never split K
     int host_batch_direct;      // 1: ter_b200_gemv_host_batch lets the kernel write results into pinned host buffers
     int prefill_tile;           // prompt positions per pass (at most 1024)

@@ -137,7 +137,8 @@ def test_token_batch_through_tensor_core_gemm(tb, cfg, seed):
 
 def test_batch_of_sixteen_prompts_as_token_batches_and_tensor_core_lm_head(tb):
     """Sixteen sequences: the prompts run one sequence after the other as token batches, the decode steps take
-    the multi-row GEMV, and the lm_head runs on the tensor cores (rounding-level differences in the logits).
+    the tensor-core GEMM (bit-exact integer sums), and the lm_head runs on the tensor cores (rounding-level
+    differences in the logits).
     Every sequence must reproduce its own single-sequence tokens; logits within 1e-4 of the largest."""
     cfg, seed, B = dict(SMALL_BITNET, H=512, V=3000), 71, 16
     modelutil.build_gpu(tb, cfg, seed, max_batch=B)
@@ -303,13 +304,15 @@ def test_dispatch_rule_names_the_kernel(tb):
     assert tb.pick_kernel(1, 2048, 512) == "gemv_trit_split_kernel"
     assert tb.pick_kernel(1, 2048, 128256) == "gemv_trit_kernel"
     assert tb.pick_kernel(8, 2560, 6912) == "gemv_trit_rows_kernel"
-    assert tb.pick_kernel(16, 2560, 6912) == "gemv_trit_rows_kernel"
+    assert tb.pick_kernel(9, 2560, 6912) == "gemm_trit_kernel"
     assert tb.pick_kernel(64, 2560, 6912) == "gemm_trit_kernel"
     try:
         tb.set_option("gemm_min_m", 4)
         assert tb.pick_kernel(8, 2560, 6912) == "gemm_trit_kernel"
-    finally:
         tb.set_option("gemm_min_m", 17)
+        assert tb.pick_kernel(16, 2560, 6912) == "gemv_trit_rows_kernel"
+    finally:
+        tb.set_option("gemm_min_m", 9)
 
 
 def test_model_state_errors(tb):

@@ -59,22 +59,23 @@ def test_bitnet_shapes(tb, name, M):
 
 @pytest.mark.parametrize("K,N", [(2560, 640), (6912, 2560), (432, 80)])
 def test_few_rows_one_launch_and_tensor_core_gemm_agree(tb, K, N):
-    """Up to 16 token rows take the multi-row GEMV (one launch, the weights stream once); from option
-    "gemm_min_m" rows on the tcgen05 GEMM.  Both must give the checker's bits at the same M."""
+    """Few token rows take the multi-row GEMV (one launch for up to 16 rows; the default rule uses it up to 8); from
+    option "gemm_min_m" rows on the tcgen05 GEMM.  Both must give the checker's bits at the same M."""
     for M in (2, 3, 8, 13, 16):
         t, ws, X, xs = make(K, N, M, K + M)
         tb.install("fr", synth.pack_v11(t), FMT_V11, K, N, float(ws))
         want = (X.astype(np.int64) @ t.astype(np.int64))
         want_f = np.stack([oracle.gemv_epilogue(want[m].astype(np.int32), xs[m], ws) for m in range(M)])
-        l0 = tb.launch_count()
-        out_rows = tb.gemm("fr", dev(X), dev(xs)).cpu().numpy()
-        assert tb.launch_count() - l0 == 1                       # one launch for all rows
-        assert np.array_equal(tb.gemm_acc("fr", dev(X)).cpu().numpy().astype(np.int64), want)
         try:
+            tb.set_option("gemm_min_m", 17)
+            l0 = tb.launch_count()
+            out_rows = tb.gemm("fr", dev(X), dev(xs)).cpu().numpy()
+            assert tb.launch_count() - l0 == 1                       # one launch for all rows
+            assert np.array_equal(tb.gemm_acc("fr", dev(X)).cpu().numpy().astype(np.int64), want)
             tb.set_option("gemm_min_m", 2)
             out_tc = tb.gemm("fr", dev(X), dev(xs)).cpu().numpy()
         finally:
-            tb.set_option("gemm_min_m", 17)
+            tb.set_option("gemm_min_m", 9)
         assert np.array_equal(out_rows.view(np.uint32), want_f.view(np.uint32)), (K, N, M)
         assert np.array_equal(out_tc.view(np.uint32), want_f.view(np.uint32)), (K, N, M)
     assert tb.device_status() == 0
@@ -91,7 +92,7 @@ def test_split_k_and_row_path_agree(tb):
     tb.set_option("gemm_split_k", 1)
     tb.set_option("gemm_min_m", 1000)              # row-at-a-time through the GEMV kernel
     assert torch.equal(tb.gemm("sk", Xd, sd), base)
-    tb.set_option("gemm_min_m", 17)
+    tb.set_option("gemm_min_m", 9)
 
 
 def test_extreme_values(tb):
