@@ -50,6 +50,15 @@ __device__ __forceinline__ void locate(const GemvParams& p, int strip, int& m, i
     ls = strip - p.tile_begin[m];
 }
 
+// Shared-memory bytes of a table-mode launch: the descriptors plus a coarse index (for every kCoarse-th strip the
+// matrix that holds it), which replaces a binary search per strip by a short scan.
+constexpr int kCoarseShift = 6, kCoarse = 1 << kCoarseShift;
+__host__ __device__ inline int gemv_table_bytes(int n_mats, int n_tiles) {
+    const int desc = (n_mats * (int)sizeof(GemvDesc) + 15) & ~15;
+    const int coarse = ((n_tiles >> kCoarseShift) + 1) * 2;
+    return (desc + coarse + 127) & ~127;
+}
+
 // Per-matrix fields of strip `strip`: from the by-value parameter arrays, or (TABLE) from the
 // descriptor table that the CTA copied into shared memory.
 struct MatRef {
@@ -64,11 +73,11 @@ template <bool TABLE>
 __device__ __forceinline__ MatRef locate(const GemvParams& p, const GemvDesc* tab, int strip) {
     MatRef r;
     if constexpr (TABLE) {
-        int lo = 0, hi = p.n_mats - 1;           // last matrix whose first strip is <= strip
-        while (lo < hi) {
-            const int mid = (lo + hi + 1) >> 1;
-            if (tab[mid].tile_begin <= strip) lo = mid; else hi = mid - 1;
-        }
+        // last matrix whose first strip is <= strip: start from the coarse index, scan forward
+        const uint16_t* coarse = reinterpret_cast<const uint16_t*>(reinterpret_cast<const uint8_t*>(tab) +
+                                                                   ((p.n_mats * (int)sizeof(GemvDesc) + 15) & ~15));
+        int lo = coarse[strip >> kCoarseShift];
+        while (lo + 1 < p.n_mats && tab[lo + 1].tile_begin <= strip) ++lo;
         const GemvDesc d = tab[lo];
         r.W = d.W; r.out = d.out; r.acc = nullptr; r.w_scale = d.w_scale; r.N = d.N; r.xid = d.xid;
         r.ls = strip - d.tile_begin;
@@ -89,7 +98,7 @@ __global__ void __launch_bounds__(kThreads) gemv_trit_kernel(const __grid_consta
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kBarOff);
     int* xsum_s = reinterpret_cast<int*>(smem + kXsumOff);           // one per activation vector
-    const int tab_bytes = TABLE ? ((p.n_mats * (int)sizeof(GemvDesc) + 127) & ~127) : 0;
+    const int tab_bytes = TABLE ? gemv_table_bytes(p.n_mats, p.n_tiles) : 0;
     GemvDesc* tab = reinterpret_cast<GemvDesc*>(smem + kHdrBytes);
     int8_t* xs = reinterpret_cast<int8_t*>(smem + kHdrBytes + tab_bytes);
     uint8_t* wbuf = smem + kHdrBytes + tab_bytes + p.x_bytes;
@@ -113,6 +122,18 @@ __global__ void __launch_bounds__(kThreads) gemv_trit_kernel(const __grid_consta
         const int4* src = reinterpret_cast<const int4*>(p.table);
         int4* dst = reinterpret_cast<int4*>(tab);
         for (int i = tid; i < p.n_mats * (int)(sizeof(GemvDesc) / 16); i += kThreads) dst[i] = src[i];
+        __syncthreads();
+        // coarse index: one binary search per kCoarse strips, once per CTA
+        uint16_t* coarse = reinterpret_cast<uint16_t*>(reinterpret_cast<uint8_t*>(tab) + ((p.n_mats * (int)sizeof(GemvDesc) + 15) & ~15));
+        for (int c = tid; c <= (p.n_tiles >> kCoarseShift); c += kThreads) {
+            const int strip = c << kCoarseShift;
+            int lo = 0, hi = p.n_mats - 1;
+            while (lo < hi) {
+                const int mid = (lo + hi + 1) >> 1;
+                if (tab[mid].tile_begin <= strip) lo = mid; else hi = mid - 1;
+            }
+            coarse[c] = (uint16_t)lo;
+        }
         __syncthreads();
     } else {
         __syncwarp();
@@ -671,7 +692,7 @@ cudaError_t launch_gemv(const GemvParams& p_in, const GemvLaunchCfg& cfg, cudaSt
     if (p.table ? (p.n_mats < 1 || p.n_mats > kGemvMaxTable) : (p.n_mats < 1 || p.n_mats > kGemvMaxGroup))
         return cudaErrorInvalidValue;
     if (p.n_x < 1 || p.n_x > kGemvMaxX || p.x_bytes > kGemvMaxXBytes) return cudaErrorInvalidValue;
-    const int tab_bytes = p.table ? ((p.n_mats * (int)sizeof(GemvDesc) + 127) & ~127) : 0;
+    const int tab_bytes = p.table ? gemv_table_bytes(p.n_mats, p.n_tiles) : 0;
     int per_sm = cfg.ctas_per_sm < 1 ? 1 : cfg.ctas_per_sm;
     int stages = cfg.stages > 0 ? cfg.stages : 3;
     if (stages > kMaxStages) stages = kMaxStages;
