@@ -139,7 +139,7 @@ int ter_b200_dump_op_stats(const ter_b200_handle_t* h, const char* label, int hi
  * the row count).  Returns one of TER_B200_KERNEL_*; ter_b200_kernel_name gives its name. */
 #define TER_B200_KERNEL_GEMV_SPLIT   0   /* M = 1, few strips: register-prefetch split-K GEMV (decode projections) */
 #define TER_B200_KERNEL_GEMV_STREAM  1   /* M = 1, many strips: persistent TMA-ring GEMV (lm_head, sweeps) */
-#define TER_B200_KERNEL_GEMV_ROWS    2   /* 2 <= M <= 16: multi-row GEMV, the weights stream once */
+#define TER_B200_KERNEL_GEMV_ROWS    2   /* 2 <= M < "gemm_min_m" (at most 16): multi-row GEMV, the weights stream once */
 #define TER_B200_KERNEL_GEMM_TCGEN05 3   /* M >= "gemm_min_m": tcgen05 kind::i8 GEMM, TMEM accumulators */
 #define TER_B200_KERNEL_GEMV_PER_ROW 4   /* otherwise: one GEMV launch per row */
 int ter_b200_pick_kernel(const ter_b200_handle_t* h, int M, int K, int N);
