@@ -40,6 +40,44 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// The same test with a suspend-time hint: the thread may sleep up to `ns` nanoseconds inside the instruction and
+// is woken when the phase completes, so a waiting warp stops competing for issue slots with working ones.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait built on it, limited by time (about two seconds) rather than by a poll count, since one poll may
+// now take up to the hint.  Same contract as mbar_wait_bounded.
+__device__ __forceinline__ bool mbar_wait_sleepy(uint64_t* bar, uint32_t parity, int* status) {
+    constexpr uint32_t kHintNs = 20000;
+    if (mbar_try_wait_hint(bar, parity, kHintNs)) return true;
+    unsigned long long t0;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    bool expired_elsewhere = false;
+    for (uint32_t i = 1;; ++i) {
+        if (mbar_try_wait_hint(bar, parity, kHintNs)) return true;
+        if ((i & 63u) == 0) {
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            if (status && *reinterpret_cast<volatile int*>(status) != DEV_OK) { expired_elsewhere = true; break; }
+            if (t - t0 > 2000000000ull) break;
+        }
+    }
+    if (status) atomicExch(status, DEV_TIMEOUT_MBAR);
+    // Second bounded chance for copies still in flight before the CTA moves on.
+    const uint32_t second = expired_elsewhere ? 64u : 50000u;
+    for (uint32_t i = 0; i < second; ++i)
+        if (mbar_try_wait_hint(bar, parity, kHintNs)) return false;
+    return false;
+}
+
 // Bounded wait.  On expiry records DEV_TIMEOUT_MBAR in *status and returns false;
 // the caller carries on (its results are then meaningless, and the host sees the code).
 // Once any wait of the launch has expired (the status word is set), later waits give up after a short

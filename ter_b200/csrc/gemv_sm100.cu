@@ -203,7 +203,7 @@ __global__ void __launch_bounds__(kThreads) gemv_trit_kernel(const __grid_consta
         int a0 = 0, a1 = 0, a2 = 0, a3 = 0;
         for (int q = 0; q < nb; ++q) {
             const int kc = (q == nb - 1) ? last_kc : kGemvKC;
-            mbar_wait_bounded(&mybars[stage], parity, p.status);
+            mbar_wait_sleepy(&mybars[stage], parity, p.status);
             const uint8_t* wt = mybuf + (size_t)stage * kStageBytes + c * kc + sgm * 16;
             const int8_t* xp = xm + q * kGemvKC;
             if (kc == kGemvKC) {
