@@ -50,9 +50,9 @@ __device__ __forceinline__ void locate(const GemvParams& p, int strip, int& m, i
     ls = strip - p.tile_begin[m];
 }
 
-// Shared-memory bytes of a table-mode launch: the descriptors plus a coarse index (for every kCoarse-th strip the
+// Shared-memory bytes of a table-mode launch: the descriptors plus a coarse index (for every 64th strip the
 // matrix that holds it), which replaces a binary search per strip by a short scan.
-constexpr int kCoarseShift = 6, kCoarse = 1 << kCoarseShift;
+constexpr int kCoarseShift = 6;     // one coarse entry per 64 strips
 __host__ __device__ inline int gemv_table_bytes(int n_mats, int n_tiles) {
     const int desc = (n_mats * (int)sizeof(GemvDesc) + 15) & ~15;
     const int coarse = ((n_tiles >> kCoarseShift) + 1) * 2;

@@ -139,7 +139,7 @@ cudaError_t launch_rope_kv(const RopeKvParams& p, bool pdl, cudaStream_t st) {
 namespace {
 
 template <int HD, int G, bool COMPACT>
-__global__ void __launch_bounds__(kT, COMPACT ? 2 : 1) attn_partial_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(kT, COMPACT ? (G <= 4 ? 3 : 2) : 1) attn_partial_kernel(const AttnParams p) {
     extern __shared__ __align__(128) uint8_t asmem[];
     using L = AttnSmem<HD, G, COMPACT>;
     uint64_t* bars = reinterpret_cast<uint64_t*>(asmem + L::kBarOff);
