@@ -247,6 +247,7 @@ void ter_b200_destroy(ter_b200_handle_t* h) {
     if (h->hx_dev) cudaFree(h->hx_dev);
     if (h->hout_dev) cudaFree(h->hout_dev);
     if (h->hpin) cudaFreeHost(h->hpin);
+    free(h->hb_memo);
     for (int i = 0; i < TER_B200_MAX_PLANS; ++i)
         if (h->plans[i].used && h->plans[i].table_dev) cudaFree(h->plans[i].table_dev);
     if (h->stream) cudaStreamDestroy(h->stream);

@@ -60,6 +60,8 @@ struct ter_b200_handle_t {
     float* hscale_dev;
     uint8_t* hpin;            // pinned host image of the staging buffer (host batch entry point)
     size_t hpin_cap;
+    TerbSlot** hb_memo;       // slots resolved by the previous host-batch call, by position (tried first)
+    int hb_memo_n;
     TerbPlan plans[TER_B200_MAX_PLANS];
     uint64_t weights_epoch;   // advances whenever a weight slot is replaced or removed
     TerbModel* model;

@@ -256,7 +256,10 @@ int ter_b200_gemv_host_batch(ter_b200_handle_t* h, int n, const char* const* slo
     size_t o_total = 0;
     for (int i = 0; i < n; ++i) {
         if (!slots[i] || !x_hosts[i] || !out_hosts[i]) { cleanup(); return TER_B200_E_NULL; }
-        sl[i] = find_slot(h, slots[i]);
+        // a loop that calls with the same list finds every slot where the previous call found it
+        TerbSlot* m = i < h->hb_memo_n ? h->hb_memo[i] : nullptr;
+        if (m && m->used && strncmp(m->name, slots[i], TER_B200_MAX_NAME + 1) == 0) sl[i] = m;
+        else sl[i] = find_slot(h, slots[i]);
         if (!sl[i]) { cleanup(); return TER_B200_E_UNKNOWN; }
         o_total += (size_t)sl[i]->w.Npad;
     }
@@ -368,6 +371,12 @@ int ter_b200_gemv_host_batch(ter_b200_handle_t* h, int n, const char* const* slo
         i = j;
     }
     free(direct);
+    if (!rc) {      // keep the resolved slots for the next call
+        free(h->hb_memo);
+        h->hb_memo = sl;
+        h->hb_memo_n = n;
+        sl = nullptr;
+    }
     cleanup();
     if (rc) return rc;
     TERB_CUDA(h, cudaStreamSynchronize(st));   // the pinned image is reused by the next call
