@@ -274,6 +274,26 @@ def test_full_size_shapes_few_layers(tb, base, L):
     assert np.array_equal(lg.view(np.uint32), want_logits[-1].view(np.uint32))
 
 
+def test_long_prompt_at_full_width_through_the_token_batch_path(tb):
+    """One BitNet-2B layer at full width, a 520-position prompt: the prompt runs as token batches (three token
+    tiles, so the gate+up group takes the two-tiles-per-CTA form of the GEMM and the rows' attention the
+    three-CTA form), the checker is fed one position at a time.  Last-position logits bit for bit, same tokens."""
+    cfg = dict(synth.BITNET_2B_CFG, L=1, Smax=640)
+    modelutil.build_gpu(tb, cfg, 33)
+    om = modelutil.build_oracle(cfg, 33)
+    prompt = np.random.default_rng(2).integers(0, cfg["V"], size=520).astype(np.int32)
+    st = om.new_state(1)
+    for pos in range(len(prompt) - 1):
+        om.forward(st, 0, int(prompt[pos]), pos, want_logits=False)
+    tok, want_lg, _ = om.forward(st, 0, int(prompt[-1]), len(prompt) - 1, want_logits=True)
+    out = tb.generate(prompt, 1)
+    assert tb.last_prefill_ms() > 0.0                   # the prompt did run as token batches
+    lg = tb.model_logits()[0]
+    assert int(out[0][0]) == int(tok)
+    assert np.array_equal(lg.view(np.uint32), want_lg.view(np.uint32))
+    assert tb.device_status() == 0
+
+
 def test_command_line_front_end_prints_the_reference_tokens(golden_dir, tmp_path):
     """ter_b200_generate (the counterpart of the reference programs' main(): n_gen, model file) on a packed-model
     file: greedy tokens from BOS equal to the ones the reference's NumPy forward printed, with the device
