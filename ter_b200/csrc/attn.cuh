@@ -36,7 +36,9 @@ struct AttnSmem {
 
 // One (chunk, KV head, row) work item and what follows from the row's position.
 struct AttnItem {
-    int c, g, b, bs;        // chunk, KV head, row, sequence whose cache is read
+    int c, g, b, bs;        // chunk, head group (= KV head unless the params deal a KV head's heads to several items), row,
+                            // sequence whose cache is read
+    int gk;                 // KV head
     int pos, seq_len, s0, cnt, n_copy;
     bool active, fused, owner;
     size_t head_off;
@@ -46,6 +48,8 @@ template <int HD>
 __device__ __forceinline__ AttnItem attn_item(const AttnParams& p, int c, int g, int b, int pos) {
     AttnItem it;
     it.c = c; it.g = g; it.b = b;
+    const int kvd = p.kv_div > 1 ? p.kv_div : 1;
+    it.gk = g / kvd;
     it.bs = p.shared_seq ? p.shared_seq - 1 : b;
     it.pos = pos;
     it.seq_len = pos + 1;
@@ -55,7 +59,7 @@ __device__ __forceinline__ AttnItem attn_item(const AttnParams& p, int c, int g,
     it.fused = p.rope_table != nullptr;
     it.owner = it.fused && (pos >= it.s0) && (pos < it.s0 + kAttnChunk);   // this chunk holds the new row
     it.n_copy = it.owner ? it.cnt - 1 : it.cnt;                            // rows already in the cache
-    it.head_off = ((size_t)it.bs * p.Nkv + g) * (size_t)p.Smax * HD;
+    it.head_off = ((size_t)it.bs * (p.Nkv / kvd) + it.gk) * (size_t)p.Smax * HD;
     return it;
 }
 
@@ -159,8 +163,9 @@ __device__ __forceinline__ void attn_compute(const AttnParams& p, const AttnItem
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (!it.active) return;
     ATR(0);
-    const int g = it.g, b = it.b, c = it.c, pos = it.pos, s0 = it.s0, cnt = it.cnt, n_copy = it.n_copy;
+    const int g = it.g, gk = it.gk, b = it.b, c = it.c, pos = it.pos, s0 = it.s0, cnt = it.cnt, n_copy = it.n_copy;
     const bool owner = it.owner;
+    const bool cache_writer = p.kv_div <= 1 || g % p.kv_div == 0;   // one of the items of a KV head appends the new row
     const size_t head_off = it.head_off;
     const uint16_t* V = p.vcache + head_off;
 
@@ -197,13 +202,13 @@ __device__ __forceinline__ void attn_compute(const AttnParams& p, const AttnItem
             qs[hh * HD + i1] = d + e;
         }
         if (owner) {
-            const float* kn = p.k_new + ((size_t)b * p.Nkv + g) * HD;
-            const float* vn = p.v_new + ((size_t)b * p.Nkv + g) * HD;
+            const float* kn = p.k_new + ((size_t)b * p.Nkv + gk) * HD;
+            const float* vn = p.v_new + ((size_t)b * p.Nkv + gk) * HD;
             auto ldk = [&](int i) -> float {
-                if constexpr (MODE == 2) return tagged_ld(tg->k, g * HD + i); else return kn[i];
+                if constexpr (MODE == 2) return tagged_ld(tg->k, gk * HD + i); else return kn[i];
             };
             auto ldv = [&](int i) -> float {
-                if constexpr (MODE == 2) return tagged_ld(tg->v, g * HD + i); else return vn[i];
+                if constexpr (MODE == 2) return tagged_ld(tg->v, gk * HD + i); else return vn[i];
             };
             uint16_t* Kw = p.kcache_w + head_off + (size_t)pos * HD;
             uint16_t* Vw = p.vcache_w + head_off + (size_t)pos * HD;
@@ -212,18 +217,18 @@ __device__ __forceinline__ void attn_compute(const AttnParams& p, const AttnItem
                 const int i0 = p.neox ? kk : 2 * kk, i1 = p.neox ? kk + half : 2 * kk + 1;
                 const float cs = row[2 * kk], sn = row[2 * kk + 1];
                 float v0, v1;
-                if constexpr (MODE == 2) ld_pair(tg->k, g * HD, i0, i1, v0, v1);
+                if constexpr (MODE == 2) ld_pair(tg->k, gk * HD, i0, i1, v0, v1);
                 else { v0 = ldk(i0); v1 = ldk(i1); }
                 const float a = v0 * cs, bb = v1 * sn;
                 const float d = v0 * sn, e = v1 * cs;
                 const uint16_t k0 = f32_to_bf16_bits(a - bb), k1 = f32_to_bf16_bits(d + e);
                 Ks[r * HD + i0] = k0; Ks[r * HD + i1] = k1;
-                Kw[i0] = k0; Kw[i1] = k1;
+                if (cache_writer) { Kw[i0] = k0; Kw[i1] = k1; }
             }
             for (int d = tid; d < HD; d += kT) {
                 const uint16_t vb = f32_to_bf16_bits(ldv(d));
                 if (!COMPACT) Vs[r * HD + d] = vb;     // COMPACT: the buffer still holds K; written after the scores
-                Vw[d] = vb;
+                if (cache_writer) Vw[d] = vb;
             }
         }
     } else {

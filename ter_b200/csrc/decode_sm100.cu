@@ -150,10 +150,18 @@ __device__ __forceinline__ const uint8_t* unit_src(const Cursor& c, int& kc) {
     return W + (size_t)ls * 4u * (size_t)c.g.Kpad + (size_t)q * kBlockBytes;
 }
 
-template <int HD, int G>
+// Query heads per attention item: with four or more query heads per KV head the heads of a KV head are dealt to
+// two items.  A lone sequence has far fewer (chunk, KV head) pairs than there are CTAs, and an item with half the
+// heads is the shorter link in the layer's chain.  Both items of a KV head stage the same K/V chunk.
+__host__ __device__ constexpr int attn_item_heads(int G) { return G >= 4 ? G / 2 : G; }
+
+// GA: query heads per attention item (attn_item_heads(G), or 1 where even one item per query head and chunk of the
+// longest context leaves CTAs to spare).
+template <int HD, int G, int GA>
 __global__ void __launch_bounds__(kT, 1) decode_layers_kernel(const __grid_constant__ DecodeParams p) {
     extern __shared__ __align__(128) uint8_t sm[];
-    using AL = AttnSmem<HD, G, false>;
+    constexpr int KVD = G / GA;
+    using AL = AttnSmem<HD, GA, false>;
     constexpr int kAttnBytes = (AL::kBytes + 127) & ~127;
     uint64_t* ring_bars = reinterpret_cast<uint64_t*>(sm + kOffRingBars);
     int* acc_s = reinterpret_cast<int*>(sm + kOffAcc);
@@ -252,7 +260,8 @@ __global__ void __launch_bounds__(kT, 1) decode_layers_kernel(const __grid_const
         st_volatile16(p.hid_t + (lo_h * 16 + 2 * i) / 2, tag2(own[2 * i], own[2 * i + 1], seq_hid(0)));
 
     const int nc = pos / kAttnChunk + 1;                 // chunks of the context
-    const int n_items = nc * p.Nkv;
+    const int nkv_v = p.Nkv * KVD;
+    const int n_items = nc * nkv_v;
     const int act = p.bitnet ? PRE_RELU2_MUL : PRE_SILU_MUL;
     // attention items of this CTA: i = my_first, my_first - grid, ... (descending: the merging items of
     // chunk 0 have the lowest numbers and come last, so a merger never waits on work queued behind it)
@@ -269,15 +278,15 @@ __global__ void __launch_bounds__(kT, 1) decode_layers_kernel(const __grid_const
     for (int layer = 0; layer < p.L; ++layer) {
         const DecodeLayerDev* ld = tab + layer;
         const uint32_t sl = seq_layer(layer);
-        AttnParams ap{nullptr, ld->kcache, ld->vcache, p.pos, nullptr, nullptr, 1, p.Nh, p.Nkv, p.Hd, p.Smax,
+        AttnParams ap{nullptr, ld->kcache, ld->vcache, p.pos, nullptr, nullptr, 1, p.Nh, nkv_v, p.Hd, p.Smax,
                       (p.Smax + kAttnChunk - 1) / kAttnChunk, p.rope, nullptr, nullptr, ld->kcache, ld->vcache,
-                      p.bitnet ? 1 : 0, p.status, nullptr, 0};
+                      p.bitnet ? 1 : 0, p.status, nullptr, 0, KVD};
         // the cached K/V rows of this CTA's first attention item start moving now
         if (my_first >= 0) {
-            const AttnItem it = attn_item<HD>(ap, my_first / p.Nkv, my_first % p.Nkv, 0, pos);
+            const AttnItem it = attn_item<HD>(ap, my_first / nkv_v, my_first % nkv_v, 0, pos);
             if (tid == 0 && it.active && it.n_copy > 0) {
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                attn_issue_kv<HD, G, false>(ap, it, asmem);
+                attn_issue_kv<HD, GA, false>(ap, it, asmem);
             }
             kv_pending = it.active && it.n_copy > 0;
         }
@@ -413,16 +422,16 @@ __global__ void __launch_bounds__(kT, 1) decode_layers_kernel(const __grid_const
                 tg.trace = (layer == 1 && p.trace) ? p.trace + (size_t)cta * 32 + 20 : nullptr;
 #endif
                 for (int i = my_first; i >= 0; i -= grid) {
-                    const AttnItem it = attn_item<HD>(ap, i / p.Nkv, i % p.Nkv, 0, pos);
+                    const AttnItem it = attn_item<HD>(ap, i / nkv_v, i % nkv_v, 0, pos);
                     if (i != my_first) {
                         __syncthreads();
                         if (tid == 0 && it.active && it.n_copy > 0) {
                             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                            attn_issue_kv<HD, G, false>(ap, it, asmem);
+                            attn_issue_kv<HD, GA, false>(ap, it, asmem);
                         }
                     }
                     kv_pending = false;
-                    attn_compute<HD, G, false, 2>(ap, it, asmem, redg, &misc[0], kv_parity, &tg);
+                    attn_compute<HD, GA, false, 2>(ap, it, asmem, redg, &misc[0], kv_parity, &tg);
                     if (it.active && it.n_copy > 0) kv_parity ^= 1u;
                 }
                 __syncthreads();
@@ -465,10 +474,10 @@ bool decode_layers_supported(int H, int F, int Nh, int Nkv, int Hd, int L) {
 }
 
 namespace {
-template <int HD, int G>
-cudaError_t launch_variant(DecodeParams& p, int sm_count, cudaStream_t st, int dev) {
+template <int HD, int G, int GA>
+cudaError_t launch_variant_ga(DecodeParams& p, int sm_count, cudaStream_t st, int dev) {
     constexpr int kMaxSmem = 227 * 1024;
-    constexpr int kAttnBytes = (AttnSmem<HD, G, false>::kBytes + 127) & ~127;
+    constexpr int kAttnBytes = (AttnSmem<HD, GA, false>::kBytes + 127) & ~127;
     const size_t fixed = (size_t)kHdr + (size_t)p.tab_bytes + (size_t)p.own_bytes + (size_t)p.x_bytes + kAttnBytes;
     if (fixed + (size_t)kDecWarps * kBlockBytes > (size_t)kMaxSmem) return cudaErrorInvalidValue;
     int stages = (int)((kMaxSmem - fixed) / ((size_t)kDecWarps * kBlockBytes));
@@ -476,7 +485,7 @@ cudaError_t launch_variant(DecodeParams& p, int sm_count, cudaStream_t st, int d
     p.stages = stages;
     const size_t smem = fixed + (size_t)kDecWarps * stages * kBlockBytes;
     static bool attr_set[64] = {};
-    auto kern = decode_layers_kernel<HD, G>;
+    auto kern = decode_layers_kernel<HD, G, GA>;
     if (!attr_set[dev]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
         if (e != cudaSuccess) return e;
@@ -493,6 +502,13 @@ cudaError_t launch_variant(DecodeParams& p, int sm_count, cudaStream_t st, int d
     lc.attrs = attr;
     lc.numAttrs = 1;
     return cudaLaunchKernelEx(&lc, kern, p);
+}
+template <int HD, int G>
+cudaError_t launch_variant(DecodeParams& p, int sm_count, cudaStream_t st, int dev) {
+    // one item per query head when the items of the longest context still fit the CTAs
+    const long per_head_items = (long)((p.Smax + kAttnChunk - 1) / kAttnChunk) * p.Nh;
+    if (G >= 2 && per_head_items <= sm_count) return launch_variant_ga<HD, G, 1>(p, sm_count, st, dev);
+    return launch_variant_ga<HD, G, attn_item_heads(G)>(p, sm_count, st, dev);
 }
 template <int HD>
 cudaError_t launch_hd(DecodeParams& p, int sm_count, cudaStream_t st, int dev) {

@@ -61,6 +61,9 @@ struct AttnParams {
                              // the chunks itself (no second kernel); null = merge in attn_combine_kernel
     int shared_seq;          // 0: row b reads the cache of sequence b; s > 0: every row reads sequence s - 1
                              // (the rows are positions of one prompt, each with its own pos[b])
+    int kv_div;              // 0 / 1: Nkv counts the KV heads.  d > 1: the query heads of a KV head are dealt to d items
+                             // (Nkv = d x the KV heads, Nh / Nkv query heads per item; item g reads KV head g / d): more,
+                             // shorter items for a lone sequence whose items do not fill the SMs
     int mma;                 // 1: the two contractions on the tensor cores (attn_mma.cuh): equal to the fixed-order
                              // kernel up to the rounding of fp32 sums, not bit for bit; for token batches
 };
