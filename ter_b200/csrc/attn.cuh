@@ -486,30 +486,49 @@ __device__ __forceinline__ void attn_compute(const AttnParams& p, const AttnItem
                 uint4* rec = tg->rec_t + ((size_t)head * p.max_chunks) * kRecWords;
                 if (c == 0) {
                     float M = tg->ml_s[hh], Lsum = tg->ml_s[G + hh], O0 = acc0[i], O1 = acc1[i];
-                    // the other chunks' records, four chunks' loads in flight at a time, merged in chunk order
-                    for (int c0 = 1; c0 < nc; c0 += 4) {
-                        uint4 w0[4], w1[4];
+                    // The other chunks' records, merged in chunk order.  All lanes of a warp serve the same head, so
+                    // lane k prepares chunk cb + k: its header (m, l), the running maximum before and after it (a
+                    // prefix maximum over the lanes) and the two rescaling factors; the ordered pass then takes them
+                    // by shuffle.  Same operations on the same values as a thread doing all of it alone, but the
+                    // exponentials of all chunks are evaluated side by side instead of one after the other.
+                    for (int cb = 1; cb < nc; cb += 32) {
+                        const int nb = min(32, nc - cb);
+                        float mk = -CUDART_INF_F, lk = 0.0f;
+                        if (lane < nb) {
+                            const uint4* r = rec + (size_t)(cb + lane) * kRecWords;
+                            uint4 w = ld_volatile16(r);
+                            if (w.y != seq || w.w != seq) w = poll_tagged(r, seq, tg->q.ctx);
+                            mk = __uint_as_float(w.x);
+                            lk = __uint_as_float(w.z);
+                        }
+                        float Mn = mk;                                   // inclusive prefix maximum over the lanes
 #pragma unroll
-                        for (int k = 0; k < 4; ++k)
-                            if (c0 + k < nc) {
-                                const uint4* r = rec + (size_t)(c0 + k) * kRecWords;
-                                w0[k] = ld_volatile16(r);
-                                w1[k] = ld_volatile16(r + 1 + dp);
-                            }
+                        for (int o = 1; o < 32; o <<= 1) {
+                            const float up = __shfl_up_sync(0xffffffffu, Mn, o);
+                            if (lane >= o) Mn = fmaxf(Mn, up);
+                        }
+                        Mn = fmaxf(M, Mn);                               // running maximum after chunk cb + lane
+                        float Mp = __shfl_up_sync(0xffffffffu, Mn, 1);   // ... and before it
+                        if (lane == 0) Mp = M;
+                        const float ak = exp_fixed(Mp - Mn), bk = exp_fixed(mk - Mn);
+                        for (int k0 = 0; k0 < nb; k0 += 4) {
+                            uint4 w1[4];
 #pragma unroll
-                        for (int k = 0; k < 4; ++k)
-                            if (c0 + k < nc) {
-                                const uint4* r = rec + (size_t)(c0 + k) * kRecWords;
-                                if (w0[k].y != seq || w0[k].w != seq) w0[k] = poll_tagged(r, seq, tg->q.ctx);
-                                if (w1[k].y != seq || w1[k].w != seq) w1[k] = poll_tagged(r + 1 + dp, seq, tg->q.ctx);
-                                const float mc = __uint_as_float(w0[k].x), lc = __uint_as_float(w0[k].z);
-                                const float Mn = fmaxf(M, mc);
-                                const float a = exp_fixed(M - Mn), bb = exp_fixed(mc - Mn);
-                                Lsum = fmaf(lc, bb, Lsum * a);
-                                O0 = fmaf(__uint_as_float(w1[k].x), bb, O0 * a);
-                                O1 = fmaf(__uint_as_float(w1[k].z), bb, O1 * a);
-                                M = Mn;
-                            }
+                            for (int k = 0; k < 4; ++k)
+                                if (k0 + k < nb) w1[k] = ld_volatile16(rec + (size_t)(cb + k0 + k) * kRecWords + 1 + dp);
+#pragma unroll
+                            for (int k = 0; k < 4; ++k)
+                                if (k0 + k < nb) {
+                                    const uint4* r = rec + (size_t)(cb + k0 + k) * kRecWords;
+                                    if (w1[k].y != seq || w1[k].w != seq) w1[k] = poll_tagged(r + 1 + dp, seq, tg->q.ctx);
+                                    const float a = __shfl_sync(0xffffffffu, ak, k0 + k), bb = __shfl_sync(0xffffffffu, bk, k0 + k);
+                                    const float lc = __shfl_sync(0xffffffffu, lk, k0 + k);
+                                    Lsum = fmaf(lc, bb, Lsum * a);
+                                    O0 = fmaf(__uint_as_float(w1[k].x), bb, O0 * a);
+                                    O1 = fmaf(__uint_as_float(w1[k].z), bb, O1 * a);
+                                }
+                        }
+                        M = __shfl_sync(0xffffffffu, Mn, nb - 1);
                     }
                     st_volatile16(tg->att_t + ((size_t)head * HD) / 2 + dp, tag2(O0 / Lsum, O1 / Lsum, seq));
                 } else {
