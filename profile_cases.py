@@ -11,6 +11,10 @@
     python profile_cases.py attn 64          # attention of 64 sequences at context 2048 (335 MB of K/V): tensor-core and
                                              # fixed-order kernels, 4 launches each, CUDA-event times printed
 
+    python profile_cases.py trace_gemm       # with a library built by `TER_B200_NVCC_EXTRA=-DTERB_TRACE python -m
+    python profile_cases.py trace_decode bitnet 2100   # ter_b200.build --force`: phase timestamps (globaltimer) of the
+                                             # GEMM's CTAs / of one layer inside the persistent decode kernel
+
 Each holds at most a few GB on the device and finishes in seconds, so an `ncu` capture of it ends by itself.
 """
 from __future__ import annotations
@@ -197,7 +201,71 @@ def attn(batch="64"):
     print("attn ok, status", tb.device_status())
 
 
+def trace_gemm():
+    """Phase timestamps of the GEMM's CTAs (library built with -DTERB_TRACE): microseconds from the first CTA's
+    entry to: tensor memory allocated, griddepcontrol.wait passed, first stage full, last MMA issued, accumulators
+    complete, epilogue done, exit (minimum / median / maximum over the CTAs of the last launch)."""
+    import ctypes
+    import torch
+    from ter_b200 import FMT_V11, TerB200, synth
+    tb = TerB200(0)
+    if not hasattr(tb.L, "ter_b200_debug_gemm_trace"):
+        raise SystemExit("build the library with TER_B200_NVCC_EXTRA=-DTERB_TRACE first")
+    dev = torch.device("cuda:0")
+    names = ["entry", "tmem", "pdl", "first_full", "mma_issued", "done", "epi_end", "end"]
+    for nm, M in (("q", 1024), ("gate", 1024), ("gate", 64)):
+        K, N = synth.BITNET_2B_SHAPES[nm]
+        tb.install("g", synth.packed_v11_cuda(K, N, 5, dev), FMT_V11, K, N, 0.02)
+        X = torch.randint(-127, 128, (M, K), dtype=torch.int8, device=dev)
+        xs = torch.rand(M, device=dev) * 0.05 + 0.001
+        out = torch.empty((M, N), device=dev)
+        for _ in range(3):
+            tb.gemm("g", X, xs, out)
+        torch.cuda.synchronize()
+        buf = np.zeros((512, 8), np.uint64)
+        tb.L.ter_b200_debug_gemm_trace(buf.ctypes.data_as(ctypes.c_void_p))
+        t = buf.astype(np.int64)
+        t = t[t[:, 0] > 0]
+        rel = (t - t[:, 0].min()) / 1e3
+        print(nm, "M", M, "CTAs", len(t))
+        for k in range(8):
+            print(f"  {names[k]:10s} min {rel[:, k].min():7.2f} med {np.median(rel[:, k]):7.2f} max {rel[:, k].max():7.2f}")
+        tb.remove("g")
+    tb.close()
+
+
+def trace_decode(which="llama", n_prompt="300"):
+    """Timestamps of layer 1 inside the persistent decode kernel (library built with -DTERB_TRACE): per CTA the
+    stage boundaries (microseconds from the first CTA's entry into the layer) and, for CTAs with an attention item,
+    its phases (start, q staged, K landed, scores, softmax, output, merged)."""
+    import ctypes
+    import torch
+    from ter_b200 import TerB200, synth
+    tb = TerB200(0)
+    if not hasattr(tb.L, "ter_b200_debug_trace"):
+        raise SystemExit("build the library with TER_B200_NVCC_EXTRA=-DTERB_TRACE first")
+    dev = torch.device("cuda:0")
+    n_prompt = int(n_prompt)
+    base = synth.LLAMA_1B_CFG if which == "llama" else synth.BITNET_2B_CFG
+    cfg = dict(base, Smax=n_prompt + 40)
+    build_random_model(tb, cfg, dev)
+    prompt = np.random.default_rng(1).integers(0, cfg["V"], size=n_prompt).astype(np.int32)
+    tb.generate(prompt, 16)
+    tb.generate(prompt, 16)
+    print(which, "ms per step", (tb.last_generate_ms() - tb.last_prompt_ms()) / 15)
+    buf = np.zeros((148, 32), np.uint64)
+    tb.L.ter_b200_debug_trace(buf.ctypes.data_as(ctypes.c_void_p))
+    t = buf.astype(np.int64)
+    rel = np.where(t > 0, (t - t[:, 0].min()) / 1000.0, -1)
+    np.set_printoptions(linewidth=250, precision=2, suppress=True)
+    for c in (0, 50, 100, 127, 140, 147):
+        print(c, "stages", rel[c, :20])
+        print(c, "  attention", rel[c, 20:28])
+    tb.close()
+
+
 if __name__ == "__main__":
     case = sys.argv[1] if len(sys.argv) > 1 else "gemv_stream"
     {"gemv_stream": gemv_stream, "sweep": sweep, "gemm": gemm, "decode": lambda: decode(*sys.argv[2:4]), "glue": glue,
-     "attn": lambda: attn(*sys.argv[2:3])}[case]()
+     "attn": lambda: attn(*sys.argv[2:3]), "trace_gemm": trace_gemm,
+     "trace_decode": lambda: trace_decode(*sys.argv[2:4])}[case]()

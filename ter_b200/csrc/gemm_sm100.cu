@@ -561,7 +561,11 @@ extern "C" int ter_b200_debug_gemm_steps(unsigned long long* host) {
 }
 extern "C" int ter_b200_debug_gemm_trace(unsigned long long* host) {
     cudaDeviceSynchronize();
-    return (int)cudaMemcpyFromSymbol(host, g_gemm_trace, sizeof(unsigned long long) * 512 * 8);
+    cudaError_t e = cudaMemcpyFromSymbol(host, g_gemm_trace, sizeof(unsigned long long) * 512 * 8);
+    void* ptr = nullptr;     // cleared for the next launch (a smaller grid would leave old rows behind)
+    if (e == cudaSuccess && cudaGetSymbolAddress(&ptr, g_gemm_trace) == cudaSuccess)
+        e = cudaMemset(ptr, 0, sizeof(unsigned long long) * 512 * 8);
+    return (int)e;
 }
 #endif
 
