@@ -81,6 +81,25 @@ __device__ __forceinline__ void attn_issue_kv(const AttnParams& p, const AttnIte
     }
 }
 
+// Rescaling factors of an ordered merge of up to 32 chunk records, prepared side by side: lane k of the warp
+// passes the chunk maximum mk of its record (-inf beyond the last one); M is the running maximum before the first
+// of them.  On return lane k holds a = exp(M_before_k - M_after_k) and b = exp(mk - M_after_k), the two factors
+// a thread merging the records one after the other would compute for record k, and Mn = M_after_k.  The whole warp
+// calls it.  Same operations on the same values; only the exponentials no longer wait for one another.
+__device__ __forceinline__ void merge_factors(float M, float mk, int lane, float& a, float& b, float& Mn) {
+    Mn = mk;                                             // inclusive prefix maximum over the lanes
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const float up = __shfl_up_sync(0xffffffffu, Mn, o);
+        if (lane >= o) Mn = fmaxf(Mn, up);
+    }
+    Mn = fmaxf(M, Mn);
+    float Mp = __shfl_up_sync(0xffffffffu, Mn, 1);
+    if (lane == 0) Mp = M;
+    a = exp_fixed(Mp - Mn);
+    b = exp_fixed(mk - Mn);
+}
+
 // Merge of the chunks by the last CTA of this (row, KV head) to finish, when the caller gave arrival
 // counters; the order of the merge is fixed (chunk 0, 1, 2, ...) whoever performs it.  All threads call it.
 template <int HD, int G>
@@ -100,18 +119,29 @@ __device__ __forceinline__ void attn_merge_last(const AttnParams& p, const AttnI
     __syncthreads();
     if (*is_last) {
         __threadfence();
-        for (int idx = tid; idx < G * HD; idx += kT) {
+        const int lane = tid & 31;
+        for (int idx = tid; idx < G * HD; idx += kT) {      // HD is a multiple of 32: a warp serves one head
             const int hh = idx / HD, d = idx % HD;
             const float* rec = p.scratch + ((size_t)b * p.Nh + (size_t)g * G + hh) * rec_stride;
             float M = __ldcg(rec), Lsum = __ldcg(rec + 1), O = __ldcg(rec + 2 + d);
-            for (int cc = 1; cc < nc; ++cc) {
-                const float* r = rec + (size_t)cc * (HD + 2);
-                const float mc = __ldcg(r), lc = __ldcg(r + 1), oc = __ldcg(r + 2 + d);
-                const float Mn = fmaxf(M, mc);
-                const float a = exp_fixed(M - Mn), bb = exp_fixed(mc - Mn);
-                Lsum = fmaf(lc, bb, Lsum * a);
-                O = fmaf(oc, bb, O * a);
-                M = Mn;
+            for (int cb = 1; cb < nc; cb += 32) {
+                const int nb = min(32, nc - cb);
+                float mk = -CUDART_INF_F, lk = 0.0f;
+                if (lane < nb) {
+                    const float* r = rec + (size_t)(cb + lane) * (HD + 2);
+                    mk = __ldcg(r);
+                    lk = __ldcg(r + 1);
+                }
+                float ak, bk, Mn;
+                merge_factors(M, mk, lane, ak, bk, Mn);
+                for (int k = 0; k < nb; ++k) {
+                    const float oc = __ldcg(rec + (size_t)(cb + k) * (HD + 2) + 2 + d);
+                    const float a = __shfl_sync(0xffffffffu, ak, k), bb = __shfl_sync(0xffffffffu, bk, k);
+                    const float lc = __shfl_sync(0xffffffffu, lk, k);
+                    Lsum = fmaf(lc, bb, Lsum * a);
+                    O = fmaf(oc, bb, O * a);
+                }
+                M = __shfl_sync(0xffffffffu, Mn, nb - 1);
             }
             p.out[((size_t)b * p.Nh + (size_t)g * G + hh) * HD + d] = O / Lsum;
         }
@@ -501,16 +531,8 @@ __device__ __forceinline__ void attn_compute(const AttnParams& p, const AttnItem
                             mk = __uint_as_float(w.x);
                             lk = __uint_as_float(w.z);
                         }
-                        float Mn = mk;                                   // inclusive prefix maximum over the lanes
-#pragma unroll
-                        for (int o = 1; o < 32; o <<= 1) {
-                            const float up = __shfl_up_sync(0xffffffffu, Mn, o);
-                            if (lane >= o) Mn = fmaxf(Mn, up);
-                        }
-                        Mn = fmaxf(M, Mn);                               // running maximum after chunk cb + lane
-                        float Mp = __shfl_up_sync(0xffffffffu, Mn, 1);   // ... and before it
-                        if (lane == 0) Mp = M;
-                        const float ak = exp_fixed(Mp - Mn), bk = exp_fixed(mk - Mn);
+                        float ak, bk, Mn;
+                        merge_factors(M, mk, lane, ak, bk, Mn);
                         for (int k0 = 0; k0 < nb; k0 += 4) {
                             uint4 w1[4];
 #pragma unroll

@@ -219,15 +219,25 @@ __global__ void __launch_bounds__(HD) attn_combine_kernel(const AttnParams p) {
     if (seq_len < 1 || seq_len > p.Smax) return;
     const int nc = (seq_len + kAttnChunk - 1) / kAttnChunk;
     const float* rec = p.scratch + ((size_t)b * p.Nh + h) * (size_t)p.max_chunks * (HD + 2);
+    const int lane = d & 31;     // the block is HD threads (a multiple of 32), all of one head
     float M = rec[0], L = rec[1], O = rec[2 + d];
-    for (int c = 1; c < nc; ++c) {
-        const float* r = rec + (size_t)c * (HD + 2);
-        const float mc = r[0], lc = r[1], oc = r[2 + d];
-        const float Mn = fmaxf(M, mc);
-        const float a = exp_fixed(M - Mn), bb = exp_fixed(mc - Mn);
-        L = fmaf(lc, bb, L * a);
-        O = fmaf(oc, bb, O * a);
-        M = Mn;
+    for (int cb = 1; cb < nc; cb += 32) {
+        const int nb = min(32, nc - cb);
+        float mk = -CUDART_INF_F, lk = 0.0f;
+        if (lane < nb) {
+            mk = rec[(size_t)(cb + lane) * (HD + 2)];
+            lk = rec[(size_t)(cb + lane) * (HD + 2) + 1];
+        }
+        float ak, bk, Mn;
+        merge_factors(M, mk, lane, ak, bk, Mn);
+        for (int k = 0; k < nb; ++k) {
+            const float oc = rec[(size_t)(cb + k) * (HD + 2) + 2 + d];
+            const float a = __shfl_sync(0xffffffffu, ak, k), bb = __shfl_sync(0xffffffffu, bk, k);
+            const float lc = __shfl_sync(0xffffffffu, lk, k);
+            L = fmaf(lc, bb, L * a);
+            O = fmaf(oc, bb, O * a);
+        }
+        M = __shfl_sync(0xffffffffu, Mn, nb - 1);
     }
     p.out[((size_t)b * p.Nh + h) * HD + d] = O / L;
 }
