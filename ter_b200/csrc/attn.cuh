@@ -456,6 +456,37 @@ __device__ __forceinline__ void attn_compute(const AttnParams& p, const AttnItem
             prp[i] = scf + hh * kAttnChunk;
             vp[i] = Vs + 2 * (idx % (HD / 2));
         }
+        if constexpr (G * HD <= kT / 2) {
+            // Few chains (at most 128): one thread per (head, dim), so that twice as many warps share the
+            // positions' loads and conversions (a chain is 3.25 instead of 5.25 instructions per position); the
+            // values then go through the query buffer (free since the scores) to the thread of their dim pair.
+            float a = 0.0f;
+            if (tid < G * HD) {
+                const float* pq = scf + (tid / HD) * kAttnChunk;
+                const uint16_t* vq = Vs + (tid % HD);
+                const int cnt4 = cnt & ~3;
+                float4 pn = make_float4(0.f, 0.f, 0.f, 0.f);
+                uint16_t wn[4] = {0, 0, 0, 0};
+                auto load = [&](int t) {
+                    pn = *reinterpret_cast<const float4*>(pq + t);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) wn[k] = vq[(t + k) * HD];
+                };
+                if (cnt4 > 0) load(0);
+                for (int t = 0; t < cnt4; t += 4) {
+                    const float4 pc = pn;
+                    const float v0 = bf16_bits_to_f32(wn[0]), v1 = bf16_bits_to_f32(wn[1]);
+                    const float v2 = bf16_bits_to_f32(wn[2]), v3 = bf16_bits_to_f32(wn[3]);
+                    if (t + 4 < cnt4) load(t + 4);
+                    a = fmaf(pc.x, v0, a);
+                    a = fmaf(pc.y, v1, a);
+                    a = fmaf(pc.z, v2, a);
+                    a = fmaf(pc.w, v3, a);
+                }
+                for (int t = cnt4; t < cnt; ++t) a = fmaf(pq[t], bf16_bits_to_f32(vq[t * HD]), a);
+                qs[tid] = a;
+            }
+        } else
         if (tid < kPairs) {
             // the loads of step t+4 are issued before the multiply-adds of step t (explicit double buffering:
             // with one or two warps per scheduler nothing else hides the shared-memory latency)
@@ -503,6 +534,9 @@ __device__ __forceinline__ void attn_compute(const AttnParams& p, const AttnItem
             }
         }
         __syncthreads();   // the chunk's (m, l) of every head are in tg->ml_s
+        if constexpr (G * HD <= kT / 2) {
+            if (tid < kPairs) { acc0[0] = qs[2 * tid]; acc1[0] = qs[2 * tid + 1]; }
+        }
         ATR(5);
         const int nc = (it.seq_len + kAttnChunk - 1) / kAttnChunk;
         const uint32_t seq = tg->seq;
