@@ -275,21 +275,27 @@ def test_full_size_shapes_few_layers(tb, base, L):
 
 
 def test_long_prompt_at_full_width_through_the_token_batch_path(tb):
-    """One BitNet-2B layer at full width, a 520-position prompt: the prompt runs as token batches (three token
-    tiles, so the gate+up group takes the two-tiles-per-CTA form of the GEMM and the rows' attention the
-    three-CTA form), the checker is fed one position at a time.  Last-position logits bit for bit, same tokens."""
-    cfg = dict(synth.BITNET_2B_CFG, L=1, Smax=640)
+    """One BitNet-2B layer at full width and the benchmark's cache length, a 520-position prompt: the prompt runs
+    as token batches (three token tiles, so the gate+up group takes the two-tiles-per-CTA form of the GEMM and the
+    rows' attention the three-CTA form); the decode steps after it run in the persistent kernel with three context
+    chunks and, at this cache length, two attention items per KV head.  The checker is fed one position at a time.
+    Same tokens; logits of the last step bit for bit."""
+    cfg = dict(synth.BITNET_2B_CFG, L=1, Smax=2176)
+    n_gen = 4
     modelutil.build_gpu(tb, cfg, 33)
     om = modelutil.build_oracle(cfg, 33)
     prompt = np.random.default_rng(2).integers(0, cfg["V"], size=520).astype(np.int32)
     st = om.new_state(1)
     for pos in range(len(prompt) - 1):
         om.forward(st, 0, int(prompt[pos]), pos, want_logits=False)
-    tok, want_lg, _ = om.forward(st, 0, int(prompt[-1]), len(prompt) - 1, want_logits=True)
-    out = tb.generate(prompt, 1)
+    tok, want, want_lg = int(prompt[-1]), [], None
+    for i in range(n_gen):
+        tok, want_lg, _ = om.forward(st, 0, tok, len(prompt) - 1 + i, want_logits=True)
+        want.append(int(tok))
+    out = tb.generate(prompt, n_gen)
     assert tb.last_prefill_ms() > 0.0                   # the prompt did run as token batches
     lg = tb.model_logits()[0]
-    assert int(out[0][0]) == int(tok)
+    assert out[0].tolist() == want
     assert np.array_equal(lg.view(np.uint32), want_lg.view(np.uint32))
     assert tb.device_status() == 0
 
