@@ -16,7 +16,7 @@
 //   * roles: warp 4 lane 0 = TMA loader, warp 5 lane 0 = MMA issuer (warp 5 allocates / frees TMEM),
 //     warps 0-3 = epilogue (tcgen05.ld, one vocabulary row per thread, stores coalesced over the vocabulary).
 //   * two CTAs per SM (three stages each), so one CTA's epilogue overlaps the other's main loop.
-// The TMA loads carry no cluster multicast.  Every wait is bounded; TMEM is freed on every path.
+// The TMA loads are plain per-CTA loads.  Every wait is bounded; TMEM is freed on every path.
 #include <cuda_bf16.h>
 #include <string.h>
 
