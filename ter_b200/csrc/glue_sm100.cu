@@ -31,11 +31,22 @@ __global__ void __launch_bounds__(kT) norm_quant_kernel(const NormQuantParams p)
     int8_t* qo = p.q ? p.q + off : nullptr;
     float* no = p.normed ? p.normed + off : nullptr;
     __shared__ float red16[16];
-    const float stored = norm_quant_fast_ok(p, (int)blockIdx.x, qo, no)
-                             ? block_norm_quant_fast(p, (int)blockIdx.x, red16, qo, no)
-                             : block_norm_quant(p, (int)blockIdx.x, vals, red, qo, no);
+    const bool fast = norm_quant_fast_ok(p, (int)blockIdx.x, qo, no);
+    int mine = 0;      // fast path: the sum of the int8 values this thread wrote
+    const float stored = fast ? block_norm_quant_fast(p, (int)blockIdx.x, red16, qo, no, nullptr, &mine)
+                              : block_norm_quant(p, (int)blockIdx.x, vals, red, qo, no);
     if (p.q && threadIdx.x == 0) p.scale_out[blockIdx.x] = stored;
-    if (p.rowsum_out && qo) {
+    if (p.rowsum_out && qo && fast) {
+        // exact integer sum of the row from the values still in registers: no second pass over the stores
+        __shared__ int rsf;
+        if (threadIdx.x == 0) rsf = 0;
+        __syncthreads();
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
+        if ((threadIdx.x & 31) == 0 && mine != 0) atomicAdd(&rsf, mine);
+        __syncthreads();
+        if (threadIdx.x == 0) p.rowsum_out[blockIdx.x] = rsf;
+    } else if (p.rowsum_out && qo) {
         // exact integer sum of the row just written (this CTA's own stores, visible after the barrier)
         __shared__ int rs;
         if (threadIdx.x == 0) rs = 0;

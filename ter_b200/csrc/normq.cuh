@@ -213,9 +213,11 @@ __device__ __forceinline__ void norm_quant_prefetch_gamma(const NormQuantParams&
 // ts (optional): the row comes from a flag-in-data vector instead of p.x (persistent decode kernel: the
 // values are polled until the producing CTAs have stored them); p.u must then be null.
 // R: float4 slots per thread compiled in (the row has at most 1024*R elements).
+// qsum: when not null, receives the sum of the int8 values THIS thread wrote (for the row sum of a token batch).
 template <int R>
 __device__ __forceinline__ float block_norm_quant_fast_r(const NormQuantParams& p, int row, float* red16,
-                                                         int8_t* q_out, float* normed_out, const TaggedSrc* ts) {
+                                                         int8_t* q_out, float* normed_out, const TaggedSrc* ts,
+                                                         int* qsum = nullptr) {
     const int tid = threadIdx.x, n = p.n;
     const size_t off = (size_t)row * (size_t)n;
     const float4* x4 = reinterpret_cast<const float4*>(p.x + off);
@@ -307,6 +309,7 @@ __device__ __forceinline__ float block_norm_quant_fast_r(const NormQuantParams& 
         const float scale = 127.0f / amax;
         stored = 1.0f / scale;
         uint32_t* q4 = reinterpret_cast<uint32_t*>(q_out);
+        int mine = 0;
 #pragma unroll
         for (int r = 0; r < R; ++r)
             if (4 * (tid + kT * r) < n) {
@@ -314,7 +317,9 @@ __device__ __forceinline__ float block_norm_quant_fast_r(const NormQuantParams& 
                 const int q2 = quant_one(v[r].z, scale), q3 = quant_one(v[r].w, scale);
                 q4[tid + kT * r] = (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) |
                                    ((uint32_t)(q3 & 0xff) << 24);
+                mine += (q0 + q1) + (q2 + q3);
             }
+        if (qsum) *qsum = mine;
     }
     return stored;
 }
@@ -322,9 +327,9 @@ __device__ __forceinline__ float block_norm_quant_fast_r(const NormQuantParams& 
 // Dispatch on the row length, so that a short row does not pay for the slots of a long one.
 __device__ __forceinline__ float block_norm_quant_fast(const NormQuantParams& p, int row, float* red16,
                                                        int8_t* q_out, float* normed_out,
-                                                       const TaggedSrc* ts = nullptr) {
-    if (p.n <= 3072) return block_norm_quant_fast_r<3>(p, row, red16, q_out, normed_out, ts);
-    return block_norm_quant_fast_r<kNqFastMax / (4 * kT)>(p, row, red16, q_out, normed_out, ts);
+                                                       const TaggedSrc* ts = nullptr, int* qsum = nullptr) {
+    if (p.n <= 3072) return block_norm_quant_fast_r<3>(p, row, red16, q_out, normed_out, ts, qsum);
+    return block_norm_quant_fast_r<kNqFastMax / (4 * kT)>(p, row, red16, q_out, normed_out, ts, qsum);
 }
 
 }  // namespace
